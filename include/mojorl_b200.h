@@ -1,0 +1,277 @@
+/*
+ * mojorl_b200.h - C ABI of libmojorl_b200.so.
+ *
+ * Drop-in boundary for the on-policy PPO hot path of denislabs/mojo-rl:
+ * every entry point replaces one Mojo GPU function (or one phase of
+ * DeepPPOAgent.train_gpu) and takes exactly the buffers that function takes,
+ * as raw device pointers (Mojo: DeviceBuffer.unsafe_ptr()).  Citations are
+ * paths inside the reference repository.
+ *
+ * Conventions
+ *   - every function returns 0 (MRL_OK) or a negative mrl_status; nothing
+ *     aborts, traps or blocks without bound;
+ *   - all pointers are DEVICE pointers unless the name ends in _host;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = default stream);
+ *     work is enqueued asynchronously like DeviceContext.enqueue_function,
+ *     the caller synchronises;
+ *   - the caller owns every buffer; the library allocates only inside
+ *     mrl_create (persistent workspaces) unless stated otherwise;
+ *   - flags (done, action index, contact) are float 0.0/1.0/k as in the
+ *     reference.
+ */
+#ifndef MOJORL_B200_H
+#define MOJORL_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum mrl_status {
+    MRL_OK = 0,
+    MRL_ERR_INVALID_ARG = -1,
+    MRL_ERR_CUDA = -2,
+    MRL_ERR_NCCL = -3,
+    MRL_ERR_UNSUPPORTED = -4,
+    MRL_ERR_NO_DEVICE = -5,
+    MRL_ERR_TIMEOUT = -6,
+    MRL_ERR_TOO_LARGE = -7
+} mrl_status;
+
+/* Environment kinds (the implementors of GPUDiscreteEnv / GPUContinuousEnv,
+ * core/env_traits.mojo:230-397, that the five benchmark configs use). */
+typedef enum mrl_env_kind {
+    MRL_ENV_CARTPOLE = 0,       /* envs/cartpole.mojo                           */
+    MRL_ENV_PENDULUM = 1,       /* envs/pendulum/pendulum_v2.mojo               */
+    MRL_ENV_LUNAR_LANDER = 2,   /* envs/lunar_lander/lunar_lander_v2.mojo       */
+    MRL_ENV_BIPEDAL_WALKER = 3, /* envs/bipedal_walker/bipedal_walker_v2.mojo   */
+    MRL_ENV_HALF_CHEETAH = 4,   /* envs/half_cheetah/cheetah_planar_v2.mojo     */
+    MRL_ENV_LUNAR_LANDER_CONTINUOUS = 5 /* lunar_lander_v2.mojo:2781-3495       */
+} mrl_env_kind;
+
+typedef enum mrl_activation { MRL_ACT_RELU = 0, MRL_ACT_TANH = 1 } mrl_activation;
+typedef enum mrl_head { MRL_HEAD_LINEAR = 0, MRL_HEAD_STOCHASTIC_ACTOR = 1 } mrl_head;
+
+/* Compile-time constants of the env structs (STATE_SIZE, OBS_DIM, NUM_ACTIONS
+ * or ACTION_DIM); host only.  num_actions is 0 for continuous envs and
+ * action_dim is 0 for discrete ones. */
+int mrl_env_info(int env_kind, int* state_size, int* obs_dim, int* num_actions, int* action_dim);
+
+/* ------------------------------------------------------------------------
+ * L3 boundary: GPUDiscreteEnv / GPUContinuousEnv static methods
+ * (core/env_traits.mojo:242-310, :328-397).
+ *   states  [batch, STATE_SIZE]  in the reference's row layout
+ *           (physics2d/layout.mojo:41-239), observation at columns 0..OBS-1
+ *   actions [batch] float-encoded index, or [batch, ACTION_DIM]
+ *   rewards, dones [batch];  obs [batch, OBS_DIM]
+ * ---------------------------------------------------------------------- */
+
+/* EnvType.reset_kernel_gpu[BATCH, STATE_SIZE](ctx, states, rng_seed) */
+int mrl_env_reset(int env_kind, int batch, float* states, uint64_t rng_seed, void* stream);
+
+/* EnvType.step_kernel_gpu[BATCH, STATE_SIZE, OBS_DIM(, ACTION_DIM)](ctx, states,
+ * actions, rewards, dones, obs, rng_seed) */
+int mrl_env_step(int env_kind, int batch, float* states, const float* actions, float* rewards,
+                 float* dones, float* obs, uint64_t rng_seed, void* stream);
+
+/* EnvType.selective_reset_kernel_gpu[BATCH, STATE_SIZE](ctx, states, dones, rng_seed) */
+int mrl_env_selective_reset(int env_kind, int batch, float* states, float* dones,
+                            uint64_t rng_seed, void* stream);
+
+/* ------------------------------------------------------------------------
+ * L2 boundary: Model / Optimizer (deep_rl/model/model.mojo:201-273,
+ * deep_rl/optimizer/optimizer.mojo:51-68).  A network is
+ * seq(Hidden[in,h], Hidden[h,h], Head[h,out]) with flat fp32 parameters
+ * [W0(in*h) | b0 | W1(h*h) | b1 | W2(h*out) | b2 (| log_std(out))], W row-major
+ * [IN, OUT] (linear.mojo:14-27, stochastic_actor.mojo:47-49).
+ * ---------------------------------------------------------------------- */
+typedef struct mrl_net_spec {
+    int32_t in_dim;
+    int32_t hidden_dim;
+    int32_t out_dim;    /* weight columns of the head (A for the Gaussian actor) */
+    int32_t activation; /* mrl_activation of both hidden layers                  */
+    int32_t head;       /* mrl_head                                              */
+} mrl_net_spec;
+
+/* Host helpers: PARAM_SIZE, CACHE_SIZE per sample, output columns. */
+int mrl_net_param_size(const mrl_net_spec* net);
+int mrl_net_cache_per_sample(const mrl_net_spec* net);
+int mrl_net_out_cols(const mrl_net_spec* net);
+/* Floats of workspace mrl_mlp_forward / mrl_mlp_backward need for `batch` rows. */
+int64_t mrl_mlp_workspace_floats(const mrl_net_spec* net, int batch);
+
+/* Model.forward_gpu_ws / forward_gpu_no_cache_ws (sequential.mojo:537-722).
+ * out [batch, out_cols]; cache (NULL = no cache) [batch * CACHE_SIZE] blocked per
+ * layer as in sequential.mojo:41-44; workspace: mrl_mlp_workspace_floats floats. */
+int mrl_mlp_forward(const mrl_net_spec* net, int batch, const float* in, const float* params,
+                    float* out, float* cache, float* workspace, void* stream);
+
+/* Model.backward_gpu_ws (sequential.mojo:724-865).  grad_out [batch, out_cols];
+ * grads [PARAM_SIZE] is overwritten; grad_in [batch, in] may be NULL. */
+int mrl_mlp_backward(const mrl_net_spec* net, int batch, const float* grad_out,
+                     const float* params, const float* cache, float* grad_in, float* grads,
+                     float* workspace, void* stream);
+
+/* Adam.step_gpu (deep_rl/optimizer/adam.mojo:113-247).  state_mv is the
+ * interleaved [n, 2] (m, v) vector; bc1/bc2 are the host-computed bias
+ * corrections 1 - beta^t. */
+int mrl_adam_step(int n, float* params, const float* grads, float* state_mv, float lr,
+                  float beta1, float beta2, float eps, float bc1, float bc2, void* stream);
+
+/* ------------------------------------------------------------------------
+ * L4 kernels of DeepPPOAgent.train_gpu, one entry point per reference kernel.
+ * ---------------------------------------------------------------------- */
+
+/* _sample_actions_kernel (deep_agents/ppo/ppo.mojo:4064-4123) */
+int mrl_sample_actions(int n_envs, int num_actions, const float* logits, float* actions,
+                       float* log_probs, uint32_t seed, void* stream);
+
+/* Greedy action of select_action(training=False) (ppo.mojo:1019-1022). */
+int mrl_argmax_actions(int n_envs, int num_actions, const float* logits, float* actions,
+                       void* stream);
+
+/* GAE + returns over a time-major [T, N] rollout; replaces the host loop of
+ * train_gpu (ppo.mojo:2316-2353). */
+int mrl_gae(int rollout_len, int n_envs, const float* rewards, const float* values,
+            const float* dones, const float* bootstrap_values, double gamma, double gae_lambda,
+            float* advantages, float* returns, void* stream);
+
+/* Advantage normalisation (ppo.mojo:2356-2371, :2483-2511, :637-653): in place,
+ * (x - mean) / (sqrt(var + 1e-8) + 1e-8), population variance.
+ * scratch: 4 floats of device memory. */
+int mrl_normalize_advantages(int64_t n, float* advantages, float* scratch, void* stream);
+
+/* ppo_gather_minibatch_kernel (ppo.mojo:135-191) */
+int mrl_ppo_gather_minibatch(int batch, int obs_dim, const int32_t* indices,
+                             const float* rollout_obs, const float* rollout_actions,
+                             const float* advantages, const float* returns,
+                             const float* rollout_log_probs, const float* rollout_values,
+                             float* mb_obs, float* mb_actions, float* mb_advantages,
+                             float* mb_returns, float* mb_old_log_probs, float* mb_old_values,
+                             void* stream);
+
+/* ppo_actor_grad_with_kl_kernel (ppo.mojo:285-378) */
+int mrl_ppo_actor_grad(int batch, int num_actions, const float* logits,
+                       const float* old_log_probs, const float* advantages,
+                       const float* actions, float clip_epsilon, float entropy_coef,
+                       float* grad_logits, float* kl_divergences, void* stream);
+
+/* ppo_critic_grad_kernel / ppo_critic_grad_clipped_kernel (ppo.mojo:538-633) */
+int mrl_ppo_critic_grad(int batch, const float* values, const float* old_values,
+                        const float* returns, float value_loss_coef, float clip_epsilon,
+                        int clip_value, float* grad_values, void* stream);
+
+/* gradient_norm_kernel + gradient_reduce_and_compute_scale_kernel +
+ * gradient_apply_scale_kernel (ppo.mojo:382-534).  scratch: 4 floats; after the
+ * call scratch[0] holds the squared norm and scratch[1] the applied scale. */
+int mrl_grad_clip(int n, float* grads, float max_grad_norm, float* scratch, void* stream);
+
+/* ------------------------------------------------------------------------
+ * L4 fused path: the three phases of DeepPPOAgent.train_gpu
+ * (ppo.mojo:1558-2840) with every buffer resident in HBM and no host crossing
+ * inside a phase.
+ * ---------------------------------------------------------------------- */
+typedef struct mrl_config {
+    int32_t env_kind;
+    int32_t n_envs;          /* per process (per GPU)                               */
+    int32_t rollout_len;
+    int32_t hidden_dim;
+    int32_t minibatch_size;  /* gpu_minibatch_size; T*N // B minibatches per epoch   */
+    int32_t num_epochs;
+    int32_t precision;       /* 0: fp32 everywhere; 1: bf16 tensor-core update GEMMs */
+    int32_t normalize_advantages;
+    int32_t norm_adv_per_minibatch;
+    int32_t clip_value;
+    int32_t deterministic;   /* 1: greedy actions in the rollout (evaluation / parity) */
+    int32_t world_size;      /* data-parallel ranks; gradients are averaged over them  */
+    int32_t rank;
+    double gamma;            /* Float64 in the reference; cast to f32 where it does    */
+    double gae_lambda;       /* (gamma * gae_lambda is formed in f64, ppo.mojo:2319)   */
+    float clip_epsilon;
+    float value_loss_coef;
+    float target_kl;         /* <= 0 disables the early stop                          */
+    float max_grad_norm;     /* <= 0 disables clipping                                */
+    float adam_beta1;
+    float adam_beta2;
+    float adam_eps;
+} mrl_config;
+
+/* Reference defaults (ppo.mojo:869-892; adam.mojo:38-50). */
+void mrl_config_defaults(mrl_config* cfg);
+
+typedef struct mrl_ctx mrl_ctx;
+
+int mrl_create(mrl_ctx** out, const mrl_config* cfg);
+int mrl_destroy(mrl_ctx* ctx);
+const char* mrl_last_error_string(void);
+
+/* Network.copy_params_to_device / copy_state_to_device and back
+ * (deep_rl/training/network.mojo:698-772).  HOST pointers; which = 0 actor,
+ * 1 critic.  Optimizer state is the interleaved (m, v) vector. */
+int mrl_set_params(mrl_ctx* ctx, int which, const float* params_host, const float* opt_state_host);
+int mrl_get_params(mrl_ctx* ctx, int which, float* params_host, float* opt_state_host);
+int mrl_param_size(mrl_ctx* ctx, int which);
+
+/* NCCL bootstrap for world_size > 1: rank 0 fills a 128-byte id, every rank
+ * passes the same bytes to mrl_comm_init. */
+int mrl_comm_unique_id(uint8_t id_host[128]);
+int mrl_comm_init(mrl_ctx* ctx, const uint8_t id_host[128]);
+
+/* reset_kernel_gpu + _extract_obs_from_state_kernel at the top of train_gpu
+ * (ppo.mojo:1943-1955). */
+int mrl_ppo_reset(mrl_ctx* ctx, uint64_t rng_seed);
+
+/* Phase 1 (ppo.mojo:2069-2286): rollout_len steps of actor/critic forward,
+ * sampling, store, env step, episode tracking, selective reset. */
+int mrl_ppo_rollout(mrl_ctx* ctx);
+
+/* Phase 2 (ppo.mojo:2300-2376): bootstrap value, GAE, global normalisation. */
+int mrl_ppo_gae(mrl_ctx* ctx);
+
+/* Phase 3 (ppo.mojo:2386-2728).  Learning rates and entropy coefficient are the
+ * host-annealed values (ppo.mojo:2396-2406).  permutations_host: NULL = the
+ * library shuffles on the device; otherwise [num_epochs, T*N] int32 indices
+ * (the reference's host Fisher-Yates output) used verbatim. */
+int mrl_ppo_update(mrl_ctx* ctx, float actor_lr, float critic_lr, float entropy_coef,
+                   const int32_t* permutations_host);
+
+/* Device pointers of the context's resident buffers (for inspection). */
+typedef enum mrl_buffer {
+    MRL_BUF_STATES = 0, MRL_BUF_OBS = 1, MRL_BUF_ROLLOUT_OBS = 2, MRL_BUF_ROLLOUT_ACTIONS = 3,
+    MRL_BUF_ROLLOUT_LOG_PROBS = 4, MRL_BUF_ROLLOUT_VALUES = 5, MRL_BUF_ROLLOUT_REWARDS = 6,
+    MRL_BUF_ROLLOUT_DONES = 7, MRL_BUF_ADVANTAGES = 8, MRL_BUF_RETURNS = 9,
+    MRL_BUF_ACTOR_PARAMS = 10, MRL_BUF_CRITIC_PARAMS = 11, MRL_BUF_ACTOR_GRADS = 12,
+    MRL_BUF_CRITIC_GRADS = 13, MRL_BUF_DONES = 14
+} mrl_buffer;
+int mrl_get_buffer(mrl_ctx* ctx, int which, float** device_ptr, int64_t* n_floats);
+
+/* Counters kept on the device across phases; a host copy is returned. */
+typedef struct mrl_stats {
+    int64_t total_steps;        /* env steps of this rank                          */
+    int64_t completed_episodes; /* episodes finished so far                        */
+    double  sum_episode_reward; /* over completed episodes                         */
+    double  sum_episode_steps;
+    int32_t minibatches_done;   /* optimiser steps in the last update              */
+    int32_t kl_early_stop;      /* 1 if the last update stopped on target_kl       */
+    float   last_mean_kl;
+    int32_t actor_adam_t;
+    int32_t critic_adam_t;
+} mrl_stats;
+int mrl_get_stats(mrl_ctx* ctx, mrl_stats* out_host);
+
+/* Completed (return, length) pairs since the last drain, replacing the
+ * per-step D->H copies of ppo.mojo:2212-2225.  Returns the count written
+ * (<= capacity) or a negative status. */
+int mrl_drain_episodes(mrl_ctx* ctx, float* returns_host, float* lengths_host, int capacity);
+
+/* The stream all fused phases run on (cudaStream_t as void*). */
+void* mrl_stream(mrl_ctx* ctx);
+
+/* Kernels launched by this library since load (all entry points). */
+int64_t mrl_kernel_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOJORL_B200_H */

@@ -1,0 +1,221 @@
+// CPU ORACLE - test infrastructure, not product code.
+//
+// C entry points over the oracle headers so that the pytest harness can drive
+// the checker through ctypes.  Only tests/, __graft_entry__.smoke() and the
+// cpu_baseline / --impl reference legs of bench.py may load this library.
+#include <cstdlib>
+#include "train.hpp"
+
+using namespace oracle;
+
+extern "C" {
+
+int orc_env_info(int kind, int* state_size, int* obs_dim, int* num_actions, int* action_dim) {
+    return env_dims(kind, state_size, obs_dim, num_actions, action_dim) ? 0 : -1;
+}
+void orc_env_reset(int kind, int n, float* states, uint64_t seed) { env_reset(kind, states, n, seed); }
+void orc_env_step(int kind, int n, float* states, const float* actions, float* rewards, float* dones,
+                  float* obs, uint64_t seed) {
+    env_step(kind, states, actions, rewards, dones, obs, n, seed);
+}
+void orc_env_selective_reset(int kind, int n, float* states, float* dones, uint64_t seed) {
+    env_selective_reset(kind, states, dones, n, seed);
+}
+
+// LunarLander step that also returns the contact list (for contact-order checks).
+int orc_lunar_step_one(float* state, int env_index, float action, float* reward, float* done,
+                       float* contacts_out) {
+    float shapes[3 * SHAPE_MAX_SIZE];
+    lunar::init_shapes(shapes);
+    int a = (int)action;
+    lunar::setup_env_discrete(state, env_index, a);
+    int nc = lunar::physics_step(state, shapes, contacts_out);
+    float fuel = a == 2 ? (float)lunar::MAIN_ENGINE_FUEL_COST
+                        : ((a == 1 || a == 3) ? (float)lunar::SIDE_ENGINE_FUEL_COST : 0.0f);
+    lunar::finalize_env(state, contacts_out, nc, fuel, reward, done);
+    return nc;
+}
+
+// Generic falling-body scenario of tests/test_cpu_gpu_equivalence.mojo:33-82:
+// rows of the LunarLander layout are reused with one dynamic body and no edges.
+void orc_integrate(float* state, int num_bodies, int bodies_off, int forces_off, float gx, float gy,
+                   float dt, int steps) {
+    for (int i = 0; i < steps; ++i) {
+        integrate_velocities(state, num_bodies, bodies_off, forces_off, gx, gy, dt);
+        integrate_positions(state, num_bodies, bodies_off, dt);
+    }
+}
+
+void orc_philox(uint64_t seed, uint64_t offset, int nsteps, uint32_t* out) {
+    Philox p(seed, offset);
+    for (int i = 0; i < nsteps; ++i) p.step(out + 4 * i);
+}
+void orc_philox_raw(const uint32_t ctr[4], const uint32_t key[2], uint32_t out[4]) {
+    Philox p(0, 0);
+    p.key[0] = key[0]; p.key[1] = key[1];
+    for (int i = 0; i < 4; ++i) p.ctr[i] = ctr[i];
+    p.step(out);
+}
+void orc_philox_uniform(uint64_t seed, uint64_t offset, int nsteps, float* out) {
+    Philox p(seed, offset);
+    for (int i = 0; i < nsteps; ++i) p.step_uniform(out + 4 * i);
+}
+uint32_t orc_xorshift32(uint32_t x) { return xorshift32(x); }
+
+// fn: 0 sin, 1 cos, 2 exp, 3 log, 4 tanh
+void orc_detmath(int fn, const float* x, float* y, int n) {
+    for (int i = 0; i < n; ++i) {
+        switch (fn) {
+            case 0: y[i] = mrl_sinf(x[i]); break;
+            case 1: y[i] = mrl_cosf(x[i]); break;
+            case 2: y[i] = mrl_expf(x[i]); break;
+            case 3: y[i] = mrl_logf(x[i]); break;
+            default: y[i] = mrl_tanhf(x[i]); break;
+        }
+    }
+}
+
+static ppo::NetSpec to_spec(const mrl_net_spec* n) {
+    return ppo::NetSpec{n->in_dim, n->hidden_dim, n->out_dim, n->activation, n->head};
+}
+int orc_net_param_size(const mrl_net_spec* n) { return to_spec(n).param_size(); }
+int orc_net_cache_per_sample(const mrl_net_spec* n) { return to_spec(n).cache_per_sample(); }
+void orc_mlp_forward(const mrl_net_spec* n, int batch, const float* in, const float* params, float* out,
+                     float* cache) {
+    ppo::mlp_forward(to_spec(n), batch, in, params, out, cache);
+}
+void orc_mlp_backward(const mrl_net_spec* n, int batch, const float* grad_out, const float* params,
+                      const float* cache, float* grad_in, float* grads, int acc64) {
+    if (acc64) ppo::mlp_backward<double>(to_spec(n), batch, grad_out, params, cache, grad_in, grads);
+    else ppo::mlp_backward<float>(to_spec(n), batch, grad_out, params, cache, grad_in, grads);
+}
+void orc_adam_step(int n, float* params, const float* grads, float* state_mv, float lr, float beta1,
+                   float beta2, float eps, float bc1, float bc2) {
+    ppo::adam_step(params, grads, state_mv, n, lr, beta1, beta2, eps, bc1, bc2);
+}
+void orc_adam_bias_corrections(double beta1, double beta2, int t, float* bc1, float* bc2) {
+    ppo::adam_bias_corrections(beta1, beta2, t, bc1, bc2);
+}
+void orc_sample_actions(int n, int num_actions, const float* logits, float* actions, float* log_probs,
+                        uint32_t seed) {
+    ppo::sample_actions(logits, n, num_actions, seed, actions, log_probs);
+}
+void orc_argmax_actions(int n, int num_actions, const float* logits, float* actions) {
+    ppo::argmax_actions(logits, n, num_actions, actions);
+}
+void orc_gae(int T, int N, const float* rewards, const float* values, const float* dones,
+             const float* bootstrap, double gamma, double gae_lambda, float* advantages, float* returns) {
+    ppo::gae(rewards, values, dones, bootstrap, T, N, (float)gamma, (float)(gamma * gae_lambda), advantages,
+             returns);
+}
+void orc_normalize_advantages(int64_t n, float* adv, int acc64) {
+    if (acc64) ppo::normalize_advantages<double>(adv, (size_t)n);
+    else ppo::normalize_advantages<float>(adv, (size_t)n);
+}
+void orc_ppo_actor_grad(int batch, int num_actions, const float* logits, const float* old_log_probs,
+                        const float* advantages, const float* actions, float clip_epsilon,
+                        float entropy_coef, float* grad_logits, float* kl) {
+    ppo::actor_grad_with_kl(logits, old_log_probs, advantages, actions, batch, num_actions, clip_epsilon,
+                            entropy_coef, (float)batch, grad_logits, kl);
+}
+void orc_ppo_critic_grad(int batch, const float* values, const float* old_values, const float* returns,
+                         float value_loss_coef, float clip_epsilon, int clip_value, float* grad_values) {
+    ppo::critic_grad(values, old_values, returns, batch, value_loss_coef, clip_epsilon, clip_value != 0,
+                     (float)batch, grad_values);
+}
+float orc_grad_clip(int n, float* grads, float max_norm, int acc64) {
+    return acc64 ? ppo::clip_grad_norm<double>(grads, n, max_norm)
+                 : ppo::clip_grad_norm<float>(grads, n, max_norm);
+}
+
+// ---- fused phases -------------------------------------------------------
+void* orc_agent_create(const mrl_config* cfg) {
+    int a, b, c, d;
+    if (!env_dims(cfg->env_kind, &a, &b, &c, &d)) return nullptr;
+    return new Agent(*cfg);
+}
+void orc_agent_destroy(void* h) { delete (Agent*)h; }
+int orc_agent_param_size(void* h, int which) {
+    Agent* a = (Agent*)h;
+    return (int)(which == 0 ? a->actor_params.size() : a->critic_params.size());
+}
+void orc_agent_set_params(void* h, int which, const float* params, const float* state) {
+    Agent* a = (Agent*)h;
+    auto& p = which == 0 ? a->actor_params : a->critic_params;
+    auto& s = which == 0 ? a->actor_state : a->critic_state;
+    if (params) std::memcpy(p.data(), params, sizeof(float) * p.size());
+    if (state) std::memcpy(s.data(), state, sizeof(float) * s.size());
+}
+void orc_agent_get_params(void* h, int which, float* params, float* state) {
+    Agent* a = (Agent*)h;
+    auto& p = which == 0 ? a->actor_params : a->critic_params;
+    auto& s = which == 0 ? a->actor_state : a->critic_state;
+    if (params) std::memcpy(params, p.data(), sizeof(float) * p.size());
+    if (state) std::memcpy(state, s.data(), sizeof(float) * s.size());
+}
+void orc_agent_reset(void* h, uint64_t seed) { ((Agent*)h)->reset(seed); }
+void orc_agent_rollout(void* h) { ((Agent*)h)->rollout(); }
+void orc_agent_gae(void* h, int acc64) {
+    if (acc64) ((Agent*)h)->gae_phase<double>(); else ((Agent*)h)->gae_phase<float>();
+}
+void orc_agent_update(void* h, float actor_lr, float critic_lr, float entropy_coef, const int32_t* perms,
+                      int acc64) {
+    if (acc64) ((Agent*)h)->update<double>(actor_lr, critic_lr, entropy_coef, perms);
+    else ((Agent*)h)->update<float>(actor_lr, critic_lr, entropy_coef, perms);
+}
+// which follows mrl_buffer
+int orc_agent_get_buffer(void* h, int which, float** ptr, int64_t* n) {
+    Agent* a = (Agent*)h;
+    std::vector<float>* v = nullptr;
+    switch (which) {
+        case MRL_BUF_STATES: v = &a->states; break;
+        case MRL_BUF_OBS: v = &a->obs; break;
+        case MRL_BUF_ROLLOUT_OBS: v = &a->r_obs; break;
+        case MRL_BUF_ROLLOUT_ACTIONS: v = &a->r_actions; break;
+        case MRL_BUF_ROLLOUT_LOG_PROBS: v = &a->r_log_probs; break;
+        case MRL_BUF_ROLLOUT_VALUES: v = &a->r_values; break;
+        case MRL_BUF_ROLLOUT_REWARDS: v = &a->r_rewards; break;
+        case MRL_BUF_ROLLOUT_DONES: v = &a->r_dones; break;
+        case MRL_BUF_ADVANTAGES: v = &a->advantages; break;
+        case MRL_BUF_RETURNS: v = &a->returns; break;
+        case MRL_BUF_ACTOR_PARAMS: v = &a->actor_params; break;
+        case MRL_BUF_CRITIC_PARAMS: v = &a->critic_params; break;
+        case MRL_BUF_ACTOR_GRADS: v = &a->actor_grads; break;
+        case MRL_BUF_CRITIC_GRADS: v = &a->critic_grads; break;
+        case MRL_BUF_DONES: v = &a->dones; break;
+        default: return -1;
+    }
+    *ptr = v->data();
+    *n = (int64_t)v->size();
+    return 0;
+}
+void orc_agent_get_stats(void* h, mrl_stats* s) {
+    Agent* a = (Agent*)h;
+    s->total_steps = a->total_steps;
+    s->completed_episodes = a->completed_episodes;
+    s->sum_episode_reward = a->sum_ep_reward;
+    s->sum_episode_steps = a->sum_ep_steps;
+    s->minibatches_done = a->minibatches_done;
+    s->kl_early_stop = a->kl_early_stop;
+    s->last_mean_kl = a->last_mean_kl;
+    s->actor_adam_t = a->actor_t;
+    s->critic_adam_t = a->critic_t;
+}
+int orc_agent_drain_episodes(void* h, float* returns, float* lengths, int capacity) {
+    Agent* a = (Agent*)h;
+    int n = (int)a->ep_returns.size();
+    if (n > capacity) n = capacity;
+    for (int i = 0; i < n; ++i) { returns[i] = a->ep_returns[i]; lengths[i] = a->ep_lengths[i]; }
+    a->ep_returns.clear();
+    a->ep_lengths.clear();
+    return n;
+}
+int orc_num_threads() {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+}  // extern "C"

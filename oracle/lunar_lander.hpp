@@ -1,0 +1,363 @@
+// CPU ORACLE - test infrastructure, not product code.
+//
+// fp32 restatement of LunarLanderV2's GPU path (discrete and continuous action
+// variants): envs/lunar_lander/lunar_lander_v2.mojo:1453-2774 (discrete),
+// :2781-3495 (continuous), constants.mojo:9-130, helpers.mojo:10-133.
+// Parity unpinned at the Philox boundary (see physics2d.hpp).
+#pragma once
+#include "physics2d.hpp"
+
+namespace oracle {
+namespace lunar {
+
+// envs/lunar_lander/constants.mojo:9-75 (Float64 constants, cast where used)
+constexpr double GRAVITY_X = 0.0, GRAVITY_Y = -10.0, DT = 0.02;
+constexpr int VELOCITY_ITERATIONS = 6, POSITION_ITERATIONS = 2;
+constexpr double SCALE = 30.0;
+constexpr double LEG_AWAY = 20.0 / SCALE, LEG_DOWN = 18.0 / SCALE, LEG_W = 2.0 / SCALE,
+                 LEG_H = 8.0 / SCALE;
+constexpr double LANDER_MASS = 5.0, LANDER_INERTIA = 2.0, LEG_MASS = 0.2, LEG_INERTIA = 0.02;
+constexpr double LEG_SPRING_STIFFNESS = 400.0, LEG_SPRING_DAMPING = 40.0;
+constexpr double MAIN_ENGINE_POWER = 13.0, SIDE_ENGINE_POWER = 0.6;
+constexpr double MAIN_ENGINE_Y_OFFSET = 4.0 / SCALE, SIDE_ENGINE_HEIGHT = 14.0 / SCALE,
+                 SIDE_ENGINE_AWAY = 12.0 / SCALE;
+constexpr double CRASH_PENALTY = -100.0, LAND_REWARD = 100.0, MAIN_ENGINE_FUEL_COST = 0.30,
+                 SIDE_ENGINE_FUEL_COST = 0.03;
+constexpr double VIEWPORT_W = 600.0, VIEWPORT_H = 400.0, FPS = 50.0;
+constexpr double W_UNITS = VIEWPORT_W / SCALE, H_UNITS = VIEWPORT_H / SCALE;
+constexpr double HELIPAD_Y = H_UNITS / 4.0, HELIPAD_X = W_UNITS / 2.0;
+constexpr double FRICTION = 0.1, RESTITUTION = 0.0, BAUMGARTE = 0.2, SLOP = 0.005;
+constexpr int TERRAIN_CHUNKS = 11;
+
+constexpr Layout L = LUNAR_LAYOUT;
+constexpr int STATE_SIZE = L.state_size();
+constexpr int OBS_DIM = 8, NUM_ACTIONS = 4, ACTION_DIM = 2;
+constexpr int NUM_BODIES = 3, MAX_CONTACTS = 8, MAX_JOINTS = 2, MAX_TERRAIN_EDGES = 16;
+constexpr int BODIES_OFFSET = L.bodies_offset(), FORCES_OFFSET = L.forces_offset(),
+              JOINTS_OFFSET = L.joints_offset(), JOINT_COUNT_OFFSET = L.joint_count_offset(),
+              EDGES_OFFSET = L.edges_offset(), EDGE_COUNT_OFFSET = L.edge_count_offset(),
+              METADATA_OFFSET = L.metadata_offset();
+constexpr int META_STEP_COUNT = 0, META_TOTAL_REWARD = 1, META_PREV_SHAPING = 2, META_DONE = 3;
+
+// lunar_lander_v2.mojo:1969-2026 - three polygons, rewritten every step there.
+inline void init_shapes(float* shapes) {
+    for (int i = 0; i < 3 * SHAPE_MAX_SIZE; ++i) shapes[i] = 0.0f;
+    shapes[0] = (float)SHAPE_POLYGON;
+    shapes[1] = 6.0f;
+    shapes[2] = (float)(-14.0 / SCALE); shapes[3] = (float)(17.0 / SCALE);
+    shapes[4] = (float)(-17.0 / SCALE); shapes[5] = 0.0f;
+    shapes[6] = (float)(-17.0 / SCALE); shapes[7] = (float)(-10.0 / SCALE);
+    shapes[8] = (float)(17.0 / SCALE);  shapes[9] = (float)(-10.0 / SCALE);
+    shapes[10] = (float)(17.0 / SCALE); shapes[11] = 0.0f;
+    shapes[12] = (float)(14.0 / SCALE); shapes[13] = (float)(17.0 / SCALE);
+    for (int leg = 0; leg < 2; ++leg) {
+        float* sh = shapes + (leg + 1) * SHAPE_MAX_SIZE;
+        sh[0] = (float)SHAPE_POLYGON;
+        sh[1] = 4.0f;
+        sh[2] = (float)(-LEG_W); sh[3] = (float)(LEG_H);
+        sh[4] = (float)(-LEG_W); sh[5] = (float)(-LEG_H);
+        sh[6] = (float)(LEG_W);  sh[7] = (float)(-LEG_H);
+        sh[8] = (float)(LEG_W);  sh[9] = (float)(LEG_H);
+    }
+}
+
+// lunar_lander_v2.mojo:1709-1966.  Writes only the fields the reference writes
+// (body mass/force slots, joint motor/impulse slots and edges 10..15 are left
+// as they are).
+inline void reset_env(float* s, int64_t seed) {
+    Philox velocity_rng((uint64_t)seed, 0);
+    float velocity_rand[4];
+    velocity_rng.step_uniform(velocity_rand);
+    Philox terrain_rng((uint64_t)(seed + 1000), 0);
+
+    const int n_edges = TERRAIN_CHUNKS - 1, n_chunks = TERRAIN_CHUNKS;
+    s[EDGE_COUNT_OFFSET] = (float)n_edges;
+    const float x_spacing = (float)(W_UNITS / (TERRAIN_CHUNKS - 1));
+    float raw[12];
+    const float h_units_half = (float)(H_UNITS / 2.0);
+    for (int c = 0; c < n_chunks + 1; ++c) {
+        float r[4];
+        terrain_rng.step_uniform(r);
+        raw[c] = r[0] * h_units_half;
+    }
+    float smooth[11];
+    for (int c = 0; c < n_chunks; ++c) {
+        float h;
+        if (c == 0) h = (raw[0] + raw[0] + raw[1]) / 3.0f;
+        else if (c == n_chunks - 1) h = (raw[c - 1] + raw[c] + raw[c]) / 3.0f;
+        else h = (raw[c - 1] + raw[c] + raw[c + 1]) / 3.0f;
+        smooth[c] = h;
+    }
+    for (int c = TERRAIN_CHUNKS / 2 - 2; c < TERRAIN_CHUNKS / 2 + 3; ++c)
+        if (c >= 0 && c < n_chunks) smooth[c] = (float)HELIPAD_Y;
+    for (int e = 0; e < n_edges; ++e) {
+        float x0 = (float)e * x_spacing, x1 = (float)(e + 1) * x_spacing;
+        float y0 = smooth[e], y1 = smooth[e + 1];
+        float dx = x1 - x0, dy = y1 - y0;
+        float length = sqrtf(dx * dx + dy * dy);
+        float nx = -dy / length, ny = dx / length;
+        if (ny < 0.0f) { nx = -nx; ny = -ny; }
+        float* edge = s + EDGES_OFFSET + e * 6;
+        edge[0] = x0; edge[1] = y0; edge[2] = x1; edge[3] = y1; edge[4] = nx; edge[5] = ny;
+    }
+    const float init_random_scale = (float)(1000.0 * DT / LANDER_MASS);
+    float init_vx = (velocity_rand[0] * 2.0f - 1.0f) * init_random_scale;
+    float init_vy = (velocity_rand[1] * 2.0f - 1.0f) * init_random_scale;
+
+    float* lander = s + BODIES_OFFSET;
+    lander[IDX_X] = (float)HELIPAD_X;
+    lander[IDX_Y] = (float)H_UNITS;
+    lander[IDX_ANGLE] = 0.0f;
+    lander[IDX_VX] = init_vx;
+    lander[IDX_VY] = init_vy;
+    lander[IDX_OMEGA] = 0.0f;
+    lander[IDX_INV_MASS] = (float)(1.0 / LANDER_MASS);
+    lander[IDX_INV_INERTIA] = (float)(1.0 / LANDER_INERTIA);
+    lander[IDX_SHAPE] = 0.0f;
+    for (int leg = 0; leg < 2; ++leg) {
+        float* lb = s + BODIES_OFFSET + (leg + 1) * BODY_STATE_SIZE;
+        float leg_offset_x = leg == 1 ? (float)LEG_AWAY : (float)(-LEG_AWAY);
+        lb[IDX_X] = (float)HELIPAD_X + leg_offset_x;
+        lb[IDX_Y] = (float)(H_UNITS - 10.0 / SCALE - LEG_DOWN);
+        lb[IDX_ANGLE] = 0.0f;
+        lb[IDX_VX] = init_vx;
+        lb[IDX_VY] = init_vy;
+        lb[IDX_OMEGA] = 0.0f;
+        lb[IDX_INV_MASS] = (float)(1.0 / LEG_MASS);
+        lb[IDX_INV_INERTIA] = (float)(1.0 / LEG_INERTIA);
+        lb[IDX_SHAPE] = (float)(leg + 1);
+    }
+    s[JOINT_COUNT_OFFSET] = 2.0f;
+    for (int j = 0; j < 2; ++j) {
+        float* jt = s + JOINTS_OFFSET + j * JOINT_DATA_SIZE;
+        float leg_offset_x = j == 1 ? (float)LEG_AWAY : (float)(-LEG_AWAY);
+        jt[JOINT_TYPE] = (float)JOINT_REVOLUTE;
+        jt[JOINT_BODY_A] = 0.0f;
+        jt[JOINT_BODY_B] = (float)(j + 1);
+        jt[JOINT_ANCHOR_AX] = leg_offset_x;
+        jt[JOINT_ANCHOR_AY] = (float)(-10.0 / SCALE);
+        jt[JOINT_ANCHOR_BX] = 0.0f;
+        jt[JOINT_ANCHOR_BY] = (float)LEG_H;
+        jt[JOINT_REF_ANGLE] = 0.0f;
+        jt[JOINT_LOWER_LIMIT] = j == 1 ? -0.9f : 0.4f;
+        jt[JOINT_UPPER_LIMIT] = j == 1 ? -0.4f : 0.9f;
+        jt[JOINT_STIFFNESS] = (float)LEG_SPRING_STIFFNESS;
+        jt[JOINT_DAMPING] = (float)LEG_SPRING_DAMPING;
+        jt[JOINT_FLAGS] = (float)(JOINT_FLAG_LIMIT_ENABLED | JOINT_FLAG_SPRING_ENABLED);
+    }
+    for (int b = 0; b < NUM_BODIES; ++b) {
+        float* f = s + FORCES_OFFSET + b * 3;
+        f[0] = 0.0f; f[1] = 0.0f; f[2] = 0.0f;
+    }
+    float y_norm = (float)((H_UNITS - (HELIPAD_Y + LEG_DOWN / SCALE)) / (H_UNITS / 2.0));
+    float vx_norm = init_vx * (float)(W_UNITS / 2.0) / 50.0f;
+    float vy_norm = init_vy * (float)(H_UNITS / 2.0) / 50.0f;
+    s[0] = 0.0f; s[1] = y_norm; s[2] = vx_norm; s[3] = vy_norm;
+    s[4] = 0.0f; s[5] = 0.0f; s[6] = 0.0f; s[7] = 0.0f;
+    float y_norm_abs = y_norm;
+    if (y_norm < 0.0f) y_norm_abs = -y_norm;
+    float dist = y_norm_abs;
+    float speed = sqrtf(vx_norm * vx_norm + vy_norm * vy_norm);
+    float init_shaping = -100.0f * dist - 100.0f * speed;
+    s[METADATA_OFFSET + META_STEP_COUNT] = 0.0f;
+    s[METADATA_OFFSET + META_TOTAL_REWARD] = 0.0f;
+    s[METADATA_OFFSET + META_PREV_SHAPING] = init_shaping;
+    s[METADATA_OFFSET + META_DONE] = 0.0f;
+}
+
+// lunar_lander_v2.mojo:1620,1638,1685,1691: the UInt64 seed passes through a
+// float32 kernel argument before Int(); the combination wraps in 64 bits.
+inline int64_t combined_seed(uint64_t rng_seed, int env) {
+    float seed_f = (float)rng_seed;
+    int64_t si = (int64_t)seed_f;
+    return (int64_t)((uint64_t)si * 2654435761ull + (uint64_t)(env + 1) * 12345ull);
+}
+
+inline void reset_all(float* states, int n, uint64_t rng_seed) {
+    for (int i = 0; i < n; ++i) reset_env(states + (size_t)i * STATE_SIZE, combined_seed(rng_seed, i));
+}
+
+// lunar_lander_v2.mojo:1643-1701: dones are read, never cleared.
+inline void selective_reset(float* states, const float* dones, int n, uint64_t rng_seed) {
+    for (int i = 0; i < n; ++i)
+        if (dones[i] > 0.5f) reset_env(states + (size_t)i * STATE_SIZE, combined_seed(rng_seed, i));
+}
+
+// Engine impulse shared by the discrete (:2166-2262) and continuous (:2905-3040)
+// setup routines.  m_power in [0,1]; s_power = 0 or signed direction * power.
+struct EngineCmd { float m_power; float s_dir; float s_power; };
+
+// lunar_lander_v2.mojo:2109-2262 (discrete)
+inline void setup_env_discrete(float* s, int env, int action) {
+    for (int b = 0; b < NUM_BODIES; ++b) {
+        float* f = s + FORCES_OFFSET + b * 3;
+        f[0] = 0.0f; f[1] = 0.0f; f[2] = 0.0f;
+    }
+    if (s[METADATA_OFFSET + META_DONE] > 0.5f) return;
+    int step_count = (int)s[METADATA_OFFSET + META_STEP_COUNT];
+    if (action == 0) return;
+    Philox rng((uint64_t)(int64_t)(env + 12345), (uint64_t)(int64_t)step_count);
+    float r[4];
+    rng.step_uniform(r);
+    float dispersion_x = (r[0] * 2.0f - 1.0f) / (float)SCALE;
+    float dispersion_y = (r[1] * 2.0f - 1.0f) / (float)SCALE;
+    float angle = s[BODIES_OFFSET + IDX_ANGLE];
+    float tip_x, tip_y;
+    mrl_sincosf(angle, &tip_x, &tip_y);
+    float side_x = -tip_y, side_y = tip_x;
+    float vx = s[BODIES_OFFSET + IDX_VX], vy = s[BODIES_OFFSET + IDX_VY];
+    float omega = s[BODIES_OFFSET + IDX_OMEGA];
+    float dvx = 0.0f, dvy = 0.0f, domega = 0.0f;
+    const float main_y_offset = (float)MAIN_ENGINE_Y_OFFSET, side_away = (float)SIDE_ENGINE_AWAY;
+    const float side_height = (float)SIDE_ENGINE_HEIGHT, main_power = (float)MAIN_ENGINE_POWER;
+    const float side_power = (float)SIDE_ENGINE_POWER, lander_mass = (float)LANDER_MASS;
+    const float lander_inertia = (float)LANDER_INERTIA, scale = (float)SCALE;
+    if (action == 2) {
+        float ox = tip_x * (main_y_offset + 2.0f * dispersion_x) + side_x * dispersion_y;
+        float oy = -tip_y * (main_y_offset + 2.0f * dispersion_x) - side_y * dispersion_y;
+        float impulse_x = -ox * main_power, impulse_y = -oy * main_power;
+        dvx += impulse_x / lander_mass;
+        dvy += impulse_y / lander_mass;
+        float torque = ox * impulse_y - oy * impulse_x;
+        domega += torque / lander_inertia;
+    } else if (action == 1 || action == 3) {
+        float direction = action == 1 ? -1.0f : 1.0f;
+        float ox = tip_x * dispersion_x + side_x * (3.0f * dispersion_y + direction * side_away);
+        float oy = -tip_y * dispersion_x - side_y * (3.0f * dispersion_y + direction * side_away);
+        float impulse_x = -ox * side_power, impulse_y = -oy * side_power;
+        dvx += impulse_x / lander_mass;
+        dvy += impulse_y / lander_mass;
+        float r_x = ox - tip_x * 17.0f / scale;
+        float r_y = oy + tip_y * side_height;
+        float torque = r_x * impulse_y - r_y * impulse_x;
+        domega += torque / lander_inertia;
+    }
+    s[BODIES_OFFSET + IDX_VX] = vx + dvx;
+    s[BODIES_OFFSET + IDX_VY] = vy + dvy;
+    s[BODIES_OFFSET + IDX_OMEGA] = omega + domega;
+}
+
+// helpers.mojo:10-133
+inline float compute_shaping(float x_norm, float y_norm, float vx_norm, float vy_norm, float angle,
+                             float left_contact, float right_contact) {
+    float dist = sqrtf(x_norm * x_norm + y_norm * y_norm);
+    float speed = sqrtf(vx_norm * vx_norm + vy_norm * vy_norm);
+    float abs_angle = angle >= 0.0f ? angle : -angle;
+    return -100.0f * dist - 100.0f * speed - 100.0f * abs_angle + 10.0f * left_contact +
+           10.0f * right_contact;
+}
+
+inline float terrain_y_at(const float* s, float leg_x) {
+    const int n_edges = TERRAIN_CHUNKS - 1;
+    const float x_spacing = (float)(W_UNITS / (double)(TERRAIN_CHUNKS - 1));
+    int chunk = (int)(leg_x / x_spacing);
+    if (chunk < 0) chunk = 0;
+    if (chunk >= n_edges) return s[EDGES_OFFSET + (n_edges - 1) * 6 + 3];
+    return s[EDGES_OFFSET + chunk * 6 + 1];
+}
+
+// lunar_lander_v2.mojo:2266-2482.  fuel_cost: 0 none, 1 side, 2 main for the
+// discrete variant; the continuous variant passes its own fuel term.
+inline void finalize_env(float* s, const float* contacts, int n_contacts, float fuel_penalty,
+                         float* reward_out, float* done_out) {
+    if (s[METADATA_OFFSET + META_DONE] > 0.5f) {
+        *reward_out = 0.0f;
+        *done_out = 1.0f;
+        return;
+    }
+    const float* lander = s + BODIES_OFFSET;
+    float x = lander[IDX_X], y = lander[IDX_Y], vx = lander[IDX_VX], vy = lander[IDX_VY];
+    float angle = lander[IDX_ANGLE], omega = lander[IDX_OMEGA];
+    float x_norm = (x - (float)HELIPAD_X) / (float)(W_UNITS / 2.0);
+    float y_norm = (y - (float)(HELIPAD_Y + LEG_DOWN / SCALE)) / (float)(H_UNITS / 2.0);
+    float vx_norm = vx * (float)(W_UNITS / 2.0) / (float)FPS;
+    float vy_norm = vy * (float)(H_UNITS / 2.0) / (float)FPS;
+    float omega_norm = 20.0f * omega / (float)FPS;
+    float left_contact = 0.0f, right_contact = 0.0f;
+    float left_x = s[BODIES_OFFSET + BODY_STATE_SIZE + IDX_X];
+    float left_y = s[BODIES_OFFSET + BODY_STATE_SIZE + IDX_Y];
+    float right_x = s[BODIES_OFFSET + 2 * BODY_STATE_SIZE + IDX_X];
+    float right_y = s[BODIES_OFFSET + 2 * BODY_STATE_SIZE + IDX_Y];
+    float left_terrain_y = terrain_y_at(s, left_x);
+    float right_terrain_y = terrain_y_at(s, right_x);
+    const float leg_h = (float)LEG_H, contact_tolerance = 0.01f;
+    if (left_y - leg_h <= left_terrain_y + contact_tolerance) left_contact = 1.0f;
+    if (right_y - leg_h <= right_terrain_y + contact_tolerance) right_contact = 1.0f;
+    s[0] = x_norm; s[1] = y_norm; s[2] = vx_norm; s[3] = vy_norm;
+    s[4] = angle; s[5] = omega_norm; s[6] = left_contact; s[7] = right_contact;
+    float shaping = compute_shaping(x_norm, y_norm, vx_norm, vy_norm, angle, left_contact, right_contact);
+    float prev_shaping = s[METADATA_OFFSET + META_PREV_SHAPING];
+    float reward = shaping - prev_shaping;
+    s[METADATA_OFFSET + META_PREV_SHAPING] = shaping;
+    reward = reward - fuel_penalty;
+    float done = 0.0f;
+    if (x_norm >= 1.0f || x_norm <= -1.0f) { done = 1.0f; reward = (float)CRASH_PENALTY; }
+    const float h_units_max = (float)(H_UNITS * 1.5);
+    if (y > h_units_max) { done = 1.0f; reward = (float)CRASH_PENALTY; }
+    bool lander_contact = false;
+    for (int c = 0; c < n_contacts; ++c)
+        if ((int)contacts[c * CONTACT_DATA_SIZE + CONTACT_BODY_A] == 0) { lander_contact = true; break; }
+    if (lander_contact) { done = 1.0f; reward = (float)CRASH_PENALTY; }
+    bool both_legs = left_contact > 0.5f && right_contact > 0.5f;
+    float speed_val = sqrtf(vx * vx + vy * vy);
+    float abs_omega = omega;
+    if (omega < 0.0f) abs_omega = -omega;
+    if (both_legs && speed_val < 0.01f && abs_omega < 0.01f) {
+        done = 1.0f;
+        reward = reward + (float)LAND_REWARD;
+    }
+    float step_count = s[METADATA_OFFSET + META_STEP_COUNT];
+    if (step_count > 1000.0f) done = 1.0f;
+    s[METADATA_OFFSET + META_STEP_COUNT] = step_count + 1.0f;
+    s[METADATA_OFFSET + META_DONE] = done;
+    *reward_out = reward;
+    *done_out = done;
+}
+
+// lunar_lander_v2.mojo:2671-2752 - the fused physics step of one environment.
+// contacts: scratch of MAX_CONTACTS*9 floats; returns the contact count.
+inline int physics_step(float* s, const float* shapes, float* contacts) {
+    const float gx = (float)GRAVITY_X, gy = (float)GRAVITY_Y, dt = (float)DT;
+    const float friction = (float)FRICTION, restitution = (float)RESTITUTION;
+    const float baumgarte = (float)BAUMGARTE, slop = (float)SLOP;
+    int n_edges = (int)s[EDGE_COUNT_OFFSET];
+    int n_joints = (int)s[JOINT_COUNT_OFFSET];
+    integrate_velocities(s, NUM_BODIES, BODIES_OFFSET, FORCES_OFFSET, gx, gy, dt);
+    int n_contacts = edge_terrain_detect(s, shapes, NUM_BODIES, BODIES_OFFSET, EDGES_OFFSET,
+                                         MAX_TERRAIN_EDGES, n_edges, contacts, MAX_CONTACTS);
+    for (int it = 0; it < VELOCITY_ITERATIONS; ++it) {
+        solve_velocity_contacts(s, BODIES_OFFSET, contacts, n_contacts, friction, restitution);
+        solve_velocity_joints(s, BODIES_OFFSET, JOINTS_OFFSET, MAX_JOINTS, n_joints, dt);
+    }
+    integrate_positions(s, NUM_BODIES, BODIES_OFFSET, dt);
+    for (int it = 0; it < POSITION_ITERATIONS; ++it) {
+        solve_position_contacts(s, BODIES_OFFSET, contacts, n_contacts, baumgarte, slop);
+        solve_position_joints(s, BODIES_OFFSET, JOINTS_OFFSET, MAX_JOINTS, n_joints, baumgarte, slop);
+    }
+    return n_contacts;
+}
+
+// lunar_lander_v2.mojo:1453-1517: one discrete step of every environment.
+inline void step_all(float* states, const float* actions, float* rewards, float* dones, float* obs,
+                     int n) {
+    float shapes[3 * SHAPE_MAX_SIZE];
+    init_shapes(shapes);
+#ifdef _OPENMP
+#pragma omp parallel for schedule(static)
+#endif
+    for (int env = 0; env < n; ++env) {
+        float* s = states + (size_t)env * STATE_SIZE;
+        float contacts[MAX_CONTACTS * CONTACT_DATA_SIZE];
+        int action = (int)actions[env];
+        setup_env_discrete(s, env, action);
+        int n_contacts = physics_step(s, shapes, contacts);
+        float fuel = 0.0f;
+        if (action == 2) fuel = (float)MAIN_ENGINE_FUEL_COST;
+        else if (action == 1 || action == 3) fuel = (float)SIDE_ENGINE_FUEL_COST;
+        finalize_env(s, contacts, n_contacts, fuel, &rewards[env], &dones[env]);
+        for (int d = 0; d < OBS_DIM; ++d) obs[(size_t)env * OBS_DIM + d] = s[d];
+    }
+}
+
+}  // namespace lunar
+}  // namespace oracle

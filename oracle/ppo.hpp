@@ -1,0 +1,371 @@
+// CPU ORACLE - test infrastructure, not product code.
+//
+// fp32 restatement of the reference's actor-critic MLP (deep_rl/model/*.mojo),
+// the discrete PPO kernels (deep_agents/ppo/ppo.mojo), GAE and advantage
+// normalisation as written in train_gpu (ppo.mojo:2316-2371), per-network
+// gradient clipping (ppo.mojo:382-534) and Adam (deep_rl/optimizer/adam.mojo).
+//
+// Dot products start from the bias and add terms in ascending k with one
+// fused multiply-add per term - the order of the reference's tiled kernels
+// (linear.mojo:167-225).  Whether the Mojo compiler fuses is unknown; fmaf is
+// this build's documented choice on both sides.
+#pragma once
+#include <vector>
+#include "physics2d.hpp"
+
+namespace oracle {
+namespace ppo {
+
+enum Activation { ACT_RELU = 0, ACT_TANH = 1 };
+enum Head { HEAD_LINEAR = 0, HEAD_STOCHASTIC = 1 };
+
+// seq(Hidden[in,h], Hidden[h,h], Head[h,out]) - ppo.mojo:807-830,
+// ppo_continuous.mojo:171-194.  out_dim is the number of head columns with
+// weights (A for the Gaussian actor, whose output row is [mean | log_std]).
+struct NetSpec {
+    int in_dim, hidden, out_dim;
+    int act;   // Activation of the two hidden layers
+    int head;  // Head kind
+    int param_size() const {
+        int p = in_dim * hidden + hidden + hidden * hidden + hidden + hidden * out_dim + out_dim;
+        if (head == HEAD_STOCHASTIC) p += out_dim;  // stochastic_actor.mojo:47-49
+        return p;
+    }
+    int out_cols() const { return head == HEAD_STOCHASTIC ? 2 * out_dim : out_dim; }
+    // linear_relu.mojo:26-32, linear_tanh.mojo:24-33, linear.mojo cache = input
+    int cache_per_sample() const { return (in_dim + hidden) + (hidden + hidden) + hidden; }
+};
+
+// One fused hidden layer; linear_relu.mojo:134-219 / linear_tanh.mojo:135-230.
+// cache (nullable) is [batch, in + out]: input then pre-activation (ReLU) or
+// activation output (tanh).
+inline void hidden_forward(int batch, int in, int out, int act, const float* x, const float* W,
+                           const float* b, float* y, float* cache) {
+#ifdef _OPENMP
+#pragma omp parallel for schedule(static) if (batch >= 256)
+#endif
+    for (int r = 0; r < batch; ++r) {
+        const float* xr = x + (size_t)r * in;
+        float* cr = cache ? cache + (size_t)r * (in + out) : nullptr;
+        if (cr) for (int k = 0; k < in; ++k) cr[k] = xr[k];
+        for (int j = 0; j < out; ++j) {
+            float acc = b[j];
+            for (int k = 0; k < in; ++k) acc = fmaf(xr[k], W[(size_t)k * out + j], acc);
+            float yv;
+            if (act == ACT_RELU) {
+                if (cr) cr[in + j] = acc;
+                yv = acc > 0.0f ? acc : 0.0f;
+            } else {
+                yv = mrl_tanhf(acc);
+                if (cr) cr[in + j] = yv;
+            }
+            y[(size_t)r * out + j] = yv;
+        }
+    }
+}
+
+// linear.mojo:135-294; cache (nullable) is the input.
+inline void linear_forward(int batch, int in, int out, const float* x, const float* W,
+                           const float* b, float* y, int y_stride, float* cache) {
+#ifdef _OPENMP
+#pragma omp parallel for schedule(static) if (batch >= 256)
+#endif
+    for (int r = 0; r < batch; ++r) {
+        const float* xr = x + (size_t)r * in;
+        if (cache) for (int k = 0; k < in; ++k) cache[(size_t)r * in + k] = xr[k];
+        for (int j = 0; j < out; ++j) {
+            float acc = b[j];
+            for (int k = 0; k < in; ++k) acc = fmaf(xr[k], W[(size_t)k * out + j], acc);
+            y[(size_t)r * y_stride + j] = acc;
+        }
+    }
+}
+
+// sequential.mojo:537-722 - forward through the three layers.  `out` is
+// [batch, out_cols].  cache (nullable) is blocked per layer:
+// [batch*(in+H)] [batch*(H+H)] [batch*H]  (sequential.mojo:41-44).
+inline void mlp_forward(const NetSpec& n, int batch, const float* in, const float* params,
+                        float* out, float* cache) {
+    const int I = n.in_dim, H = n.hidden, O = n.out_dim;
+    const float* W0 = params;            const float* b0 = W0 + (size_t)I * H;
+    const float* W1 = b0 + H;            const float* b1 = W1 + (size_t)H * H;
+    const float* W2 = b1 + H;            const float* b2 = W2 + (size_t)H * O;
+    std::vector<float> h0((size_t)batch * H), h1((size_t)batch * H);
+    float* c0 = cache;
+    float* c1 = cache ? cache + (size_t)batch * (I + H) : nullptr;
+    float* c2 = cache ? c1 + (size_t)batch * (H + H) : nullptr;
+    hidden_forward(batch, I, H, n.act, in, W0, b0, h0.data(), c0);
+    hidden_forward(batch, H, H, n.act, h0.data(), W1, b1, h1.data(), c1);
+    linear_forward(batch, H, O, h1.data(), W2, b2, out, n.out_cols(), c2);
+    if (n.head == HEAD_STOCHASTIC) {
+        // stochastic_actor.mojo:386-575: state-independent log_std clamped to [-5, 2]
+        const float* log_std = b2 + O;
+        for (int r = 0; r < batch; ++r)
+            for (int j = 0; j < O; ++j) {
+                float ls = log_std[j];
+                if (ls < -5.0f) ls = -5.0f;
+                else if (ls > 2.0f) ls = 2.0f;
+                out[(size_t)r * 2 * O + O + j] = ls;
+            }
+    }
+}
+
+// Backward of one layer.  dy is [batch, out] and already holds dL/dy of the
+// layer's OUTPUT; for hidden layers the activation derivative is applied here
+// (ReLU mask pre_act > 0, linear_relu.mojo:374,427; tanh 1 - y^2,
+// linear_tanh.mojo:377,431).  Writes dW, db (overwrite, linear.mojo:480-655)
+// and dx (nullable).  ACC is the accumulator type for the batch reductions.
+template <typename ACC>
+inline void layer_backward(int batch, int in, int out, int act_or_neg, const float* dy,
+                           const float* W, const float* cache, int cache_stride, float* dx,
+                           float* dW, float* db) {
+    std::vector<float> g((size_t)batch * out);
+    for (int r = 0; r < batch; ++r)
+        for (int j = 0; j < out; ++j) {
+            float gv = dy[(size_t)r * out + j];
+            if (act_or_neg == ACT_RELU) {
+                float pre = cache[(size_t)r * cache_stride + in + j];
+                gv = pre > 0.0f ? gv : 0.0f;
+            } else if (act_or_neg == ACT_TANH) {
+                float yv = cache[(size_t)r * cache_stride + in + j];
+                gv = gv * (1.0f - yv * yv);
+            }
+            g[(size_t)r * out + j] = gv;
+        }
+    if (dx) {
+#ifdef _OPENMP
+#pragma omp parallel for schedule(static) if (batch >= 256)
+#endif
+        for (int r = 0; r < batch; ++r)
+            for (int i = 0; i < in; ++i) {
+                float acc = 0.0f;
+                for (int j = 0; j < out; ++j) acc = fmaf(g[(size_t)r * out + j], W[(size_t)i * out + j], acc);
+                dx[(size_t)r * in + i] = acc;
+            }
+    }
+#ifdef _OPENMP
+#pragma omp parallel for schedule(static)
+#endif
+    for (int i = 0; i < in; ++i)
+        for (int j = 0; j < out; ++j) {
+            ACC acc = 0;
+            for (int r = 0; r < batch; ++r)
+                acc += (ACC)cache[(size_t)r * cache_stride + i] * (ACC)g[(size_t)r * out + j];
+            dW[(size_t)i * out + j] = (float)acc;
+        }
+    for (int j = 0; j < out; ++j) {
+        ACC acc = 0;
+        for (int r = 0; r < batch; ++r) acc += (ACC)g[(size_t)r * out + j];
+        db[j] = (float)acc;
+    }
+}
+
+// sequential.mojo:724-865.  grad_out is [batch, out_cols]; grads is the flat
+// gradient vector in parameter order; grad_in (nullable) is [batch, in].
+template <typename ACC>
+inline void mlp_backward(const NetSpec& n, int batch, const float* grad_out, const float* params,
+                         const float* cache, float* grad_in, float* grads) {
+    const int I = n.in_dim, H = n.hidden, O = n.out_dim;
+    const float* W0 = params;
+    const float* W1 = W0 + (size_t)I * H + H;
+    const float* W2 = W1 + (size_t)H * H + H;
+    float* dW0 = grads;                  float* db0 = dW0 + (size_t)I * H;
+    float* dW1 = db0 + H;                float* db1 = dW1 + (size_t)H * H;
+    float* dW2 = db1 + H;                float* db2 = dW2 + (size_t)H * O;
+    const float* c0 = cache;
+    const float* c1 = c0 + (size_t)batch * (I + H);
+    const float* c2 = c1 + (size_t)batch * (H + H);
+    std::vector<float> dh1((size_t)batch * H), dh0((size_t)batch * H);
+    if (n.head == HEAD_STOCHASTIC) {
+        // stochastic_actor.mojo:727-966: only the mean columns reach W/b/dx;
+        // d_log_std[j] = sum_b dY[b, A + j], not masked by the forward clamp.
+        std::vector<float> gm((size_t)batch * O);
+        for (int r = 0; r < batch; ++r)
+            for (int j = 0; j < O; ++j) gm[(size_t)r * O + j] = grad_out[(size_t)r * 2 * O + j];
+        layer_backward<ACC>(batch, H, O, -1, gm.data(), W2, c2, H, dh1.data(), dW2, db2);
+        float* dls = db2 + O;
+        for (int j = 0; j < O; ++j) {
+            ACC acc = 0;
+            for (int r = 0; r < batch; ++r) acc += (ACC)grad_out[(size_t)r * 2 * O + O + j];
+            dls[j] = (float)acc;
+        }
+    } else {
+        layer_backward<ACC>(batch, H, O, -1, grad_out, W2, c2, H, dh1.data(), dW2, db2);
+    }
+    layer_backward<ACC>(batch, H, H, n.act, dh1.data(), W1, c1, H + H, dh0.data(), dW1, db1);
+    layer_backward<ACC>(batch, I, H, n.act, dh0.data(), W0, c0, I + H, grad_in, dW0, db0);
+}
+
+// ppo.mojo:4064-4123
+inline void sample_actions(const float* logits, int n, int num_actions, uint32_t seed,
+                           float* actions, float* log_probs) {
+    for (int i = 0; i < n; ++i) {
+        const float* l = logits + (size_t)i * num_actions;
+        uint32_t rng = seed ^ ((uint32_t)i * 2654435761u);
+        rng = xorshift32(rng);
+        float max_logit = l[0];
+        for (int a = 1; a < num_actions; ++a) if (l[a] > max_logit) max_logit = l[a];
+        float sum_exp = 0.0f;
+        for (int a = 0; a < num_actions; ++a) sum_exp = sum_exp + mrl_expf(l[a] - max_logit);
+        float rand_val = random_uniform(rng);
+        float cumsum = 0.0f;
+        int selected = 0;
+        for (int a = 0; a < num_actions; ++a) {
+            float prob = mrl_expf(l[a] - max_logit) / sum_exp;
+            cumsum = cumsum + prob;
+            if (rand_val < cumsum) { selected = a; break; }
+        }
+        actions[i] = (float)selected;
+        float sp = mrl_expf(l[selected] - max_logit) / sum_exp;
+        log_probs[i] = mrl_logf(sp + 1e-8f);
+    }
+}
+
+// Deterministic evaluation policy: ppo.mojo:1019-1022 (select_action with
+// training=False) = first maximum of the softmax probabilities
+// (core/utils/softmax.mojo:73-115, :248-270).
+inline void argmax_actions(const float* logits, int n, int num_actions, float* actions) {
+    for (int i = 0; i < n; ++i) {
+        const float* l = logits + (size_t)i * num_actions;
+        float max_logit = l[0];
+        for (int a = 1; a < num_actions; ++a) if (l[a] > max_logit) max_logit = l[a];
+        float probs[16];
+        float sum_exp = 0.0f;
+        for (int a = 0; a < num_actions; ++a) { probs[a] = mrl_expf(l[a] - max_logit); sum_exp += probs[a]; }
+        for (int a = 0; a < num_actions; ++a) probs[a] /= sum_exp;
+        int best = 0;
+        float best_prob = probs[0];
+        for (int a = 1; a < num_actions; ++a) if (probs[a] > best_prob) { best_prob = probs[a]; best = a; }
+        actions[i] = (float)best;
+    }
+}
+
+// ppo.mojo:2316-2353 - time-major [T, N]
+inline void gae(const float* rewards, const float* values, const float* dones,
+                const float* bootstrap, int T, int N, float gamma, float gae_lambda_times_gamma,
+                float* advantages, float* returns) {
+    for (int env = 0; env < N; ++env) {
+        float g = 0.0f;
+        const float gae_decay = gae_lambda_times_gamma;
+        for (int t = T - 1; t >= 0; --t) {
+            size_t idx = (size_t)t * N + env;
+            float next_val = t == T - 1 ? bootstrap[env] : values[idx + N];
+            if (dones[idx] > 0.5f) { next_val = 0.0f; g = 0.0f; }
+            float delta = rewards[idx] + gamma * next_val - values[idx];
+            g = delta + gae_decay * g;
+            advantages[idx] = g;
+            returns[idx] = g + values[idx];
+        }
+    }
+}
+
+// ppo.mojo:2356-2371 and :2483-2511: mean, population variance,
+// std = sqrt(var + 1e-8), x = (x - mean) / (std + 1e-8).  ACC = float follows
+// the reference's serial fp32 sums; ACC = double gives the exact statistics.
+template <typename ACC>
+inline void normalize_advantages(float* adv, size_t n) {
+    ACC mean = 0;
+    for (size_t i = 0; i < n; ++i) mean += (ACC)adv[i];
+    mean /= (ACC)n;
+    ACC var_sum = 0;
+    for (size_t i = 0; i < n; ++i) {
+        ACC d = (ACC)adv[i] - mean;
+        var_sum += d * d;
+    }
+    float meanf = (float)mean;
+    float variance = (float)(var_sum / (ACC)n);
+    float stdv = sqrtf(variance + 1e-8f);
+    for (size_t i = 0; i < n; ++i) adv[i] = (adv[i] - meanf) / (stdv + 1e-8f);
+}
+
+// ppo.mojo:285-378.  batch_div is the compile-time BATCH_SIZE the gradient is
+// divided by.  Gradient is zero whenever the ratio is outside [1-eps, 1+eps].
+inline void actor_grad_with_kl(const float* logits, const float* old_log_probs,
+                               const float* advantages, const float* actions, int batch,
+                               int num_actions, float clip_epsilon, float entropy_coef,
+                               float batch_div, float* grad_logits, float* kl) {
+    for (int b = 0; b < batch; ++b) {
+        const float* l = logits + (size_t)b * num_actions;
+        int action = (int)actions[b];
+        float advantage = advantages[b];
+        float max_logit = l[0];
+        for (int a = 1; a < num_actions; ++a) if (l[a] > max_logit) max_logit = l[a];
+        float sum_exp = 0.0f;
+        for (int a = 0; a < num_actions; ++a) sum_exp = sum_exp + mrl_expf(l[a] - max_logit);
+        float probs[16];
+        for (int a = 0; a < num_actions; ++a) probs[a] = mrl_expf(l[a] - max_logit) / sum_exp;
+        float new_log_prob = mrl_logf(probs[action] + 1e-8f);
+        kl[b] = old_log_probs[b] - new_log_prob;
+        float ratio = mrl_expf(new_log_prob - old_log_probs[b]);
+        bool is_clipped = (ratio < 1.0f - clip_epsilon) || (ratio > 1.0f + clip_epsilon);
+        for (int a = 0; a < num_actions; ++a) {
+            float* g = grad_logits + (size_t)b * num_actions + a;
+            if (is_clipped) { *g = 0.0f; continue; }
+            float d_log_prob = a == action ? 1.0f - probs[a] : -probs[a];
+            float log_prob_ent = mrl_logf(probs[a] + 1e-8f);
+            float d_entropy = -probs[a] * (1.0f + log_prob_ent);
+            *g = (-advantage * ratio * d_log_prob - entropy_coef * d_entropy) / batch_div;
+        }
+    }
+}
+
+// ppo.mojo:538-633
+inline void critic_grad(const float* values, const float* old_values, const float* returns,
+                        int batch, float value_loss_coef, float clip_epsilon, bool clip_value,
+                        float batch_div, float* grad_values) {
+    for (int b = 0; b < batch; ++b) {
+        float v_new = values[b], ret = returns[b];
+        if (!clip_value) {
+            grad_values[b] = 2.0f * value_loss_coef * (v_new - ret) / batch_div;
+            continue;
+        }
+        float v_old = old_values[b];
+        float v_diff = v_new - v_old;
+        float v_clipped;
+        if (v_diff > clip_epsilon) v_clipped = v_old + clip_epsilon;
+        else if (v_diff < -clip_epsilon) v_clipped = v_old - clip_epsilon;
+        else v_clipped = v_new;
+        float loss_unclipped = (v_new - ret) * (v_new - ret);
+        float loss_clipped = (v_clipped - ret) * (v_clipped - ret);
+        float grad;
+        if (loss_unclipped > loss_clipped) grad = 2.0f * (v_new - ret);
+        else if (v_diff > clip_epsilon || v_diff < -clip_epsilon) grad = 0.0f;
+        else grad = 2.0f * (v_new - ret);
+        grad_values[b] = value_loss_coef * grad / batch_div;
+    }
+}
+
+// ppo.mojo:382-534: scale = max_norm / (norm + 1e-8) when norm > max_norm.
+template <typename ACC>
+inline float clip_grad_norm(float* grads, int n, float max_norm) {
+    ACC sq = 0;
+    for (int i = 0; i < n; ++i) sq += (ACC)grads[i] * (ACC)grads[i];
+    float norm = sqrtf((float)sq);
+    float scale = 1.0f;
+    if (norm > max_norm) scale = max_norm / (norm + 1e-8f);
+    for (int i = 0; i < n; ++i) grads[i] = grads[i] * scale;
+    return norm;
+}
+
+// adam.mojo:113-156; bias corrections computed in f64 on the host (:183-188).
+inline void adam_step(float* params, const float* grads, float* state_mv, int n, float lr,
+                      float beta1, float beta2, float eps, float bc1, float bc2) {
+    for (int i = 0; i < n; ++i) {
+        float g = grads[i];
+        float m_new = beta1 * state_mv[2 * i] + (1.0f - beta1) * g;
+        float v_new = beta2 * state_mv[2 * i + 1] + (1.0f - beta2) * g * g;
+        state_mv[2 * i] = m_new;
+        state_mv[2 * i + 1] = v_new;
+        float m_hat = m_new / bc1;
+        float v_hat = v_new / bc2;
+        params[i] = params[i] - lr * m_hat / (sqrtf(v_hat) + eps);
+    }
+}
+
+inline void adam_bias_corrections(double beta1, double beta2, int t, float* bc1, float* bc2) {
+    *bc1 = (float)(1.0 - std::pow(beta1, (double)t));
+    *bc2 = (float)(1.0 - std::pow(beta2, (double)t));
+}
+
+}  // namespace ppo
+}  // namespace oracle

@@ -1,0 +1,222 @@
+// CPU ORACLE - test infrastructure, not product code.
+//
+// The three phases of DeepPPOAgent.train_gpu (deep_agents/ppo/ppo.mojo:1558-2840)
+// for the discrete-action envs, restated serially on the host with the
+// reference's buffer layouts (time-major [T, N] rollout).  The minibatch
+// permutations are an input: the reference draws them from Mojo's global
+// random_float64() (ppo.mojo:2425-2434), which is not in the reference tree.
+#pragma once
+#include <cstring>
+#include <vector>
+#include "../include/mojorl_b200.h"
+#include "cartpole.hpp"
+#include "lunar_lander.hpp"
+#include "ppo.hpp"
+
+namespace oracle {
+
+inline bool env_dims(int kind, int* state_size, int* obs_dim, int* num_actions, int* action_dim) {
+    switch (kind) {
+        case MRL_ENV_CARTPOLE: *state_size = 4; *obs_dim = 4; *num_actions = 2; *action_dim = 0; return true;
+        case MRL_ENV_LUNAR_LANDER: *state_size = lunar::STATE_SIZE; *obs_dim = 8; *num_actions = 4; *action_dim = 0; return true;
+        default: return false;
+    }
+}
+
+inline void env_reset(int kind, float* states, int n, uint64_t seed) {
+    if (kind == MRL_ENV_CARTPOLE) cartpole::reset_all(states, n);
+    else if (kind == MRL_ENV_LUNAR_LANDER) lunar::reset_all(states, n, seed);
+}
+inline void env_step(int kind, float* states, const float* actions, float* rewards, float* dones,
+                     float* obs, int n, uint64_t seed) {
+    (void)seed;
+    if (kind == MRL_ENV_CARTPOLE) cartpole::step_all(states, actions, rewards, dones, obs, n);
+    else if (kind == MRL_ENV_LUNAR_LANDER) lunar::step_all(states, actions, rewards, dones, obs, n);
+}
+inline void env_selective_reset(int kind, float* states, float* dones, int n, uint64_t seed) {
+    if (kind == MRL_ENV_CARTPOLE) cartpole::selective_reset(states, dones, n, seed);
+    else if (kind == MRL_ENV_LUNAR_LANDER) lunar::selective_reset(states, dones, n, seed);
+}
+
+struct Agent {
+    mrl_config cfg;
+    int state_size, obs_dim, num_actions, action_dim;
+    ppo::NetSpec actor_net, critic_net;
+    std::vector<float> actor_params, critic_params, actor_state, critic_state;
+    std::vector<float> actor_grads, critic_grads;
+    int actor_t = 0, critic_t = 0;
+    int64_t total_steps = 0, completed_episodes = 0;
+    double sum_ep_reward = 0, sum_ep_steps = 0;
+    std::vector<float> ep_returns, ep_lengths;  // completed episodes, in completion order
+    std::vector<float> states, obs, actions, log_probs, values, rewards, dones;
+    std::vector<float> episode_rewards, episode_steps;
+    std::vector<float> r_obs, r_actions, r_log_probs, r_values, r_rewards, r_dones;
+    std::vector<float> advantages, returns, bootstrap;
+    int minibatches_done = 0, kl_early_stop = 0;
+    float last_mean_kl = 0;
+
+    explicit Agent(const mrl_config& c) : cfg(c) {
+        env_dims(c.env_kind, &state_size, &obs_dim, &num_actions, &action_dim);
+        actor_net = {obs_dim, c.hidden_dim, num_actions, ppo::ACT_RELU, ppo::HEAD_LINEAR};
+        critic_net = {obs_dim, c.hidden_dim, 1, ppo::ACT_RELU, ppo::HEAD_LINEAR};
+        const size_t N = c.n_envs, T = c.rollout_len;
+        actor_params.assign(actor_net.param_size(), 0.f);
+        critic_params.assign(critic_net.param_size(), 0.f);
+        actor_state.assign(2 * actor_params.size(), 0.f);
+        critic_state.assign(2 * critic_params.size(), 0.f);
+        actor_grads.assign(actor_params.size(), 0.f);
+        critic_grads.assign(critic_params.size(), 0.f);
+        states.assign(N * state_size, 0.f);
+        obs.assign(N * obs_dim, 0.f);
+        actions.assign(N, 0.f); log_probs.assign(N, 0.f); values.assign(N, 0.f);
+        rewards.assign(N, 0.f); dones.assign(N, 0.f);
+        episode_rewards.assign(N, 0.f); episode_steps.assign(N, 0.f);
+        r_obs.assign(T * N * obs_dim, 0.f);
+        r_actions.assign(T * N, 0.f); r_log_probs.assign(T * N, 0.f); r_values.assign(T * N, 0.f);
+        r_rewards.assign(T * N, 0.f); r_dones.assign(T * N, 0.f);
+        advantages.assign(T * N, 0.f); returns.assign(T * N, 0.f); bootstrap.assign(N, 0.f);
+    }
+
+    // ppo.mojo:1943-1955
+    void reset(uint64_t seed) {
+        env_reset(cfg.env_kind, states.data(), cfg.n_envs, seed);
+        extract_obs();
+    }
+    // ppo.mojo:712-736
+    void extract_obs() {
+        for (int i = 0; i < cfg.n_envs; ++i)
+            for (int d = 0; d < obs_dim; ++d) obs[(size_t)i * obs_dim + d] = states[(size_t)i * state_size + d];
+    }
+
+    // Phase 1, ppo.mojo:2069-2286
+    void rollout() {
+        const int N = cfg.n_envs, T = cfg.rollout_len;
+        std::vector<float> logits((size_t)N * num_actions);
+        for (int t = 0; t < T; ++t) {
+            uint32_t rng_seed = (uint32_t)((uint64_t)total_steps * 2654435761ull + (uint64_t)t * 7919ull);
+            ppo::mlp_forward(actor_net, N, obs.data(), actor_params.data(), logits.data(), nullptr);
+            ppo::mlp_forward(critic_net, N, obs.data(), critic_params.data(), values.data(), nullptr);
+            if (cfg.deterministic) {
+                ppo::argmax_actions(logits.data(), N, num_actions, actions.data());
+                // log-prob of the greedy action, same formula as the sampler
+                for (int i = 0; i < N; ++i) {
+                    const float* l = logits.data() + (size_t)i * num_actions;
+                    float mx = l[0];
+                    for (int a = 1; a < num_actions; ++a) if (l[a] > mx) mx = l[a];
+                    float se = 0.f;
+                    for (int a = 0; a < num_actions; ++a) se = se + mrl_expf(l[a] - mx);
+                    log_probs[i] = mrl_logf(mrl_expf(l[(int)actions[i]] - mx) / se + 1e-8f);
+                }
+            } else {
+                ppo::sample_actions(logits.data(), N, num_actions, rng_seed, actions.data(), log_probs.data());
+            }
+            size_t off = (size_t)t * N;
+            std::memcpy(&r_obs[off * obs_dim], obs.data(), sizeof(float) * N * obs_dim);
+            std::memcpy(&r_actions[off], actions.data(), sizeof(float) * N);
+            std::memcpy(&r_log_probs[off], log_probs.data(), sizeof(float) * N);
+            std::memcpy(&r_values[off], values.data(), sizeof(float) * N);
+            uint64_t env_step_seed = (uint64_t)total_steps * 1103515245ull + (uint64_t)t * 12345ull;
+            env_step(cfg.env_kind, states.data(), actions.data(), rewards.data(), dones.data(),
+                     obs.data(), N, env_step_seed);
+            std::memcpy(&r_rewards[off], rewards.data(), sizeof(float) * N);
+            std::memcpy(&r_dones[off], dones.data(), sizeof(float) * N);
+            // deep_rl/gpu/rl_kernels.mojo:103-230
+            for (int i = 0; i < N; ++i) { episode_rewards[i] += rewards[i]; episode_steps[i] += 1.0f; }
+            total_steps += N;
+            for (int i = 0; i < N; ++i)
+                if (dones[i] > 0.5f) {
+                    ep_returns.push_back(episode_rewards[i]);
+                    ep_lengths.push_back(episode_steps[i]);
+                    sum_ep_reward += episode_rewards[i];
+                    sum_ep_steps += episode_steps[i];
+                    completed_episodes += 1;
+                    episode_rewards[i] = 0.f;
+                    episode_steps[i] = 0.f;
+                }
+            uint64_t reset_seed = (uint64_t)total_steps * 1013904223ull + (uint64_t)t * 2654435761ull;
+            env_selective_reset(cfg.env_kind, states.data(), dones.data(), N, reset_seed);
+            extract_obs();
+        }
+    }
+
+    // Phase 2, ppo.mojo:2300-2376
+    template <typename ACC>
+    void gae_phase() {
+        const int N = cfg.n_envs, T = cfg.rollout_len;
+        ppo::mlp_forward(critic_net, N, obs.data(), critic_params.data(), bootstrap.data(), nullptr);
+        float gamma = (float)cfg.gamma;
+        float decay = (float)(cfg.gamma * cfg.gae_lambda);
+        ppo::gae(r_rewards.data(), r_values.data(), r_dones.data(), bootstrap.data(), T, N, gamma,
+                 decay, advantages.data(), returns.data());
+        if (cfg.normalize_advantages) ppo::normalize_advantages<ACC>(advantages.data(), (size_t)T * N);
+    }
+
+    // Phase 3, ppo.mojo:2386-2728.  perms: [num_epochs, T*N].
+    template <typename ACC>
+    void update(float actor_lr, float critic_lr, float entropy_coef, const int32_t* perms) {
+        const int N = cfg.n_envs, T = cfg.rollout_len, B = cfg.minibatch_size;
+        const size_t total = (size_t)T * N;
+        const int num_minibatches = (int)(total / B);
+        std::vector<float> mb_obs((size_t)B * obs_dim), mb_actions(B), mb_adv(B), mb_ret(B),
+            mb_old_lp(B), mb_old_v(B), kl(B);
+        std::vector<float> logits((size_t)B * num_actions), grad_logits((size_t)B * num_actions);
+        std::vector<float> vals(B), grad_vals(B);
+        std::vector<float> actor_cache((size_t)B * actor_net.cache_per_sample());
+        std::vector<float> critic_cache((size_t)B * critic_net.cache_per_sample());
+        minibatches_done = 0;
+        kl_early_stop = 0;
+        for (int epoch = 0; epoch < cfg.num_epochs; ++epoch) {
+            if (kl_early_stop) break;
+            const int32_t* perm = perms + (size_t)epoch * total;
+            for (int mb = 0; mb < num_minibatches; ++mb) {
+                // ppo.mojo:135-191
+                for (int i = 0; i < B; ++i) {
+                    size_t src = (size_t)perm[(size_t)mb * B + i];
+                    for (int d = 0; d < obs_dim; ++d) mb_obs[(size_t)i * obs_dim + d] = r_obs[src * obs_dim + d];
+                    mb_actions[i] = r_actions[src];
+                    mb_adv[i] = advantages[src];
+                    mb_ret[i] = returns[src];
+                    mb_old_lp[i] = r_log_probs[src];
+                    mb_old_v[i] = r_values[src];
+                }
+                if (cfg.norm_adv_per_minibatch) ppo::normalize_advantages<ACC>(mb_adv.data(), B);
+                ppo::mlp_forward(actor_net, B, mb_obs.data(), actor_params.data(), logits.data(), actor_cache.data());
+                ppo::actor_grad_with_kl(logits.data(), mb_old_lp.data(), mb_adv.data(), mb_actions.data(), B,
+                                        num_actions, cfg.clip_epsilon, entropy_coef, (float)B,
+                                        grad_logits.data(), kl.data());
+                if (cfg.target_kl > 0.0f) {
+                    ACC kl_sum = 0;
+                    for (int i = 0; i < B; ++i) kl_sum += (ACC)kl[i];
+                    double mean_kl = (double)(float)kl_sum / (double)B;
+                    last_mean_kl = (float)mean_kl;
+                    if (mean_kl > (double)cfg.target_kl) { kl_early_stop = 1; break; }
+                }
+                ppo::mlp_backward<ACC>(actor_net, B, grad_logits.data(), actor_params.data(),
+                                       actor_cache.data(), nullptr, actor_grads.data());
+                if (cfg.max_grad_norm > 0.0f)
+                    ppo::clip_grad_norm<ACC>(actor_grads.data(), (int)actor_grads.size(), cfg.max_grad_norm);
+                actor_t += 1;
+                float bc1, bc2;
+                ppo::adam_bias_corrections(cfg.adam_beta1, cfg.adam_beta2, actor_t, &bc1, &bc2);
+                ppo::adam_step(actor_params.data(), actor_grads.data(), actor_state.data(),
+                               (int)actor_params.size(), actor_lr, cfg.adam_beta1, cfg.adam_beta2,
+                               cfg.adam_eps, bc1, bc2);
+                ppo::mlp_forward(critic_net, B, mb_obs.data(), critic_params.data(), vals.data(), critic_cache.data());
+                ppo::critic_grad(vals.data(), mb_old_v.data(), mb_ret.data(), B, cfg.value_loss_coef,
+                                 cfg.clip_epsilon, cfg.clip_value != 0, (float)B, grad_vals.data());
+                ppo::mlp_backward<ACC>(critic_net, B, grad_vals.data(), critic_params.data(),
+                                       critic_cache.data(), nullptr, critic_grads.data());
+                if (cfg.max_grad_norm > 0.0f)
+                    ppo::clip_grad_norm<ACC>(critic_grads.data(), (int)critic_grads.size(), cfg.max_grad_norm);
+                critic_t += 1;
+                ppo::adam_bias_corrections(cfg.adam_beta1, cfg.adam_beta2, critic_t, &bc1, &bc2);
+                ppo::adam_step(critic_params.data(), critic_grads.data(), critic_state.data(),
+                               (int)critic_params.size(), critic_lr, cfg.adam_beta1, cfg.adam_beta2,
+                               cfg.adam_eps, bc1, bc2);
+                minibatches_done += 1;
+            }
+        }
+    }
+};
+
+}  // namespace oracle
