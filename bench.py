@@ -1,0 +1,306 @@
+#!/usr/bin/env python
+"""PPO env-steps/s including the update (BASELINE.json metric).
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload lunar_lander]
+
+One "step" = one full PPO iteration of the workload: a rollout of T steps over
+N_envs environments per GPU (policy forward, sampling, env step, store), GAE,
+and num_epochs x minibatches of clipped-surrogate / value updates with Adam.
+Data is synthetic: seeded environment resets and reference-style uniform
+random-initialised networks (nothing is read from disk or network).
+
+`--impl reference` times the CPU oracle (the reference's own Mojo code cannot be
+built here: no Mojo toolchain) with all host threads on a bounded sample of the
+same workload.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+# n_envs per GPU, rollout_len, hidden, epochs, minibatches per epoch (BASELINE.json configs)
+WORKLOADS = {
+    "lunar_lander": dict(env="lunar_lander", kind=2, obs=8, act=4, n_envs=8192, T=128, hidden=256, epochs=4, mbs=4,
+                         step_bytes=256, label="LunarLander discrete PPO, 8192 envs/GPU x 128 steps, 8-256-256-{4,1}"),
+    "cartpole": dict(env="cartpole", kind=0, obs=4, act=2, n_envs=4096, T=128, hidden=64, epochs=4, mbs=4,
+                     step_bytes=60, label="CartPole PPO, 4096 envs x 128 steps, 4-64-64-{2,1}"),
+}
+
+
+def mlp_flops_per_env_step(w):
+    """2*MACs of actor + critic forward, x (1 + 3E): one rollout forward plus E epochs of fwd + 2x bwd."""
+    i, h, a = w["obs"], w["hidden"], w["act"]
+    fwd = 2 * ((i * h + h * h + h * a) + (i * h + h * h + h * 1))
+    return fwd * (1 + 3 * w["epochs"])
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu, self.samples, self.stop_flag, self.thread = gpu_index, [], False, None
+
+    def _run(self):
+        while not self.stop_flag:
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i",
+                                      str(self.gpu)], capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([x.strip() for x in out.split(",")])
+            except Exception:
+                pass
+            time.sleep(0.2)
+
+    def start(self):
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
+
+    def stop(self):
+        self.stop_flag = True
+        if self.thread:
+            self.thread.join(timeout=6)
+        mhz = [float(s[0]) for s in self.samples if s and s[0].replace(".", "").isdigit()]
+        mx = [float(s[1]) for s in self.samples if len(s) > 1 and s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for s in self.samples for i in range(4) if len(s) > 2 + i and s[2 + i] == "Active"})
+        return {"sm_mhz": float(np.median(mhz)) if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def make_params(w, seed):
+    from mojo_rl_b200 import DeepPPOAgent
+    total = w["n_envs"] * w["T"]
+    agent = DeepPPOAgent(w["obs"], w["act"], hidden_dim=w["hidden"], rollout_len=w["T"], n_envs=w["n_envs"],
+                         gpu_minibatch_size=total // w["mbs"], num_epochs=w["epochs"], actor_lr=3e-4, critic_lr=3e-4,
+                         target_kl=0.0, seed=seed)
+    return agent
+
+
+def cpu_baseline(w, seconds_budget=20.0, path=None):
+    """Times the oracle (OpenMP build, all host threads) on a bounded sample of the workload:
+    same T, networks, epochs and minibatch count, fewer environments."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import _util
+    so = path or os.path.join(ROOT, "oracle", "liboracle_omp.so")
+    if not os.path.exists(so):
+        subprocess.check_call(["make", "-C", os.path.join(ROOT, "oracle")])
+    o = _util.oracle(so)
+    n_envs = 256
+    total = n_envs * w["T"]
+    cfg = _util.default_config(env_kind=w["kind"], n_envs=n_envs, rollout_len=w["T"], hidden_dim=w["hidden"],
+                               minibatch_size=total // w["mbs"], num_epochs=w["epochs"], target_kl=0.0)
+    rng = np.random.default_rng(0)
+    h = o.orc_agent_create(ctypes.byref(cfg))
+    for which, out in ((0, w["act"]), (1, 1)):
+        spec = _util.NetSpec(w["obs"], w["hidden"], out, 0, 0)
+        p = _util.xavier_params(spec, rng)
+        o.orc_agent_set_params(h, which, _util.fp(p), _util.fp(np.zeros(2 * p.size, np.float32)))
+    o.orc_agent_reset(h, 0)
+    perms = np.stack([rng.permutation(total) for _ in range(w["epochs"])]).astype(np.int32)
+    iters, t0 = 0, time.perf_counter()
+    while True:
+        o.orc_agent_rollout(h)
+        o.orc_agent_gae(h, 0)
+        o.orc_agent_update(h, 3e-4, 3e-4, 0.01, _util.ip(perms), 0)
+        iters += 1
+        if time.perf_counter() - t0 > seconds_budget * 0.5 or iters >= 8:
+            break
+    dt = time.perf_counter() - t0
+    o.orc_agent_destroy(h)
+    return {"value": iters * total / dt, "unit": "env-steps/s", "cores": int(o.orc_num_threads()), "kind": "port",
+            "sample": f"{iters} PPO iterations of {n_envs} envs x {w['T']} steps (same nets, epochs, minibatch count), "
+                      f"oracle/liboracle_omp.so, {dt:.1f} s"}, dt, iters, total
+
+
+def run_reference(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    per_step = max(4.0, min(30.0, 120.0 / max(1, args.steps + args.warmup)))
+    vals = []
+    for i in range(args.warmup + args.steps):
+        cb, dt, iters, total = cpu_baseline(w, seconds_budget=per_step)
+        if i >= args.warmup:
+            vals.append((cb, dt))
+    value = float(np.mean([c["value"] for c, _ in vals]))
+    cb = dict(vals[-1][0]); cb["value"] = value
+    line = {"impl": "reference", "metric": "ppo_env_steps_per_sec_incl_update", "value": value, "unit": "env-steps/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": float(np.mean([d for _, d in vals])) * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": w["label"], "note": "CPU oracle (C++ restatement of the reference), bounded sample"},
+            "cpu_baseline": cb,
+            "e2e": {"value": value, "unit": "env-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="lunar_lander", choices=sorted(WORKLOADS))
+    ap.add_argument("--precision", type=int, default=None, help="0 fp32, 1 bf16 tensor-core update")
+    ap.add_argument("--n-envs", type=int, default=None, help="override envs per GPU (profiling of small cases)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = dict(WORKLOADS[args.workload])
+    if args.n_envs:
+        w["n_envs"] = args.n_envs
+    if args.impl == "reference":
+        run_reference(args, w)
+        return
+
+    import torch
+    from mojo_rl_b200 import _lib
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    L = _lib.lib()
+    agent = make_params(w, seed=0)   # same seed on every rank: replicas start identical
+    agent.precision = args.precision if args.precision is not None else int(os.environ.get("MRL_PRECISION", "0"))
+    h = agent.create_context(w["kind"], world_size=world, rank=rank)
+    if world > 1:
+        idt = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            buf = (ctypes.c_uint8 * 128)()
+            _lib.check(L.mrl_comm_unique_id(buf))
+            idt = torch.tensor(list(buf), dtype=torch.uint8)
+        idt = idt.cuda()
+        dist.broadcast(idt, 0)
+        idb = (ctypes.c_uint8 * 128)(*idt.cpu().tolist())
+        _lib.check(L.mrl_comm_init(h, idb))
+    stream = torch.cuda.ExternalStream(L.mrl_stream(h))
+    total = w["n_envs"] * w["T"]
+    _lib.check(L.mrl_ppo_reset(h, rank))
+
+    def one_iteration():
+        _lib.check(L.mrl_ppo_rollout(h))
+        _lib.check(L.mrl_ppo_gae(h))
+        _lib.check(L.mrl_ppo_update(h, 3e-4, 3e-4, 0.01, None))
+
+    def barrier():
+        stream.synchronize()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    ms3, calls3 = (ctypes.c_float * 3)(), (ctypes.c_int * 3)()
+    for _ in range(args.warmup):
+        one_iteration()
+    barrier()
+    _lib.check(L.mrl_get_timers(h, ms3, calls3))   # clear warm-up timings
+    launches0 = L.mrl_kernel_launch_count()
+    clocks = ClockSampler(local_rank)
+    if rank == 0:
+        clocks.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record(stream)
+    for _ in range(args.steps):
+        one_iteration()
+    ev1.record(stream)
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    launches = L.mrl_kernel_launch_count() - launches0
+    clk = clocks.stop() if rank == 0 else None
+    _lib.check(L.mrl_get_timers(h, ms3, calls3))
+    phase_ms = [ms3[i] / max(1, calls3[i]) for i in range(3)]
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = world * total * args.steps / (ms * 1e-3)
+
+    # ---- end to end through the public API: every step uploads parameters and optimiser state from
+    # pinned host memory, runs one PPO iteration, and reads back parameters, state and episode metrics.
+    pa, pc = L.mrl_param_size(h, 0), L.mrl_param_size(h, 1)
+    pin = [torch.empty(n, dtype=torch.float32).pin_memory() for n in (pa, 2 * pa, pc, 2 * pc)]
+    _lib.check(L.mrl_get_params(h, 0, _lib.ptr(pin[0]), _lib.ptr(pin[1])))
+    _lib.check(L.mrl_get_params(h, 1, _lib.ptr(pin[2]), _lib.ptr(pin[3])))
+    rets, lens = torch.empty(1 << 16).pin_memory(), torch.empty(1 << 16).pin_memory()
+    stats = _lib.Stats()
+    e2e_steps = max(2, min(args.steps, 5))
+
+    def e2e_iteration():
+        _lib.check(L.mrl_set_params(h, 0, _lib.ptr(pin[0]), _lib.ptr(pin[1])))
+        _lib.check(L.mrl_set_params(h, 1, _lib.ptr(pin[2]), _lib.ptr(pin[3])))
+        one_iteration()
+        n = _lib.check(L.mrl_drain_episodes(h, _lib.ptr(rets), _lib.ptr(lens), 1 << 16))
+        _lib.check(L.mrl_get_stats(h, ctypes.byref(stats)))
+        _lib.check(L.mrl_get_params(h, 0, _lib.ptr(pin[0]), _lib.ptr(pin[1])))
+        _lib.check(L.mrl_get_params(h, 1, _lib.ptr(pin[2]), _lib.ptr(pin[3])))
+        return n
+
+    e2e_iteration()
+    barrier()
+    t0 = time.perf_counter()
+    n_eps = 0
+    for _ in range(e2e_steps):
+        n_eps += e2e_iteration()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if dist is not None:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = world * total * e2e_steps / e2e_s
+    h2d = 4 * 3 * (pa + pc)
+    d2h = 4 * 3 * (pa + pc) + 8 * (n_eps // max(1, e2e_steps)) + ctypes.sizeof(stats)
+
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        tf_peak = peaks.get("bf16_tflops_sustained", 1400.0)
+        peak_src = "measured" if peaks else "fallback"
+        flops_update = mlp_flops_per_env_step(w) * total * (3.0 * w["epochs"]) / (1 + 3.0 * w["epochs"])
+        achieved = flops_update / (phase_ms[2] * 1e-3) / 1e12 if phase_ms[2] > 0 else 0.0
+        line = {
+            "metric": "ppo_env_steps_per_sec_incl_update", "value": value, "unit": "env-steps/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16" if agent.precision == 1 else "f32", "data": "synthetic",
+            "config": {"workload": w["label"], "n_envs_per_gpu": w["n_envs"], "rollout_len": w["T"],
+                       "epochs": w["epochs"], "minibatches": w["mbs"], "minibatch_size": total // w["mbs"],
+                       "l2": "rollout slab + activations per minibatch exceed the 126 MB L2",
+                       "phase_ms": {"rollout": phase_ms[0], "gae": phase_ms[1], "update": phase_ms[2]}},
+            "e2e": {"value": e2e_value, "unit": "env-steps/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(launches),
+            "clocks": clk,
+            "roofline": {"bound": "tensor", "kernel": "update-phase MLP GEMMs (fwd + dX + dW, actor and critic)",
+                         "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s", "frac": achieved / tf_peak,
+                         "peak_source": f"bf16_tflops_sustained of {peak_src}", "traffic": None},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(w)[0]
+        print(json.dumps(line), flush=True)
+    L.mrl_destroy(h)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

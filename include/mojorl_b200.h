@@ -245,6 +245,14 @@ typedef enum mrl_buffer {
     MRL_BUF_CRITIC_GRADS = 13, MRL_BUF_DONES = 14
 } mrl_buffer;
 int mrl_get_buffer(mrl_ctx* ctx, int which, float** device_ptr, int64_t* n_floats);
+/* Synchronous copy of one resident buffer to HOST memory (n_floats must match). */
+int mrl_read_buffer(mrl_ctx* ctx, int which, float* out_host, int64_t n_floats);
+
+/* Device-side replacement of the host Fisher-Yates shuffle (ppo.mojo:2425-2434,
+ * core/utils/shuffle.mojo:51-82): indices[i] = P_key(i), a keyed bijection of
+ * [0, n).  The reference's permutation comes from Mojo's global RNG, so the
+ * sequences differ; mrl_ppo_update accepts explicit permutations for parity. */
+int mrl_make_permutation(int64_t n, uint64_t key, int32_t* indices, void* stream);
 
 /* Counters kept on the device across phases; a host copy is returned. */
 typedef struct mrl_stats {
@@ -264,6 +272,12 @@ int mrl_get_stats(mrl_ctx* ctx, mrl_stats* out_host);
  * per-step D->H copies of ppo.mojo:2212-2225.  Returns the count written
  * (<= capacity) or a negative status. */
 int mrl_drain_episodes(mrl_ctx* ctx, float* returns_host, float* lengths_host, int capacity);
+
+/* CUDA-event phase timers (the reference keeps perf_counter phase timers inside
+ * train_gpu, ppo.mojo:2045-2052, :2777-2838).  Sums the device time of every
+ * rollout / GAE / update call since the last query into ms_host[0..2], the call
+ * counts into calls_host[0..2], and clears them.  Synchronises the stream. */
+int mrl_get_timers(mrl_ctx* ctx, float ms_host[3], int calls_host[3]);
 
 /* The stream all fused phases run on (cudaStream_t as void*). */
 void* mrl_stream(mrl_ctx* ctx);

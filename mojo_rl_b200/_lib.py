@@ -1,0 +1,132 @@
+"""ctypes binding of libmojorl_b200.so (the C ABI declared in include/mojorl_b200.h).
+
+There is no CPU fallback: if the CUDA library is missing or cannot be loaded
+every entry point raises.
+"""
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libmojorl_b200.so")
+
+c_float_p = ctypes.POINTER(ctypes.c_float)
+c_int32_p = ctypes.POINTER(ctypes.c_int32)
+c_void_p = ctypes.c_void_p
+
+
+class NetSpec(ctypes.Structure):
+    """mrl_net_spec"""
+    _fields_ = [("in_dim", ctypes.c_int32), ("hidden_dim", ctypes.c_int32), ("out_dim", ctypes.c_int32),
+                ("activation", ctypes.c_int32), ("head", ctypes.c_int32)]
+
+
+class Config(ctypes.Structure):
+    """mrl_config"""
+    _fields_ = [("env_kind", ctypes.c_int32), ("n_envs", ctypes.c_int32), ("rollout_len", ctypes.c_int32),
+                ("hidden_dim", ctypes.c_int32), ("minibatch_size", ctypes.c_int32), ("num_epochs", ctypes.c_int32),
+                ("precision", ctypes.c_int32), ("normalize_advantages", ctypes.c_int32),
+                ("norm_adv_per_minibatch", ctypes.c_int32), ("clip_value", ctypes.c_int32),
+                ("deterministic", ctypes.c_int32), ("world_size", ctypes.c_int32), ("rank", ctypes.c_int32),
+                ("gamma", ctypes.c_double), ("gae_lambda", ctypes.c_double), ("clip_epsilon", ctypes.c_float),
+                ("value_loss_coef", ctypes.c_float), ("target_kl", ctypes.c_float),
+                ("max_grad_norm", ctypes.c_float), ("adam_beta1", ctypes.c_float), ("adam_beta2", ctypes.c_float),
+                ("adam_eps", ctypes.c_float)]
+
+
+class Stats(ctypes.Structure):
+    """mrl_stats"""
+    _fields_ = [("total_steps", ctypes.c_int64), ("completed_episodes", ctypes.c_int64),
+                ("sum_episode_reward", ctypes.c_double), ("sum_episode_steps", ctypes.c_double),
+                ("minibatches_done", ctypes.c_int32), ("kl_early_stop", ctypes.c_int32),
+                ("last_mean_kl", ctypes.c_float), ("actor_adam_t", ctypes.c_int32), ("critic_adam_t", ctypes.c_int32)]
+
+
+# name -> (restype, argtypes).  Every symbol include/mojorl_b200.h declares.
+SIGNATURES = {
+    "mrl_env_info": (ctypes.c_int, [ctypes.c_int] + [ctypes.POINTER(ctypes.c_int)] * 4),
+    "mrl_env_reset": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, c_void_p, ctypes.c_uint64, c_void_p]),
+    "mrl_env_step": (ctypes.c_int, [ctypes.c_int, ctypes.c_int] + [c_void_p] * 5 + [ctypes.c_uint64, c_void_p]),
+    "mrl_env_selective_reset": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, c_void_p, c_void_p, ctypes.c_uint64, c_void_p]),
+    "mrl_net_param_size": (ctypes.c_int, [ctypes.POINTER(NetSpec)]),
+    "mrl_net_cache_per_sample": (ctypes.c_int, [ctypes.POINTER(NetSpec)]),
+    "mrl_net_out_cols": (ctypes.c_int, [ctypes.POINTER(NetSpec)]),
+    "mrl_mlp_workspace_floats": (ctypes.c_int64, [ctypes.POINTER(NetSpec), ctypes.c_int]),
+    "mrl_mlp_forward": (ctypes.c_int, [ctypes.POINTER(NetSpec), ctypes.c_int] + [c_void_p] * 6),
+    "mrl_mlp_backward": (ctypes.c_int, [ctypes.POINTER(NetSpec), ctypes.c_int] + [c_void_p] * 7),
+    "mrl_adam_step": (ctypes.c_int, [ctypes.c_int, c_void_p, c_void_p, c_void_p] + [ctypes.c_float] * 6 + [c_void_p]),
+    "mrl_sample_actions": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, c_void_p, c_void_p, c_void_p, ctypes.c_uint32, c_void_p]),
+    "mrl_argmax_actions": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, c_void_p, c_void_p, c_void_p]),
+    "mrl_gae": (ctypes.c_int, [ctypes.c_int, ctypes.c_int] + [c_void_p] * 4 + [ctypes.c_double, ctypes.c_double] + [c_void_p] * 3),
+    "mrl_normalize_advantages": (ctypes.c_int, [ctypes.c_int64, c_void_p, c_void_p, c_void_p]),
+    "mrl_ppo_gather_minibatch": (ctypes.c_int, [ctypes.c_int, ctypes.c_int] + [c_void_p] * 14),
+    "mrl_ppo_actor_grad": (ctypes.c_int, [ctypes.c_int, ctypes.c_int] + [c_void_p] * 4 + [ctypes.c_float, ctypes.c_float] + [c_void_p] * 3),
+    "mrl_ppo_critic_grad": (ctypes.c_int, [ctypes.c_int] + [c_void_p] * 3 + [ctypes.c_float, ctypes.c_float, ctypes.c_int, c_void_p, c_void_p]),
+    "mrl_grad_clip": (ctypes.c_int, [ctypes.c_int, c_void_p, ctypes.c_float, c_void_p, c_void_p]),
+    "mrl_config_defaults": (None, [ctypes.POINTER(Config)]),
+    "mrl_create": (ctypes.c_int, [ctypes.POINTER(c_void_p), ctypes.POINTER(Config)]),
+    "mrl_destroy": (ctypes.c_int, [c_void_p]),
+    "mrl_last_error_string": (ctypes.c_char_p, []),
+    "mrl_set_params": (ctypes.c_int, [c_void_p, ctypes.c_int, c_void_p, c_void_p]),
+    "mrl_get_params": (ctypes.c_int, [c_void_p, ctypes.c_int, c_void_p, c_void_p]),
+    "mrl_param_size": (ctypes.c_int, [c_void_p, ctypes.c_int]),
+    "mrl_comm_unique_id": (ctypes.c_int, [c_void_p]),
+    "mrl_comm_init": (ctypes.c_int, [c_void_p, c_void_p]),
+    "mrl_ppo_reset": (ctypes.c_int, [c_void_p, ctypes.c_uint64]),
+    "mrl_ppo_rollout": (ctypes.c_int, [c_void_p]),
+    "mrl_ppo_gae": (ctypes.c_int, [c_void_p]),
+    "mrl_ppo_update": (ctypes.c_int, [c_void_p, ctypes.c_float, ctypes.c_float, ctypes.c_float, c_void_p]),
+    "mrl_get_buffer": (ctypes.c_int, [c_void_p, ctypes.c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(ctypes.c_int64)]),
+    "mrl_read_buffer": (ctypes.c_int, [c_void_p, ctypes.c_int, c_void_p, ctypes.c_int64]),
+    "mrl_make_permutation": (ctypes.c_int, [ctypes.c_int64, ctypes.c_uint64, c_void_p, c_void_p]),
+    "mrl_get_stats": (ctypes.c_int, [c_void_p, ctypes.POINTER(Stats)]),
+    "mrl_drain_episodes": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_int]),
+    "mrl_get_timers": (ctypes.c_int, [c_void_p, c_void_p, c_void_p]),
+    "mrl_stream": (c_void_p, [c_void_p]),
+    "mrl_kernel_launch_count": (ctypes.c_int64, []),
+}
+
+_lib = None
+
+
+class MojoRLError(RuntimeError):
+    pass
+
+
+def lib():
+    """The loaded library; raises MojoRLError if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise MojoRLError(f"{LIB_PATH} is missing: build it with `python -m mojo_rl_b200.build` "
+                              "(there is no CPU fallback)")
+        l = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(l, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = l
+    return _lib
+
+
+def check(rc):
+    """Raises MojoRLError with the library's message on a negative status."""
+    if rc is not None and rc < 0:
+        msg = lib().mrl_last_error_string()
+        raise MojoRLError(f"libmojorl_b200 status {rc}: {msg.decode() if msg else ''}")
+    return rc
+
+
+def ptr(t):
+    """Device (or pinned host) address of a torch tensor / numpy array, or None."""
+    if t is None:
+        return None
+    if hasattr(t, "data_ptr"):
+        return ctypes.c_void_p(t.data_ptr())
+    return ctypes.c_void_p(t.ctypes.data)
+
+
+def stream_ptr(stream=None):
+    """cudaStream_t of a torch stream (default: torch's current stream)."""
+    import torch
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return ctypes.c_void_p(s.cuda_stream)

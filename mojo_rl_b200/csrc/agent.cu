@@ -1,0 +1,710 @@
+// The three phases of DeepPPOAgent.train_gpu (deep_agents/ppo/ppo.mojo:1558-2840)
+// with every buffer resident in HBM and no host crossing inside a phase:
+// counters (total_steps, Adam t, KL stop flag, completed-episode ring) live on
+// the device, so a phase is a fixed sequence of launches on one stream.
+#include <dlfcn.h>
+#include <math.h>
+#include <stdarg.h>
+#include <string.h>
+#include <atomic>
+#include <vector>
+#include "env_cartpole.cuh"
+#include "env_lunar.cuh"
+#include "ppo_kernels.cuh"
+
+namespace mrl {
+
+static thread_local char g_error[512] = "";
+static std::atomic<long long> g_launches{0};
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+constexpr int EP_RING = 1 << 16;
+
+// Device-resident counters shared by the phases.
+struct DeviceCounters {
+    long long total_steps;
+    unsigned long long completed_episodes;
+    double sum_episode_reward, sum_episode_steps;
+    unsigned long long ring_head;  // episodes ever pushed; ring index = head % EP_RING
+    int kl_stop;
+    int minibatches_done;
+    float last_mean_kl;
+    int actor_t, critic_t;
+    float bc1, bc2;  // bias corrections of the optimiser step about to run
+    int adam_skip;   // 1: the step about to run is skipped (KL stop)
+};
+
+// ---- NCCL through dlopen: the library loads (and every single-GPU path runs)
+// on machines without NCCL.
+typedef struct ncclComm* ncclComm_t;
+typedef struct { char internal[128]; } ncclUniqueId;
+struct NcclApi {
+    void* handle = nullptr;
+    int (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    int (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*CommDestroy)(ncclComm_t) = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+    bool load() {
+        if (handle) return true;
+        const char* names[] = {"libnccl.so.2", "libnccl.so"};
+        for (const char* n : names) { handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL); if (handle) break; }
+        if (!handle) return false;
+        GetUniqueId = (int (*)(ncclUniqueId*))dlsym(handle, "ncclGetUniqueId");
+        CommInitRank = (int (*)(ncclComm_t*, int, ncclUniqueId, int))dlsym(handle, "ncclCommInitRank");
+        AllReduce = (int (*)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t))dlsym(handle, "ncclAllReduce");
+        CommDestroy = (int (*)(ncclComm_t))dlsym(handle, "ncclCommDestroy");
+        GetErrorString = (const char* (*)(int))dlsym(handle, "ncclGetErrorString");
+        return GetUniqueId && CommInitRank && AllReduce && CommDestroy;
+    }
+};
+static NcclApi g_nccl;
+constexpr int NCCL_FLOAT32 = 7, NCCL_FLOAT64 = 8, NCCL_SUM = 0;
+
+}  // namespace mrl
+
+using namespace mrl;
+
+struct mrl_ctx {
+    mrl_config cfg;
+    int state_size, obs_dim, num_actions, action_dim;
+    mrl_net_spec actor_net, critic_net;
+    int actor_p, critic_p;
+    cudaStream_t stream;
+    std::vector<void*> allocs;
+    // env + rollout
+    float *states, *obs, *actions, *log_probs, *values, *rewards, *dones, *logits;
+    float *episode_rewards, *episode_steps;
+    float *r_obs, *r_actions, *r_log_probs, *r_values, *r_rewards, *r_dones;
+    float *advantages, *returns, *bootstrap;
+    float *ring_returns, *ring_lengths;
+    // nets.  *_grads has actor_p (+4) floats: the tail carries the KL sum through the all-reduce.
+    float *actor_params, *actor_state, *actor_grads, *critic_params, *critic_state, *critic_grads;
+    // minibatch
+    float *mb_obs, *mb_actions, *mb_adv, *mb_ret, *mb_old_lp, *mb_old_v, *mb_kl;
+    float *mb_logits, *mb_grad_logits, *mb_values, *mb_grad_values;
+    float *actor_cache, *critic_cache, *workspace;
+    int32_t* perm;
+    double* stats;  // 8 doubles of reduction scratch
+    DeviceCounters* counters;
+    ncclComm_t comm;
+    std::vector<cudaEvent_t> timer_events[3];  // start/stop pairs per phase, resolved by mrl_get_timers
+    unsigned long long ring_tail;  // host: episodes already drained
+    unsigned long long update_count;
+};
+
+namespace mrl {
+
+template <typename T>
+static int dalloc(mrl_ctx* c, T** p, size_t n) {
+    void* q = nullptr;
+    cudaError_t e = cudaMalloc(&q, n * sizeof(T));
+    if (e != cudaSuccess) { set_error("cudaMalloc(%zu bytes): %s", n * sizeof(T), cudaGetErrorString(e)); return MRL_ERR_CUDA; }
+    cudaMemset(q, 0, n * sizeof(T));
+    c->allocs.push_back(q);
+    *p = (T*)q;
+    return MRL_OK;
+}
+
+// ---- rollout kernels --------------------------------------------------------
+
+// _sample_actions_kernel + _store_pre_step_kernel (ppo.mojo:4064-4123, :662-690).
+// The seed is UInt32(total_steps * 2654435761 + t * 7919) (ppo.mojo:2071).
+__global__ void rollout_pre_step_kernel(const float* __restrict__ logits, const float* __restrict__ values,
+                                        const float* __restrict__ obs, float* __restrict__ actions,
+                                        float* __restrict__ r_obs, float* __restrict__ r_actions,
+                                        float* __restrict__ r_log_probs, float* __restrict__ r_values,
+                                        const DeviceCounters* __restrict__ ctr, int t, int n, int A, int obs_dim,
+                                        int greedy) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    uint32_t seed = (uint32_t)((unsigned long long)ctr->total_steps * 2654435761ull + (unsigned long long)t * 7919ull);
+    float a, lp;
+    sample_one(logits + (size_t)i * A, A, seed, i, greedy, a, lp);
+    actions[i] = a;
+    size_t off = (size_t)t * n + i;
+    r_actions[off] = a;
+    r_log_probs[off] = lp;
+    r_values[off] = values[i];
+    for (int d = 0; d < obs_dim; ++d) r_obs[off * obs_dim + d] = obs[(size_t)i * obs_dim + d];
+}
+
+// _store_post_step_kernel + accumulate_rewards + increment_steps +
+// extract_completed_episodes + selective_reset_tracking (ppo.mojo:692-708,
+// deep_rl/gpu/rl_kernels.mojo:103-230).  Completed episodes go to a device
+// ring instead of a per-step D->H copy.
+__global__ void rollout_post_step_kernel(const float* __restrict__ rewards, const float* __restrict__ dones,
+                                         float* __restrict__ r_rewards, float* __restrict__ r_dones,
+                                         float* __restrict__ episode_rewards, float* __restrict__ episode_steps,
+                                         float* __restrict__ ring_returns, float* __restrict__ ring_lengths,
+                                         DeviceCounters* __restrict__ ctr, int t, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float r = rewards[i], d = dones[i];
+    size_t off = (size_t)t * n + i;
+    r_rewards[off] = r;
+    r_dones[off] = d;
+    float er = episode_rewards[i] + r;
+    float es = episode_steps[i] + 1.0f;
+    if (d > 0.5f) {
+        unsigned long long slot = atomicAdd(&ctr->ring_head, 1ull);
+        ring_returns[slot % EP_RING] = er;
+        ring_lengths[slot % EP_RING] = es;
+        atomicAdd(&ctr->completed_episodes, 1ull);
+        atomicAdd(&ctr->sum_episode_reward, (double)er);
+        atomicAdd(&ctr->sum_episode_steps, (double)es);
+        er = 0.0f;
+        es = 0.0f;
+    }
+    episode_rewards[i] = er;
+    episode_steps[i] = es;
+}
+
+__global__ void add_total_steps_kernel(DeviceCounters* ctr, int n) { ctr->total_steps += n; }
+
+// Selective reset with the seed of ppo.mojo:2275, then _extract_obs_from_state
+// (ppo.mojo:712-736).  total_steps has already been advanced.
+__global__ void cartpole_auto_reset_kernel(float* __restrict__ states, float* __restrict__ dones,
+                                           float* __restrict__ obs, const DeviceCounters* __restrict__ ctr,
+                                           int t, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    if (!(dones[i] < 0.5f)) {
+        unsigned long long seed64 = (unsigned long long)ctr->total_steps * 1013904223ull + (unsigned long long)t * 2654435761ull;
+        float s[4];
+        cartpole::reset(s, (uint32_t)((unsigned long long)i * 2654435761ull + (uint32_t)seed64));
+        float4 v = make_float4(s[0], s[1], s[2], s[3]);
+        reinterpret_cast<float4*>(states)[i] = v;
+        reinterpret_cast<float4*>(obs)[i] = v;
+        dones[i] = 0.0f;
+    }
+}
+__global__ void lunar_auto_reset_kernel(float* __restrict__ states, const float* __restrict__ dones,
+                                        float* __restrict__ obs, const DeviceCounters* __restrict__ ctr,
+                                        int t, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    if (dones[i] > 0.5f) {
+        unsigned long long seed64 = (unsigned long long)ctr->total_steps * 1013904223ull + (unsigned long long)t * 2654435761ull;
+        float* s = states + (size_t)i * lunar::STATE_SIZE;
+        lunar::reset_row(s, lunar::combined_seed((float)seed64, i));
+        for (int d = 0; d < lunar::OBS_DIM; ++d) obs[(size_t)i * lunar::OBS_DIM + d] = s[d];
+    }
+}
+__global__ void extract_obs_kernel(const float* __restrict__ states, float* __restrict__ obs, int n,
+                                   int state_size, int obs_dim) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n * obs_dim) return;
+    int e = i / obs_dim, d = i % obs_dim;
+    obs[i] = states[(size_t)e * state_size + d];
+}
+
+// ---- update kernels ---------------------------------------------------------
+
+// A keyed bijection of [0, n): 4-round Feistel network on 2*half bits with
+// cycle walking.  Replaces the host Fisher-Yates shuffle of ppo.mojo:2425-2434
+// (whose random stream is Mojo's global RNG) when no permutation is supplied.
+__host__ __device__ __forceinline__ uint32_t feistel_perm(uint32_t i, uint32_t n, int half, uint64_t key) {
+    const uint32_t mask = (1u << half) - 1u;
+    uint32_t x = i;
+    do {
+        uint32_t l = x >> half, r = x & mask;
+#pragma unroll
+        for (int round = 0; round < 4; ++round) {
+            uint32_t k = (uint32_t)(key >> (16 * (round & 3))) + 0x9E3779B9u * (uint32_t)(round + 1);
+            uint32_t f = (r + k) * 0x85EBCA6Bu;
+            f ^= f >> 13;
+            f *= 0xC2B2AE35u;
+            f ^= f >> 16;
+            uint32_t nl = r, nr = l ^ (f & mask);
+            l = nl; r = nr;
+        }
+        x = (l << half) | r;
+    } while (x >= n);
+    return x;
+}
+
+__global__ void make_indices_kernel(int32_t* __restrict__ out, int batch, uint32_t start, uint32_t total,
+                                    int half, uint64_t key) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= batch) return;
+    out[i] = (int32_t)feistel_perm(start + (uint32_t)i, total, half, key);
+}
+
+__global__ void begin_update_kernel(DeviceCounters* ctr) {
+    ctr->kl_stop = 0;
+    ctr->minibatches_done = 0;
+}
+
+// Sum of the per-sample KL values into grads_tail[0] (f32, like the host loop of
+// ppo.mojo:2556-2559 but tree-ordered).
+__global__ void kl_sum_kernel(const float* __restrict__ kl, int n, float* __restrict__ out) {
+    __shared__ double sm[32];
+    double acc = 0.0;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) acc += (double)kl[i];
+    acc = block_sum(acc, sm);
+    if (threadIdx.x == 0) out[0] = (float)acc;
+}
+
+// KL early stop (ppo.mojo:2549-2572) and Adam time step / bias corrections
+// (adam.mojo:176-188) for the actor; which = 1: the critic step of the same
+// minibatch, which only inherits the stop flag.
+__global__ void adam_prepare_kernel(DeviceCounters* ctr, const float* kl_sum, float kl_count, float target_kl,
+                                    double beta1, double beta2, int which) {
+    if (which == 0) {
+        if (!ctr->kl_stop && target_kl > 0.0f) {
+            double mean_kl = (double)kl_sum[0] / (double)kl_count;
+            ctr->last_mean_kl = (float)mean_kl;
+            if (mean_kl > (double)target_kl) ctr->kl_stop = 1;
+        }
+    }
+    if (ctr->kl_stop) { ctr->adam_skip = 1; return; }
+    ctr->adam_skip = 0;
+    int t;
+    if (which == 0) t = ++ctr->actor_t; else { t = ++ctr->critic_t; ctr->minibatches_done += 1; }
+    ctr->bc1 = (float)(1.0 - pow(beta1, (double)t));
+    ctr->bc2 = (float)(1.0 - pow(beta2, (double)t));
+}
+
+// Adam.step_kernel_impl (adam.mojo:113-156) with the device-side skip flag;
+// grad_scale folds the 1/world_size of the gradient average.
+__global__ void adam_ctx_kernel(float* __restrict__ params, const float* __restrict__ grads,
+                                float* __restrict__ state, int n, float lr, float beta1, float beta2, float eps,
+                                const DeviceCounters* __restrict__ ctr) {
+    if (ctr->adam_skip) return;
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float bc1 = ctr->bc1, bc2 = ctr->bc2;
+    float g = grads[i];
+    float2 mv = reinterpret_cast<float2*>(state)[i];
+    float m_new = beta1 * mv.x + (1.0f - beta1) * g;
+    float v_new = beta2 * mv.y + (1.0f - beta2) * g * g;
+    reinterpret_cast<float2*>(state)[i] = make_float2(m_new, v_new);
+    float m_hat = m_new / bc1;
+    float v_hat = v_new / bc2;
+    params[i] = params[i] - lr * m_hat / (sqrtf(v_hat) + eps);
+}
+
+__global__ void scale_kernel(float* __restrict__ x, int n, float s) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = x[i] * s;
+}
+
+// Records a start/stop event pair around one phase call.
+struct PhaseTimer {
+    mrl_ctx* c; int phase; cudaEvent_t stop;
+    PhaseTimer(mrl_ctx* ctx, int ph) : c(ctx), phase(ph), stop(nullptr) {
+        cudaEvent_t start;
+        if (cudaEventCreate(&start) != cudaSuccess) return;
+        if (cudaEventCreate(&stop) != cudaSuccess) { cudaEventDestroy(start); stop = nullptr; return; }
+        cudaEventRecord(start, c->stream);
+        c->timer_events[phase].push_back(start);
+        c->timer_events[phase].push_back(stop);
+    }
+    ~PhaseTimer() { if (stop) cudaEventRecord(stop, c->stream); }
+};
+
+static int env_step_launch(mrl_ctx* c) {
+    return mrl_env_step(c->cfg.env_kind, c->cfg.n_envs, c->states, c->actions, c->rewards, c->dones, c->obs, 0,
+                        c->stream);
+}
+
+static int allreduce_f32(mrl_ctx* c, float* buf, size_t n) {
+    if (c->cfg.world_size <= 1) return MRL_OK;
+    if (!c->comm) { set_error("world_size > 1 but mrl_comm_init was not called"); return MRL_ERR_NCCL; }
+    int rc = g_nccl.AllReduce(buf, buf, n, NCCL_FLOAT32, NCCL_SUM, c->comm, c->stream);
+    if (rc != 0) { set_error("ncclAllReduce: %s", g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "?"); return MRL_ERR_NCCL; }
+    return MRL_OK;
+}
+static int allreduce_f64(mrl_ctx* c, double* buf, size_t n) {
+    if (c->cfg.world_size <= 1) return MRL_OK;
+    if (!c->comm) { set_error("world_size > 1 but mrl_comm_init was not called"); return MRL_ERR_NCCL; }
+    int rc = g_nccl.AllReduce(buf, buf, n, NCCL_FLOAT64, NCCL_SUM, c->comm, c->stream);
+    if (rc != 0) { set_error("ncclAllReduce: %s", g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "?"); return MRL_ERR_NCCL; }
+    return MRL_OK;
+}
+
+}  // namespace mrl
+
+extern "C" void mrl_config_defaults(mrl_config* cfg) {
+    memset(cfg, 0, sizeof(*cfg));
+    cfg->env_kind = MRL_ENV_LUNAR_LANDER;
+    cfg->n_envs = 1024;        // ppo.mojo:749
+    cfg->rollout_len = 128;    // ppo.mojo:748
+    cfg->hidden_dim = 64;      // ppo.mojo:747
+    cfg->minibatch_size = 256; // ppo.mojo:750
+    cfg->num_epochs = 4;
+    cfg->precision = 0;
+    cfg->normalize_advantages = 1;
+    cfg->norm_adv_per_minibatch = 1;
+    cfg->clip_value = 1;
+    cfg->deterministic = 0;
+    cfg->world_size = 1;
+    cfg->rank = 0;
+    cfg->gamma = 0.99;
+    cfg->gae_lambda = 0.95;
+    cfg->clip_epsilon = 0.2f;
+    cfg->value_loss_coef = 0.5f;
+    cfg->target_kl = 0.015f;
+    cfg->max_grad_norm = 0.5f;
+    cfg->adam_beta1 = 0.9f;
+    cfg->adam_beta2 = 0.999f;
+    cfg->adam_eps = 1e-8f;
+}
+
+extern "C" const char* mrl_last_error_string(void) { return g_error; }
+extern "C" int64_t mrl_kernel_launch_count(void) { return (int64_t)g_launches.load(); }
+
+extern "C" int mrl_create(mrl_ctx** out, const mrl_config* cfg) {
+    MRL_CHECK_ARG(out && cfg);
+    MRL_CHECK_ARG(cfg->n_envs > 0 && cfg->rollout_len > 0 && cfg->hidden_dim > 0 && cfg->minibatch_size > 0 &&
+                  cfg->num_epochs >= 0 && cfg->world_size >= 1 && cfg->rank >= 0 && cfg->rank < cfg->world_size);
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+        set_error("no CUDA device: this library has no CPU path");
+        return MRL_ERR_NO_DEVICE;
+    }
+    int ss, od, na, ad;
+    int rc = mrl_env_info(cfg->env_kind, &ss, &od, &na, &ad);
+    if (rc) return rc;
+    if (na == 0) { set_error("continuous-action envs are not built into the fused path yet"); return MRL_ERR_UNSUPPORTED; }
+    const int64_t total = (int64_t)cfg->n_envs * cfg->rollout_len;
+    MRL_CHECK_ARG(cfg->minibatch_size <= total && total < (1ll << 31));
+    mrl_ctx* c = new mrl_ctx();
+    c->cfg = *cfg;
+    c->state_size = ss; c->obs_dim = od; c->num_actions = na; c->action_dim = ad;
+    c->actor_net = mrl_net_spec{od, cfg->hidden_dim, na, MRL_ACT_RELU, MRL_HEAD_LINEAR};   // ppo.mojo:807-818
+    c->critic_net = mrl_net_spec{od, cfg->hidden_dim, 1, MRL_ACT_RELU, MRL_HEAD_LINEAR};   // ppo.mojo:820-830
+    c->actor_p = mrl_net_param_size(&c->actor_net);
+    c->critic_p = mrl_net_param_size(&c->critic_net);
+    c->comm = nullptr;
+    c->ring_tail = 0;
+    c->update_count = 0;
+    if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) {
+        set_error("cudaStreamCreate failed");
+        delete c;
+        return MRL_ERR_CUDA;
+    }
+    const size_t N = cfg->n_envs, T = cfg->rollout_len, B = cfg->minibatch_size;
+    int64_t ws = mlp_workspace_floats(&c->actor_net, (int)(B > N ? B : N));
+#define A_(p, n) do { rc = dalloc(c, &c->p, (n)); if (rc) { mrl_destroy(c); return rc; } } while (0)
+    A_(states, N * ss); A_(obs, N * od); A_(actions, N); A_(log_probs, N); A_(values, N);
+    A_(rewards, N); A_(dones, N); A_(logits, N * na); A_(episode_rewards, N); A_(episode_steps, N);
+    A_(r_obs, T * N * od); A_(r_actions, T * N); A_(r_log_probs, T * N); A_(r_values, T * N);
+    A_(r_rewards, T * N); A_(r_dones, T * N); A_(advantages, T * N); A_(returns, T * N); A_(bootstrap, N);
+    A_(ring_returns, EP_RING); A_(ring_lengths, EP_RING);
+    A_(actor_params, c->actor_p); A_(actor_state, 2 * (size_t)c->actor_p); A_(actor_grads, c->actor_p + 4);
+    A_(critic_params, c->critic_p); A_(critic_state, 2 * (size_t)c->critic_p); A_(critic_grads, c->critic_p + 4);
+    A_(mb_obs, B * od); A_(mb_actions, B); A_(mb_adv, B); A_(mb_ret, B); A_(mb_old_lp, B); A_(mb_old_v, B);
+    A_(mb_kl, B); A_(mb_logits, B * na); A_(mb_grad_logits, B * na); A_(mb_values, B); A_(mb_grad_values, B);
+    A_(actor_cache, B * (size_t)mrl_net_cache_per_sample(&c->actor_net));
+    A_(critic_cache, B * (size_t)mrl_net_cache_per_sample(&c->critic_net));
+    A_(workspace, (size_t)ws);
+    A_(perm, T * N);
+    A_(stats, 8);
+    A_(counters, 1);
+#undef A_
+    *out = c;
+    return MRL_OK;
+}
+
+extern "C" int mrl_destroy(mrl_ctx* c) {
+    if (!c) return MRL_OK;
+    cudaStreamSynchronize(c->stream);
+    if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
+    for (auto& ev : c->timer_events) for (cudaEvent_t e : ev) cudaEventDestroy(e);
+    for (void* p : c->allocs) cudaFree(p);
+    cudaStreamDestroy(c->stream);
+    delete c;
+    return MRL_OK;
+}
+
+extern "C" int mrl_get_timers(mrl_ctx* c, float ms_host[3], int calls_host[3]) {
+    MRL_CHECK_ARG(c && ms_host && calls_host);
+    MRL_CUDA_OK(cudaStreamSynchronize(c->stream));
+    for (int ph = 0; ph < 3; ++ph) {
+        float total = 0.0f;
+        auto& ev = c->timer_events[ph];
+        for (size_t i = 0; i + 1 < ev.size(); i += 2) {
+            float ms = 0.0f;
+            if (cudaEventElapsedTime(&ms, ev[i], ev[i + 1]) == cudaSuccess) total += ms;
+            cudaEventDestroy(ev[i]);
+            cudaEventDestroy(ev[i + 1]);
+        }
+        calls_host[ph] = (int)(ev.size() / 2);
+        ms_host[ph] = total;
+        ev.clear();
+    }
+    return MRL_OK;
+}
+
+extern "C" void* mrl_stream(mrl_ctx* c) { return c ? (void*)c->stream : nullptr; }
+extern "C" int mrl_param_size(mrl_ctx* c, int which) {
+    if (!c || which < 0 || which > 1) return MRL_ERR_INVALID_ARG;
+    return which == 0 ? c->actor_p : c->critic_p;
+}
+
+extern "C" int mrl_set_params(mrl_ctx* c, int which, const float* params_host, const float* opt_state_host) {
+    MRL_CHECK_ARG(c && (which == 0 || which == 1));
+    int p = which == 0 ? c->actor_p : c->critic_p;
+    float* dp = which == 0 ? c->actor_params : c->critic_params;
+    float* ds = which == 0 ? c->actor_state : c->critic_state;
+    if (params_host) MRL_CUDA_OK(cudaMemcpyAsync(dp, params_host, sizeof(float) * p, cudaMemcpyHostToDevice, c->stream));
+    if (opt_state_host) MRL_CUDA_OK(cudaMemcpyAsync(ds, opt_state_host, sizeof(float) * 2 * p, cudaMemcpyHostToDevice, c->stream));
+    MRL_CUDA_OK(cudaStreamSynchronize(c->stream));
+    return MRL_OK;
+}
+extern "C" int mrl_get_params(mrl_ctx* c, int which, float* params_host, float* opt_state_host) {
+    MRL_CHECK_ARG(c && (which == 0 || which == 1));
+    int p = which == 0 ? c->actor_p : c->critic_p;
+    float* dp = which == 0 ? c->actor_params : c->critic_params;
+    float* ds = which == 0 ? c->actor_state : c->critic_state;
+    if (params_host) MRL_CUDA_OK(cudaMemcpyAsync(params_host, dp, sizeof(float) * p, cudaMemcpyDeviceToHost, c->stream));
+    if (opt_state_host) MRL_CUDA_OK(cudaMemcpyAsync(opt_state_host, ds, sizeof(float) * 2 * p, cudaMemcpyDeviceToHost, c->stream));
+    MRL_CUDA_OK(cudaStreamSynchronize(c->stream));
+    return MRL_OK;
+}
+
+extern "C" int mrl_comm_unique_id(uint8_t id_host[128]) {
+    MRL_CHECK_ARG(id_host);
+    if (!g_nccl.load()) { set_error("libnccl.so.2 not found"); return MRL_ERR_NCCL; }
+    ncclUniqueId id;
+    int rc = g_nccl.GetUniqueId(&id);
+    if (rc != 0) { set_error("ncclGetUniqueId failed (%d)", rc); return MRL_ERR_NCCL; }
+    memcpy(id_host, id.internal, 128);
+    return MRL_OK;
+}
+extern "C" int mrl_comm_init(mrl_ctx* c, const uint8_t id_host[128]) {
+    MRL_CHECK_ARG(c && id_host);
+    if (c->cfg.world_size <= 1) return MRL_OK;
+    if (!g_nccl.load()) { set_error("libnccl.so.2 not found"); return MRL_ERR_NCCL; }
+    ncclUniqueId id;
+    memcpy(id.internal, id_host, 128);
+    int rc = g_nccl.CommInitRank(&c->comm, c->cfg.world_size, id, c->cfg.rank);
+    if (rc != 0) { set_error("ncclCommInitRank: %s", g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "?"); return MRL_ERR_NCCL; }
+    return MRL_OK;
+}
+
+extern "C" int mrl_ppo_reset(mrl_ctx* c, uint64_t rng_seed) {
+    MRL_CHECK_ARG(c);
+    const int N = c->cfg.n_envs;
+    int rc = mrl_env_reset(c->cfg.env_kind, N, c->states, rng_seed, c->stream);
+    if (rc) return rc;
+    MRL_LAUNCH(extract_obs_kernel, ceil_div((int64_t)N * c->obs_dim, 256), 256, 0, c->stream, c->states, c->obs, N,
+               c->state_size, c->obs_dim);
+    MRL_CUDA_OK(cudaMemsetAsync(c->episode_rewards, 0, sizeof(float) * N, c->stream));
+    MRL_CUDA_OK(cudaMemsetAsync(c->episode_steps, 0, sizeof(float) * N, c->stream));
+    return MRL_OK;
+}
+
+extern "C" int mrl_ppo_rollout(mrl_ctx* c) {
+    MRL_CHECK_ARG(c);
+    const int N = c->cfg.n_envs, T = c->cfg.rollout_len, A = c->num_actions;
+    cudaStream_t st = c->stream;
+    int rc;
+    PhaseTimer timer(c, 0);
+    for (int t = 0; t < T; ++t) {
+        if ((rc = mlp_forward_impl(&c->actor_net, N, c->obs, c->actor_params, c->logits, nullptr, c->workspace, st))) return rc;
+        if ((rc = mlp_forward_impl(&c->critic_net, N, c->obs, c->critic_params, c->values, nullptr, c->workspace, st))) return rc;
+        MRL_LAUNCH(rollout_pre_step_kernel, ceil_div(N, 128), 128, 0, st, c->logits, c->values, c->obs, c->actions,
+                   c->r_obs, c->r_actions, c->r_log_probs, c->r_values, c->counters, t, N, A, c->obs_dim,
+                   c->cfg.deterministic);
+        if ((rc = env_step_launch(c))) return rc;
+        MRL_LAUNCH(rollout_post_step_kernel, ceil_div(N, 128), 128, 0, st, c->rewards, c->dones, c->r_rewards,
+                   c->r_dones, c->episode_rewards, c->episode_steps, c->ring_returns, c->ring_lengths, c->counters,
+                   t, N);
+        MRL_LAUNCH(add_total_steps_kernel, 1, 1, 0, st, c->counters, N);
+        if (c->cfg.env_kind == MRL_ENV_CARTPOLE) {
+            MRL_LAUNCH(cartpole_auto_reset_kernel, ceil_div(N, 128), 128, 0, st, c->states, c->dones, c->obs,
+                       c->counters, t, N);
+        } else {
+            MRL_LAUNCH(lunar_auto_reset_kernel, ceil_div(N, 128), 128, 0, st, c->states, c->dones, c->obs,
+                       c->counters, t, N);
+        }
+    }
+    return MRL_OK;
+}
+
+extern "C" int mrl_ppo_gae(mrl_ctx* c) {
+    MRL_CHECK_ARG(c);
+    const int N = c->cfg.n_envs, T = c->cfg.rollout_len;
+    cudaStream_t st = c->stream;
+    int rc;
+    PhaseTimer timer(c, 1);
+    if ((rc = mlp_forward_impl(&c->critic_net, N, c->obs, c->critic_params, c->bootstrap, nullptr, c->workspace, st))) return rc;
+    if ((rc = mrl_gae(T, N, c->r_rewards, c->r_values, c->r_dones, c->bootstrap, c->cfg.gamma, c->cfg.gae_lambda,
+                      c->advantages, c->returns, st))) return rc;
+    if (c->cfg.normalize_advantages) {
+        if ((rc = normalize_advantages_impl((int64_t)T * N, c->advantages, c->stats, st))) return rc;
+    }
+    return MRL_OK;
+}
+
+extern "C" int mrl_ppo_update(mrl_ctx* c, float actor_lr, float critic_lr, float entropy_coef,
+                              const int32_t* permutations_host) {
+    MRL_CHECK_ARG(c);
+    const mrl_config& cfg = c->cfg;
+    const int N = cfg.n_envs, T = cfg.rollout_len, B = cfg.minibatch_size, A = c->num_actions;
+    const uint32_t total = (uint32_t)((int64_t)N * T);
+    const int num_mb = (int)(total / (uint32_t)B);
+    cudaStream_t st = c->stream;
+    int rc;
+    int bits = 1;
+    while ((1ull << bits) < total) ++bits;
+    int half = (bits + 1) / 2;
+    PhaseTimer timer(c, 2);
+    MRL_LAUNCH(begin_update_kernel, 1, 1, 0, st, c->counters);
+    for (int epoch = 0; epoch < cfg.num_epochs; ++epoch) {
+        if (permutations_host) {
+            MRL_CUDA_OK(cudaMemcpyAsync(c->perm, permutations_host + (size_t)epoch * total, sizeof(int32_t) * total,
+                                        cudaMemcpyHostToDevice, st));
+        }
+        uint64_t key = (c->update_count * 1000003ull + (uint64_t)epoch) * 0x9E3779B97F4A7C15ull + 0xD1B54A32D192ED03ull;
+        for (int mb = 0; mb < num_mb; ++mb) {
+            int32_t* idx = c->perm + (size_t)mb * B;
+            if (!permutations_host) {
+                MRL_LAUNCH(make_indices_kernel, ceil_div(B, 256), 256, 0, st, idx, B, (uint32_t)mb * (uint32_t)B, total,
+                           half, key);
+            }
+            if ((rc = mrl_ppo_gather_minibatch(B, c->obs_dim, idx, c->r_obs, c->r_actions, c->advantages, c->returns,
+                                               c->r_log_probs, c->r_values, c->mb_obs, c->mb_actions, c->mb_adv,
+                                               c->mb_ret, c->mb_old_lp, c->mb_old_v, st))) return rc;
+            if (cfg.norm_adv_per_minibatch) {
+                if ((rc = normalize_advantages_impl(B, c->mb_adv, c->stats, st))) return rc;
+            }
+            // ---- actor (ppo.mojo:2513-2624)
+            if ((rc = mlp_forward_impl(&c->actor_net, B, c->mb_obs, c->actor_params, c->mb_logits, c->actor_cache,
+                                       c->workspace, st))) return rc;
+            if ((rc = mrl_ppo_actor_grad(B, A, c->mb_logits, c->mb_old_lp, c->mb_adv, c->mb_actions, cfg.clip_epsilon,
+                                         entropy_coef, c->mb_grad_logits, c->mb_kl, st))) return rc;
+            MRL_LAUNCH(kl_sum_kernel, 1, 1024, 0, st, c->mb_kl, B, c->actor_grads + c->actor_p);
+            if ((rc = mlp_backward_impl(&c->actor_net, B, c->mb_grad_logits, c->actor_params, c->actor_cache, nullptr,
+                                        c->actor_grads, c->workspace, st))) return rc;
+            if (cfg.world_size > 1) {
+                if ((rc = allreduce_f32(c, c->actor_grads, (size_t)c->actor_p + 1))) return rc;
+                MRL_LAUNCH(scale_kernel, ceil_div(c->actor_p, 256), 256, 0, st, c->actor_grads, c->actor_p,
+                           1.0f / (float)cfg.world_size);
+            }
+            MRL_LAUNCH(adam_prepare_kernel, 1, 1, 0, st, c->counters, c->actor_grads + c->actor_p,
+                       (float)B * (float)cfg.world_size, cfg.target_kl, (double)cfg.adam_beta1, (double)cfg.adam_beta2, 0);
+            if (cfg.max_grad_norm > 0.0f) {
+                if ((rc = grad_clip_impl(c->actor_p, c->actor_grads, cfg.max_grad_norm, c->stats + 4, nullptr, st))) return rc;
+            }
+            MRL_LAUNCH(adam_ctx_kernel, ceil_div(c->actor_p, 256), 256, 0, st, c->actor_params, c->actor_grads,
+                       c->actor_state, c->actor_p, actor_lr, cfg.adam_beta1, cfg.adam_beta2, cfg.adam_eps, c->counters);
+            // ---- critic (ppo.mojo:2626-2728)
+            if ((rc = mlp_forward_impl(&c->critic_net, B, c->mb_obs, c->critic_params, c->mb_values, c->critic_cache,
+                                       c->workspace, st))) return rc;
+            if ((rc = mrl_ppo_critic_grad(B, c->mb_values, c->mb_old_v, c->mb_ret, cfg.value_loss_coef,
+                                          cfg.clip_epsilon, cfg.clip_value, c->mb_grad_values, st))) return rc;
+            if ((rc = mlp_backward_impl(&c->critic_net, B, c->mb_grad_values, c->critic_params, c->critic_cache,
+                                        nullptr, c->critic_grads, c->workspace, st))) return rc;
+            if (cfg.world_size > 1) {
+                if ((rc = allreduce_f32(c, c->critic_grads, (size_t)c->critic_p))) return rc;
+                MRL_LAUNCH(scale_kernel, ceil_div(c->critic_p, 256), 256, 0, st, c->critic_grads, c->critic_p,
+                           1.0f / (float)cfg.world_size);
+            }
+            MRL_LAUNCH(adam_prepare_kernel, 1, 1, 0, st, c->counters, c->actor_grads + c->actor_p, 1.0f, 0.0f,
+                       (double)cfg.adam_beta1, (double)cfg.adam_beta2, 1);
+            if (cfg.max_grad_norm > 0.0f) {
+                if ((rc = grad_clip_impl(c->critic_p, c->critic_grads, cfg.max_grad_norm, c->stats + 4, nullptr, st))) return rc;
+            }
+            MRL_LAUNCH(adam_ctx_kernel, ceil_div(c->critic_p, 256), 256, 0, st, c->critic_params, c->critic_grads,
+                       c->critic_state, c->critic_p, critic_lr, cfg.adam_beta1, cfg.adam_beta2, cfg.adam_eps, c->counters);
+        }
+    }
+    c->update_count += 1;
+    return MRL_OK;
+}
+
+extern "C" int mrl_get_buffer(mrl_ctx* c, int which, float** device_ptr, int64_t* n_floats) {
+    MRL_CHECK_ARG(c && device_ptr && n_floats);
+    const int64_t N = c->cfg.n_envs, T = c->cfg.rollout_len;
+    float* p = nullptr;
+    int64_t n = 0;
+    switch (which) {
+        case MRL_BUF_STATES: p = c->states; n = N * c->state_size; break;
+        case MRL_BUF_OBS: p = c->obs; n = N * c->obs_dim; break;
+        case MRL_BUF_ROLLOUT_OBS: p = c->r_obs; n = T * N * c->obs_dim; break;
+        case MRL_BUF_ROLLOUT_ACTIONS: p = c->r_actions; n = T * N; break;
+        case MRL_BUF_ROLLOUT_LOG_PROBS: p = c->r_log_probs; n = T * N; break;
+        case MRL_BUF_ROLLOUT_VALUES: p = c->r_values; n = T * N; break;
+        case MRL_BUF_ROLLOUT_REWARDS: p = c->r_rewards; n = T * N; break;
+        case MRL_BUF_ROLLOUT_DONES: p = c->r_dones; n = T * N; break;
+        case MRL_BUF_ADVANTAGES: p = c->advantages; n = T * N; break;
+        case MRL_BUF_RETURNS: p = c->returns; n = T * N; break;
+        case MRL_BUF_ACTOR_PARAMS: p = c->actor_params; n = c->actor_p; break;
+        case MRL_BUF_CRITIC_PARAMS: p = c->critic_params; n = c->critic_p; break;
+        case MRL_BUF_ACTOR_GRADS: p = c->actor_grads; n = c->actor_p; break;
+        case MRL_BUF_CRITIC_GRADS: p = c->critic_grads; n = c->critic_p; break;
+        case MRL_BUF_DONES: p = c->dones; n = N; break;
+        default: set_error("mrl_get_buffer: unknown buffer %d", which); return MRL_ERR_INVALID_ARG;
+    }
+    *device_ptr = p;
+    *n_floats = n;
+    return MRL_OK;
+}
+
+extern "C" int mrl_read_buffer(mrl_ctx* c, int which, float* out_host, int64_t n_floats) {
+    float* p = nullptr;
+    int64_t n = 0;
+    int rc = mrl_get_buffer(c, which, &p, &n);
+    if (rc) return rc;
+    MRL_CHECK_ARG(out_host && n_floats == n);
+    MRL_CUDA_OK(cudaStreamSynchronize(c->stream));
+    MRL_CUDA_OK(cudaMemcpy(out_host, p, sizeof(float) * n, cudaMemcpyDeviceToHost));
+    return MRL_OK;
+}
+
+extern "C" int mrl_make_permutation(int64_t n, uint64_t key, int32_t* indices, void* stream) {
+    MRL_CHECK_ARG(n > 0 && n < (1ll << 31) && indices);
+    int bits = 1;
+    while ((1ll << bits) < n) ++bits;
+    int half = (bits + 1) / 2;
+    MRL_LAUNCH(make_indices_kernel, ceil_div(n, 256), 256, 0, as_stream(stream), indices, (int)n, 0u, (uint32_t)n,
+               half, key);
+    return MRL_OK;
+}
+
+extern "C" int mrl_get_stats(mrl_ctx* c, mrl_stats* out) {
+    MRL_CHECK_ARG(c && out);
+    DeviceCounters h;
+    MRL_CUDA_OK(cudaMemcpyAsync(&h, c->counters, sizeof(h), cudaMemcpyDeviceToHost, c->stream));
+    MRL_CUDA_OK(cudaStreamSynchronize(c->stream));
+    out->total_steps = h.total_steps;
+    out->completed_episodes = (int64_t)h.completed_episodes;
+    out->sum_episode_reward = h.sum_episode_reward;
+    out->sum_episode_steps = h.sum_episode_steps;
+    out->minibatches_done = h.minibatches_done;
+    out->kl_early_stop = h.kl_stop;
+    out->last_mean_kl = h.last_mean_kl;
+    out->actor_adam_t = h.actor_t;
+    out->critic_adam_t = h.critic_t;
+    return MRL_OK;
+}
+
+extern "C" int mrl_drain_episodes(mrl_ctx* c, float* returns_host, float* lengths_host, int capacity) {
+    MRL_CHECK_ARG(c && returns_host && lengths_host && capacity >= 0);
+    DeviceCounters h;
+    MRL_CUDA_OK(cudaMemcpyAsync(&h, c->counters, sizeof(h), cudaMemcpyDeviceToHost, c->stream));
+    MRL_CUDA_OK(cudaStreamSynchronize(c->stream));
+    unsigned long long head = h.ring_head, tail = c->ring_tail;
+    if (head - tail > (unsigned long long)EP_RING) tail = head - EP_RING;  // older entries were overwritten
+    int n = 0;
+    std::vector<float> rr(EP_RING), rl(EP_RING);
+    MRL_CUDA_OK(cudaMemcpy(rr.data(), c->ring_returns, sizeof(float) * EP_RING, cudaMemcpyDeviceToHost));
+    MRL_CUDA_OK(cudaMemcpy(rl.data(), c->ring_lengths, sizeof(float) * EP_RING, cudaMemcpyDeviceToHost));
+    while (tail < head && n < capacity) {
+        returns_host[n] = rr[tail % EP_RING];
+        lengths_host[n] = rl[tail % EP_RING];
+        ++n; ++tail;
+    }
+    c->ring_tail = tail;
+    return n;
+}

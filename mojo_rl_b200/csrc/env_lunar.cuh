@@ -1,0 +1,369 @@
+// LunarLanderV2 on the register-resident physics core.
+// Reference: envs/lunar_lander/lunar_lander_v2.mojo:1453-2774 (discrete GPU
+// path), constants.mojo:9-130, helpers.mojo:10-133.
+#pragma once
+#include "physics2d.cuh"
+
+namespace mrl {
+namespace lunar {
+
+using namespace phys;
+
+// constants.mojo:9-75 - Float64 in the reference, cast to f32 where it casts.
+constexpr double GRAVITY_X = 0.0, GRAVITY_Y = -10.0, DT = 0.02;
+constexpr int VELOCITY_ITERATIONS = 6, POSITION_ITERATIONS = 2;
+constexpr double SCALE = 30.0;
+constexpr double LEG_AWAY = 20.0 / SCALE, LEG_DOWN = 18.0 / SCALE, LEG_W = 2.0 / SCALE,
+                 LEG_H = 8.0 / SCALE;
+constexpr double LANDER_MASS = 5.0, LANDER_INERTIA = 2.0, LEG_MASS = 0.2, LEG_INERTIA = 0.02;
+constexpr double LEG_SPRING_STIFFNESS = 400.0, LEG_SPRING_DAMPING = 40.0;
+constexpr double MAIN_ENGINE_POWER = 13.0, SIDE_ENGINE_POWER = 0.6;
+constexpr double MAIN_ENGINE_Y_OFFSET = 4.0 / SCALE, SIDE_ENGINE_HEIGHT = 14.0 / SCALE,
+                 SIDE_ENGINE_AWAY = 12.0 / SCALE;
+constexpr double CRASH_PENALTY = -100.0, LAND_REWARD = 100.0, MAIN_ENGINE_FUEL_COST = 0.30,
+                 SIDE_ENGINE_FUEL_COST = 0.03;
+constexpr double FPS = 50.0, W_UNITS = 600.0 / SCALE, H_UNITS = 400.0 / SCALE;
+constexpr double HELIPAD_Y = H_UNITS / 4.0, HELIPAD_X = W_UNITS / 2.0;
+constexpr double FRICTION = 0.1, RESTITUTION = 0.0, BAUMGARTE = 0.2, SLOP = 0.005;
+constexpr int TERRAIN_CHUNKS = 11, N_EDGES = TERRAIN_CHUNKS - 1;
+
+// physics2d/layout.mojo:247-255 (LunarLanderLayout)
+constexpr int NUM_BODIES = 3, MAX_CONTACTS = 8, MAX_JOINTS = 2, MAX_TERRAIN_EDGES = 16;
+constexpr int OBS_DIM = 8, NUM_ACTIONS = 4;
+constexpr int BODIES_OFFSET = 8, FORCES_OFFSET = 47, JOINTS_OFFSET = 56, JOINT_COUNT_OFFSET = 90,
+              EDGES_OFFSET = 91, EDGE_COUNT_OFFSET = 187, METADATA_OFFSET = 188, STATE_SIZE = 192;
+constexpr int META_STEP_COUNT = 0, META_TOTAL_REWARD = 1, META_PREV_SHAPING = 2, META_DONE = 3;
+
+struct Traits {
+    __host__ __device__ static constexpr int ja(int) { return 0; }
+    __host__ __device__ static constexpr int jb(int j) { return j + 1; }
+};
+
+// Polygon vertices of _init_shapes_gpu (lunar_lander_v2.mojo:1969-2026).
+__device__ __forceinline__ int shape_nverts(int body) { return body == 0 ? 6 : 4; }
+__device__ __forceinline__ void shape_vertex(int body, int v, float& lx, float& ly) {
+    if (body == 0) {
+        const float hx[6] = {(float)(-14.0 / SCALE), (float)(-17.0 / SCALE), (float)(-17.0 / SCALE),
+                             (float)(17.0 / SCALE),  (float)(17.0 / SCALE),  (float)(14.0 / SCALE)};
+        const float hy[6] = {(float)(17.0 / SCALE), 0.0f, (float)(-10.0 / SCALE),
+                             (float)(-10.0 / SCALE), 0.0f, (float)(17.0 / SCALE)};
+        lx = hx[v]; ly = hy[v];
+    } else {
+        const float lxs[4] = {(float)(-LEG_W), (float)(-LEG_W), (float)(LEG_W), (float)(LEG_W)};
+        const float lys[4] = {(float)(LEG_H), (float)(-LEG_H), (float)(-LEG_H), (float)(LEG_H)};
+        lx = lxs[v]; ly = lys[v];
+    }
+}
+
+// Dynamic state of one environment while it is being stepped.
+struct Env {
+    Bodies<NUM_BODIES> b;
+    JointParams jp[MAX_JOINTS];
+    float step_count, prev_shaping, done;
+    int n_edges, n_joints;
+};
+
+// ---- reference row layout (the GPUDiscreteEnv boundary) -------------------
+__device__ __forceinline__ void load_row(const float* __restrict__ s, Env& e) {
+#pragma unroll
+    for (int i = 0; i < NUM_BODIES; ++i) {
+        const float* body = s + BODIES_OFFSET + i * BODY_STATE_SIZE;
+        e.b.x[i] = body[IDX_X]; e.b.y[i] = body[IDX_Y]; e.b.a[i] = body[IDX_ANGLE];
+        e.b.vx[i] = body[IDX_VX]; e.b.vy[i] = body[IDX_VY]; e.b.w[i] = body[IDX_OMEGA];
+        e.b.inv_m[i] = body[IDX_INV_MASS]; e.b.inv_i[i] = body[IDX_INV_INERTIA];
+    }
+#pragma unroll
+    for (int j = 0; j < MAX_JOINTS; ++j) {
+        const float* jt = s + JOINTS_OFFSET + j * JOINT_DATA_SIZE;
+        e.jp[j].ax = jt[JOINT_ANCHOR_AX]; e.jp[j].ay = jt[JOINT_ANCHOR_AY];
+        e.jp[j].bx = jt[JOINT_ANCHOR_BX]; e.jp[j].by = jt[JOINT_ANCHOR_BY];
+        e.jp[j].ref = jt[JOINT_REF_ANGLE]; e.jp[j].lo = jt[JOINT_LOWER_LIMIT];
+        e.jp[j].hi = jt[JOINT_UPPER_LIMIT]; e.jp[j].max_torque = jt[JOINT_MAX_MOTOR_TORQUE];
+        e.jp[j].motor_speed = jt[JOINT_MOTOR_SPEED]; e.jp[j].stiffness = jt[JOINT_STIFFNESS];
+        e.jp[j].damping = jt[JOINT_DAMPING]; e.jp[j].flags = (int)jt[JOINT_FLAGS];
+    }
+    e.step_count = s[METADATA_OFFSET + META_STEP_COUNT];
+    e.prev_shaping = s[METADATA_OFFSET + META_PREV_SHAPING];
+    e.done = s[METADATA_OFFSET + META_DONE];
+    e.n_edges = (int)s[EDGE_COUNT_OFFSET];
+    e.n_joints = (int)s[JOINT_COUNT_OFFSET];
+}
+
+__device__ __forceinline__ void store_row(float* __restrict__ s, const Env& e) {
+#pragma unroll
+    for (int i = 0; i < NUM_BODIES; ++i) {
+        float* body = s + BODIES_OFFSET + i * BODY_STATE_SIZE;
+        body[IDX_X] = e.b.x[i]; body[IDX_Y] = e.b.y[i]; body[IDX_ANGLE] = e.b.a[i];
+        body[IDX_VX] = e.b.vx[i]; body[IDX_VY] = e.b.vy[i]; body[IDX_OMEGA] = e.b.w[i];
+        float* f = s + FORCES_OFFSET + i * 3;  // cleared by the setup step (:2139-2144)
+        f[0] = 0.0f; f[1] = 0.0f; f[2] = 0.0f;
+    }
+    s[METADATA_OFFSET + META_STEP_COUNT] = e.step_count;
+    s[METADATA_OFFSET + META_PREV_SHAPING] = e.prev_shaping;
+    s[METADATA_OFFSET + META_DONE] = e.done;
+}
+
+// Terrain access through the reference row.
+struct RowEdges {
+    const float* s;
+    __device__ __forceinline__ void get(int e, float& x0, float& y0, float& x1, float& y1, float& nx,
+                                        float& ny) const {
+        const float* p = s + EDGES_OFFSET + e * 6;
+        x0 = p[0]; y0 = p[1]; x1 = p[2]; y1 = p[3]; nx = p[4]; ny = p[5];
+    }
+    __device__ __forceinline__ float y0_of(int e) const { return s[EDGES_OFFSET + e * 6 + 1]; }
+    __device__ __forceinline__ float y1_of(int e) const { return s[EDGES_OFFSET + e * 6 + 3]; }
+};
+
+// _setup_single_env, lunar_lander_v2.mojo:2109-2262 (wind is compile-time off).
+__device__ __forceinline__ void apply_engines(Env& e, int env, int action) {
+    if (e.done > 0.5f) return;
+    if (action == 0) return;
+    int step_count = (int)e.step_count;
+    Philox rng((uint64_t)(int64_t)(env + 12345), (uint64_t)(int64_t)step_count);
+    float r[4];
+    rng.step_uniform(r);
+    float dispersion_x = (r[0] * 2.0f - 1.0f) / (float)SCALE;
+    float dispersion_y = (r[1] * 2.0f - 1.0f) / (float)SCALE;
+    float tip_x, tip_y;
+    mrl_sincosf(e.b.a[0], &tip_x, &tip_y);
+    float side_x = -tip_y, side_y = tip_x;
+    float dvx = 0.0f, dvy = 0.0f, domega = 0.0f;
+    const float main_y_offset = (float)MAIN_ENGINE_Y_OFFSET, side_away = (float)SIDE_ENGINE_AWAY;
+    const float side_height = (float)SIDE_ENGINE_HEIGHT, main_power = (float)MAIN_ENGINE_POWER;
+    const float side_power = (float)SIDE_ENGINE_POWER, lander_mass = (float)LANDER_MASS;
+    const float lander_inertia = (float)LANDER_INERTIA, scale = (float)SCALE;
+    if (action == 2) {
+        float ox = tip_x * (main_y_offset + 2.0f * dispersion_x) + side_x * dispersion_y;
+        float oy = -tip_y * (main_y_offset + 2.0f * dispersion_x) - side_y * dispersion_y;
+        float impulse_x = -ox * main_power, impulse_y = -oy * main_power;
+        dvx += impulse_x / lander_mass;
+        dvy += impulse_y / lander_mass;
+        float torque = ox * impulse_y - oy * impulse_x;
+        domega += torque / lander_inertia;
+    } else if (action == 1 || action == 3) {
+        float direction = action == 1 ? -1.0f : 1.0f;
+        float ox = tip_x * dispersion_x + side_x * (3.0f * dispersion_y + direction * side_away);
+        float oy = -tip_y * dispersion_x - side_y * (3.0f * dispersion_y + direction * side_away);
+        float impulse_x = -ox * side_power, impulse_y = -oy * side_power;
+        dvx += impulse_x / lander_mass;
+        dvy += impulse_y / lander_mass;
+        float r_x = ox - tip_x * 17.0f / scale;
+        float r_y = oy + tip_y * side_height;
+        float torque = r_x * impulse_y - r_y * impulse_x;
+        domega += torque / lander_inertia;
+    }
+    e.b.vx[0] = e.b.vx[0] + dvx;
+    e.b.vy[0] = e.b.vy[0] + dvy;
+    e.b.w[0] = e.b.w[0] + domega;
+}
+
+// The fused physics step, lunar_lander_v2.mojo:2671-2752.
+template <class Edges>
+__device__ __forceinline__ void physics_step(Env& e, const Edges& edges, Contacts<MAX_CONTACTS>& c) {
+    const float gx = (float)GRAVITY_X, gy = (float)GRAVITY_Y, dt = (float)DT;
+    const float zero[NUM_BODIES] = {0.0f, 0.0f, 0.0f};
+    integrate_velocities(e.b, zero, zero, zero, gx, gy, dt);
+    refresh_trig(e.b);
+    // EdgeTerrainCollision.detect_single_env: body-major, vertex, edge order.
+    c.n = 0;
+#pragma unroll
+    for (int body = 0; body < NUM_BODIES; ++body) {
+        const int nv = shape_nverts(body);
+#pragma unroll
+        for (int v = 0; v < 6; ++v) {
+            if (v >= nv) break;
+            float lx, ly;
+            shape_vertex(body, v, lx, ly);
+            float wx = e.b.x[body] + lx * e.b.cs[body] - ly * e.b.sn[body];
+            float wy = e.b.y[body] + lx * e.b.sn[body] + ly * e.b.cs[body];
+            for (int ed = 0; ed < MAX_TERRAIN_EDGES; ++ed) {
+                if (ed >= e.n_edges) break;
+                float x0, y0, x1, y1, nx, ny;
+                edges.get(ed, x0, y0, x1, y1, nx, ny);
+                vertex_edge_test(c, body, wx, wy, x0, y0, x1, y1, nx, ny);
+            }
+        }
+    }
+    ContactPre<MAX_CONTACTS> cp;
+    prepare_contacts(e.b, c, cp);
+    JointPre jpre[MAX_JOINTS];
+    prepare_joints<Traits>(e.b, e.jp, jpre);
+    for (int it = 0; it < VELOCITY_ITERATIONS; ++it) {
+        solve_velocity_contacts(e.b, c, cp, (float)FRICTION, (float)RESTITUTION);
+        solve_velocity_joints<Traits>(e.b, e.jp, jpre, e.n_joints, dt);
+    }
+    integrate_positions(e.b, dt);
+    for (int it = 0; it < POSITION_ITERATIONS; ++it) {
+        solve_position_contacts(e.b, c, (float)BAUMGARTE, (float)SLOP);
+        solve_position_joints<Traits>(e.b, e.jp, e.n_joints, (float)BAUMGARTE, (float)SLOP);
+    }
+}
+
+template <class Edges>
+__device__ __forceinline__ float terrain_y_at(const Edges& edges, float leg_x) {
+    const float x_spacing = (float)(W_UNITS / (double)(TERRAIN_CHUNKS - 1));
+    int chunk = (int)(leg_x / x_spacing);
+    if (chunk < 0) chunk = 0;
+    if (chunk >= N_EDGES) return edges.y1_of(N_EDGES - 1);
+    return edges.y0_of(chunk);
+}
+
+// _finalize_single_env, lunar_lander_v2.mojo:2266-2482.  obs[8] is written
+// only when the env was not already done (the reference leaves the row's
+// observation untouched in that case).
+template <class Edges>
+__device__ __forceinline__ void finalize(Env& e, const Edges& edges, const Contacts<MAX_CONTACTS>& c,
+                                         int action, float (&obs)[OBS_DIM], bool& obs_written,
+                                         float& reward_out, float& done_out) {
+    obs_written = false;
+    if (e.done > 0.5f) { reward_out = 0.0f; done_out = 1.0f; return; }
+    float x = e.b.x[0], y = e.b.y[0], vx = e.b.vx[0], vy = e.b.vy[0], angle = e.b.a[0], omega = e.b.w[0];
+    float x_norm = (x - (float)HELIPAD_X) / (float)(W_UNITS / 2.0);
+    float y_norm = (y - (float)(HELIPAD_Y + LEG_DOWN / SCALE)) / (float)(H_UNITS / 2.0);
+    float vx_norm = vx * (float)(W_UNITS / 2.0) / (float)FPS;
+    float vy_norm = vy * (float)(H_UNITS / 2.0) / (float)FPS;
+    float omega_norm = 20.0f * omega / (float)FPS;
+    float left_contact = 0.0f, right_contact = 0.0f;
+    float left_terrain_y = terrain_y_at(edges, e.b.x[1]);
+    float right_terrain_y = terrain_y_at(edges, e.b.x[2]);
+    const float leg_h = (float)LEG_H, contact_tolerance = 0.01f;
+    if (e.b.y[1] - leg_h <= left_terrain_y + contact_tolerance) left_contact = 1.0f;
+    if (e.b.y[2] - leg_h <= right_terrain_y + contact_tolerance) right_contact = 1.0f;
+    obs[0] = x_norm; obs[1] = y_norm; obs[2] = vx_norm; obs[3] = vy_norm;
+    obs[4] = angle; obs[5] = omega_norm; obs[6] = left_contact; obs[7] = right_contact;
+    obs_written = true;
+    float dist = sqrtf(x_norm * x_norm + y_norm * y_norm);
+    float speed = sqrtf(vx_norm * vx_norm + vy_norm * vy_norm);
+    float abs_angle = angle >= 0.0f ? angle : -angle;
+    float shaping = -100.0f * dist - 100.0f * speed - 100.0f * abs_angle + 10.0f * left_contact +
+                    10.0f * right_contact;
+    float reward = shaping - e.prev_shaping;
+    e.prev_shaping = shaping;
+    if (action == 2) reward = reward - (float)MAIN_ENGINE_FUEL_COST;
+    else if (action == 1 || action == 3) reward = reward - (float)SIDE_ENGINE_FUEL_COST;
+    float done = 0.0f;
+    if (x_norm >= 1.0f || x_norm <= -1.0f) { done = 1.0f; reward = (float)CRASH_PENALTY; }
+    if (y > (float)(H_UNITS * 1.5)) { done = 1.0f; reward = (float)CRASH_PENALTY; }
+    bool lander_contact = false;
+#pragma unroll
+    for (int k = 0; k < MAX_CONTACTS; ++k)
+        if (k < c.n && c.body[k] == 0) lander_contact = true;
+    if (lander_contact) { done = 1.0f; reward = (float)CRASH_PENALTY; }
+    bool both_legs = left_contact > 0.5f && right_contact > 0.5f;
+    float speed_val = sqrtf(vx * vx + vy * vy);
+    float abs_omega = omega < 0.0f ? -omega : omega;
+    if (both_legs && speed_val < 0.01f && abs_omega < 0.01f) {
+        done = 1.0f;
+        reward = reward + (float)LAND_REWARD;
+    }
+    if (e.step_count > 1000.0f) done = 1.0f;
+    e.step_count = e.step_count + 1.0f;
+    e.done = done;
+    reward_out = reward;
+    done_out = done;
+}
+
+// _reset_env_gpu, lunar_lander_v2.mojo:1709-1966, writing the reference row.
+// Only the fields the reference writes are touched.
+__device__ __forceinline__ void reset_row(float* __restrict__ s, int64_t seed) {
+    Philox velocity_rng((uint64_t)seed, 0);
+    float velocity_rand[4];
+    velocity_rng.step_uniform(velocity_rand);
+    Philox terrain_rng((uint64_t)(seed + 1000), 0);
+    s[EDGE_COUNT_OFFSET] = (float)N_EDGES;
+    const float x_spacing = (float)(W_UNITS / (TERRAIN_CHUNKS - 1));
+    float raw[TERRAIN_CHUNKS + 1];
+    const float h_units_half = (float)(H_UNITS / 2.0);
+#pragma unroll
+    for (int ch = 0; ch < TERRAIN_CHUNKS + 1; ++ch) {
+        float r[4];
+        terrain_rng.step_uniform(r);
+        raw[ch] = r[0] * h_units_half;
+    }
+    float smooth[TERRAIN_CHUNKS];
+#pragma unroll
+    for (int ch = 0; ch < TERRAIN_CHUNKS; ++ch) {
+        float h;
+        if (ch == 0) h = (raw[0] + raw[0] + raw[1]) / 3.0f;
+        else if (ch == TERRAIN_CHUNKS - 1) h = (raw[ch - 1] + raw[ch] + raw[ch]) / 3.0f;
+        else h = (raw[ch - 1] + raw[ch] + raw[ch + 1]) / 3.0f;
+        smooth[ch] = h;
+    }
+#pragma unroll
+    for (int ch = TERRAIN_CHUNKS / 2 - 2; ch < TERRAIN_CHUNKS / 2 + 3; ++ch) smooth[ch] = (float)HELIPAD_Y;
+#pragma unroll
+    for (int ed = 0; ed < N_EDGES; ++ed) {
+        float x0 = (float)ed * x_spacing, x1 = (float)(ed + 1) * x_spacing;
+        float y0 = smooth[ed], y1 = smooth[ed + 1];
+        float dx = x1 - x0, dy = y1 - y0;
+        float length = sqrtf(dx * dx + dy * dy);
+        float nx = -dy / length, ny = dx / length;
+        if (ny < 0.0f) { nx = -nx; ny = -ny; }
+        float* edge = s + EDGES_OFFSET + ed * 6;
+        edge[0] = x0; edge[1] = y0; edge[2] = x1; edge[3] = y1; edge[4] = nx; edge[5] = ny;
+    }
+    const float init_random_scale = (float)(1000.0 * DT / LANDER_MASS);
+    float init_vx = (velocity_rand[0] * 2.0f - 1.0f) * init_random_scale;
+    float init_vy = (velocity_rand[1] * 2.0f - 1.0f) * init_random_scale;
+    float* lander = s + BODIES_OFFSET;
+    lander[IDX_X] = (float)HELIPAD_X; lander[IDX_Y] = (float)H_UNITS; lander[IDX_ANGLE] = 0.0f;
+    lander[IDX_VX] = init_vx; lander[IDX_VY] = init_vy; lander[IDX_OMEGA] = 0.0f;
+    lander[IDX_INV_MASS] = (float)(1.0 / LANDER_MASS);
+    lander[IDX_INV_INERTIA] = (float)(1.0 / LANDER_INERTIA);
+    lander[IDX_SHAPE] = 0.0f;
+#pragma unroll
+    for (int leg = 0; leg < 2; ++leg) {
+        float* lb = s + BODIES_OFFSET + (leg + 1) * BODY_STATE_SIZE;
+        float leg_offset_x = leg == 1 ? (float)LEG_AWAY : (float)(-LEG_AWAY);
+        lb[IDX_X] = (float)HELIPAD_X + leg_offset_x;
+        lb[IDX_Y] = (float)(H_UNITS - 10.0 / SCALE - LEG_DOWN);
+        lb[IDX_ANGLE] = 0.0f;
+        lb[IDX_VX] = init_vx; lb[IDX_VY] = init_vy; lb[IDX_OMEGA] = 0.0f;
+        lb[IDX_INV_MASS] = (float)(1.0 / LEG_MASS);
+        lb[IDX_INV_INERTIA] = (float)(1.0 / LEG_INERTIA);
+        lb[IDX_SHAPE] = (float)(leg + 1);
+    }
+    s[JOINT_COUNT_OFFSET] = 2.0f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        float* jt = s + JOINTS_OFFSET + j * JOINT_DATA_SIZE;
+        jt[JOINT_TYPE] = 0.0f;
+        jt[JOINT_BODY_A] = 0.0f;
+        jt[JOINT_BODY_B] = (float)(j + 1);
+        jt[JOINT_ANCHOR_AX] = j == 1 ? (float)LEG_AWAY : (float)(-LEG_AWAY);
+        jt[JOINT_ANCHOR_AY] = (float)(-10.0 / SCALE);
+        jt[JOINT_ANCHOR_BX] = 0.0f;
+        jt[JOINT_ANCHOR_BY] = (float)LEG_H;
+        jt[JOINT_REF_ANGLE] = 0.0f;
+        jt[JOINT_LOWER_LIMIT] = j == 1 ? -0.9f : 0.4f;
+        jt[JOINT_UPPER_LIMIT] = j == 1 ? -0.4f : 0.9f;
+        jt[JOINT_STIFFNESS] = (float)LEG_SPRING_STIFFNESS;
+        jt[JOINT_DAMPING] = (float)LEG_SPRING_DAMPING;
+        jt[JOINT_FLAGS] = (float)(JOINT_FLAG_LIMIT | JOINT_FLAG_SPRING);
+    }
+#pragma unroll
+    for (int i = 0; i < NUM_BODIES * 3; ++i) s[FORCES_OFFSET + i] = 0.0f;
+    float y_norm = (float)((H_UNITS - (HELIPAD_Y + LEG_DOWN / SCALE)) / (H_UNITS / 2.0));
+    float vx_norm = init_vx * (float)(W_UNITS / 2.0) / 50.0f;
+    float vy_norm = init_vy * (float)(H_UNITS / 2.0) / 50.0f;
+    s[0] = 0.0f; s[1] = y_norm; s[2] = vx_norm; s[3] = vy_norm;
+    s[4] = 0.0f; s[5] = 0.0f; s[6] = 0.0f; s[7] = 0.0f;
+    float dist = y_norm < 0.0f ? -y_norm : y_norm;
+    float speed = sqrtf(vx_norm * vx_norm + vy_norm * vy_norm);
+    float init_shaping = -100.0f * dist - 100.0f * speed;
+    s[METADATA_OFFSET + META_STEP_COUNT] = 0.0f;
+    s[METADATA_OFFSET + META_TOTAL_REWARD] = 0.0f;
+    s[METADATA_OFFSET + META_PREV_SHAPING] = init_shaping;
+    s[METADATA_OFFSET + META_DONE] = 0.0f;
+}
+
+// lunar_lander_v2.mojo:1620,1638,1685,1691: the UInt64 seed reaches the kernel
+// as a float32 argument; Int(seed) * 2654435761 + (i + 1) * 12345 wraps in 64 bits.
+__host__ __device__ __forceinline__ int64_t combined_seed(float seed_f32, int env) {
+    int64_t si = (int64_t)seed_f32;
+    return (int64_t)((uint64_t)si * 2654435761ull + (uint64_t)(env + 1) * 12345ull);
+}
+
+}  // namespace lunar
+}  // namespace mrl

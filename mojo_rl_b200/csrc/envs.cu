@@ -1,0 +1,163 @@
+// GPUDiscreteEnv / GPUContinuousEnv boundary (core/env_traits.mojo:230-397):
+// reset / step / selective-reset kernels over the reference's row layout.
+// Compile with -fmad=false (bit-level parity with the CPU checker).
+#include "env_cartpole.cuh"
+#include "env_lunar.cuh"
+
+namespace mrl {
+
+constexpr int ENV_TPB = 128;
+
+// ---------------------------------------------------------------- CartPole
+__global__ void cartpole_step_kernel(float* __restrict__ states, const float* __restrict__ actions,
+                                     float* __restrict__ rewards, float* __restrict__ dones,
+                                     float* __restrict__ obs, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float4 v = reinterpret_cast<float4*>(states)[i];
+    float s[4] = {v.x, v.y, v.z, v.w};
+    bool done = cartpole::step(s, (int)actions[i]);
+    float4 o = make_float4(s[0], s[1], s[2], s[3]);
+    reinterpret_cast<float4*>(states)[i] = o;
+    reinterpret_cast<float4*>(obs)[i] = o;
+    rewards[i] = 1.0f;
+    dones[i] = done ? 1.0f : 0.0f;
+}
+
+__global__ void cartpole_reset_kernel(float* __restrict__ states, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float s[4];
+    cartpole::reset(s, (uint32_t)((uint64_t)i * 2654435761ull + 12345ull));
+    reinterpret_cast<float4*>(states)[i] = make_float4(s[0], s[1], s[2], s[3]);
+}
+
+__global__ void cartpole_selective_reset_kernel(float* __restrict__ states, float* __restrict__ dones,
+                                                uint32_t seed32, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    if (dones[i] < 0.5f) return;
+    float s[4];
+    cartpole::reset(s, (uint32_t)((uint64_t)i * 2654435761ull + seed32));
+    reinterpret_cast<float4*>(states)[i] = make_float4(s[0], s[1], s[2], s[3]);
+    dones[i] = 0.0f;
+}
+
+// ------------------------------------------------------------- LunarLander
+__global__ void __launch_bounds__(ENV_TPB)
+lunar_step_rows_kernel(float* __restrict__ states, const float* __restrict__ actions,
+                       float* __restrict__ rewards, float* __restrict__ dones,
+                       float* __restrict__ obs, int n) {
+    int env = blockIdx.x * blockDim.x + threadIdx.x;
+    if (env >= n) return;
+    float* s = states + (size_t)env * lunar::STATE_SIZE;
+    lunar::Env e;
+    lunar::load_row(s, e);
+    int action = (int)actions[env];
+    lunar::apply_engines(e, env, action);
+    lunar::RowEdges edges{s};
+    phys::Contacts<lunar::MAX_CONTACTS> c;
+    lunar::physics_step(e, edges, c);
+    float o[lunar::OBS_DIM];
+    bool obs_written;
+    float reward, done;
+    lunar::finalize(e, edges, c, action, o, obs_written, reward, done);
+    lunar::store_row(s, e);
+    if (obs_written) {
+#pragma unroll
+        for (int d = 0; d < lunar::OBS_DIM; ++d) s[d] = o[d];
+    } else {
+#pragma unroll
+        for (int d = 0; d < lunar::OBS_DIM; ++d) o[d] = s[d];
+    }
+    float4* ob = reinterpret_cast<float4*>(obs + (size_t)env * lunar::OBS_DIM);
+    ob[0] = make_float4(o[0], o[1], o[2], o[3]);
+    ob[1] = make_float4(o[4], o[5], o[6], o[7]);
+    rewards[env] = reward;
+    dones[env] = done;
+}
+
+__global__ void lunar_reset_rows_kernel(float* __restrict__ states, const float* __restrict__ dones,
+                                        float seed_f32, int n) {
+    int env = blockIdx.x * blockDim.x + threadIdx.x;
+    if (env >= n) return;
+    if (dones != nullptr && !(dones[env] > 0.5f)) return;  // dones are not cleared (:1643-1701)
+    lunar::reset_row(states + (size_t)env * lunar::STATE_SIZE, lunar::combined_seed(seed_f32, env));
+}
+
+}  // namespace mrl
+
+using namespace mrl;
+
+extern "C" int mrl_env_info(int env_kind, int* state_size, int* obs_dim, int* num_actions,
+                            int* action_dim) {
+    int ss, od, na, ad;
+    switch (env_kind) {
+        case MRL_ENV_CARTPOLE: ss = 4; od = 4; na = 2; ad = 0; break;
+        case MRL_ENV_LUNAR_LANDER: ss = lunar::STATE_SIZE; od = 8; na = 4; ad = 0; break;
+        default:
+            set_error("mrl_env_info: env kind %d is not built", env_kind);
+            return MRL_ERR_UNSUPPORTED;
+    }
+    if (state_size) *state_size = ss;
+    if (obs_dim) *obs_dim = od;
+    if (num_actions) *num_actions = na;
+    if (action_dim) *action_dim = ad;
+    return MRL_OK;
+}
+
+extern "C" int mrl_env_reset(int env_kind, int batch, float* states, uint64_t rng_seed, void* stream) {
+    MRL_CHECK_ARG(batch > 0 && states != nullptr);
+    cudaStream_t st = as_stream(stream);
+    switch (env_kind) {
+        case MRL_ENV_CARTPOLE:
+            MRL_LAUNCH(cartpole_reset_kernel, ceil_div(batch, 256), 256, 0, st, states, batch);
+            return MRL_OK;
+        case MRL_ENV_LUNAR_LANDER:
+            MRL_LAUNCH(lunar_reset_rows_kernel, ceil_div(batch, ENV_TPB), ENV_TPB, 0, st, states,
+                       (const float*)nullptr, (float)rng_seed, batch);
+            return MRL_OK;
+        default:
+            set_error("mrl_env_reset: env kind %d is not built", env_kind);
+            return MRL_ERR_UNSUPPORTED;
+    }
+}
+
+extern "C" int mrl_env_step(int env_kind, int batch, float* states, const float* actions,
+                            float* rewards, float* dones, float* obs, uint64_t rng_seed, void* stream) {
+    MRL_CHECK_ARG(batch > 0 && states && actions && rewards && dones && obs);
+    (void)rng_seed;  // neither CartPole nor LunarLander consumes the per-step seed
+    cudaStream_t st = as_stream(stream);
+    switch (env_kind) {
+        case MRL_ENV_CARTPOLE:
+            MRL_LAUNCH(cartpole_step_kernel, ceil_div(batch, 256), 256, 0, st, states, actions, rewards,
+                       dones, obs, batch);
+            return MRL_OK;
+        case MRL_ENV_LUNAR_LANDER:
+            MRL_LAUNCH(lunar_step_rows_kernel, ceil_div(batch, ENV_TPB), ENV_TPB, 0, st, states, actions,
+                       rewards, dones, obs, batch);
+            return MRL_OK;
+        default:
+            set_error("mrl_env_step: env kind %d is not built", env_kind);
+            return MRL_ERR_UNSUPPORTED;
+    }
+}
+
+extern "C" int mrl_env_selective_reset(int env_kind, int batch, float* states, float* dones,
+                                       uint64_t rng_seed, void* stream) {
+    MRL_CHECK_ARG(batch > 0 && states && dones);
+    cudaStream_t st = as_stream(stream);
+    switch (env_kind) {
+        case MRL_ENV_CARTPOLE:
+            MRL_LAUNCH(cartpole_selective_reset_kernel, ceil_div(batch, 256), 256, 0, st, states, dones,
+                       (uint32_t)rng_seed, batch);
+            return MRL_OK;
+        case MRL_ENV_LUNAR_LANDER:
+            MRL_LAUNCH(lunar_reset_rows_kernel, ceil_div(batch, ENV_TPB), ENV_TPB, 0, st, states,
+                       (const float*)dones, (float)rng_seed, batch);
+            return MRL_OK;
+        default:
+            set_error("mrl_env_selective_reset: env kind %d is not built", env_kind);
+            return MRL_ERR_UNSUPPORTED;
+    }
+}

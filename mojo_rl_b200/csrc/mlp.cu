@@ -1,0 +1,384 @@
+// fp32 actor/critic MLP: Model.forward_gpu_ws / backward_gpu_ws of
+// seq(Hidden, Hidden, Head) (deep_rl/model/sequential.mojo:537-865,
+// linear.mojo, linear_relu.mojo, linear_tanh.mojo, stochastic_actor.mojo).
+//
+// One register-tiled SIMT GEMM serves every layer and direction.  Each output
+// element is one chain of fused multiply-adds in ascending k that starts from
+// the bias - the summation order of the reference's 16x16 tiled kernels
+// (linear.mojo:167-225) - so forward results are bit-identical to the CPU
+// checker.  Batch reductions (dW, db) are split over CTAs and summed in a fixed
+// order (deterministic, but not the reference's serial order).
+#include "common.cuh"
+
+namespace mrl {
+
+constexpr int BM = 64, BN = 64, BK = 16, GEMM_THREADS = 256;
+
+// C[m, n] = epi( init(m, n) + sum_k A(m, k) * B(k, n) ), k in [split*k_chunk, ...).
+// ALoad / BLoad are element functors; *_K_CONTIG says which index is contiguous
+// in memory so that tile loads coalesce.
+template <class ALoad, class BLoad, class Epi>
+__global__ void __launch_bounds__(GEMM_THREADS)
+gemm_kernel(int M, int N, int K, int k_chunk, ALoad aload, BLoad bload, Epi epi) {
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Bs[BK][BN + 4];
+    const int tid = threadIdx.x;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int split = blockIdx.z;
+    const int k_begin = split * k_chunk;
+    const int k_end = min(K, k_begin + k_chunk);
+    const int tm = (tid / 16) * 4, tn = (tid % 16) * 4;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = epi.init(m0 + tm + i, n0 + tn + j, M, N);
+
+    for (int kt = k_begin; kt < k_end; kt += BK) {
+        // A tile: BM x BK = 1024 elements, 4 per thread
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            int e = tid + r * GEMM_THREADS;
+            int mm, kk;
+            if (ALoad::K_CONTIG) { kk = e % BK; mm = e / BK; } else { mm = e % BM; kk = e / BM; }
+            int gm = m0 + mm, gk = kt + kk;
+            As[kk][mm] = (gm < M && gk < k_end) ? aload(gm, gk) : 0.0f;
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            int e = tid + r * GEMM_THREADS;
+            int nn, kk;
+            if (BLoad::K_CONTIG) { kk = e % BK; nn = e / BK; } else { nn = e % BN; kk = e / BN; }
+            int gn = n0 + nn, gk = kt + kk;
+            Bs[kk][nn] = (gn < N && gk < k_end) ? bload(gk, gn) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float4 a4 = *reinterpret_cast<const float4*>(&As[kk][tm]);
+            float4 b4 = *reinterpret_cast<const float4*>(&Bs[kk][tn]);
+            float a[4] = {a4.x, a4.y, a4.z, a4.w};
+            float b[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int gm = m0 + tm + i, gn = n0 + tn + j;
+            if (gm < M && gn < N) epi.store(gm, gn, acc[i][j], split);
+        }
+}
+
+// ---- element functors -----------------------------------------------------
+struct RowMajor {  // X[m, k], k contiguous (also W^T: W[n? ...] see users)
+    static constexpr bool K_CONTIG = true;
+    const float* p; int ld;
+    __device__ __forceinline__ float operator()(int m, int k) const { return p[(size_t)m * ld + k]; }
+};
+struct WeightKN {  // W[k, n], n contiguous
+    static constexpr bool K_CONTIG = false;
+    const float* p; int ld;
+    __device__ __forceinline__ float operator()(int k, int n) const { return p[(size_t)k * ld + n]; }
+};
+struct WeightT {  // B(k, n) = W[n, k] (for dX = g . W^T, W is [IN=n, OUT=k]), k contiguous
+    static constexpr bool K_CONTIG = true;
+    const float* p; int ld;
+    __device__ __forceinline__ float operator()(int k, int n) const { return p[(size_t)n * ld + k]; }
+};
+struct ColMajorA {  // A(m, k) = X[k, m] (for dW = X^T . g), m contiguous
+    static constexpr bool K_CONTIG = false;
+    const float* p; int ld;
+    __device__ __forceinline__ float operator()(int m, int k) const { return p[(size_t)k * ld + m]; }
+};
+// Upstream gradient with the activation derivative folded in:
+// mode 0 none, 1 ReLU (cache holds the pre-activation, mask pre > 0;
+// linear_relu.mojo:374,427), 2 tanh (cache holds y, factor 1 - y^2;
+// linear_tanh.mojo:377,431).
+template <bool AS_A>
+struct MaskedGrad {
+    static constexpr bool K_CONTIG = AS_A;   // as A(m=row, k=col): col contiguous; as B(k=row, n=col): n contiguous
+    const float* g; int ldg; const float* cache; int ldc; int cache_off; int mode;
+    __device__ __forceinline__ float at(int row, int col) const {
+        float v = g[(size_t)row * ldg + col];
+        if (mode == 1) {
+            float pre = cache[(size_t)row * ldc + cache_off + col];
+            v = pre > 0.0f ? v : 0.0f;
+        } else if (mode == 2) {
+            float y = cache[(size_t)row * ldc + cache_off + col];
+            v = v * (1.0f - y * y);
+        }
+        return v;
+    }
+    __device__ __forceinline__ float operator()(int a, int b) const { return at(a, b); }
+};
+
+struct ForwardEpi {
+    const float* bias; float* y; int ldy; float* cache; int ldc; int in_dim; int act;  // act: 0 relu, 1 tanh, -1 none
+    __device__ __forceinline__ float init(int, int n, int, int N) const { return n < N ? bias[n] : 0.0f; }
+    __device__ __forceinline__ void store(int m, int n, float acc, int) const {
+        float out = acc;
+        if (act == 0) {
+            if (cache) cache[(size_t)m * ldc + in_dim + n] = acc;
+            out = acc > 0.0f ? acc : 0.0f;
+        } else if (act == 1) {
+            out = mrl_tanhf(acc);
+            if (cache) cache[(size_t)m * ldc + in_dim + n] = out;
+        }
+        y[(size_t)m * ldy + n] = out;
+    }
+};
+struct PlainEpi {
+    float* c; int ldc;
+    __device__ __forceinline__ float init(int, int, int, int) const { return 0.0f; }
+    __device__ __forceinline__ void store(int m, int n, float acc, int) const { c[(size_t)m * ldc + n] = acc; }
+};
+struct SplitEpi {  // partial[split][m][n]
+    float* partial; int M, N;
+    __device__ __forceinline__ float init(int, int, int, int) const { return 0.0f; }
+    __device__ __forceinline__ void store(int m, int n, float acc, int split) const {
+        partial[((size_t)split * M + m) * N + n] = acc;
+    }
+};
+
+// out[i] = sum_s partial[s][i], s ascending.
+__global__ void reduce_splits_kernel(const float* __restrict__ partial, float* __restrict__ out, int n,
+                                     int splits) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float acc = 0.0f;
+    for (int s = 0; s < splits; ++s) acc += partial[(size_t)s * n + i];
+    out[i] = acc;
+}
+
+// Copies the layer input into its cache block (cache row = [input | ...]).
+__global__ void copy_rows_kernel(const float* __restrict__ src, int lds, float* __restrict__ dst, int ldd,
+                                 int rows, int cols) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)rows * cols) return;
+    int r = (int)(i / cols), c = (int)(i % cols);
+    dst[(size_t)r * ldd + c] = src[(size_t)r * lds + c];
+}
+
+// Column sums of a masked gradient: partial[chunk][col], then reduce.
+template <class G>
+__global__ void colsum_kernel(G g, int rows, int cols, int rows_per_chunk, float* __restrict__ partial) {
+    int col = blockIdx.x * blockDim.x + threadIdx.x;
+    int chunk = blockIdx.y;
+    if (col >= cols) return;
+    int r0 = chunk * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
+    float acc = 0.0f;
+    for (int r = r0; r < r1; ++r) acc += g.at(r, col);
+    partial[(size_t)chunk * cols + col] = acc;
+}
+
+// stochastic_actor.mojo:386-575: out[:, A + j] = clamp(log_std[j], -5, 2).
+__global__ void fill_log_std_kernel(const float* __restrict__ log_std, float* __restrict__ out, int batch,
+                                    int A) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= batch * A) return;
+    int r = i / A, j = i % A;
+    float ls = log_std[j];
+    if (ls < -5.0f) ls = -5.0f;
+    else if (ls > 2.0f) ls = 2.0f;
+    out[(size_t)r * 2 * A + A + j] = ls;
+}
+
+static int pick_splits(int rows) {
+    int s = rows / 2048;
+    if (s < 1) s = 1;
+    if (s > 64) s = 64;
+    return s;
+}
+
+struct NetDims {
+    int I, H, O, act, head, out_cols;
+    const float *W0, *b0, *W1, *b1, *W2, *b2, *log_std;
+    size_t oW0, ob0, oW1, ob1, oW2, ob2, ols;
+};
+static NetDims dims_of(const mrl_net_spec* n, const float* params) {
+    NetDims d;
+    d.I = n->in_dim; d.H = n->hidden_dim; d.O = n->out_dim; d.act = n->activation; d.head = n->head;
+    d.out_cols = n->head == MRL_HEAD_STOCHASTIC_ACTOR ? 2 * d.O : d.O;
+    d.oW0 = 0; d.ob0 = (size_t)d.I * d.H; d.oW1 = d.ob0 + d.H; d.ob1 = d.oW1 + (size_t)d.H * d.H;
+    d.oW2 = d.ob1 + d.H; d.ob2 = d.oW2 + (size_t)d.H * d.O; d.ols = d.ob2 + d.O;
+    d.W0 = params + d.oW0; d.b0 = params + d.ob0; d.W1 = params + d.oW1; d.b1 = params + d.ob1;
+    d.W2 = params + d.oW2; d.b2 = params + d.ob2; d.log_std = params + d.ols;
+    return d;
+}
+
+static bool spec_ok(const mrl_net_spec* n) {
+    return n && n->in_dim > 0 && n->hidden_dim > 0 && n->out_dim > 0 &&
+           (n->activation == MRL_ACT_RELU || n->activation == MRL_ACT_TANH) &&
+           (n->head == MRL_HEAD_LINEAR || n->head == MRL_HEAD_STOCHASTIC_ACTOR);
+}
+
+int mlp_forward_impl(const mrl_net_spec* net, int batch, const float* in, const float* params, float* out,
+                     float* cache, float* workspace, cudaStream_t st) {
+    NetDims d = dims_of(net, params);
+    float* h0 = workspace;
+    float* h1 = workspace + (size_t)batch * d.H;
+    float* c0 = cache;
+    float* c1 = cache ? cache + (size_t)batch * (d.I + d.H) : nullptr;
+    float* c2 = cache ? c1 + (size_t)batch * (d.H + d.H) : nullptr;
+    dim3 grid_h(ceil_div(d.H, BN), ceil_div(batch, BM), 1);
+    if (cache) {
+        MRL_LAUNCH(copy_rows_kernel, ceil_div((int64_t)batch * d.I, 256), 256, 0, st, in, d.I, c0, d.I + d.H,
+                   batch, d.I);
+    }
+    MRL_LAUNCH((gemm_kernel<RowMajor, WeightKN, ForwardEpi>), grid_h, GEMM_THREADS, 0, st, batch, d.H, d.I,
+               d.I, RowMajor{in, d.I}, WeightKN{d.W0, d.H},
+               ForwardEpi{d.b0, h0, d.H, c0, d.I + d.H, d.I, d.act});
+    if (cache) {
+        MRL_LAUNCH(copy_rows_kernel, ceil_div((int64_t)batch * d.H, 256), 256, 0, st, h0, d.H, c1, d.H + d.H,
+                   batch, d.H);
+    }
+    MRL_LAUNCH((gemm_kernel<RowMajor, WeightKN, ForwardEpi>), grid_h, GEMM_THREADS, 0, st, batch, d.H, d.H,
+               d.H, RowMajor{h0, d.H}, WeightKN{d.W1, d.H},
+               ForwardEpi{d.b1, h1, d.H, c1, d.H + d.H, d.H, d.act});
+    if (cache) {
+        MRL_LAUNCH(copy_rows_kernel, ceil_div((int64_t)batch * d.H, 256), 256, 0, st, h1, d.H, c2, d.H, batch,
+                   d.H);
+    }
+    dim3 grid_o(ceil_div(d.O, BN), ceil_div(batch, BM), 1);
+    MRL_LAUNCH((gemm_kernel<RowMajor, WeightKN, ForwardEpi>), grid_o, GEMM_THREADS, 0, st, batch, d.O, d.H,
+               d.H, RowMajor{h1, d.H}, WeightKN{d.W2, d.O},
+               ForwardEpi{d.b2, out, d.out_cols, nullptr, 0, 0, -1});
+    if (d.head == MRL_HEAD_STOCHASTIC_ACTOR) {
+        MRL_LAUNCH(fill_log_std_kernel, ceil_div((int64_t)batch * d.O, 256), 256, 0, st, d.log_std, out, batch,
+                   d.O);
+    }
+    return MRL_OK;
+}
+
+// One layer of the backward pass.  g = upstream gradient with the layer's own
+// activation derivative folded in (mode), [batch, out] with leading dim ldg.
+template <int DUMMY = 0>
+static int layer_backward(int batch, int in, int out, const float* gout, int ldg, int mode,
+                          const float* cache, int ldc, const float* W, float* dx, float* dW, float* db,
+                          float* partial, cudaStream_t st) {
+    MaskedGrad<true> gA{gout, ldg, cache, ldc, in, mode};
+    MaskedGrad<false> gB{gout, ldg, cache, ldc, in, mode};
+    if (dx) {
+        dim3 grid(ceil_div(in, BN), ceil_div(batch, BM), 1);
+        MRL_LAUNCH((gemm_kernel<MaskedGrad<true>, WeightT, PlainEpi>), grid, GEMM_THREADS, 0, st, batch, in,
+                   out, out, gA, WeightT{W, out}, PlainEpi{dx, in});
+    }
+    int splits = pick_splits(batch);
+    int k_chunk = ceil_div(ceil_div(batch, splits), BK) * BK;
+    splits = ceil_div(batch, k_chunk);
+    dim3 gridw(ceil_div(out, BN), ceil_div(in, BM), splits);
+    MRL_LAUNCH((gemm_kernel<ColMajorA, MaskedGrad<false>, SplitEpi>), gridw, GEMM_THREADS, 0, st, in, out,
+               batch, k_chunk, ColMajorA{cache, ldc}, gB, SplitEpi{partial, in, out});
+    MRL_LAUNCH(reduce_splits_kernel, ceil_div((int64_t)in * out, 256), 256, 0, st, partial, dW, in * out,
+               splits);
+    dim3 gridb(ceil_div(out, 128), splits, 1);
+    MRL_LAUNCH((colsum_kernel<MaskedGrad<true>>), gridb, 128, 0, st, gA, batch, out, k_chunk, partial);
+    MRL_LAUNCH(reduce_splits_kernel, ceil_div(out, 256), 256, 0, st, partial, db, out, splits);
+    return MRL_OK;
+}
+
+int mlp_backward_impl(const mrl_net_spec* net, int batch, const float* grad_out, const float* params,
+                      const float* cache, float* grad_in, float* grads, float* workspace, cudaStream_t st) {
+    NetDims d = dims_of(net, params);
+    float* dh1 = workspace;
+    float* dh0 = workspace + (size_t)batch * d.H;
+    float* partial = workspace + (size_t)2 * batch * d.H;
+    const float* c0 = cache;
+    const float* c1 = c0 + (size_t)batch * (d.I + d.H);
+    const float* c2 = c1 + (size_t)batch * (d.H + d.H);
+    int mode = d.act == MRL_ACT_RELU ? 1 : 2;
+    int rc;
+    // head: Linear (cache = input h1).  For the Gaussian actor only the mean
+    // columns reach W/b/dx (stochastic_actor.mojo:727-966).
+    rc = layer_backward(batch, d.H, d.O, grad_out, d.out_cols, 0, c2, d.H, d.W2, dh1, grads + d.oW2,
+                        grads + d.ob2, partial, st);
+    if (rc) return rc;
+    if (d.head == MRL_HEAD_STOCHASTIC_ACTOR) {
+        int splits = pick_splits(batch);
+        int chunk = ceil_div(batch, splits);
+        splits = ceil_div(batch, chunk);
+        MaskedGrad<true> gls{grad_out + d.O, d.out_cols, nullptr, 0, 0, 0};
+        dim3 gridb(ceil_div(d.O, 128), splits, 1);
+        MRL_LAUNCH((colsum_kernel<MaskedGrad<true>>), gridb, 128, 0, st, gls, batch, d.O, chunk, partial);
+        MRL_LAUNCH(reduce_splits_kernel, 1, 256, 0, st, partial, grads + d.ols, d.O, splits);
+    }
+    rc = layer_backward(batch, d.H, d.H, dh1, d.H, mode, c1, d.H + d.H, d.W1, dh0, grads + d.oW1,
+                        grads + d.ob1, partial, st);
+    if (rc) return rc;
+    rc = layer_backward(batch, d.I, d.H, dh0, d.H, mode, c0, d.I + d.H, d.W0, grad_in, grads + d.oW0,
+                        grads + d.ob0, partial, st);
+    return rc;
+}
+
+int64_t mlp_workspace_floats(const mrl_net_spec* n, int batch) {
+    int64_t H = n->hidden_dim;
+    int64_t maxin = n->in_dim > n->hidden_dim ? n->in_dim : n->hidden_dim;
+    return 2 * (int64_t)batch * H + 64 * maxin * H + 1024;
+}
+
+__global__ void adam_kernel(float* __restrict__ params, const float* __restrict__ grads,
+                            float* __restrict__ state, int n, float lr, float beta1, float beta2, float eps,
+                            float bc1, float bc2) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float g = grads[i];
+    float2 mv = reinterpret_cast<float2*>(state)[i];
+    float m_new = beta1 * mv.x + (1.0f - beta1) * g;
+    float v_new = beta2 * mv.y + (1.0f - beta2) * g * g;
+    reinterpret_cast<float2*>(state)[i] = make_float2(m_new, v_new);
+    float m_hat = m_new / bc1;
+    float v_hat = v_new / bc2;
+    params[i] = params[i] - lr * m_hat / (sqrtf(v_hat) + eps);
+}
+
+}  // namespace mrl
+
+using namespace mrl;
+
+extern "C" int mrl_net_param_size(const mrl_net_spec* n) {
+    if (!spec_ok(n)) return MRL_ERR_INVALID_ARG;
+    int p = n->in_dim * n->hidden_dim + n->hidden_dim + n->hidden_dim * n->hidden_dim + n->hidden_dim +
+            n->hidden_dim * n->out_dim + n->out_dim;
+    if (n->head == MRL_HEAD_STOCHASTIC_ACTOR) p += n->out_dim;
+    return p;
+}
+extern "C" int mrl_net_cache_per_sample(const mrl_net_spec* n) {
+    if (!spec_ok(n)) return MRL_ERR_INVALID_ARG;
+    return n->in_dim + 4 * n->hidden_dim;
+}
+extern "C" int mrl_net_out_cols(const mrl_net_spec* n) {
+    if (!spec_ok(n)) return MRL_ERR_INVALID_ARG;
+    return n->head == MRL_HEAD_STOCHASTIC_ACTOR ? 2 * n->out_dim : n->out_dim;
+}
+extern "C" int64_t mrl_mlp_workspace_floats(const mrl_net_spec* n, int batch) {
+    if (!spec_ok(n) || batch <= 0) return MRL_ERR_INVALID_ARG;
+    return mlp_workspace_floats(n, batch);
+}
+
+extern "C" int mrl_mlp_forward(const mrl_net_spec* net, int batch, const float* in, const float* params,
+                               float* out, float* cache, float* workspace, void* stream) {
+    MRL_CHECK_ARG(spec_ok(net) && batch > 0 && in && params && out && workspace);
+    return mlp_forward_impl(net, batch, in, params, out, cache, workspace, as_stream(stream));
+}
+
+extern "C" int mrl_mlp_backward(const mrl_net_spec* net, int batch, const float* grad_out,
+                                const float* params, const float* cache, float* grad_in, float* grads,
+                                float* workspace, void* stream) {
+    MRL_CHECK_ARG(spec_ok(net) && batch > 0 && grad_out && params && cache && grads && workspace);
+    return mlp_backward_impl(net, batch, grad_out, params, cache, grad_in, grads, workspace,
+                             as_stream(stream));
+}
+
+extern "C" int mrl_adam_step(int n, float* params, const float* grads, float* state_mv, float lr,
+                             float beta1, float beta2, float eps, float bc1, float bc2, void* stream) {
+    MRL_CHECK_ARG(n > 0 && params && grads && state_mv);
+    MRL_LAUNCH(adam_kernel, ceil_div(n, 256), 256, 0, as_stream(stream), params, grads, state_mv, n, lr,
+               beta1, beta2, eps, bc1, bc2);
+    return MRL_OK;
+}

@@ -1,0 +1,244 @@
+// PPO kernels of DeepPPOAgent.train_gpu, one per reference kernel, plus the
+// device versions of the phases the reference runs on the host (GAE,
+// advantage statistics).  Compile with -fmad=false.
+#include "ppo_kernels.cuh"
+
+namespace mrl {
+
+// _sample_actions_kernel, deep_agents/ppo/ppo.mojo:4064-4123.  greedy != 0
+// replaces the draw by select_action(training=False) (ppo.mojo:1019-1022).
+__global__ void sample_actions_kernel(const float* __restrict__ logits, float* __restrict__ actions,
+                                      float* __restrict__ log_probs, uint32_t seed, int n, int A,
+                                      int greedy) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float a_out, lp;
+    sample_one(logits + (size_t)i * A, A, seed, i, greedy, a_out, lp);
+    actions[i] = a_out;
+    if (log_probs) log_probs[i] = lp;
+}
+
+// GAE over a time-major rollout, one thread per environment walking t
+// backwards (ppo.mojo:2316-2353).  Loads and stores are coalesced across
+// environments.
+__global__ void gae_kernel(const float* __restrict__ rewards, const float* __restrict__ values,
+                           const float* __restrict__ dones, const float* __restrict__ bootstrap,
+                           float* __restrict__ advantages, float* __restrict__ returns, int T, int N,
+                           float gamma, float gae_decay) {
+    int env = blockIdx.x * blockDim.x + threadIdx.x;
+    if (env >= N) return;
+    float g = 0.0f;
+    float next_value = bootstrap[env];
+    for (int t = T - 1; t >= 0; --t) {
+        size_t idx = (size_t)t * N + env;
+        float reward = rewards[idx], value = values[idx], done = dones[idx];
+        float next_val = next_value;
+        if (done > 0.5f) { next_val = 0.0f; g = 0.0f; }
+        float delta = reward + gamma * next_val - value;
+        g = delta + gae_decay * g;
+        advantages[idx] = g;
+        returns[idx] = g + value;
+        next_value = value;
+    }
+}
+
+// Advantage statistics in double precision: stats[0] = sum, stats[1] = sum of
+// squares about the mean (two passes, as ppo.mojo:2356-2371 does).
+__global__ void sum_kernel(const float* __restrict__ x, int64_t n, double* __restrict__ out) {
+    __shared__ double sm[32];
+    double acc = 0.0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        acc += (double)x[i];
+    acc = block_sum(acc, sm);
+    if (threadIdx.x == 0) atomicAdd(out, acc);
+}
+__global__ void sqdev_kernel(const float* __restrict__ x, int64_t n, const double* __restrict__ sum,
+                             double* __restrict__ out) {
+    __shared__ double sm[32];
+    double mean = sum[0] / (double)n;
+    double acc = 0.0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        double d = (double)x[i] - mean;
+        acc += d * d;
+    }
+    acc = block_sum(acc, sm);
+    if (threadIdx.x == 0) atomicAdd(out, acc);
+}
+// x = (x - mean) / (sqrt(var + 1e-8) + 1e-8) with f32 mean / var (ppo.mojo:2363-2371)
+__global__ void normalize_apply_kernel(float* __restrict__ x, int64_t n, const double* __restrict__ stats) {
+    float mean = (float)(stats[0] / (double)n);
+    float variance = (float)(stats[1] / (double)n);
+    float stdv = sqrtf(variance + 1e-8f);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        x[i] = (x[i] - mean) / (stdv + 1e-8f);
+}
+
+// ppo_gather_minibatch_kernel, ppo.mojo:135-191
+__global__ void gather_minibatch_kernel(int batch, int obs_dim, const int32_t* __restrict__ indices,
+                                        const float* __restrict__ r_obs, const float* __restrict__ r_actions,
+                                        const float* __restrict__ adv, const float* __restrict__ ret,
+                                        const float* __restrict__ r_lp, const float* __restrict__ r_val,
+                                        float* __restrict__ mb_obs, float* __restrict__ mb_actions,
+                                        float* __restrict__ mb_adv, float* __restrict__ mb_ret,
+                                        float* __restrict__ mb_lp, float* __restrict__ mb_val) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= batch) return;
+    size_t src = (size_t)indices[i];
+    for (int d = 0; d < obs_dim; ++d) mb_obs[(size_t)i * obs_dim + d] = r_obs[src * obs_dim + d];
+    mb_actions[i] = r_actions[src];
+    mb_adv[i] = adv[src];
+    mb_ret[i] = ret[src];
+    mb_lp[i] = r_lp[src];
+    mb_val[i] = r_val[src];
+}
+
+// ppo_actor_grad_with_kl_kernel, ppo.mojo:285-378
+__global__ void actor_grad_kernel(int batch, int A, const float* __restrict__ logits,
+                                  const float* __restrict__ old_log_probs,
+                                  const float* __restrict__ advantages, const float* __restrict__ actions,
+                                  float clip_epsilon, float entropy_coef, float batch_div,
+                                  float* __restrict__ grad_logits, float* __restrict__ kl) {
+    int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= batch) return;
+    float g[MAX_ACTIONS];
+    float klv;
+    actor_grad_one(logits + (size_t)b * A, A, old_log_probs[b], advantages[b], (int)actions[b], clip_epsilon,
+                   entropy_coef, batch_div, g, klv);
+    for (int a = 0; a < A; ++a) grad_logits[(size_t)b * A + a] = g[a];
+    kl[b] = klv;
+}
+
+// ppo_critic_grad_kernel / ppo_critic_grad_clipped_kernel, ppo.mojo:538-633
+__global__ void critic_grad_kernel(int batch, const float* __restrict__ values,
+                                   const float* __restrict__ old_values, const float* __restrict__ returns,
+                                   float value_loss_coef, float clip_epsilon, int clip_value, float batch_div,
+                                   float* __restrict__ grad_values) {
+    int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= batch) return;
+    grad_values[b] = critic_grad_one(values[b], old_values ? old_values[b] : 0.0f, returns[b], value_loss_coef,
+                                     clip_epsilon, clip_value, batch_div);
+}
+
+// gradient_norm_kernel, ppo.mojo:382-430 (sum of squares; accumulated in f64)
+__global__ void sumsq_kernel(const float* __restrict__ g, int n, double* __restrict__ out) {
+    __shared__ double sm[32];
+    double acc = 0.0;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+        acc += (double)g[i] * (double)g[i];
+    acc = block_sum(acc, sm);
+    if (threadIdx.x == 0) atomicAdd(out, acc);
+}
+// gradient_reduce_and_compute_scale_kernel + gradient_apply_scale_kernel,
+// ppo.mojo:454-534.  report (nullable): [0] squared norm, [1] scale.
+__global__ void clip_apply_kernel(float* __restrict__ g, int n, const double* __restrict__ sumsq,
+                                  float max_norm, float* __restrict__ report) {
+    float total = (float)sumsq[0];
+    float norm = sqrtf(total);
+    float scale = 1.0f;
+    if (norm > max_norm) scale = max_norm / (norm + 1e-8f);
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i == 0 && report) { report[0] = total; report[1] = scale; }
+    if (i < n) g[i] = g[i] * scale;
+}
+
+}  // namespace mrl
+
+using namespace mrl;
+
+extern "C" int mrl_sample_actions(int n_envs, int num_actions, const float* logits, float* actions,
+                                  float* log_probs, uint32_t seed, void* stream) {
+    MRL_CHECK_ARG(n_envs > 0 && num_actions > 0 && num_actions <= MAX_ACTIONS && logits && actions && log_probs);
+    MRL_LAUNCH(sample_actions_kernel, ceil_div(n_envs, 256), 256, 0, as_stream(stream), logits, actions,
+               log_probs, seed, n_envs, num_actions, 0);
+    return MRL_OK;
+}
+
+extern "C" int mrl_argmax_actions(int n_envs, int num_actions, const float* logits, float* actions,
+                                  void* stream) {
+    MRL_CHECK_ARG(n_envs > 0 && num_actions > 0 && num_actions <= MAX_ACTIONS && logits && actions);
+    MRL_LAUNCH(sample_actions_kernel, ceil_div(n_envs, 256), 256, 0, as_stream(stream), logits, actions,
+               (float*)nullptr, 0u, n_envs, num_actions, 1);
+    return MRL_OK;
+}
+
+extern "C" int mrl_gae(int rollout_len, int n_envs, const float* rewards, const float* values,
+                       const float* dones, const float* bootstrap_values, double gamma, double gae_lambda,
+                       float* advantages, float* returns, void* stream) {
+    MRL_CHECK_ARG(rollout_len > 0 && n_envs > 0 && rewards && values && dones && bootstrap_values &&
+                  advantages && returns);
+    MRL_LAUNCH(gae_kernel, ceil_div(n_envs, 128), 128, 0, as_stream(stream), rewards, values, dones,
+               bootstrap_values, advantages, returns, rollout_len, n_envs, (float)gamma,
+               (float)(gamma * gae_lambda));
+    return MRL_OK;
+}
+
+namespace mrl {
+int normalize_advantages_impl(int64_t n, float* adv, double* stats2, cudaStream_t st) {
+    MRL_CUDA_OK(cudaMemsetAsync(stats2, 0, 2 * sizeof(double), st));
+    int blocks = (int)((n + 1023) / 1024);
+    if (blocks > 592) blocks = 592;
+    if (blocks < 1) blocks = 1;
+    MRL_LAUNCH(sum_kernel, blocks, 256, 0, st, adv, n, stats2);
+    MRL_LAUNCH(sqdev_kernel, blocks, 256, 0, st, adv, n, stats2, stats2 + 1);
+    MRL_LAUNCH(normalize_apply_kernel, blocks, 256, 0, st, adv, n, stats2);
+    return MRL_OK;
+}
+int grad_clip_impl(int n, float* grads, float max_norm, double* sumsq, float* report, cudaStream_t st) {
+    MRL_CUDA_OK(cudaMemsetAsync(sumsq, 0, sizeof(double), st));
+    int blocks = ceil_div(n, 1024);
+    if (blocks > 296) blocks = 296;
+    MRL_LAUNCH(sumsq_kernel, blocks, 256, 0, st, grads, n, sumsq);
+    MRL_LAUNCH(clip_apply_kernel, ceil_div(n, 256), 256, 0, st, grads, n, sumsq, max_norm, report);
+    return MRL_OK;
+}
+}  // namespace mrl
+
+extern "C" int mrl_normalize_advantages(int64_t n, float* advantages, float* scratch, void* stream) {
+    MRL_CHECK_ARG(n > 0 && advantages && scratch);
+    MRL_CHECK_ARG(((uintptr_t)scratch & 7) == 0);
+    return normalize_advantages_impl(n, advantages, reinterpret_cast<double*>(scratch), as_stream(stream));
+}
+
+extern "C" int mrl_ppo_gather_minibatch(int batch, int obs_dim, const int32_t* indices,
+                                        const float* rollout_obs, const float* rollout_actions,
+                                        const float* advantages, const float* returns,
+                                        const float* rollout_log_probs, const float* rollout_values,
+                                        float* mb_obs, float* mb_actions, float* mb_advantages,
+                                        float* mb_returns, float* mb_old_log_probs, float* mb_old_values,
+                                        void* stream) {
+    MRL_CHECK_ARG(batch > 0 && obs_dim > 0 && indices && rollout_obs && rollout_actions && advantages &&
+                  returns && rollout_log_probs && rollout_values && mb_obs && mb_actions && mb_advantages &&
+                  mb_returns && mb_old_log_probs && mb_old_values);
+    MRL_LAUNCH(gather_minibatch_kernel, ceil_div(batch, 256), 256, 0, as_stream(stream), batch, obs_dim,
+               indices, rollout_obs, rollout_actions, advantages, returns, rollout_log_probs, rollout_values,
+               mb_obs, mb_actions, mb_advantages, mb_returns, mb_old_log_probs, mb_old_values);
+    return MRL_OK;
+}
+
+extern "C" int mrl_ppo_actor_grad(int batch, int num_actions, const float* logits,
+                                  const float* old_log_probs, const float* advantages, const float* actions,
+                                  float clip_epsilon, float entropy_coef, float* grad_logits,
+                                  float* kl_divergences, void* stream) {
+    MRL_CHECK_ARG(batch > 0 && num_actions > 0 && num_actions <= MAX_ACTIONS && logits && old_log_probs &&
+                  advantages && actions && grad_logits && kl_divergences);
+    MRL_LAUNCH(actor_grad_kernel, ceil_div(batch, 256), 256, 0, as_stream(stream), batch, num_actions, logits,
+               old_log_probs, advantages, actions, clip_epsilon, entropy_coef, (float)batch, grad_logits,
+               kl_divergences);
+    return MRL_OK;
+}
+
+extern "C" int mrl_ppo_critic_grad(int batch, const float* values, const float* old_values,
+                                   const float* returns, float value_loss_coef, float clip_epsilon,
+                                   int clip_value, float* grad_values, void* stream) {
+    MRL_CHECK_ARG(batch > 0 && values && returns && grad_values && (!clip_value || old_values));
+    MRL_LAUNCH(critic_grad_kernel, ceil_div(batch, 256), 256, 0, as_stream(stream), batch, values, old_values,
+               returns, value_loss_coef, clip_epsilon, clip_value, (float)batch, grad_values);
+    return MRL_OK;
+}
+
+extern "C" int mrl_grad_clip(int n, float* grads, float max_grad_norm, float* scratch, void* stream) {
+    MRL_CHECK_ARG(n > 0 && grads && scratch && ((uintptr_t)scratch & 7) == 0);
+    // scratch: [0..1] report (squared norm, scale), [2..3] one double accumulator
+    return grad_clip_impl(n, grads, max_grad_norm, reinterpret_cast<double*>(scratch + 2), scratch,
+                          as_stream(stream));
+}

@@ -1,0 +1,78 @@
+"""GPUDiscreteEnv implementors (reference: core/env_traits.mojo:230-310).
+
+Each class mirrors the static trait methods of the reference struct of the same
+name; buffers are torch CUDA float32 tensors standing in for DeviceBuffer, and
+`ctx` is a DeviceContext (a CUDA stream).
+"""
+import ctypes
+
+from . import _lib
+
+ENV_KINDS = {"cartpole": 0, "pendulum": 1, "lunar_lander": 2, "bipedal_walker": 3, "half_cheetah": 4,
+             "lunar_lander_continuous": 5}
+
+
+class DeviceContext:
+    """Stand-in for Mojo's gpu.host.DeviceContext: one in-order CUDA stream."""
+
+    def __init__(self, stream=None, device=0):
+        import torch
+        self.device = torch.device("cuda", device)
+        self.stream = stream if stream is not None else torch.cuda.current_stream(self.device)
+
+    @property
+    def handle(self):
+        return ctypes.c_void_p(self.stream.cuda_stream)
+
+    def synchronize(self):
+        self.stream.synchronize()
+
+    def enqueue_create_buffer(self, n, dtype=None):
+        import torch
+        with torch.cuda.stream(self.stream):
+            return torch.zeros(n, dtype=dtype or torch.float32, device=self.device)
+
+
+def _info(kind):
+    vals = [ctypes.c_int() for _ in range(4)]
+    _lib.check(_lib.lib().mrl_env_info(kind, *[ctypes.byref(v) for v in vals]))
+    return [v.value for v in vals]
+
+
+class _GPUDiscreteEnv:
+    KIND = None
+    STATE_SIZE = None
+    OBS_DIM = None
+    NUM_ACTIONS = None
+
+    @classmethod
+    def step_kernel_gpu(cls, ctx, states, actions, rewards, dones, obs, rng_seed=0):
+        """step_kernel_gpu[BATCH_SIZE, STATE_SIZE, OBS_DIM](ctx, states, actions, rewards, dones, obs, rng_seed)"""
+        batch = states.numel() // cls.STATE_SIZE
+        _lib.check(_lib.lib().mrl_env_step(cls.KIND, batch, _lib.ptr(states), _lib.ptr(actions), _lib.ptr(rewards),
+                                           _lib.ptr(dones), _lib.ptr(obs), rng_seed, ctx.handle))
+
+    @classmethod
+    def reset_kernel_gpu(cls, ctx, states, rng_seed=0):
+        """reset_kernel_gpu[BATCH_SIZE, STATE_SIZE](ctx, states, rng_seed)"""
+        batch = states.numel() // cls.STATE_SIZE
+        _lib.check(_lib.lib().mrl_env_reset(cls.KIND, batch, _lib.ptr(states), rng_seed, ctx.handle))
+
+    @classmethod
+    def selective_reset_kernel_gpu(cls, ctx, states, dones, rng_seed):
+        """selective_reset_kernel_gpu[BATCH_SIZE, STATE_SIZE](ctx, states, dones, rng_seed)"""
+        batch = states.numel() // cls.STATE_SIZE
+        _lib.check(_lib.lib().mrl_env_selective_reset(cls.KIND, batch, _lib.ptr(states), _lib.ptr(dones), rng_seed,
+                                                      ctx.handle))
+
+
+class CartPoleEnv(_GPUDiscreteEnv):
+    """envs/cartpole.mojo: STATE_SIZE 4, OBS_DIM 4, NUM_ACTIONS 2."""
+    KIND = ENV_KINDS["cartpole"]
+    STATE_SIZE, OBS_DIM, NUM_ACTIONS = 4, 4, 2
+
+
+class LunarLanderV2(_GPUDiscreteEnv):
+    """envs/lunar_lander/lunar_lander_v2.mojo: STATE_SIZE 192, OBS_DIM 8, NUM_ACTIONS 4."""
+    KIND = ENV_KINDS["lunar_lander"]
+    STATE_SIZE, OBS_DIM, NUM_ACTIONS = 192, 8, 4

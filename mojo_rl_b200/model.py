@@ -1,0 +1,163 @@
+"""Model / Optimizer / Network mirrors (reference: deep_rl/model/*.mojo,
+deep_rl/optimizer/adam.mojo, deep_rl/training/network.mojo).
+
+Layers are stateless descriptions, exactly as in the reference; parameters are
+one flat fp32 vector per network in the reference's order
+[W0 | b0 | W1 | b1 | W2 | b2 (| log_std)], W row-major [IN, OUT].
+"""
+import math
+
+import numpy as np
+
+from . import _lib
+
+ACT_RELU, ACT_TANH = 0, 1
+HEAD_LINEAR, HEAD_STOCHASTIC = 0, 1
+
+
+class _Layer:
+    def __init__(self, in_dim, out_dim):
+        self.IN_DIM, self.OUT_DIM = in_dim, out_dim
+        self.PARAM_SIZE = in_dim * out_dim + out_dim
+
+
+class Linear(_Layer):
+    """deep_rl/model/linear.mojo: y = x @ W + b; cache = input."""
+
+    def __init__(self, in_dim, out_dim):
+        super().__init__(in_dim, out_dim)
+        self.CACHE_SIZE = in_dim
+
+
+class LinearReLU(_Layer):
+    """deep_rl/model/linear_relu.mojo: cache = [input | pre-activation]."""
+    ACT = ACT_RELU
+
+    def __init__(self, in_dim, out_dim):
+        super().__init__(in_dim, out_dim)
+        self.CACHE_SIZE = in_dim + out_dim
+
+
+class LinearTanh(_Layer):
+    """deep_rl/model/linear_tanh.mojo: cache = [input | tanh output]."""
+    ACT = ACT_TANH
+
+    def __init__(self, in_dim, out_dim):
+        super().__init__(in_dim, out_dim)
+        self.CACHE_SIZE = in_dim + out_dim
+
+
+class StochasticActor(_Layer):
+    """deep_rl/model/stochastic_actor.mojo: [mean | log_std], state-independent log_std."""
+
+    def __init__(self, in_dim, action_dim):
+        super().__init__(in_dim, action_dim)
+        self.PARAM_SIZE += action_dim
+        self.CACHE_SIZE = in_dim
+        self.OUT_DIM = 2 * action_dim
+        self.ACTION_DIM = action_dim
+
+
+class Seq:
+    """seq(Hidden, Hidden, Head) = Seq2[Seq2[L0, L1], L2] (deep_rl/model/sequential.mojo)."""
+
+    def __init__(self, l0, l1, l2):
+        if not (isinstance(l0, (LinearReLU, LinearTanh)) and type(l0) is type(l1)):
+            raise ValueError("supported: seq(LinearReLU|LinearTanh, same, Linear|StochasticActor)")
+        if l0.OUT_DIM != l1.IN_DIM or l1.OUT_DIM != l2.IN_DIM or l0.OUT_DIM != l1.OUT_DIM:
+            raise ValueError("layer dimensions do not chain")
+        self.layers = (l0, l1, l2)
+        self.IN_DIM, self.OUT_DIM = l0.IN_DIM, l2.OUT_DIM
+        self.PARAM_SIZE = sum(l.PARAM_SIZE for l in self.layers)
+        self.CACHE_SIZE = sum(l.CACHE_SIZE for l in self.layers)
+        self.WORKSPACE_SIZE_PER_SAMPLE = 4 * l0.OUT_DIM
+        head = HEAD_STOCHASTIC if isinstance(l2, StochasticActor) else HEAD_LINEAR
+        out = l2.ACTION_DIM if head == HEAD_STOCHASTIC else l2.OUT_DIM
+        self.spec = _lib.NetSpec(l0.IN_DIM, l0.OUT_DIM, out, l0.ACT, head)
+
+    def workspace_floats(self, batch):
+        return int(_lib.lib().mrl_mlp_workspace_floats(self.spec, batch))
+
+    def forward_gpu_ws(self, ctx, batch, output_buf, input_buf, params_buf, cache_buf, workspace_buf):
+        """Model.forward_gpu_ws[BATCH](ctx, output, input, params, cache, workspace)"""
+        _lib.check(_lib.lib().mrl_mlp_forward(self.spec, batch, _lib.ptr(input_buf), _lib.ptr(params_buf),
+                                              _lib.ptr(output_buf), _lib.ptr(cache_buf), _lib.ptr(workspace_buf),
+                                              ctx.handle))
+
+    def forward_gpu_no_cache_ws(self, ctx, batch, output_buf, input_buf, params_buf, workspace_buf):
+        """Model.forward_gpu_no_cache_ws[BATCH](ctx, output, input, params, workspace)"""
+        self.forward_gpu_ws(ctx, batch, output_buf, input_buf, params_buf, None, workspace_buf)
+
+    def backward_gpu_ws(self, ctx, batch, grad_input_buf, grad_output_buf, params_buf, cache_buf, grads_buf,
+                        workspace_buf):
+        """Model.backward_gpu_ws[BATCH](ctx, grad_input, grad_output, params, cache, grads, workspace)"""
+        _lib.check(_lib.lib().mrl_mlp_backward(self.spec, batch, _lib.ptr(grad_output_buf), _lib.ptr(params_buf),
+                                               _lib.ptr(cache_buf), _lib.ptr(grad_input_buf), _lib.ptr(grads_buf),
+                                               _lib.ptr(workspace_buf), ctx.handle))
+
+
+def seq(l0, l1, l2):
+    return Seq(l0, l1, l2)
+
+
+class Adam:
+    """deep_rl/optimizer/adam.mojo: state is the interleaved [P, 2] (m, v) vector; t lives here."""
+    STATE_PER_PARAM = 2
+
+    def __init__(self, lr=0.001, beta1=0.9, beta2=0.999, eps=1e-8):
+        self.lr, self.beta1, self.beta2, self.eps, self.t = lr, beta1, beta2, eps, 0
+
+    def step_gpu(self, ctx, param_size, params_buf, grads_buf, state_buf):
+        """Adam.step_gpu[PARAM_SIZE](ctx, params, grads, state) (adam.mojo:162-247)"""
+        self.t += 1
+        bc1 = np.float32(1.0 - self.beta1 ** self.t)
+        bc2 = np.float32(1.0 - self.beta2 ** self.t)
+        _lib.check(_lib.lib().mrl_adam_step(param_size, _lib.ptr(params_buf), _lib.ptr(grads_buf), _lib.ptr(state_buf),
+                                            self.lr, self.beta1, self.beta2, self.eps, float(bc1), float(bc2),
+                                            ctx.handle))
+
+
+class Xavier:
+    """deep_rl/initializer/initializers.mojo:69-78: every parameter (biases too)
+    uniform in +-sqrt(2 / (fan_in + fan_out)) with the model's IN_DIM / OUT_DIM."""
+
+    def init(self, size, fan_in, fan_out, rng):
+        std = math.sqrt(2.0 / float(fan_in + fan_out))
+        return ((rng.random(size) * 2.0 - 1.0) * std).astype(np.float32)
+
+
+class Kaiming:
+    """initializers.mojo:97-104: uniform in +-sqrt(2 / fan_in)."""
+
+    def init(self, size, fan_in, fan_out, rng):
+        std = math.sqrt(2.0 / float(fan_in))
+        return ((rng.random(size) * 2.0 - 1.0) * std).astype(np.float32)
+
+
+class Network:
+    """deep_rl/training/network.mojo:59-131: owner of params / grads / optimizer state (host copies).
+
+    The reference draws from Mojo's global RNG; here a numpy Generator is passed in.
+    """
+
+    def __init__(self, model, optimizer, initializer, rng=None):
+        self.model, self.optimizer, self.initializer = model, optimizer, initializer
+        rng = rng if rng is not None else np.random.default_rng(0)
+        self.params = initializer.init(model.PARAM_SIZE, model.IN_DIM, model.OUT_DIM, rng)
+        self.grads = np.zeros(model.PARAM_SIZE, np.float32)
+        self.optimizer_state = np.zeros(model.PARAM_SIZE * optimizer.STATE_PER_PARAM, np.float32)
+
+    # network.mojo:698-772
+    def copy_params_to_device(self, ctx, params_buf):
+        import torch
+        params_buf.copy_(torch.from_numpy(self.params), non_blocking=False)
+
+    def copy_state_to_device(self, ctx, state_buf):
+        import torch
+        state_buf.copy_(torch.from_numpy(self.optimizer_state), non_blocking=False)
+
+    def copy_params_from_device(self, ctx, params_buf):
+        self.params = params_buf.detach().cpu().numpy().copy()
+
+    def copy_state_from_device(self, ctx, state_buf):
+        self.optimizer_state = state_buf.detach().cpu().numpy().copy()

@@ -1,0 +1,226 @@
+"""DeepPPOAgent mirror (reference: deep_agents/ppo/ppo.mojo:744-4055).
+
+`train_gpu` keeps the reference's three-phase loop and its host-side decisions
+(learning-rate / entropy annealing, episode logging, stopping rule) and hands
+each phase to one C-ABI call; no tensor maths happens in Python.
+"""
+import ctypes
+
+import numpy as np
+
+from . import _lib
+from .model import Adam, Linear, LinearReLU, Network, Xavier, seq
+
+
+class EpisodeMetrics:
+    def __init__(self, episode, total_reward, steps, epsilon=0.0):
+        self.episode, self.total_reward, self.steps, self.epsilon = episode, total_reward, steps, epsilon
+
+
+class TrainingMetrics:
+    """core/metrics.mojo:44-262"""
+
+    def __init__(self, algorithm_name="", environment_name=""):
+        self.episodes = []
+        self.algorithm_name, self.environment_name = algorithm_name, environment_name
+
+    def log_episode(self, episode, total_reward, steps, epsilon=0.0):
+        self.episodes.append(EpisodeMetrics(episode, float(total_reward), int(steps), epsilon))
+
+    def num_episodes(self):
+        return len(self.episodes)
+
+    def get_rewards(self):
+        return [e.total_reward for e in self.episodes]
+
+    def mean_reward(self):
+        return float(np.mean(self.get_rewards())) if self.episodes else 0.0
+
+    def mean_reward_last_n(self, n):
+        if not self.episodes:
+            return 0.0
+        return float(np.mean(self.get_rewards()[-min(n, len(self.episodes)):]))
+
+    def to_csv(self, filepath):
+        rewards = self.get_rewards()
+        with open(filepath, "w") as f:
+            f.write("episode,reward,steps,epsilon,moving_avg_100\n")
+            for i, e in enumerate(self.episodes):
+                ma = float(np.mean(rewards[max(0, i - 99):i + 1]))
+                f.write(f"{e.episode},{e.total_reward},{e.steps},{e.epsilon},{ma}\n")
+
+
+class DeepPPOAgent:
+    """DeepPPOAgent[obs_dim, num_actions, hidden_dim, rollout_len, n_envs, gpu_minibatch_size]
+    with the constructor defaults of ppo.mojo:869-892."""
+
+    def __init__(self, obs_dim, num_actions, hidden_dim=64, rollout_len=128, n_envs=1024, gpu_minibatch_size=256,
+                 gamma=0.99, gae_lambda=0.95, clip_epsilon=0.2, actor_lr=0.0003, critic_lr=0.001,
+                 entropy_coef=0.01, value_loss_coef=0.5, num_epochs=4, minibatch_size=64,
+                 normalize_advantages=True, target_kl=0.015, max_grad_norm=0.5, anneal_lr=True,
+                 anneal_entropy=False, target_total_steps=0, clip_value=True, norm_adv_per_minibatch=True,
+                 checkpoint_every=0, checkpoint_path="", precision=0, seed=0):
+        self.OBS, self.ACTIONS, self.HIDDEN, self.ROLLOUT = obs_dim, num_actions, hidden_dim, rollout_len
+        self.n_envs, self.gpu_minibatch_size = n_envs, gpu_minibatch_size
+        self.gamma, self.gae_lambda, self.clip_epsilon = gamma, gae_lambda, clip_epsilon
+        self.actor_lr, self.critic_lr, self.entropy_coef = actor_lr, critic_lr, entropy_coef
+        self.value_loss_coef, self.num_epochs, self.minibatch_size = value_loss_coef, num_epochs, minibatch_size
+        self.normalize_advantages, self.target_kl, self.max_grad_norm = normalize_advantages, target_kl, max_grad_norm
+        self.anneal_lr, self.anneal_entropy, self.target_total_steps = anneal_lr, anneal_entropy, target_total_steps
+        self.clip_value, self.norm_adv_per_minibatch = clip_value, norm_adv_per_minibatch
+        self.checkpoint_every, self.checkpoint_path = checkpoint_every, checkpoint_path
+        self.precision = precision
+        self.train_step_count = 0
+        rng = np.random.default_rng(seed)
+        # ppo.mojo:807-830
+        self.actor = Network(seq(LinearReLU(obs_dim, hidden_dim), LinearReLU(hidden_dim, hidden_dim),
+                                 Linear(hidden_dim, num_actions)), Adam(lr=actor_lr), Xavier(), rng)
+        self.critic = Network(seq(LinearReLU(obs_dim, hidden_dim), LinearReLU(hidden_dim, hidden_dim),
+                                  Linear(hidden_dim, 1)), Adam(lr=critic_lr), Xavier(), rng)
+        self._ctx = None
+
+    # -- fused-path plumbing ------------------------------------------------
+    def make_config(self, env_kind, deterministic=False, world_size=1, rank=0):
+        cfg = _lib.Config()
+        _lib.lib().mrl_config_defaults(ctypes.byref(cfg))
+        cfg.env_kind = env_kind
+        cfg.n_envs, cfg.rollout_len, cfg.hidden_dim = self.n_envs, self.ROLLOUT, self.HIDDEN
+        cfg.minibatch_size, cfg.num_epochs, cfg.precision = self.gpu_minibatch_size, self.num_epochs, self.precision
+        cfg.normalize_advantages = int(self.normalize_advantages)
+        cfg.norm_adv_per_minibatch = int(self.norm_adv_per_minibatch)
+        cfg.clip_value = int(self.clip_value)
+        cfg.deterministic = int(deterministic)
+        cfg.world_size, cfg.rank = world_size, rank
+        cfg.gamma, cfg.gae_lambda, cfg.clip_epsilon = self.gamma, self.gae_lambda, self.clip_epsilon
+        cfg.value_loss_coef, cfg.target_kl, cfg.max_grad_norm = self.value_loss_coef, self.target_kl, self.max_grad_norm
+        cfg.adam_beta1, cfg.adam_beta2, cfg.adam_eps = (self.actor.optimizer.beta1, self.actor.optimizer.beta2,
+                                                        self.actor.optimizer.eps)
+        return cfg
+
+    def create_context(self, env_kind, deterministic=False, world_size=1, rank=0):
+        """mrl_create + upload of params / optimizer state (network.mojo:698-750)."""
+        L = _lib.lib()
+        cfg = self.make_config(env_kind, deterministic, world_size, rank)
+        h = ctypes.c_void_p()
+        _lib.check(L.mrl_create(ctypes.byref(h), ctypes.byref(cfg)))
+        for which, net in ((0, self.actor), (1, self.critic)):
+            if L.mrl_param_size(h, which) != net.model.PARAM_SIZE:
+                L.mrl_destroy(h)
+                raise _lib.MojoRLError("parameter size mismatch between host model and library")
+            _lib.check(L.mrl_set_params(h, which, _lib.ptr(net.params), _lib.ptr(net.optimizer_state)))
+        return h
+
+    def pull_params(self, h):
+        """copy_params_from_device / copy_state_from_device for both networks (ppo.mojo:2768-2775)."""
+        L = _lib.lib()
+        for which, net in ((0, self.actor), (1, self.critic)):
+            p = np.empty(net.model.PARAM_SIZE, np.float32)
+            s = np.empty(2 * net.model.PARAM_SIZE, np.float32)
+            _lib.check(L.mrl_get_params(h, which, _lib.ptr(p), _lib.ptr(s)))
+            net.params, net.optimizer_state = p, s
+
+    def train_gpu(self, EnvType, ctx=None, num_episodes=100, verbose=False, print_every=10, max_rollouts=None):
+        """train_gpu[EnvType](ctx, num_episodes, verbose, print_every) -> TrainingMetrics (ppo.mojo:1558-2840).
+
+        Episodes are drained from the device ring once per rollout instead of once
+        per step, so the episode count can overshoot num_episodes by up to one
+        rollout's worth; max_rollouts bounds the loop for benchmarking.
+        """
+        L = _lib.lib()
+        metrics = TrainingMetrics("Deep PPO (GPU)", "GPU Environment")
+        h = self.create_context(EnvType.KIND)
+        try:
+            _lib.check(L.mrl_ppo_reset(h, 0))
+            completed, rollouts = 0, 0
+            annealing_target = self.target_total_steps or num_episodes * 200  # ppo.mojo:1968-1971
+            cap = 1 << 16
+            rets, lens = np.empty(cap, np.float32), np.empty(cap, np.float32)
+            stats = _lib.Stats()
+            while completed < num_episodes and (max_rollouts is None or rollouts < max_rollouts):
+                rollouts += 1
+                _lib.check(L.mrl_ppo_rollout(h))
+                n = _lib.check(L.mrl_drain_episodes(h, _lib.ptr(rets), _lib.ptr(lens), cap))
+                for i in range(n):
+                    metrics.log_episode(completed, float(rets[i]), int(lens[i]), 0.0)
+                    completed += 1
+                    if (self.checkpoint_every > 0 and self.checkpoint_path
+                            and completed % self.checkpoint_every == 0):
+                        self.pull_params(h)
+                        self.save_checkpoint(self.checkpoint_path)
+                if completed >= num_episodes:
+                    break
+                _lib.check(L.mrl_ppo_gae(h))
+                _lib.check(L.mrl_get_stats(h, ctypes.byref(stats)))
+                progress = min(1.0, float(stats.total_steps) / float(annealing_target))  # ppo.mojo:2386-2406
+                actor_lr, critic_lr, ent = self.actor_lr, self.critic_lr, self.entropy_coef
+                if self.anneal_lr:
+                    actor_lr, critic_lr = actor_lr * (1.0 - progress), critic_lr * (1.0 - progress)
+                    self.actor.optimizer.lr, self.critic.optimizer.lr = actor_lr, critic_lr
+                if self.anneal_entropy:
+                    ent = ent * (1.0 - progress)
+                _lib.check(L.mrl_ppo_update(h, actor_lr, critic_lr, ent, None))
+                self.train_step_count += 1
+                if verbose and rollouts % print_every == 0:
+                    print(f"Rollout {rollouts} | Episodes {completed} | Avg(100): "
+                          f"{metrics.mean_reward_last_n(100):.2f} | Steps: {stats.total_steps}")
+            self.pull_params(h)
+            _lib.check(L.mrl_get_stats(h, ctypes.byref(stats)))
+            self.actor.optimizer.t, self.critic.optimizer.t = stats.actor_adam_t, stats.critic_adam_t
+        finally:
+            L.mrl_destroy(h)
+        return metrics
+
+    # -- text checkpoints, ppo.mojo:3926-4055 ----------------------------------
+    def save_checkpoint(self, filepath):
+        lines = ["# mojo-rl checkpoint v1", "# type: ppo_agent",
+                 f"# actor_param_size: {self.actor.model.PARAM_SIZE}",
+                 f"# critic_param_size: {self.critic.model.PARAM_SIZE}"]
+        for name, arr in (("actor_params:", self.actor.params), ("actor_optimizer_state:", self.actor.optimizer_state),
+                          ("critic_params:", self.critic.params),
+                          ("critic_optimizer_state:", self.critic.optimizer_state)):
+            lines.append(name)
+            lines.extend(repr(float(v)) for v in arr)
+        lines.append("metadata:")
+        for k in ("gamma", "gae_lambda", "clip_epsilon", "actor_lr", "critic_lr", "entropy_coef", "value_loss_coef",
+                  "num_epochs", "minibatch_size", "normalize_advantages", "target_kl", "max_grad_norm",
+                  "train_step_count"):
+            lines.append(f"{k}={getattr(self, k)}")
+        with open(filepath, "w") as f:
+            f.write("\n".join(lines) + "\n")
+
+    def load_checkpoint(self, filepath):
+        sections = {"actor_params:": [], "actor_optimizer_state:": [], "critic_params:": [],
+                    "critic_optimizer_state:": []}
+        meta, cur = {}, None
+        with open(filepath) as f:
+            for line in f:
+                line = line.strip()
+                if not line or line.startswith("#"):
+                    continue
+                if line in sections:
+                    cur = line
+                elif line == "metadata:":
+                    cur = "meta"
+                elif cur == "meta":
+                    k, _, v = line.partition("=")
+                    meta[k] = v
+                elif cur is not None:
+                    sections[cur].append(float(line))
+        a, c = self.actor.model.PARAM_SIZE, self.critic.model.PARAM_SIZE
+        if (len(sections["actor_params:"]) != a or len(sections["critic_params:"]) != c
+                or len(sections["actor_optimizer_state:"]) != 2 * a
+                or len(sections["critic_optimizer_state:"]) != 2 * c):
+            raise ValueError("checkpoint sizes do not match this agent")
+        self.actor.params = np.asarray(sections["actor_params:"], np.float32)
+        self.actor.optimizer_state = np.asarray(sections["actor_optimizer_state:"], np.float32)
+        self.critic.params = np.asarray(sections["critic_params:"], np.float32)
+        self.critic.optimizer_state = np.asarray(sections["critic_optimizer_state:"], np.float32)
+        for k in ("gamma", "gae_lambda", "clip_epsilon", "actor_lr", "critic_lr", "entropy_coef", "value_loss_coef",
+                  "target_kl", "max_grad_norm"):
+            if k in meta:
+                setattr(self, k, float(meta[k]))
+        for k in ("num_epochs", "minibatch_size", "train_step_count"):
+            if k in meta:
+                setattr(self, k, int(meta[k]))
+        if "normalize_advantages" in meta:
+            self.normalize_advantages = meta["normalize_advantages"] == "True"

@@ -47,10 +47,18 @@ inline void hidden_forward(int batch, int in, int out, int act, const float* x, 
     for (int r = 0; r < batch; ++r) {
         const float* xr = x + (size_t)r * in;
         float* cr = cache ? cache + (size_t)r * (in + out) : nullptr;
+        float* yr = y + (size_t)r * out;
         if (cr) for (int k = 0; k < in; ++k) cr[k] = xr[k];
+        // acc[j] starts at b[j] and takes its terms in ascending k; k is the outer
+        // loop only so that the j loop vectorises - each element's chain is unchanged.
+        for (int j = 0; j < out; ++j) yr[j] = b[j];
+        for (int k = 0; k < in; ++k) {
+            const float xk = xr[k];
+            const float* Wk = W + (size_t)k * out;
+            for (int j = 0; j < out; ++j) yr[j] = fmaf(xk, Wk[j], yr[j]);
+        }
         for (int j = 0; j < out; ++j) {
-            float acc = b[j];
-            for (int k = 0; k < in; ++k) acc = fmaf(xr[k], W[(size_t)k * out + j], acc);
+            float acc = yr[j];
             float yv;
             if (act == ACT_RELU) {
                 if (cr) cr[in + j] = acc;
@@ -59,7 +67,7 @@ inline void hidden_forward(int batch, int in, int out, int act, const float* x, 
                 yv = mrl_tanhf(acc);
                 if (cr) cr[in + j] = yv;
             }
-            y[(size_t)r * out + j] = yv;
+            yr[j] = yv;
         }
     }
 }
@@ -146,13 +154,15 @@ inline void layer_backward(int batch, int in, int out, int act_or_neg, const flo
 #ifdef _OPENMP
 #pragma omp parallel for schedule(static)
 #endif
-    for (int i = 0; i < in; ++i)
-        for (int j = 0; j < out; ++j) {
-            ACC acc = 0;
-            for (int r = 0; r < batch; ++r)
-                acc += (ACC)cache[(size_t)r * cache_stride + i] * (ACC)g[(size_t)r * out + j];
-            dW[(size_t)i * out + j] = (float)acc;
+    for (int i = 0; i < in; ++i) {
+        std::vector<ACC> acc(out, (ACC)0);
+        for (int r = 0; r < batch; ++r) {
+            const ACC xi = (ACC)cache[(size_t)r * cache_stride + i];
+            const float* gr = g.data() + (size_t)r * out;
+            for (int j = 0; j < out; ++j) acc[j] += xi * (ACC)gr[j];
         }
+        for (int j = 0; j < out; ++j) dW[(size_t)i * out + j] = (float)acc[j];
+    }
     for (int j = 0; j < out; ++j) {
         ACC acc = 0;
         for (int r = 0; r < batch; ++r) acc += (ACC)g[(size_t)r * out + j];

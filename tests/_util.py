@@ -1,0 +1,143 @@
+"""Test helpers: ctypes binding of the CPU oracle (oracle/liboracle.so) and
+small conveniences shared by the CPU and GPU suites."""
+import ctypes
+import os
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ORACLE_SO = os.path.join(ROOT, "oracle", "liboracle.so")
+
+from mojo_rl_b200._lib import Config, NetSpec, Stats  # noqa: E402  (POD structs only)
+
+F = ctypes.POINTER(ctypes.c_float)
+I32 = ctypes.POINTER(ctypes.c_int32)
+U32 = ctypes.POINTER(ctypes.c_uint32)
+
+_SIGS = {
+    "orc_env_info": (ctypes.c_int, [ctypes.c_int] + [ctypes.POINTER(ctypes.c_int)] * 4),
+    "orc_env_reset": (None, [ctypes.c_int, ctypes.c_int, F, ctypes.c_uint64]),
+    "orc_env_step": (None, [ctypes.c_int, ctypes.c_int, F, F, F, F, F, ctypes.c_uint64]),
+    "orc_env_selective_reset": (None, [ctypes.c_int, ctypes.c_int, F, F, ctypes.c_uint64]),
+    "orc_lunar_step_one": (ctypes.c_int, [F, ctypes.c_int, ctypes.c_float, F, F, F]),
+    "orc_integrate": (None, [F, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_float,
+                             ctypes.c_float, ctypes.c_int]),
+    "orc_philox": (None, [ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int, U32]),
+    "orc_philox_raw": (None, [U32, U32, U32]),
+    "orc_philox_uniform": (None, [ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int, F]),
+    "orc_xorshift32": (ctypes.c_uint32, [ctypes.c_uint32]),
+    "orc_detmath": (None, [ctypes.c_int, F, F, ctypes.c_int]),
+    "orc_net_param_size": (ctypes.c_int, [ctypes.POINTER(NetSpec)]),
+    "orc_net_cache_per_sample": (ctypes.c_int, [ctypes.POINTER(NetSpec)]),
+    "orc_mlp_forward": (None, [ctypes.POINTER(NetSpec), ctypes.c_int, F, F, F, F]),
+    "orc_mlp_backward": (None, [ctypes.POINTER(NetSpec), ctypes.c_int, F, F, F, F, F, ctypes.c_int]),
+    "orc_adam_step": (None, [ctypes.c_int, F, F, F] + [ctypes.c_float] * 6),
+    "orc_adam_bias_corrections": (None, [ctypes.c_double, ctypes.c_double, ctypes.c_int, F, F]),
+    "orc_sample_actions": (None, [ctypes.c_int, ctypes.c_int, F, F, F, ctypes.c_uint32]),
+    "orc_argmax_actions": (None, [ctypes.c_int, ctypes.c_int, F, F]),
+    "orc_gae": (None, [ctypes.c_int, ctypes.c_int, F, F, F, F, ctypes.c_double, ctypes.c_double, F, F]),
+    "orc_normalize_advantages": (None, [ctypes.c_int64, F, ctypes.c_int]),
+    "orc_ppo_actor_grad": (None, [ctypes.c_int, ctypes.c_int, F, F, F, F, ctypes.c_float, ctypes.c_float, F, F]),
+    "orc_ppo_critic_grad": (None, [ctypes.c_int, F, F, F, ctypes.c_float, ctypes.c_float, ctypes.c_int, F]),
+    "orc_grad_clip": (ctypes.c_float, [ctypes.c_int, F, ctypes.c_float, ctypes.c_int]),
+    "orc_agent_create": (ctypes.c_void_p, [ctypes.POINTER(Config)]),
+    "orc_agent_destroy": (None, [ctypes.c_void_p]),
+    "orc_agent_param_size": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
+    "orc_agent_set_params": (None, [ctypes.c_void_p, ctypes.c_int, F, F]),
+    "orc_agent_get_params": (None, [ctypes.c_void_p, ctypes.c_int, F, F]),
+    "orc_agent_reset": (None, [ctypes.c_void_p, ctypes.c_uint64]),
+    "orc_agent_rollout": (None, [ctypes.c_void_p]),
+    "orc_agent_gae": (None, [ctypes.c_void_p, ctypes.c_int]),
+    "orc_agent_update": (None, [ctypes.c_void_p, ctypes.c_float, ctypes.c_float, ctypes.c_float, I32, ctypes.c_int]),
+    "orc_agent_get_buffer": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(F),
+                                            ctypes.POINTER(ctypes.c_int64)]),
+    "orc_agent_get_stats": (None, [ctypes.c_void_p, ctypes.POINTER(Stats)]),
+    "orc_agent_drain_episodes": (ctypes.c_int, [ctypes.c_void_p, F, F, ctypes.c_int]),
+    "orc_num_threads": (ctypes.c_int, []),
+}
+
+_oracle = None
+
+
+def oracle(path=ORACLE_SO):
+    global _oracle
+    if _oracle is None or path != ORACLE_SO:
+        l = ctypes.CDLL(path)
+        for name, (res, args) in _SIGS.items():
+            fn = getattr(l, name)
+            fn.restype, fn.argtypes = res, args
+        if path != ORACLE_SO:
+            return l
+        _oracle = l
+    return _oracle
+
+
+def fp(a):
+    assert a.dtype == np.float32 and a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(F)
+
+
+def ip(a):
+    assert a.dtype == np.int32 and a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(I32)
+
+
+def default_config(lib_defaults=None, **kw):
+    """mrl_config with the reference defaults (ppo.mojo:869-892), overridable."""
+    cfg = Config()
+    cfg.env_kind, cfg.n_envs, cfg.rollout_len, cfg.hidden_dim = 2, 1024, 128, 64
+    cfg.minibatch_size, cfg.num_epochs, cfg.precision = 256, 4, 0
+    cfg.normalize_advantages, cfg.norm_adv_per_minibatch, cfg.clip_value, cfg.deterministic = 1, 1, 1, 0
+    cfg.world_size, cfg.rank = 1, 0
+    cfg.gamma, cfg.gae_lambda, cfg.clip_epsilon, cfg.value_loss_coef = 0.99, 0.95, 0.2, 0.5
+    cfg.target_kl, cfg.max_grad_norm = 0.015, 0.5
+    cfg.adam_beta1, cfg.adam_beta2, cfg.adam_eps = 0.9, 0.999, 1e-8
+    for k, v in kw.items():
+        assert hasattr(cfg, k), k
+        setattr(cfg, k, v)
+    return cfg
+
+
+def xavier_params(spec, rng):
+    """Reference-style init (initializers.mojo:69-78): everything uniform in
+    +-sqrt(2 / (IN_DIM + OUT_DIM)) of the whole model."""
+    n = oracle().orc_net_param_size(spec)
+    out_cols = spec.out_dim * (2 if spec.head == 1 else 1)
+    std = np.sqrt(2.0 / float(spec.in_dim + out_cols))
+    return ((rng.random(n) * 2.0 - 1.0) * std).astype(np.float32)
+
+
+class OracleAgent:
+    """Thin wrapper over the oracle's fused-phase driver."""
+
+    def __init__(self, cfg):
+        self.o = oracle()
+        self.h = self.o.orc_agent_create(ctypes.byref(cfg))
+        assert self.h
+
+    def close(self):
+        if self.h:
+            self.o.orc_agent_destroy(self.h)
+            self.h = None
+
+    def param_size(self, which):
+        return self.o.orc_agent_param_size(self.h, which)
+
+    def set_params(self, which, params, state=None):
+        self.o.orc_agent_set_params(self.h, which, fp(params), fp(state) if state is not None else None)
+
+    def get_params(self, which):
+        n = self.param_size(which)
+        p, s = np.empty(n, np.float32), np.empty(2 * n, np.float32)
+        self.o.orc_agent_get_params(self.h, which, fp(p), fp(s))
+        return p, s
+
+    def buffer(self, which):
+        ptr, n = F(), ctypes.c_int64()
+        assert self.o.orc_agent_get_buffer(self.h, which, ctypes.byref(ptr), ctypes.byref(n)) == 0
+        return np.ctypeslib.as_array(ptr, shape=(n.value,)).copy()
+
+    def stats(self):
+        s = Stats()
+        self.o.orc_agent_get_stats(self.h, ctypes.byref(s))
+        return s

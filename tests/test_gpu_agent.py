@@ -1,0 +1,133 @@
+"""Fused phases of train_gpu (rollout, GAE, update) against the oracle's serial
+restatement, on identical parameters, seeds and permutations."""
+import numpy as np
+import pytest
+
+from _util import NetSpec, OracleAgent, default_config, xavier_params
+
+pytestmark = pytest.mark.gpu
+
+BUF = dict(states=0, obs=1, r_obs=2, r_actions=3, r_log_probs=4, r_values=5, r_rewards=6, r_dones=7,
+           advantages=8, returns=9, actor_params=10, critic_params=11, actor_grads=12, critic_grads=13, dones=14)
+OBS = {0: 4, 2: 8}
+NACT = {0: 2, 2: 4}
+
+
+def _pair(cfg, seed=0):
+    from _gpu import GpuAgent
+    rng = np.random.default_rng(seed)
+    a_spec = NetSpec(OBS[cfg.env_kind], cfg.hidden_dim, NACT[cfg.env_kind], 0, 0)
+    c_spec = NetSpec(OBS[cfg.env_kind], cfg.hidden_dim, 1, 0, 0)
+    # a little larger than Xavier so that actions are not all identical
+    pa, pc = xavier_params(a_spec, rng) * 3, xavier_params(c_spec, rng)
+    o, g = OracleAgent(cfg), GpuAgent(cfg)
+    for ag in (o, g):
+        ag.set_params(0, pa, np.zeros(2 * pa.size, np.float32))
+        ag.set_params(1, pc, np.zeros(2 * pc.size, np.float32))
+    return o, g
+
+
+def _rel(a, b, floor=1e-3):
+    return float(np.max(np.abs(a - b) / np.maximum(np.abs(b), floor)))
+
+
+@pytest.mark.parametrize("kind,det", [(0, 1), (2, 1), (0, 0), (2, 0)])
+def test_rollout_100_steps(kind, det):
+    cfg = default_config(env_kind=kind, n_envs=512, rollout_len=100, hidden_dim=64, minibatch_size=512,
+                         deterministic=det)
+    o, g = _pair(cfg, seed=kind)
+    try:
+        o.o.orc_agent_reset(o.h, 0); g.reset(0)
+        assert np.array_equal(g.buffer(BUF["states"]), o.buffer(BUF["states"]))
+        o.o.orc_agent_rollout(o.h); g.rollout()
+        # action indices and done/reset flags: bit-exact over the 100 steps
+        assert np.array_equal(g.buffer(BUF["r_actions"]), o.buffer(BUF["r_actions"]))
+        assert np.array_equal(g.buffer(BUF["r_dones"]), o.buffer(BUF["r_dones"]))
+        # per-env state after 100 steps: 1e-4 relative
+        assert _rel(g.buffer(BUF["states"]), o.buffer(BUF["states"])) <= 1e-4
+        for k in ("r_obs", "r_log_probs", "r_values", "r_rewards"):
+            assert np.allclose(g.buffer(BUF[k]), o.buffer(BUF[k]), rtol=1e-4, atol=1e-6), k
+        so, sg = o.stats(), g.stats()
+        assert sg.total_steps == so.total_steps == 512 * 100
+        assert sg.completed_episodes == so.completed_episodes
+        assert abs(sg.sum_episode_reward - so.sum_episode_reward) <= 1e-3 * max(1.0, abs(so.sum_episode_reward))
+        rg, lg = g.drain()
+        assert len(rg) == so.completed_episodes
+        if kind == 0:
+            assert so.completed_episodes > 0
+    finally:
+        o.close(); g.close()
+
+
+@pytest.mark.parametrize("kind", [0, 2])
+def test_gae_and_one_update(kind):
+    cfg = default_config(env_kind=kind, n_envs=256, rollout_len=32, hidden_dim=64, minibatch_size=1024,
+                         num_epochs=2, target_kl=0.0)
+    o, g = _pair(cfg, seed=10 + kind)
+    try:
+        o.o.orc_agent_reset(o.h, 0); g.reset(0)
+        o.o.orc_agent_rollout(o.h); g.rollout()
+        o.o.orc_agent_gae(o.h, 1); g.gae()
+        assert np.allclose(g.buffer(BUF["advantages"]), o.buffer(BUF["advantages"]), rtol=1e-4, atol=1e-5)
+        assert np.allclose(g.buffer(BUF["returns"]), o.buffer(BUF["returns"]), rtol=1e-5, atol=1e-5)
+        total = 256 * 32
+        rng = np.random.default_rng(5)
+        perms = np.stack([rng.permutation(total) for _ in range(2)]).astype(np.int32)
+        from _util import ip
+        o.o.orc_agent_update(o.h, 3e-4, 1e-3, 0.01, ip(perms), 1)
+        g.update(3e-4, 1e-3, 0.01, perms)
+        so, sg = o.stats(), g.stats()
+        assert sg.minibatches_done == so.minibatches_done == 2 * (total // 1024)
+        assert sg.actor_adam_t == so.actor_adam_t and sg.critic_adam_t == so.critic_adam_t
+        for which in (0, 1):
+            po, _ = o.get_params(which); pg, _ = g.get_params(which)
+            # one PPO update's parameters: 1e-5 relative (north-star tolerance)
+            assert _rel(pg, po, floor=1e-2) <= 1e-5, which
+    finally:
+        o.close(); g.close()
+
+
+def test_kl_early_stop_matches():
+    cfg = default_config(env_kind=0, n_envs=128, rollout_len=32, hidden_dim=64, minibatch_size=512,
+                         num_epochs=4, target_kl=1e-4)
+    o, g = _pair(cfg, seed=3)
+    try:
+        o.o.orc_agent_reset(o.h, 0); g.reset(0)
+        o.o.orc_agent_rollout(o.h); g.rollout()
+        o.o.orc_agent_gae(o.h, 1); g.gae()
+        total = 128 * 32
+        rng = np.random.default_rng(6)
+        perms = np.stack([rng.permutation(total) for _ in range(4)]).astype(np.int32)
+        from _util import ip
+        o.o.orc_agent_update(o.h, 1e-2, 1e-2, 0.01, ip(perms), 1)
+        g.update(1e-2, 1e-2, 0.01, perms)
+        so, sg = o.stats(), g.stats()
+        assert so.kl_early_stop == 1 and sg.kl_early_stop == 1
+        assert sg.minibatches_done == so.minibatches_done < 4 * (total // 512)
+        assert sg.actor_adam_t == so.actor_adam_t and sg.critic_adam_t == so.critic_adam_t
+        po, _ = o.get_params(0); pg, _ = g.get_params(0)
+        assert _rel(pg, po, floor=1e-2) <= 1e-4
+    finally:
+        o.close(); g.close()
+
+
+def test_device_side_shuffle_is_a_permutation_and_training_runs():
+    """Without a supplied permutation the library draws its own; every sample is used once per epoch."""
+    import torch
+    from _gpu import call, host, stream
+    from mojo_rl_b200 import CartPoleEnv, DeepPPOAgent
+    for n in (1, 2, 1000, 1 << 20, (1 << 20) + 7):
+        idx = torch.zeros(n, dtype=torch.int32, device="cuda")
+        call("mrl_make_permutation", n, 12345, idx, stream())
+        h = host(idx)
+        assert np.array_equal(np.sort(h), np.arange(n, dtype=np.int32))
+        if n >= 1000:
+            idx2 = torch.zeros(n, dtype=torch.int32, device="cuda")
+            call("mrl_make_permutation", n, 54321, idx2, stream())
+            assert (host(idx2) != h).mean() > 0.99 and abs(np.corrcoef(h, np.arange(n))[0, 1]) < 0.05
+    agent = DeepPPOAgent(4, 2, hidden_dim=64, rollout_len=64, n_envs=256, gpu_minibatch_size=2048, num_epochs=2)
+    before = agent.actor.params.copy()
+    m = agent.train_gpu(CartPoleEnv, None, num_episodes=10 ** 9, max_rollouts=3)
+    assert m.num_episodes() > 0 and np.isfinite(agent.actor.params).all()
+    assert not np.array_equal(before, agent.actor.params)
+    assert agent.actor.optimizer.t > 0

@@ -1,0 +1,113 @@
+"""GPUDiscreteEnv boundary parity: CUDA kernels (through the C ABI) against the
+CPU oracle on identical seeds and actions."""
+import numpy as np
+import pytest
+
+from _util import fp, oracle
+
+pytestmark = pytest.mark.gpu
+
+CARTPOLE, LUNAR = 0, 2
+STATE = {CARTPOLE: 4, LUNAR: 192}
+OBS = {CARTPOLE: 4, LUNAR: 8}
+NACT = {CARTPOLE: 2, LUNAR: 4}
+
+
+def _run_both(kind, n, steps, seed, policy):
+    import torch
+    from _gpu import call, dev, host, stream
+    o = oracle()
+    S, O = STATE[kind], OBS[kind]
+    rng = np.random.default_rng(seed)
+    garbage = rng.standard_normal((n, S)).astype(np.float32) if kind == LUNAR else np.zeros((n, S), np.float32)
+    # slots the reference never writes (mass, force, motor fields) must be inert: zero them like a fresh buffer
+    st_c = np.zeros((n, S), np.float32)
+    st_g = dev(st_c)
+    o.orc_env_reset(kind, n, fp(st_c), seed)
+    call("mrl_env_reset", kind, n, st_g, seed, stream())
+    assert np.array_equal(host(st_g), st_c), "reset states differ"
+    rew_c, done_c, obs_c = np.zeros(n, np.float32), np.zeros(n, np.float32), np.zeros((n, O), np.float32)
+    rew_g, done_g, obs_g = dev(rew_c), dev(done_c), dev(obs_c)
+    n_done = 0
+    worst = 0.0
+    for t in range(steps):
+        act = policy(rng, obs_c if t else st_c[:, :O], n)
+        act_g = dev(act)
+        o.orc_env_step(kind, n, fp(st_c), fp(act), fp(rew_c), fp(done_c), fp(obs_c), t)
+        call("mrl_env_step", kind, n, st_g, act_g, rew_g, done_g, obs_g, t, stream())
+        sg, rg, dg, og = host(st_g), host(rew_g), host(done_g), host(obs_g)
+        assert np.array_equal(dg, done_c), f"done flags differ at step {t}"
+        denom = np.maximum(np.abs(st_c), 1e-3)
+        worst = max(worst, float(np.max(np.abs(sg - st_c) / denom)))
+        assert np.allclose(sg, st_c, rtol=1e-4, atol=1e-6), f"state differs at step {t}"
+        assert np.allclose(rg, rew_c, rtol=1e-4, atol=1e-5) and np.allclose(og, obs_c, rtol=1e-4, atol=1e-6)
+        n_done += int(done_c.sum())
+        rs = 1000 + 17 * t
+        o.orc_env_selective_reset(kind, n, fp(st_c), fp(done_c), rs)
+        call("mrl_env_selective_reset", kind, n, st_g, done_g, rs, stream())
+        assert np.array_equal(host(st_g), st_c) and np.array_equal(host(done_g), done_c)
+        if kind == LUNAR:
+            obs_c[:] = st_c[:, :O]
+    return n_done, worst
+
+
+def _random_policy(kind):
+    return lambda rng, obs, n: rng.integers(0, NACT[kind], n).astype(np.float32)
+
+
+def _deterministic_policy(kind):
+    # a fixed function of the observation (stands in for argmax of a frozen net)
+    if kind == CARTPOLE:
+        return lambda rng, obs, n: (obs[:, 2] + 0.5 * obs[:, 3] > 0).astype(np.float32)
+    def pol(rng, obs, n):
+        a = np.zeros(n, np.float32)
+        a[obs[:, 3] < -0.4] = 2.0
+        a[(obs[:, 4] > 0.1) & (a == 0)] = 3.0
+        a[(obs[:, 4] < -0.1) & (a == 0)] = 1.0
+        return a
+    return pol
+
+
+@pytest.mark.parametrize("kind", [CARTPOLE, LUNAR])
+@pytest.mark.parametrize("n", [1, 33, 1024])
+def test_100_steps_deterministic_policy(kind, n):
+    n_done, worst = _run_both(kind, n, 100, 0, _deterministic_policy(kind))
+    # designed to be bit-identical; the contract is 1e-4 relative
+    assert worst <= 1e-4
+
+
+@pytest.mark.parametrize("kind", [CARTPOLE, LUNAR])
+def test_400_steps_random_policy_with_resets(kind):
+    n_done, worst = _run_both(kind, 512, 400, 7, _random_policy(kind))
+    assert n_done > 100           # crashes / landings / time-outs and their resets were exercised
+    assert worst <= 1e-4
+
+
+def test_lunar_bitwise_identity():
+    """The kernels evaluate the same IEEE operations as the oracle: expect equality, not closeness."""
+    import torch
+    from _gpu import call, dev, host, stream
+    o = oracle()
+    n = 2048
+    rng = np.random.default_rng(3)
+    st_c = np.zeros((n, 192), np.float32)
+    o.orc_env_reset(LUNAR, n, fp(st_c), 5)
+    st_g = dev(st_c)
+    rew_c, done_c, obs_c = np.zeros(n, np.float32), np.zeros(n, np.float32), np.zeros((n, 8), np.float32)
+    rew_g, done_g, obs_g = dev(rew_c), dev(done_c), dev(obs_c)
+    for t in range(150):
+        act = rng.integers(0, 4, n).astype(np.float32)
+        o.orc_env_step(LUNAR, n, fp(st_c), fp(act), fp(rew_c), fp(done_c), fp(obs_c), 0)
+        call("mrl_env_step", LUNAR, n, st_g, dev(act), rew_g, done_g, obs_g, 0, stream())
+        o.orc_env_selective_reset(LUNAR, n, fp(st_c), fp(done_c), t)
+        call("mrl_env_selective_reset", LUNAR, n, st_g, done_g, t, stream())
+    assert np.array_equal(host(st_g), st_c)
+    assert np.array_equal(host(rew_g), rew_c) and np.array_equal(host(obs_g), obs_c)
+
+
+def test_invalid_arguments_are_reported():
+    from mojo_rl_b200 import _lib
+    L = _lib.lib()
+    assert L.mrl_env_step(LUNAR, 0, None, None, None, None, None, 0, None) == -1
+    assert L.mrl_env_reset(42, 8, _lib.ptr(np.zeros(8, np.float32)), 0, None) == -4
+    assert b"42" in L.mrl_last_error_string()

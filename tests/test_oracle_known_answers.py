@@ -1,0 +1,237 @@
+"""Pins the CPU oracle against every known answer the reference states for the
+hot path (there are no recorded trajectories: the reference cannot run here and
+its tests hold only these few numbers) and against published Philox vectors."""
+import ctypes
+
+import numpy as np
+
+from _util import F, fp, oracle
+
+LUNAR, CARTPOLE = 2, 0
+BODIES, FORCES, JOINTS, EDGES, META = 8, 47, 56, 91, 188
+
+
+def test_philox4x32_10_known_answer_vectors():
+    # Random123 kat_vectors for philox4x32-10 (Salmon et al., SC'11).
+    o = oracle()
+    cases = [
+        ([0, 0, 0, 0], [0, 0], [0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8]),
+        ([0xffffffff] * 4, [0xffffffff] * 2, [0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd]),
+        ([0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344], [0xa4093822, 0x299f31d0],
+         [0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1]),
+    ]
+    for ctr, key, want in cases:
+        c = (ctypes.c_uint32 * 4)(*ctr)
+        k = (ctypes.c_uint32 * 2)(*key)
+        out = (ctypes.c_uint32 * 4)()
+        o.orc_philox_raw(c, k, out)
+        assert list(out) == want
+
+
+def test_philox_uniform_range_and_counter():
+    o = oracle()
+    u = np.zeros(4 * 1000, np.float32)
+    o.orc_philox_uniform(12345, 0, 1000, fp(u))
+    assert u.min() >= 0.0 and u.max() < 1.0
+    assert abs(u.mean() - 0.5) < 0.02
+    # offset k == k-th step of offset 0
+    v = np.zeros(4, np.float32)
+    o.orc_philox_uniform(12345, 7, 1, fp(v))
+    assert np.array_equal(v, u[28:32])
+
+
+def test_xorshift32_closed_form():
+    # deep_rl/gpu/random.mojo:11-18
+    o = oracle()
+    x = 2463534242
+    y = x ^ ((x << 13) & 0xffffffff)
+    y ^= y >> 17
+    y ^= (y << 5) & 0xffffffff
+    assert o.orc_xorshift32(x) == y
+
+
+def test_layout_sizes():
+    # physics2d/layout.mojo:247-299; tests/test_physics_architecture.mojo:31-44
+    o = oracle()
+    vals = [ctypes.c_int() for _ in range(4)]
+    assert o.orc_env_info(LUNAR, *[ctypes.byref(v) for v in vals]) == 0
+    assert [v.value for v in vals] == [192, 8, 4, 0]
+    assert o.orc_env_info(CARTPOLE, *[ctypes.byref(v) for v in vals]) == 0
+    assert [v.value for v in vals] == [4, 4, 2, 0]
+
+
+def test_free_fall_one_step_velocity():
+    # tests/test_v2gpu_cpu_vs_gpu.mojo:299: vy after one step = -10 * 0.02 = -0.2
+    o = oracle()
+    s = np.zeros(192, np.float32)
+    s[BODIES + 1] = 5.0
+    s[BODIES + 10] = 1.0
+    s[BODIES + 11] = 1.0
+    o.orc_integrate(fp(s), 1, BODIES, FORCES, 0.0, -10.0, 0.02, 1)
+    assert abs(s[BODIES + 4] - (-0.2)) < 1e-7
+    assert abs(s[BODIES + 1] - (5.0 - 0.2 * 0.02)) < 1e-6
+
+
+def test_falling_box_100_steps_matches_closed_form():
+    # tests/test_cpu_gpu_equivalence.mojo:33-82,160: boxes at 2.0 + 0.5*env, g=-10,
+    # dt=0.02, 100 steps, tolerance 1e-5 (semi-implicit Euler closed form).
+    o = oracle()
+    for env in range(4):
+        s = np.zeros(192, np.float32)
+        y0 = 2.0 + 0.5 * env + 100.0  # lifted so that nothing is in reach of a ground
+        s[BODIES + 1] = y0
+        s[BODIES + 10] = 1.0
+        s[BODIES + 11] = 1.0
+        o.orc_integrate(fp(s), 1, BODIES, FORCES, 0.0, -10.0, 0.02, 100)
+        vy = -10.0 * 0.02 * 100
+        y = y0 - 10.0 * 0.02 * 0.02 * (100 * 101 / 2)
+        assert abs(s[BODIES + 4] - vy) < 1e-4
+        assert abs(s[BODIES + 1] - y) / abs(y) < 1e-5
+
+
+def test_static_body_is_skipped():
+    # euler.mojo:233-235: inv_mass == 0 bodies do not move
+    o = oracle()
+    s = np.zeros(192, np.float32)
+    s[BODIES + 4] = 3.0
+    o.orc_integrate(fp(s), 1, BODIES, FORCES, 0.0, -10.0, 0.02, 5)
+    assert s[BODIES + 4] == 3.0 and s[BODIES + 1] == 0.0
+
+
+def test_angle_wrap_sequential_ifs():
+    # euler.mojo:296-306
+    o = oracle()
+    s = np.zeros(192, np.float32)
+    s[BODIES + 10] = 1.0
+    s[BODIES + 2] = 3.1
+    s[BODIES + 5] = 10.0  # +0.2 rad per step
+    o.orc_integrate(fp(s), 1, BODIES, FORCES, 0.0, 0.0, 0.02, 1)
+    assert abs(s[BODIES + 2] - (3.3 - 2 * np.pi)) < 1e-5
+    s[BODIES + 2] = 150.0
+    o.orc_integrate(fp(s), 1, BODIES, FORCES, 0.0, 0.0, 0.02, 1)
+    assert s[BODIES + 2] == 0.0
+
+
+def test_lunar_reset_fields():
+    # lunar_lander_v2.mojo:1806-1952
+    o = oracle()
+    n = 16
+    st = np.full((n, 192), 7.0, np.float32)
+    o.orc_env_reset(LUNAR, n, fp(st), 3)
+    for i in range(n):
+        s = st[i]
+        assert s[BODIES + 0] == np.float32(10.0) and s[BODIES + 1] == np.float32(400.0 / 30.0)
+        vx, vy = s[BODIES + 3], s[BODIES + 4]
+        assert abs(vx) <= 4.0 and abs(vy) <= 4.0  # (2r-1) * 1000 * 0.02 / 5
+        assert s[BODIES + 13 + 3] == vx and s[BODIES + 26 + 4] == vy  # all three bodies share it
+        assert s[BODIES + 10] == np.float32(0.2) and s[BODIES + 11] == np.float32(0.5)
+        assert s[BODIES + 13 + 10] == np.float32(5.0) and s[BODIES + 13 + 11] == np.float32(50.0)
+        # observation and initial shaping
+        y_norm = np.float32((400 / 30 - (400 / 30 / 4 + 18 / 30 / 30)) / (400 / 30 / 2))
+        assert s[0] == 0 and s[1] == y_norm
+        assert abs(s[2] - vx * 10 / 50) < 1e-6 and abs(s[3] - vy * np.float32(400 / 30 / 2) / 50) < 1e-6
+        shaping = -100 * abs(y_norm) - 100 * np.sqrt(s[2] ** 2 + s[3] ** 2)
+        assert abs(s[META + 2] - shaping) < 1e-3
+        assert s[META + 0] == 0 and s[META + 3] == 0
+        # terrain: 10 edges, helipad chunks 3..7 flat at H/4, normals up and unit
+        edges = s[EDGES:EDGES + 60].reshape(10, 6)
+        assert s[187] == 10
+        assert np.allclose(edges[:, 0], np.arange(10) * 2.0) and np.allclose(edges[:, 2], np.arange(1, 11) * 2.0)
+        assert np.all(edges[3:7, 1] == np.float32(400 / 30 / 4)) and np.all(edges[3:7, 3] == np.float32(400 / 30 / 4))
+        assert np.all(edges[:, 5] > 0) and np.allclose(edges[:, 4] ** 2 + edges[:, 5] ** 2, 1.0, atol=1e-6)
+        # untouched slots keep the caller's bytes (mass, force slots, motor fields, edges 10..15)
+        assert s[BODIES + 9] == 7.0 and s[BODIES + 6] == 7.0 and s[JOINTS + 10] == 7.0 and s[EDGES + 60] == 7.0
+    assert len({float(v) for v in st[:, BODIES + 3]}) == n  # per-env streams differ
+
+
+def test_lunar_selective_reset_keeps_dones():
+    # lunar_lander_v2.mojo:1643-1701 never writes dones
+    o = oracle()
+    st = np.zeros((4, 192), np.float32)
+    o.orc_env_reset(LUNAR, 4, fp(st), 0)
+    before = st.copy()
+    dones = np.array([0, 1, 0, 1], np.float32)
+    o.orc_env_selective_reset(LUNAR, 4, fp(st), fp(dones), 99)
+    assert np.array_equal(dones, [0, 1, 0, 1])
+    assert np.array_equal(st[0], before[0]) and np.array_equal(st[2], before[2])
+    assert not np.array_equal(st[1], before[1])
+
+
+def test_cartpole_reset_and_step():
+    # envs/cartpole.mojo:784-835, :702-781
+    o = oracle()
+    n = 8
+    st = np.zeros((n, 4), np.float32)
+    o.orc_env_reset(CARTPOLE, n, fp(st), 0)
+    assert np.all(np.abs(st) <= 0.05 + 1e-7)
+    # closed form of the first draw of env 0
+    def xs(x):
+        x ^= (x << 13) & 0xffffffff
+        x ^= x >> 17
+        x ^= (x << 5) & 0xffffffff
+        return x
+    r = xs(12345)
+    r = xs(r)
+    want = np.float32(-0.05) + np.float32(np.float32(r) / np.float32(4294967296.0)) * np.float32(0.1)
+    assert st[0, 0] == want
+    act = np.ones(n, np.float32)
+    rew, done, obs = np.zeros(n, np.float32), np.zeros(n, np.float32), np.zeros((n, 4), np.float32)
+    s0 = st.copy()
+    o.orc_env_step(CARTPOLE, n, fp(st), fp(act), fp(rew), fp(done), fp(obs), 0)
+    assert np.all(rew == 1.0) and np.all(done == 0.0) and np.array_equal(obs, st)
+    assert np.allclose(st[:, 0], s0[:, 0] + 0.02 * s0[:, 1], atol=1e-7)   # x uses the old x_dot
+    assert np.all(st[:, 1] > s0[:, 1])                                      # pushed right
+    # termination: |x| > 2.4, reward stays 1.0, no truncation counter
+    st[0, 0] = 2.5
+    o.orc_env_step(CARTPOLE, n, fp(st), fp(act), fp(rew), fp(done), fp(obs), 0)
+    assert done[0] == 1.0 and rew[0] == 1.0
+    d = done.copy()
+    o.orc_env_selective_reset(CARTPOLE, n, fp(st), fp(d), 77)
+    assert d[0] == 0.0 and abs(st[0, 0]) <= 0.05  # cleared and reset
+
+
+def test_lunar_step_semantics():
+    o = oracle()
+    n = 4
+    st = np.zeros((n, 192), np.float32)
+    o.orc_env_reset(LUNAR, n, fp(st), 0)
+    act = np.array([0, 1, 2, 3], np.float32)
+    rew, done, obs = np.zeros(n, np.float32), np.zeros(n, np.float32), np.zeros((n, 8), np.float32)
+    vy0 = st[:, BODIES + 4].copy()
+    o.orc_env_step(LUNAR, n, fp(st), fp(act), fp(rew), fp(done), fp(obs), 0)
+    assert abs((st[0, BODIES + 4] - vy0[0]) + 0.2) < 1e-5          # noop: pure gravity
+    assert st[2, BODIES + 4] - vy0[2] > -0.2                        # main engine pushes up
+    assert np.all(st[:, META + 0] == 1.0) and np.all(done == 0.0)
+    assert np.array_equal(obs, st[:, :8])
+    # an env that is already done: reward 0, done 1, step counter frozen, physics still runs
+    st[1, META + 3] = 1.0
+    y_before = st[1, BODIES + 1]
+    o.orc_env_step(LUNAR, n, fp(st), fp(act), fp(rew), fp(done), fp(obs), 0)
+    assert rew[1] == 0.0 and done[1] == 1.0 and st[1, META + 0] == 1.0 and st[1, BODIES + 1] != y_before
+    # out of bounds -> crash penalty
+    st[0, BODIES + 0] = 25.0
+    o.orc_env_step(LUNAR, n, fp(st), fp(act), fp(rew), fp(done), fp(obs), 0)
+    assert done[0] == 1.0 and rew[0] == -100.0
+
+
+def test_lunar_contact_order_and_crash():
+    # contacts are listed body-major / vertex / edge and body 0 touching ends the episode
+    o = oracle()
+    st = np.zeros((1, 192), np.float32)
+    o.orc_env_reset(LUNAR, 1, fp(st), 0)
+    s = st[0]
+    ground = s[EDGES + 3 * 6 + 1]
+    dy = (ground + 0.2) - s[BODIES + 1]
+    for b in range(3):
+        s[BODIES + 13 * b + 1] += dy     # hull centre 0.2 above the pad: hull bottom and legs penetrate
+        s[BODIES + 13 * b + 3] = 0.0
+        s[BODIES + 13 * b + 4] = 0.0
+    contacts = np.zeros(8 * 9, np.float32)
+    r, d = ctypes.c_float(), ctypes.c_float()
+    nc = o.orc_lunar_step_one(fp(s), 0, 0.0, ctypes.byref(r), ctypes.byref(d), fp(contacts))
+    c = contacts.reshape(8, 9)
+    assert nc == 8                                    # capped at MAX_CONTACTS
+    bodies = c[:nc, 0]
+    assert np.all(np.diff(bodies) >= 0) and bodies[0] == 0.0   # body-major order
+    assert np.all(c[:nc, 1] == -1.0) and np.all(c[:nc, 6] > 0)
+    assert d.value == 1.0 and r.value == -100.0
