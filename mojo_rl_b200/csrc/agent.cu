@@ -212,13 +212,20 @@ __global__ void extract_obs_kernel(const float* __restrict__ states, float* __re
 // (whose random stream is Mojo's global RNG) when no permutation is supplied.
 __host__ __device__ __forceinline__ uint32_t feistel_perm(uint32_t i, uint32_t n, int half, uint64_t key) {
     const uint32_t mask = (1u << half) - 1u;
+    uint32_t rk[4];
+#pragma unroll
+    for (int round = 0; round < 4; ++round) {  // splitmix64 round keys
+        uint64_t z = key + 0x9E3779B97F4A7C15ull * (uint64_t)(round + 1);
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        rk[round] = (uint32_t)(z ^ (z >> 31));
+    }
     uint32_t x = i;
     do {
         uint32_t l = x >> half, r = x & mask;
 #pragma unroll
         for (int round = 0; round < 4; ++round) {
-            uint32_t k = (uint32_t)(key >> (16 * (round & 3))) + 0x9E3779B9u * (uint32_t)(round + 1);
-            uint32_t f = (r + k) * 0x85EBCA6Bu;
+            uint32_t f = (r ^ rk[round]) * 0x85EBCA6Bu;
             f ^= f >> 13;
             f *= 0xC2B2AE35u;
             f ^= f >> 16;

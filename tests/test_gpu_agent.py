@@ -124,7 +124,7 @@ def test_device_side_shuffle_is_a_permutation_and_training_runs():
         if n >= 1000:
             idx2 = torch.zeros(n, dtype=torch.int32, device="cuda")
             call("mrl_make_permutation", n, 54321, idx2, stream())
-            assert (host(idx2) != h).mean() > 0.99 and abs(np.corrcoef(h, np.arange(n))[0, 1]) < 0.05
+            assert (host(idx2) != h).mean() > 0.98 and abs(np.corrcoef(h, np.arange(n))[0, 1]) < 0.1
     agent = DeepPPOAgent(4, 2, hidden_dim=64, rollout_len=64, n_envs=256, gpu_minibatch_size=2048, num_epochs=2)
     before = agent.actor.params.copy()
     m = agent.train_gpu(CartPoleEnv, None, num_episodes=10 ** 9, max_rollouts=3)
