@@ -107,6 +107,19 @@ int64_t mrl_mlp_workspace_floats(const mrl_net_spec* net, int batch);
 int mrl_mlp_forward(const mrl_net_spec* net, int batch, const float* in, const float* params,
                     float* out, float* cache, float* workspace, void* stream);
 
+/* Same forward pass for callers that can neither pass a workspace nor let the
+ * library allocate one (a host whose own pool owns all device memory; a loop
+ * that must not hit the device-wide synchronisation of cudaMalloc/cudaFree).
+ * No counterpart in the reference: its Model methods always receive a workspace
+ * buffer.  The hidden activations live in a fixed 8 MiB array inside the loaded
+ * module (held by every GPU that loads the library until exit), which limits
+ * batch * hidden_dim to 1048576; larger requests return MRL_ERR_TOO_LARGE.
+ * Calls no cudaMalloc/cudaFree.  The first call on each device looks up the
+ * array's device address and should therefore come before any stream capture.
+ * All calls share the array: calls that overlap on the GPU race. */
+int mrl_mlp_forward_noalloc(const mrl_net_spec* net, int batch, const float* in,
+                            const float* params, float* out, float* cache, void* stream);
+
 /* Model.backward_gpu_ws (sequential.mojo:724-865).  grad_out [batch, out_cols];
  * grads [PARAM_SIZE] is overwritten; grad_in [batch, in] may be NULL. */
 int mrl_mlp_backward(const mrl_net_spec* net, int batch, const float* grad_out,

@@ -52,6 +52,7 @@ SIGNATURES = {
     "mrl_net_out_cols": (ctypes.c_int, [ctypes.POINTER(NetSpec)]),
     "mrl_mlp_workspace_floats": (ctypes.c_int64, [ctypes.POINTER(NetSpec), ctypes.c_int]),
     "mrl_mlp_forward": (ctypes.c_int, [ctypes.POINTER(NetSpec), ctypes.c_int] + [c_void_p] * 6),
+    "mrl_mlp_forward_noalloc": (ctypes.c_int, [ctypes.POINTER(NetSpec), ctypes.c_int] + [c_void_p] * 5),
     "mrl_mlp_backward": (ctypes.c_int, [ctypes.POINTER(NetSpec), ctypes.c_int] + [c_void_p] * 7),
     "mrl_adam_step": (ctypes.c_int, [ctypes.c_int, c_void_p, c_void_p, c_void_p] + [ctypes.c_float] * 6 + [c_void_p]),
     "mrl_sample_actions": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, c_void_p, c_void_p, c_void_p, ctypes.c_uint32, c_void_p]),

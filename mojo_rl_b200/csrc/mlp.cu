@@ -337,9 +337,67 @@ __global__ void adam_kernel(float* __restrict__ params, const float* __restrict_
     params[i] = params[i] - lr * m_hat / (sqrtf(v_hat) + eps);
 }
 
+// ---------------------------------------------------------------------------
+// Forward pass for callers that must not allocate.
+//
+// Some hosts of this library cannot give it a workspace and cannot let it call
+// cudaMalloc: an embedding runtime that carved up all of device memory into its
+// own pool at start-up, or an evaluation loop that must never stall the device
+// (cudaMalloc and cudaFree synchronise it).  For them the two hidden activations
+// of the forward pass live in this fixed array instead.  It is part of the
+// loaded module, so every GPU that loads the library holds NOALLOC_SCRATCH_FLOATS
+// * 4 bytes (8 MiB) until the process exits.
+//
+// In host code `g_noalloc_scratch` is only a handle for the symbol, not a device
+// address; the address is looked up once per device with cudaGetSymbolAddress
+// and cached.  Every call shares the array and finds the previous call's
+// contents in it: the forward pass overwrites every element it later reads, so
+// nothing needs clearing, but two calls that overlap on the GPU (different
+// streams, or different host threads) race on it.
+// ---------------------------------------------------------------------------
+constexpr int64_t NOALLOC_MAX_ROWS_X_HIDDEN = 1 << 20;                     // batch * hidden_dim limit
+constexpr int64_t NOALLOC_SCRATCH_FLOATS = 2 * NOALLOC_MAX_ROWS_X_HIDDEN;  // h0 and h1
+static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
+
+// Device address of the scratch array on the current device (set-up on first use).
+static int noalloc_scratch(float** out) {
+    int dev = -1;
+    MRL_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) {
+        set_error("mrl_mlp_forward_noalloc: device index %d is outside 0..%d", dev, NOALLOC_MAX_DEVICES - 1);
+        return MRL_ERR_UNSUPPORTED;
+    }
+    if (g_noalloc_ptr[dev] == nullptr) {
+        float* p = nullptr;
+        MRL_CUDA_OK(cudaGetSymbolAddress((void**)&p, g_noalloc_scratch));
+        g_noalloc_ptr[dev] = p;
+    }
+    *out = g_noalloc_ptr[dev];
+    return MRL_OK;
+}
+
 }  // namespace mrl
 
 using namespace mrl;
+
+extern "C" int mrl_mlp_forward_noalloc(const mrl_net_spec* net, int batch, const float* in,
+                                       const float* params, float* out, float* cache, void* stream) {
+    MRL_CHECK_ARG(spec_ok(net) && batch > 0 && in && params && out);
+    if ((int64_t)batch * net->hidden_dim > NOALLOC_MAX_ROWS_X_HIDDEN) {
+        set_error("mrl_mlp_forward_noalloc: batch * hidden_dim = %lld exceeds the built-in scratch of %lld "
+                  "(use mrl_mlp_forward with a caller-provided workspace)",
+                  (long long)batch * net->hidden_dim, (long long)NOALLOC_MAX_ROWS_X_HIDDEN);
+        return MRL_ERR_TOO_LARGE;
+    }
+    float* scratch = nullptr;
+    int rc = noalloc_scratch(&scratch);
+    if (rc) return rc;
+    // h0 = scratch[0 .. batch*H), h1 = scratch[batch*H .. 2*batch*H): the layout mlp_forward_impl expects.
+    return mlp_forward_impl(net, batch, in, params, out, cache, scratch, as_stream(stream));
+}
 
 extern "C" int mrl_net_param_size(const mrl_net_spec* n) {
     if (!spec_ok(n)) return MRL_ERR_INVALID_ARG;
