@@ -132,6 +132,21 @@ int mrl_mlp_backward(const mrl_net_spec* net, int batch, const float* grad_out,
 int mrl_adam_step(int n, float* params, const float* grads, float* state_mv, float lr,
                   float beta1, float beta2, float eps, float bc1, float bc2, void* stream);
 
+/* bf16 tensor-core building blocks of the precision-1 update (tcgen05.mma, fp32
+ * accumulation in TMEM, TMA operand loads).  No counterpart in the reference,
+ * whose matmuls are fp32 16x16 tiles (linear.mojo:135-225).  Operands are bf16,
+ * row-major with the K index contiguous ("TN"):
+ *   rowtile: D[M, 256] (fp32) = A[M, 256] . B[256 (n), 256 (k)]^T
+ *   splitk : partial[s][256, 256] (fp32) = A[256 (m), K slice s] . B[256 (n), K slice s]^T,
+ *            s < *splits_host <= mrl_bf16_max_splits(); the caller sums the slices.
+ * err_flag: device int, 0 on entry; non-zero afterwards if a bounded wait inside
+ * the kernel gave up (results are then invalid). */
+int mrl_bf16_rowtile_gemm(int M, const void* A_bf16, const void* B_bf16, float* D, int* err_flag,
+                          void* stream);
+int mrl_bf16_splitk_gemm(int K, const void* A_bf16, const void* B_bf16, float* partial,
+                         int* splits_host, int* err_flag, void* stream);
+int mrl_bf16_max_splits(void);
+
 /* ------------------------------------------------------------------------
  * L4 kernels of DeepPPOAgent.train_gpu, one entry point per reference kernel.
  * ---------------------------------------------------------------------- */

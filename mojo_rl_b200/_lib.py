@@ -55,6 +55,10 @@ SIGNATURES = {
     "mrl_mlp_forward_noalloc": (ctypes.c_int, [ctypes.POINTER(NetSpec), ctypes.c_int] + [c_void_p] * 5),
     "mrl_mlp_backward": (ctypes.c_int, [ctypes.POINTER(NetSpec), ctypes.c_int] + [c_void_p] * 7),
     "mrl_adam_step": (ctypes.c_int, [ctypes.c_int, c_void_p, c_void_p, c_void_p] + [ctypes.c_float] * 6 + [c_void_p]),
+    "mrl_bf16_rowtile_gemm": (ctypes.c_int, [ctypes.c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "mrl_bf16_splitk_gemm": (ctypes.c_int, [ctypes.c_int, c_void_p, c_void_p, c_void_p, ctypes.POINTER(ctypes.c_int),
+                                            c_void_p, c_void_p]),
+    "mrl_bf16_max_splits": (ctypes.c_int, []),
     "mrl_sample_actions": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, c_void_p, c_void_p, c_void_p, ctypes.c_uint32, c_void_p]),
     "mrl_argmax_actions": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, c_void_p, c_void_p, c_void_p]),
     "mrl_gae": (ctypes.c_int, [ctypes.c_int, ctypes.c_int] + [c_void_p] * 4 + [ctypes.c_double, ctypes.c_double] + [c_void_p] * 3),

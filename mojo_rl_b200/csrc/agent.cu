@@ -11,6 +11,7 @@
 #include "env_cartpole.cuh"
 #include "env_lunar.cuh"
 #include "ppo_kernels.cuh"
+#include "update_bf16.cuh"
 
 namespace mrl {
 
@@ -92,6 +93,10 @@ struct mrl_ctx {
     float *actor_cache, *critic_cache, *workspace;
     int32_t* perm;
     double* stats;  // 8 doubles of reduction scratch
+    bool use_tc;    // precision == 1: update GEMMs on tcgen05 tensor cores in bf16
+    mrl::tc::State tc;
+    uint8_t* tc_workspace;
+    int* tc_err;    // device word written by a kernel whose bounded wait gave up
     DeviceCounters* counters;
     ncclComm_t comm;
     std::vector<cudaEvent_t> timer_events[3];  // start/stop pairs per phase, resolved by mrl_get_timers
@@ -416,6 +421,24 @@ extern "C" int mrl_create(mrl_ctx** out, const mrl_config* cfg) {
     A_(perm, T * N);
     A_(stats, 8);
     A_(counters, 1);
+    A_(tc_err, 4);
+    c->use_tc = false;
+    if (cfg->precision == 1) {
+        if (!tc::supported(&c->actor_net, (int)B) || !tc::supported(&c->critic_net, (int)B)) {
+            set_error("precision 1 (bf16 tensor-core update) needs hidden_dim 256, ReLU nets, obs_dim in {4, 8, 24}, "
+                      "head width <= 8 and a minibatch that is a multiple of 128; use precision 0");
+            mrl_destroy(c);
+            return MRL_ERR_UNSUPPORTED;
+        }
+        A_(tc_workspace, (size_t)tc::workspace_bytes((int)B));
+        rc = c->tc.init(c->tc_workspace, (int)B, c->tc_err);
+        if (rc) { mrl_destroy(c); return rc; }
+        c->use_tc = true;
+    } else if (cfg->precision != 0) {
+        set_error("precision must be 0 (fp32) or 1 (bf16 tensor-core update)");
+        mrl_destroy(c);
+        return MRL_ERR_INVALID_ARG;
+    }
 #undef A_
     *out = c;
     return MRL_OK;
@@ -586,13 +609,18 @@ extern "C" int mrl_ppo_update(mrl_ctx* c, float actor_lr, float critic_lr, float
                 if ((rc = normalize_advantages_impl(B, c->mb_adv, c->stats, st))) return rc;
             }
             // ---- actor (ppo.mojo:2513-2624)
-            if ((rc = mlp_forward_impl(&c->actor_net, B, c->mb_obs, c->actor_params, c->mb_logits, c->actor_cache,
-                                       c->workspace, st))) return rc;
+            if (c->use_tc) {
+                if ((rc = c->tc.forward(&c->actor_net, c->actor_params, c->mb_obs, c->mb_logits, st))) return rc;
+            } else if ((rc = mlp_forward_impl(&c->actor_net, B, c->mb_obs, c->actor_params, c->mb_logits,
+                                              c->actor_cache, c->workspace, st))) return rc;
             if ((rc = mrl_ppo_actor_grad(B, A, c->mb_logits, c->mb_old_lp, c->mb_adv, c->mb_actions, cfg.clip_epsilon,
                                          entropy_coef, c->mb_grad_logits, c->mb_kl, st))) return rc;
             MRL_LAUNCH(kl_sum_kernel, 1, 1024, 0, st, c->mb_kl, B, c->actor_grads + c->actor_p);
-            if ((rc = mlp_backward_impl(&c->actor_net, B, c->mb_grad_logits, c->actor_params, c->actor_cache, nullptr,
-                                        c->actor_grads, c->workspace, st))) return rc;
+            if (c->use_tc) {
+                if ((rc = c->tc.backward(&c->actor_net, c->actor_params, c->mb_obs, c->mb_grad_logits, c->actor_grads,
+                                         st))) return rc;
+            } else if ((rc = mlp_backward_impl(&c->actor_net, B, c->mb_grad_logits, c->actor_params, c->actor_cache,
+                                               nullptr, c->actor_grads, c->workspace, st))) return rc;
             if (cfg.world_size > 1) {
                 if ((rc = allreduce_f32(c, c->actor_grads, (size_t)c->actor_p + 1))) return rc;
                 MRL_LAUNCH(scale_kernel, ceil_div(c->actor_p, 256), 256, 0, st, c->actor_grads, c->actor_p,
@@ -606,12 +634,17 @@ extern "C" int mrl_ppo_update(mrl_ctx* c, float actor_lr, float critic_lr, float
             MRL_LAUNCH(adam_ctx_kernel, ceil_div(c->actor_p, 256), 256, 0, st, c->actor_params, c->actor_grads,
                        c->actor_state, c->actor_p, actor_lr, cfg.adam_beta1, cfg.adam_beta2, cfg.adam_eps, c->counters);
             // ---- critic (ppo.mojo:2626-2728)
-            if ((rc = mlp_forward_impl(&c->critic_net, B, c->mb_obs, c->critic_params, c->mb_values, c->critic_cache,
-                                       c->workspace, st))) return rc;
+            if (c->use_tc) {
+                if ((rc = c->tc.forward(&c->critic_net, c->critic_params, c->mb_obs, c->mb_values, st))) return rc;
+            } else if ((rc = mlp_forward_impl(&c->critic_net, B, c->mb_obs, c->critic_params, c->mb_values,
+                                              c->critic_cache, c->workspace, st))) return rc;
             if ((rc = mrl_ppo_critic_grad(B, c->mb_values, c->mb_old_v, c->mb_ret, cfg.value_loss_coef,
                                           cfg.clip_epsilon, cfg.clip_value, c->mb_grad_values, st))) return rc;
-            if ((rc = mlp_backward_impl(&c->critic_net, B, c->mb_grad_values, c->critic_params, c->critic_cache,
-                                        nullptr, c->critic_grads, c->workspace, st))) return rc;
+            if (c->use_tc) {
+                if ((rc = c->tc.backward(&c->critic_net, c->critic_params, c->mb_obs, c->mb_grad_values,
+                                         c->critic_grads, st))) return rc;
+            } else if ((rc = mlp_backward_impl(&c->critic_net, B, c->mb_grad_values, c->critic_params, c->critic_cache,
+                                               nullptr, c->critic_grads, c->workspace, st))) return rc;
             if (cfg.world_size > 1) {
                 if ((rc = allreduce_f32(c, c->critic_grads, (size_t)c->critic_p))) return rc;
                 MRL_LAUNCH(scale_kernel, ceil_div(c->critic_p, 256), 256, 0, st, c->critic_grads, c->critic_p,
@@ -683,7 +716,13 @@ extern "C" int mrl_get_stats(mrl_ctx* c, mrl_stats* out) {
     MRL_CHECK_ARG(c && out);
     DeviceCounters h;
     MRL_CUDA_OK(cudaMemcpyAsync(&h, c->counters, sizeof(h), cudaMemcpyDeviceToHost, c->stream));
+    int tc_err_host = 0;
+    MRL_CUDA_OK(cudaMemcpyAsync(&tc_err_host, c->tc_err, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
     MRL_CUDA_OK(cudaStreamSynchronize(c->stream));
+    if (tc_err_host != 0) {
+        set_error("a tensor-core kernel gave up waiting (code %d): results of the last update are invalid", tc_err_host);
+        return MRL_ERR_TIMEOUT;
+    }
     out->total_steps = h.total_steps;
     out->completed_episodes = (int64_t)h.completed_episodes;
     out->sum_episode_reward = h.sum_episode_reward;

@@ -1,0 +1,724 @@
+// bf16 tensor-core path of the PPO update for hidden width 256 (LunarLander,
+// BipedalWalker): the three 256-wide GEMMs of a minibatch
+//     z1  = h0 . W1            (forward,  Linear[256,256] of linear_relu.mojo:134-219)
+//     dh0 = g1 . W1^T          (backward dX, linear_relu.mojo:355-396)
+//     dW1 = h0^T . g1          (backward dW, linear_relu.mojo:398-447)
+// run on tcgen05.mma with fp32 accumulators in TMEM, operands fetched by TMA
+// (128-byte swizzle); the thin layers (K = obs_dim, N = actions) and all
+// reductions stay on CUDA cores in fp32.  Activations are stored in bf16
+// (h0, h1, g1, g0) and twice where a GEMM needs them K-major (h0^T, g1^T).
+// The reference has no counterpart: its matmuls are fp32 16x16 tiles.
+#include "update_bf16.cuh"
+
+namespace mrl {
+namespace tc {
+
+using namespace umma;
+typedef __nv_bfloat16 bf16;
+
+constexpr int TILE_M = 128, KCH = 64;
+constexpr int NTHREADS = 192;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
+
+// ---------------------------------------------------------------- K1
+// D[128-row tile, 256] = A[tile rows, 256] . B^T with B [256 (n), 256 (k)]
+// resident in shared memory for the CTA's lifetime; A tiles stream through a
+// 4-deep ring; two TMEM accumulators overlap the epilogue with the next tile.
+constexpr int K1_STAGES = 4;
+constexpr int K1_B_BYTES = 4 * H * KCH * 2;           // 131072
+constexpr int K1_A_STAGE = TILE_M * KCH * 2;          // 16384
+constexpr int K1_PARAM_FLOATS = H + H * 8 + 8;        // bias, W2 (up to 8 outputs), b2
+constexpr int K1_BAR_OFF = K1_B_BYTES + K1_STAGES * K1_A_STAGE + K1_PARAM_FLOATS * 4;
+constexpr int K1_SMEM = K1_BAR_OFF + 16 * 8 + 1024;   // + barriers + alignment slack
+
+struct K1Params {
+    int M;
+    float* out_f32;                 // mode 0: D as fp32 [M, 256]
+    const float* bias;              // mode 1: b1
+    const float* W2; const float* b2; int out_dim; bf16* h1; float* head_out; int head_ld;
+    const bf16* h0; bf16* g0;       // mode 2: mask source and masked output
+    int* err;
+};
+
+__device__ __forceinline__ void drain_on_error(const int* err) {
+    if (*(volatile const int*)err != 0)
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // let copies in flight land before the CTA exits
+}
+
+template <int MODE, int OUT>
+__global__ void __launch_bounds__(NTHREADS, 1)
+k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, K1Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sB = smem;
+    uint8_t* sA = smem + K1_B_BYTES;
+    float* sP = (float*)(smem + K1_B_BYTES + K1_STAGES * K1_A_STAGE);
+    uint64_t* bars = (uint64_t*)(smem + K1_BAR_OFF);
+    uint64_t* b_full = bars;
+    uint64_t* a_full = bars + 1;
+    uint64_t* a_empty = bars + 1 + K1_STAGES;
+    uint64_t* t_full = bars + 1 + 2 * K1_STAGES;
+    uint64_t* t_empty = t_full + 2;
+    uint32_t* tmem_slot = (uint32_t*)(t_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_tiles = (p.M + TILE_M - 1) / TILE_M;
+
+    if (threadIdx.x == 0) {
+        mbar_init(b_full, 1);
+        for (int s = 0; s < K1_STAGES; ++s) { mbar_init(&a_full[s], 1); mbar_init(&a_empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&t_full[b], 1); mbar_init(&t_empty[b], 4); }
+        fence_barrier_init();
+        prefetch_tensormap(&tmA);
+        prefetch_tensormap(&tmB);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, 512);
+    if (warp >= 2 && MODE == 1) {
+        int t = threadIdx.x - 64;
+        for (int i = t; i < H; i += 128) sP[i] = p.bias[i];
+        for (int i = t; i < H * OUT; i += 128) {
+            int j = i / OUT, a = i % OUT;
+            sP[H + i] = a < p.out_dim ? p.W2[j * p.out_dim + a] : 0.0f;
+        }
+        if (t < OUT) sP[H + H * 8 + t] = t < p.out_dim ? p.b2[t] : 0.0f;
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(b_full, K1_B_BYTES);
+            for (int c = 0; c < 4; ++c) tma_load_2d(sB + c * (H * KCH * 2), &tmB, b_full, c * KCH, 0);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                for (int c = 0; c < 4 && ok; ++c, ++it) {
+                    int s = it % K1_STAGES;
+                    uint32_t ph = (it / K1_STAGES) & 1u;
+                    ok = mbar_wait(&a_empty[s], ph ^ 1u, p.err, 101);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(&a_full[s], K1_A_STAGE);
+                    tma_load_2d(sA + s * K1_A_STAGE, &tmA, &a_full[s], c * KCH, tile * TILE_M);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc_bf16_f32(TILE_M, H);
+            bool ok = mbar_wait(b_full, 0, p.err, 102);
+            uint32_t it = 0, lt = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
+                int buf = lt & 1;
+                ok = mbar_wait(&t_empty[buf], ((lt >> 1) & 1u) ^ 1u, p.err, 103);
+                if (!ok) break;
+                tc_fence_after_sync();
+                for (int c = 0; c < 4 && ok; ++c, ++it) {
+                    int s = it % K1_STAGES;
+                    uint32_t ph = (it / K1_STAGES) & 1u;
+                    ok = mbar_wait(&a_full[s], ph, p.err, 104);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    uint64_t da = make_kmajor_sw128_desc(sA + s * K1_A_STAGE);
+                    uint64_t db = make_kmajor_sw128_desc(sB + c * (H * KCH * 2));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        mma_bf16_ss(tmem_base + buf * H, da + 2 * k, db + 2 * k, idesc, (c | k) != 0 ? 1u : 0u);
+                    mma_commit(&a_empty[s]);
+                }
+                if (ok) mma_commit(&t_full[buf]);
+            }
+        }
+    } else {
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        uint32_t lt = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
+            int buf = lt & 1;
+            ok = mbar_wait(&t_full[buf], (lt >> 1) & 1u, p.err, 105);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int row = tile * TILE_M + q * 32 + lane;
+            const bool in_range = row < p.M;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * H;
+            float o[OUT];
+            if (MODE == 1) {
+#pragma unroll
+                for (int a = 0; a < OUT; ++a) o[a] = sP[H + H * 8 + a];
+            }
+#pragma unroll 1
+            for (int ch = 0; ch < 8; ++ch) {
+                float v[32];
+                tmem_ld_32x32(taddr + ch * 32, v);
+                if (MODE == 0) {
+                    if (in_range) {
+                        float4* dst = reinterpret_cast<float4*>(p.out_f32 + (size_t)row * H + ch * 32);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    }
+                } else {
+                    uint32_t packed[16];
+                    if (MODE == 1) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            int j = ch * 32 + i;
+                            float h_lo = fmaxf(v[i] + sP[j], 0.0f), h_hi = fmaxf(v[i + 1] + sP[j + 1], 0.0f);
+#pragma unroll
+                            for (int a = 0; a < OUT; ++a) {
+                                o[a] = fmaf(h_lo, sP[H + j * OUT + a], o[a]);
+                                o[a] = fmaf(h_hi, sP[H + (j + 1) * OUT + a], o[a]);
+                            }
+                            __nv_bfloat162 pk = __floats2bfloat162_rn(h_lo, h_hi);
+                            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
+                        }
+                    } else {
+                        uint4 hm[4];
+                        if (in_range) {
+                            const uint4* src = reinterpret_cast<const uint4*>(p.h0 + (size_t)row * H + ch * 32);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) hm[i] = src[i];
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) hm[i] = make_uint4(0, 0, 0, 0);
+                        }
+                        const uint32_t* hw = reinterpret_cast<const uint32_t*>(hm);
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            uint32_t w = hw[i >> 1];
+                            // bf16 > 0  <=>  sign bit clear and magnitude non-zero
+                            bool lo_pos = (w & 0x8000u) == 0 && (w & 0x7FFFu) != 0;
+                            bool hi_pos = (w & 0x80000000u) == 0 && (w & 0x7FFF0000u) != 0;
+                            __nv_bfloat162 pk = __floats2bfloat162_rn(lo_pos ? v[i] : 0.0f, hi_pos ? v[i + 1] : 0.0f);
+                            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
+                        }
+                    }
+                    if (in_range) {
+                        bf16* dstp = (MODE == 1 ? p.h1 : p.g0) + (size_t)row * H + ch * 32;
+                        uint4* dst = reinterpret_cast<uint4*>(dstp);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                    }
+                }
+            }
+            if (MODE == 1 && in_range) {
+                for (int a = 0; a < OUT; ++a)
+                    if (a < p.out_dim) p.head_out[(size_t)row * p.head_ld + a] = o[a];
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&t_empty[buf]);
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    drain_on_error(p.err);
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---------------------------------------------------------------- K2
+// Split-K: partial[cta] [256, 256] = A[256 (m), k-slice] . B[256 (n), k-slice]^T.
+// Both operands stream (3 stages of 2 x 32 KB); the two 128-row halves of the
+// output live in the two halves of TMEM.
+constexpr int K2_STAGES = 3;
+constexpr int K2_OP_BYTES = H * KCH * 2;              // 32768 per operand per stage
+constexpr int K2_BAR_OFF = K2_STAGES * 2 * K2_OP_BYTES;
+constexpr int K2_SMEM = K2_BAR_OFF + 16 * 8 + 1024;
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+k2_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int Ktot,
+                 int k_per_cta, float* __restrict__ partial, int* err) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + K2_BAR_OFF);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + K2_STAGES;
+    uint64_t* t_full = bars + 2 * K2_STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(t_full + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k0 = blockIdx.x * k_per_cta;
+    const int k1 = min(Ktot, k0 + k_per_cta);
+    const int nk = (k1 - k0 + KCH - 1) / KCH;  // host guarantees nk >= 1
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < K2_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(t_full, 1);
+        fence_barrier_init();
+        prefetch_tensormap(&tmA);
+        prefetch_tensormap(&tmB);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, 512);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            for (int it = 0; it < nk && ok; ++it) {
+                int s = it % K2_STAGES;
+                uint32_t ph = (it / K2_STAGES) & 1u;
+                ok = mbar_wait(&empty[s], ph ^ 1u, err, 201);
+                if (!ok) break;
+                mbar_arrive_expect_tx(&full[s], 2 * K2_OP_BYTES);
+                tma_load_2d(smem + s * 2 * K2_OP_BYTES, &tmA, &full[s], k0 + it * KCH, 0);
+                tma_load_2d(smem + s * 2 * K2_OP_BYTES + K2_OP_BYTES, &tmB, &full[s], k0 + it * KCH, 0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc_bf16_f32(TILE_M, H);
+            bool ok = true;
+            for (int it = 0; it < nk && ok; ++it) {
+                int s = it % K2_STAGES;
+                uint32_t ph = (it / K2_STAGES) & 1u;
+                ok = mbar_wait(&full[s], ph, err, 202);
+                if (!ok) break;
+                tc_fence_after_sync();
+                uint8_t* a = smem + s * 2 * K2_OP_BYTES;
+                uint64_t da0 = make_kmajor_sw128_desc(a);
+                uint64_t da1 = make_kmajor_sw128_desc(a + TILE_M * KCH * 2);
+                uint64_t db = make_kmajor_sw128_desc(a + K2_OP_BYTES);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    uint32_t acc = (it | k) != 0 ? 1u : 0u;
+                    mma_bf16_ss(tmem_base, da0 + 2 * k, db + 2 * k, idesc, acc);
+                    mma_bf16_ss(tmem_base + H, da1 + 2 * k, db + 2 * k, idesc, acc);
+                }
+                mma_commit(&empty[s]);
+            }
+            if (ok) mma_commit(t_full);
+        }
+    } else {
+        const int q = warp & 3;
+        if (mbar_wait(t_full, 0, err, 203)) {
+            tc_fence_after_sync();
+            float* out = partial + (size_t)blockIdx.x * H * H;
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+                const int m = half * TILE_M + q * 32 + lane;
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + half * H;
+#pragma unroll 1
+                for (int ch = 0; ch < 8; ++ch) {
+                    float v[32];
+                    tmem_ld_32x32(taddr + ch * 32, v);
+                    float4* dst = reinterpret_cast<float4*>(out + (size_t)m * H + ch * 32);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    drain_on_error(err);
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---------------------------------------------------------------- CUDA-core kernels
+
+// W1 fp32 [256 (i), 256 (j)] -> bf16 copies: w1[i][j] (K-major for dX, where k = j)
+// and w1t[j][i] (K-major for the forward pass, where k = i).
+__global__ void convert_w1_kernel(const float* __restrict__ W1, bf16* __restrict__ w1, bf16* __restrict__ w1t) {
+    __shared__ float tile[32][33];
+    int bx = blockIdx.x * 32, by = blockIdx.y * 32;
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        float v = W1[(size_t)(by + r) * H + bx + threadIdx.x];
+        tile[r][threadIdx.x] = v;
+        w1[(size_t)(by + r) * H + bx + threadIdx.x] = __float2bfloat16_rn(v);
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += blockDim.y)
+        w1t[(size_t)(bx + r) * H + by + threadIdx.x] = __float2bfloat16_rn(tile[threadIdx.x][r]);
+}
+
+__device__ __forceinline__ void store_row32_bf16(bf16* dst, const float (&v)[32]) {
+    uint4* d = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            __nv_bfloat162 pk = __floats2bfloat162_rn(v[8 * i + 2 * k], v[8 * i + 2 * k + 1]);
+            w[k] = *reinterpret_cast<uint32_t*>(&pk);
+        }
+        d[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+// First layer (LinearReLU[obs, 256], K = obs_dim): h0 = relu(x . W0 + b0), written
+// row-major [M, 256] and transposed [256, M].  One block = 32 rows, thread j = column j.
+template <int IN>
+__global__ void __launch_bounds__(H)
+l0_forward_kernel(const float* __restrict__ x, const float* __restrict__ W0, const float* __restrict__ b0,
+                  bf16* __restrict__ h0, bf16* __restrict__ h0t, int M) {
+    __shared__ float sx[32 * IN];
+    const int j = threadIdx.x;
+    const int r0 = blockIdx.x * 32;
+    for (int i = threadIdx.x; i < 32 * IN; i += H) {
+        int r = r0 + i / IN;
+        sx[i] = r < M ? x[(size_t)r0 * IN + i] : 0.0f;
+    }
+    float w[IN];
+#pragma unroll
+    for (int k = 0; k < IN; ++k) w[k] = W0[k * H + j];
+    const float b = b0[j];
+    __syncthreads();
+    float hv[32];
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {
+        float acc = b;
+#pragma unroll
+        for (int k = 0; k < IN; ++k) acc = fmaf(sx[r * IN + k], w[k], acc);
+        hv[r] = fmaxf(acc, 0.0f);
+        if (r0 + r < M) h0[(size_t)(r0 + r) * H + j] = __float2bfloat16_rn(hv[r]);
+    }
+    store_row32_bf16(h0t + (size_t)j * M + r0, hv);   // M % 32 == 0 on this path
+}
+
+// Head backward and everything that reduces over rows next to it:
+//   g1[r][j]  = h1[r][j] > 0 ? sum_a dout[r][a] * W2[j][a] : 0      (dX of the head, ReLU mask of layer 1)
+//   dW2[j][a] = sum_r h1[r][j] * dout[r][a],  db2[a] = sum_r dout[r][a],  db1[j] = sum_r g1[r][j]
+// One block walks rows_per_block rows in groups of 32; thread j owns column j.
+// part layout per block: [OUT][256] dW2^T, [256] db1, [OUT] db2.
+template <int OUT>
+__global__ void __launch_bounds__(H)
+head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout, int ldd,
+                     const float* __restrict__ W2, int out_dim, bf16* __restrict__ g1, bf16* __restrict__ g1t,
+                     float* __restrict__ part, int M, int rows_per_block) {
+    __shared__ float sd[32 * OUT];
+    const int j = threadIdx.x;
+    float w2[OUT], dw2[OUT];
+#pragma unroll
+    for (int a = 0; a < OUT; ++a) { w2[a] = a < out_dim ? W2[j * out_dim + a] : 0.0f; dw2[a] = 0.0f; }
+    float db1 = 0.0f, db2 = 0.0f;
+    const int rb = blockIdx.x * rows_per_block;
+    const int re = min(M, rb + rows_per_block);
+    for (int r0 = rb; r0 < re; r0 += 32) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < 32 * OUT; i += H) {
+            int r = r0 + i / OUT, a = i % OUT;
+            sd[i] = (r < re && a < out_dim) ? dout[(size_t)r * ldd + a] : 0.0f;
+        }
+        __syncthreads();
+        float gv[32];
+#pragma unroll
+        for (int r = 0; r < 32; ++r) {
+            float h = 0.0f;
+            if (r0 + r < re) h = __bfloat162float(h1[(size_t)(r0 + r) * H + j]);
+            float dh = 0.0f;
+#pragma unroll
+            for (int a = 0; a < OUT; ++a) {
+                float d = sd[r * OUT + a];
+                dh = fmaf(d, w2[a], dh);
+                dw2[a] = fmaf(h, d, dw2[a]);
+            }
+            float g = h > 0.0f ? dh : 0.0f;
+            gv[r] = g;
+            db1 += g;
+            if (r0 + r < re) g1[(size_t)(r0 + r) * H + j] = __float2bfloat16_rn(g);
+        }
+        store_row32_bf16(g1t + (size_t)j * M + r0, gv);
+        if (j < OUT) {
+#pragma unroll
+            for (int r = 0; r < 32; ++r) db2 += sd[r * OUT + j];
+        }
+    }
+    float* pb = part + (size_t)blockIdx.x * ((OUT + 1) * H + OUT);
+#pragma unroll
+    for (int a = 0; a < OUT; ++a) pb[a * H + j] = dw2[a];
+    pb[OUT * H + j] = db1;
+    if (j < OUT) pb[(OUT + 1) * H + j] = db2;
+}
+
+// dW0[k][j] = sum_r x[r][k] * g0[r][j], db0[j] = sum_r g0[r][j]; part per block: [IN + 1][256].
+template <int IN>
+__global__ void __launch_bounds__(H)
+l0_backward_kernel(const bf16* __restrict__ g0, const float* __restrict__ x, float* __restrict__ part, int M,
+                   int rows_per_block) {
+    __shared__ float sx[32 * IN];
+    const int j = threadIdx.x;
+    float dw[IN];
+#pragma unroll
+    for (int k = 0; k < IN; ++k) dw[k] = 0.0f;
+    float db = 0.0f;
+    const int rb = blockIdx.x * rows_per_block;
+    const int re = min(M, rb + rows_per_block);
+    for (int r0 = rb; r0 < re; r0 += 32) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < 32 * IN; i += H) {
+            int r = r0 + i / IN;
+            sx[i] = r < re ? x[(size_t)r0 * IN + i] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int r = 0; r < 32; ++r) {
+            if (r0 + r >= re) break;
+            float g = __bfloat162float(g0[(size_t)(r0 + r) * H + j]);
+            db += g;
+#pragma unroll
+            for (int k = 0; k < IN; ++k) dw[k] = fmaf(sx[r * IN + k], g, dw[k]);
+        }
+    }
+    float* pb = part + (size_t)blockIdx.x * (IN + 1) * H;
+#pragma unroll
+    for (int k = 0; k < IN; ++k) pb[k * H + j] = dw[k];
+    pb[IN * H + j] = db;
+}
+
+// out[i] = sum_b part[b * stride + i]  (b ascending: deterministic)
+__global__ void reduce_parts_kernel(const float* __restrict__ part, int nblocks, int stride, int n,
+                                    float* __restrict__ out) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float acc = 0.0f;
+    for (int b = 0; b < nblocks; ++b) acc += part[(size_t)b * stride + i];
+    out[i] = acc;
+}
+// Head parts -> dW2 [256][out_dim] (transposed from [OUT][256]), db2, and db1.
+__global__ void reduce_head_parts_kernel(const float* __restrict__ part, int nblocks, int OUT, int out_dim,
+                                         float* __restrict__ dW2, float* __restrict__ db2,
+                                         float* __restrict__ db1) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int stride = (OUT + 1) * H + OUT;
+    if (i >= stride) return;
+    float acc = 0.0f;
+    for (int b = 0; b < nblocks; ++b) acc += part[(size_t)b * stride + i];
+    if (i < OUT * H) {
+        int a = i / H, j = i % H;
+        if (a < out_dim) dW2[j * out_dim + a] = acc;
+    } else if (i < (OUT + 1) * H) {
+        db1[i - OUT * H] = acc;
+    } else {
+        int a = i - (OUT + 1) * H;
+        if (a < out_dim) db2[a] = acc;
+    }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+static int get_encode() {
+    if (g_encode) return MRL_OK;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    MRL_CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (!fn || qres != cudaDriverEntryPointSuccess) {
+        set_error("cuTensorMapEncodeTiled is not available from the driver");
+        return MRL_ERR_CUDA;
+    }
+    g_encode = (EncodeTiledFn)fn;
+    return MRL_OK;
+}
+
+// bf16 matrix [rows, cols] with cols contiguous; box = [box_rows, 64 cols], 128-byte swizzle.
+int make_tensor_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    int rc = get_encode();
+    if (rc) return rc;
+    if (((uintptr_t)base & 15) || ((cols * 2) & 15)) {
+        set_error("tensor map: base %p / row pitch %llu bytes not 16-byte aligned", base, (unsigned long long)cols * 2);
+        return MRL_ERR_INVALID_ARG;
+    }
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * 2};
+    cuuint32_t box[2] = {64, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed (%d) for [%llu x %llu]", (int)r, (unsigned long long)rows,
+                  (unsigned long long)cols);
+        return MRL_ERR_CUDA;
+    }
+    return MRL_OK;
+}
+
+static int g_sm_count = 0;
+static int sm_count() {
+    if (g_sm_count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (g_sm_count <= 0) g_sm_count = 148;
+    }
+    return g_sm_count;
+}
+
+template <int MODE, int OUT>
+static int launch_k1(const CUtensorMap& tmA, const CUtensorMap& tmB, const K1Params& p, cudaStream_t st) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        MRL_CUDA_OK(cudaFuncSetAttribute(k1_rowtile_kernel<MODE, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, K1_SMEM));
+        attr_set = true;
+    }
+    int tiles = (p.M + TILE_M - 1) / TILE_M;
+    int grid = tiles < sm_count() ? tiles : sm_count();
+    k1_rowtile_kernel<MODE, OUT><<<grid, NTHREADS, K1_SMEM, st>>>(tmA, tmB, p);
+    count_launch();
+    MRL_CUDA_OK(cudaGetLastError());
+    return MRL_OK;
+}
+
+static int launch_k1_forward(const CUtensorMap& tmA, const CUtensorMap& tmB, const K1Params& p, cudaStream_t st) {
+    if (p.out_dim <= 1) return launch_k1<1, 1>(tmA, tmB, p, st);
+    if (p.out_dim <= 2) return launch_k1<1, 2>(tmA, tmB, p, st);
+    if (p.out_dim <= 4) return launch_k1<1, 4>(tmA, tmB, p, st);
+    if (p.out_dim <= 8) return launch_k1<1, 8>(tmA, tmB, p, st);
+    set_error("bf16 path: head width %d > 8 is not built", p.out_dim);
+    return MRL_ERR_UNSUPPORTED;
+}
+
+static int launch_k2(const CUtensorMap& tmA, const CUtensorMap& tmB, int Ktot, float* partial, int* splits_out,
+                     int* err, cudaStream_t st) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        MRL_CUDA_OK(cudaFuncSetAttribute(k2_splitk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, K2_SMEM));
+        attr_set = true;
+    }
+    int chunks = (Ktot + KCH - 1) / KCH;
+    int splits = chunks < sm_count() ? chunks : sm_count();
+    int k_per_cta = ((chunks + splits - 1) / splits) * KCH;
+    splits = (Ktot + k_per_cta - 1) / k_per_cta;
+    k2_splitk_kernel<<<splits, NTHREADS, K2_SMEM, st>>>(tmA, tmB, Ktot, k_per_cta, partial, err);
+    count_launch();
+    MRL_CUDA_OK(cudaGetLastError());
+    *splits_out = splits;
+    return MRL_OK;
+}
+
+int max_splits() { return sm_count(); }
+
+bool supported(const mrl_net_spec* net, int batch) {
+    return net->hidden_dim == H && net->activation == MRL_ACT_RELU && net->head == MRL_HEAD_LINEAR &&
+           net->out_dim <= 8 && (net->in_dim == 4 || net->in_dim == 8 || net->in_dim == 24) && batch % 128 == 0;
+}
+
+int64_t workspace_bytes(int batch) {
+    int64_t act = (int64_t)batch * H * 2;                 // one bf16 activation array
+    int64_t parts = (int64_t)max_splits() * H * H * 4;    // K2 partials (also reused by the small reductions)
+    return 6 * act + 2 * (int64_t)H * H * 2 + parts + 4096;
+}
+
+int State::init(void* workspace, int batch_, int* err_flag) {
+    batch = batch_;
+    err = err_flag;
+    uint8_t* p = (uint8_t*)workspace;
+    int64_t act = (int64_t)batch * H * 2;
+    h0 = (bf16*)p; p += act;
+    h0t = (bf16*)p; p += act;
+    h1 = (bf16*)p; p += act;
+    g1 = (bf16*)p; p += act;
+    g1t = (bf16*)p; p += act;
+    g0 = (bf16*)p; p += act;
+    w1 = (bf16*)p; p += H * H * 2;
+    w1t = (bf16*)p; p += H * H * 2;
+    part = (float*)p;
+    int rc;
+    if ((rc = make_tensor_map(&tm_h0, h0, batch, H, TILE_M))) return rc;
+    if ((rc = make_tensor_map(&tm_g1, g1, batch, H, TILE_M))) return rc;
+    if ((rc = make_tensor_map(&tm_w1t, w1t, H, H, H))) return rc;
+    if ((rc = make_tensor_map(&tm_w1, w1, H, H, H))) return rc;
+    if ((rc = make_tensor_map(&tm_h0t, h0t, H, batch, H))) return rc;
+    if ((rc = make_tensor_map(&tm_g1t, g1t, H, batch, H))) return rc;
+    return MRL_OK;
+}
+
+template <int IN>
+static int l0_forward(const float* x, const float* W0, const float* b0, bf16* h0, bf16* h0t, int M, cudaStream_t st) {
+    MRL_LAUNCH((l0_forward_kernel<IN>), M / 32, H, 0, st, x, W0, b0, h0, h0t, M);
+    return MRL_OK;
+}
+
+int State::forward(const mrl_net_spec* net, const float* params, const float* x, float* head_out, cudaStream_t st) {
+    const int I = net->in_dim, O = net->out_dim;
+    const float* W0 = params; const float* b0 = W0 + (size_t)I * H;
+    const float* W1 = b0 + H; const float* b1 = W1 + (size_t)H * H;
+    const float* W2 = b1 + H; const float* b2 = W2 + (size_t)H * O;
+    MRL_LAUNCH(convert_w1_kernel, dim3(H / 32, H / 32), dim3(32, 8), 0, st, W1, w1, w1t);
+    int rc;
+    if (I == 4) rc = l0_forward<4>(x, W0, b0, h0, h0t, batch, st);
+    else if (I == 8) rc = l0_forward<8>(x, W0, b0, h0, h0t, batch, st);
+    else rc = l0_forward<24>(x, W0, b0, h0, h0t, batch, st);
+    if (rc) return rc;
+    K1Params p{};
+    p.M = batch; p.bias = b1; p.W2 = W2; p.b2 = b2; p.out_dim = O; p.h1 = h1; p.head_out = head_out; p.head_ld = O;
+    p.err = err;
+    return launch_k1_forward(tm_h0, tm_w1t, p, st);
+}
+
+int State::backward(const mrl_net_spec* net, const float* params, const float* x, const float* dout, float* grads,
+                    cudaStream_t st) {
+    const int I = net->in_dim, O = net->out_dim;
+    const size_t oW0 = 0, ob0 = (size_t)I * H, oW1 = ob0 + H, ob1 = oW1 + (size_t)H * H, oW2 = ob1 + H,
+                 ob2 = oW2 + (size_t)H * O;
+    const float* W2 = params + oW2;
+    const int rows_per_block = 512;
+    const int nblocks = (batch + rows_per_block - 1) / rows_per_block;
+    const int OUT = O <= 1 ? 1 : (O <= 2 ? 2 : (O <= 4 ? 4 : 8));
+    if (OUT == 1) { MRL_LAUNCH((head_backward_kernel<1>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, g1t, part, batch, rows_per_block); }
+    else if (OUT == 2) { MRL_LAUNCH((head_backward_kernel<2>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, g1t, part, batch, rows_per_block); }
+    else if (OUT == 4) { MRL_LAUNCH((head_backward_kernel<4>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, g1t, part, batch, rows_per_block); }
+    else { MRL_LAUNCH((head_backward_kernel<8>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, g1t, part, batch, rows_per_block); }
+    const int hstride = (OUT + 1) * H + OUT;
+    MRL_LAUNCH(reduce_head_parts_kernel, ceil_div(hstride, 256), 256, 0, st, part, nblocks, OUT, O, grads + oW2,
+               grads + ob2, grads + ob1);
+    // dh0 = g1 . W1^T, masked by h0 > 0 -> g0
+    K1Params p{};
+    p.M = batch; p.h0 = h0; p.g0 = g0; p.err = err;
+    int rc = launch_k1<2, 1>(tm_g1, tm_w1, p, st);
+    if (rc) return rc;
+    // dW0, db0
+    if (I == 4) { MRL_LAUNCH((l0_backward_kernel<4>), nblocks, H, 0, st, g0, x, part, batch, rows_per_block); }
+    else if (I == 8) { MRL_LAUNCH((l0_backward_kernel<8>), nblocks, H, 0, st, g0, x, part, batch, rows_per_block); }
+    else { MRL_LAUNCH((l0_backward_kernel<24>), nblocks, H, 0, st, g0, x, part, batch, rows_per_block); }
+    MRL_LAUNCH(reduce_parts_kernel, ceil_div((I + 1) * H, 256), 256, 0, st, part, nblocks, (I + 1) * H, (I + 1) * H,
+               grads + oW0);  // dW0 [I][256] then db0 [256] are adjacent in the gradient vector
+    // dW1 = h0^T . g1 (split-K over the SMs), then the fixed-order reduction
+    int splits = 0;
+    rc = launch_k2(tm_h0t, tm_g1t, batch, part, &splits, err, st);
+    if (rc) return rc;
+    MRL_LAUNCH(reduce_parts_kernel, ceil_div(H * H, 256), 256, 0, st, part, splits, H * H, H * H, grads + oW1);
+    return MRL_OK;
+}
+
+}  // namespace tc
+}  // namespace mrl
+
+using namespace mrl;
+
+// Building-block entry points (no counterpart in the reference, whose matmuls are
+// fp32 16x16 tiles, linear.mojo:135-225); used by the parity tests of the kernels.
+extern "C" int mrl_bf16_rowtile_gemm(int M, const void* A_bf16, const void* B_bf16, float* D, int* err_flag,
+                                     void* stream) {
+    MRL_CHECK_ARG(M > 0 && A_bf16 && B_bf16 && D && err_flag);
+    CUtensorMap ta, tb;
+    int rc;
+    if ((rc = tc::make_tensor_map(&ta, A_bf16, (uint64_t)M, tc::H, tc::TILE_M))) return rc;
+    if ((rc = tc::make_tensor_map(&tb, B_bf16, tc::H, tc::H, tc::H))) return rc;
+    tc::K1Params p{};
+    p.M = M; p.out_f32 = D; p.err = err_flag;
+    return tc::launch_k1<0, 1>(ta, tb, p, as_stream(stream));
+}
+
+extern "C" int mrl_bf16_splitk_gemm(int K, const void* A_bf16, const void* B_bf16, float* partial, int* splits,
+                                    int* err_flag, void* stream) {
+    MRL_CHECK_ARG(K > 0 && K % 8 == 0 && A_bf16 && B_bf16 && partial && splits && err_flag);
+    CUtensorMap ta, tb;
+    int rc;
+    if ((rc = tc::make_tensor_map(&ta, A_bf16, tc::H, (uint64_t)K, tc::H))) return rc;
+    if ((rc = tc::make_tensor_map(&tb, B_bf16, tc::H, (uint64_t)K, tc::H))) return rc;
+    return tc::launch_k2(ta, tb, K, partial, splits, err_flag, as_stream(stream));
+}
+
+extern "C" int mrl_bf16_max_splits(void) { return tc::max_splits(); }

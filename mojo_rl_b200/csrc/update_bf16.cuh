@@ -1,0 +1,36 @@
+// Host interface of the bf16 tensor-core update path (update_bf16.cu).
+#pragma once
+#include "umma.cuh"
+#include "ppo_kernels.cuh"
+
+namespace mrl {
+namespace tc {
+
+constexpr int H = 256;  // hidden width this path is specialised for
+
+// True when the network / minibatch shape is covered by the tensor-core kernels.
+bool supported(const mrl_net_spec* net, int batch);
+// Bytes of device workspace State::init needs for minibatches of `batch` rows.
+int64_t workspace_bytes(int batch);
+int max_splits();
+int make_tensor_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
+
+// Activation buffers, bf16 weight copies and TMA descriptors of one minibatch
+// shape; shared by the actor and the critic, which run one after the other.
+struct State {
+    int batch;
+    int* err;  // device word: 0, or the code of the first wait that gave up
+    __nv_bfloat16 *h0, *h0t, *h1, *g1, *g1t, *g0, *w1, *w1t;
+    float* part;
+    CUtensorMap tm_h0, tm_g1, tm_w1t, tm_w1, tm_h0t, tm_g1t;
+
+    int init(void* workspace, int batch, int* err_flag);
+    // head_out [batch, out_dim] = logits / values (fp32)
+    int forward(const mrl_net_spec* net, const float* params, const float* x, float* head_out, cudaStream_t st);
+    // grads [PARAM_SIZE] is overwritten (fp32, reference parameter order)
+    int backward(const mrl_net_spec* net, const float* params, const float* x, const float* dout, float* grads,
+                 cudaStream_t st);
+};
+
+}  // namespace tc
+}  // namespace mrl

@@ -1,0 +1,101 @@
+"""bf16 tcgen05 kernels of the precision-1 update: the two GEMM building blocks
+against an fp32 matmul of the same bf16 operands, and one whole PPO update in
+precision 1 against precision 0 (the bit-checked fp32 path)."""
+import ctypes
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _err_flag():
+    import torch
+    return torch.zeros(4, dtype=torch.int32, device="cuda")
+
+
+@pytest.mark.parametrize("M", [128, 300, 4096, 60000])
+def test_rowtile_gemm(M):
+    import torch
+    from _gpu import call, stream
+    torch.manual_seed(M)
+    A = torch.randn(M, 256, device="cuda").to(torch.bfloat16)
+    B = (torch.randn(256, 256, device="cuda") / 16).to(torch.bfloat16)
+    D = torch.full((M, 256), float("nan"), device="cuda")
+    err = _err_flag()
+    call("mrl_bf16_rowtile_gemm", M, A, B, D, err, stream())
+    torch.cuda.synchronize()
+    assert int(err[0]) == 0
+    want = A.float() @ B.float().t()
+    assert torch.isfinite(D).all()
+    assert torch.allclose(D, want, rtol=1e-4, atol=1e-4), float((D - want).abs().max())
+
+
+@pytest.mark.parametrize("K", [64, 640, 9472, 262144])
+def test_splitk_gemm(K):
+    import torch
+    from _gpu import call, stream
+    from mojo_rl_b200 import _lib
+    torch.manual_seed(K)
+    A = torch.randn(256, K, device="cuda").to(torch.bfloat16)
+    B = (torch.randn(256, K, device="cuda") / 16).to(torch.bfloat16)
+    ms = _lib.lib().mrl_bf16_max_splits()
+    part = torch.full((ms, 256, 256), float("nan"), device="cuda")
+    err = _err_flag()
+    splits = ctypes.c_int(0)
+    _lib.check(_lib.lib().mrl_bf16_splitk_gemm(K, _lib.ptr(A), _lib.ptr(B), _lib.ptr(part), ctypes.byref(splits),
+                                               _lib.ptr(err), stream()))
+    torch.cuda.synchronize()
+    assert int(err[0]) == 0 and 1 <= splits.value <= ms
+    got = part[:splits.value].sum(0)
+    want = A.float() @ B.float().t()
+    scale = float(want.abs().max())
+    assert torch.allclose(got, want, rtol=1e-3, atol=1e-4 * scale), float((got - want).abs().max())
+
+
+def test_update_precision1_matches_fp32_gradients():
+    """Same rollout, same permutation, one minibatch: the bf16 tensor-core update's
+    gradients agree with the fp32 path to bf16 accuracy, and training state advances."""
+    from _gpu import GpuAgent
+    from _util import NetSpec, default_config, xavier_params
+    rng = np.random.default_rng(0)
+    pa = xavier_params(NetSpec(8, 256, 4, 0, 0), rng) * 3
+    pc = xavier_params(NetSpec(8, 256, 1, 0, 0), rng)
+    total = 256 * 32
+    perms = rng.permutation(total).astype(np.int32)[None]
+    grads = {}
+    params = {}
+    for prec in (0, 1):
+        cfg = default_config(env_kind=2, n_envs=256, rollout_len=32, hidden_dim=256, minibatch_size=total,
+                             num_epochs=1, target_kl=0.0, precision=prec, max_grad_norm=0.0)
+        g = GpuAgent(cfg)
+        try:
+            g.set_params(0, pa, np.zeros(2 * pa.size, np.float32))
+            g.set_params(1, pc, np.zeros(2 * pc.size, np.float32))
+            g.reset(0); g.rollout(); g.gae()
+            g.update(3e-4, 1e-3, 0.01, perms)
+            st = g.stats()
+            assert st.minibatches_done == 1 and st.actor_adam_t == 1
+            grads[prec] = (g.buffer(12), g.buffer(13))
+            params[prec] = (g.get_params(0)[0], g.get_params(1)[0])
+        finally:
+            g.close()
+    for which in (0, 1):
+        a, b = grads[1][which], grads[0][which]
+        assert np.isfinite(a).all()
+        denom = np.abs(b).max()
+        assert np.abs(a - b).max() <= 3e-2 * denom, (which, np.abs(a - b).max(), denom)
+        # cosine similarity of the whole gradient
+        cos = float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b)))
+        assert cos > 0.999, (which, cos)
+        assert not np.array_equal(params[1][which], pa if which == 0 else pc)
+
+
+def test_precision1_rejects_unsupported_shapes():
+    from mojo_rl_b200 import _lib
+    from _util import default_config
+    L = _lib.lib()
+    cfg = default_config(env_kind=2, n_envs=256, rollout_len=32, hidden_dim=64, minibatch_size=1024, precision=1)
+    h = ctypes.c_void_p()
+    assert L.mrl_create(ctypes.byref(h), ctypes.byref(cfg)) == -4
+    assert b"precision 1" in L.mrl_last_error_string()
