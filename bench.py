@@ -155,6 +155,7 @@ def main():
     ap.add_argument("--precision", type=int, default=None, help="0 fp32, 1 bf16 tensor-core update")
     ap.add_argument("--n-envs", type=int, default=None, help="override envs per GPU (profiling of small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
     if args.n_envs:
@@ -252,15 +253,18 @@ def main():
         _lib.check(L.mrl_get_params(h, 1, _lib.ptr(pin[2]), _lib.ptr(pin[3])))
         return n
 
-    e2e_iteration()
-    barrier()
-    t0 = time.perf_counter()
     n_eps = 0
-    for _ in range(e2e_steps):
-        n_eps += e2e_iteration()
-    barrier()
-    e2e_s = time.perf_counter() - t0
-    if dist is not None:
+    if args.no_e2e:
+        e2e_s = float("nan")
+    else:
+        e2e_iteration()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            n_eps += e2e_iteration()
+        barrier()
+        e2e_s = time.perf_counter() - t0
+    if dist is not None and not args.no_e2e:
         t = torch.tensor([e2e_s], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())

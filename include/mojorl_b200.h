@@ -145,6 +145,10 @@ int mrl_bf16_rowtile_gemm(int M, const void* A_bf16, const void* B_bf16, float* 
                           void* stream);
 int mrl_bf16_splitk_gemm(int K, const void* A_bf16, const void* B_bf16, float* partial,
                          int* splits_host, int* err_flag, void* stream);
+/* splitk_tn: the same slices of X^T . G straight from row-major X, G [K, 256]
+ * (both operands MN-major for the tensor core; no transposed copies needed). */
+int mrl_bf16_splitk_gemm_tn(int K, const void* X_bf16, const void* G_bf16, float* partial,
+                            int* splits_host, int* err_flag, void* stream);
 int mrl_bf16_max_splits(void);
 
 /* ------------------------------------------------------------------------

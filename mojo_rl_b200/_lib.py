@@ -58,6 +58,8 @@ SIGNATURES = {
     "mrl_bf16_rowtile_gemm": (ctypes.c_int, [ctypes.c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "mrl_bf16_splitk_gemm": (ctypes.c_int, [ctypes.c_int, c_void_p, c_void_p, c_void_p, ctypes.POINTER(ctypes.c_int),
                                             c_void_p, c_void_p]),
+    "mrl_bf16_splitk_gemm_tn": (ctypes.c_int, [ctypes.c_int, c_void_p, c_void_p, c_void_p,
+                                               ctypes.POINTER(ctypes.c_int), c_void_p, c_void_p]),
     "mrl_bf16_max_splits": (ctypes.c_int, []),
     "mrl_sample_actions": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, c_void_p, c_void_p, c_void_p, ctypes.c_uint32, c_void_p]),
     "mrl_argmax_actions": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, c_void_p, c_void_p, c_void_p]),

@@ -11,6 +11,7 @@
 #include "env_cartpole.cuh"
 #include "env_lunar.cuh"
 #include "ppo_kernels.cuh"
+#include "rollout.cuh"
 #include "update_bf16.cuh"
 
 namespace mrl {
@@ -24,22 +25,6 @@ void set_error(const char* fmt, ...) {
     va_end(ap);
 }
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
-
-constexpr int EP_RING = 1 << 16;
-
-// Device-resident counters shared by the phases.
-struct DeviceCounters {
-    long long total_steps;
-    unsigned long long completed_episodes;
-    double sum_episode_reward, sum_episode_steps;
-    unsigned long long ring_head;  // episodes ever pushed; ring index = head % EP_RING
-    int kl_stop;
-    int minibatches_done;
-    float last_mean_kl;
-    int actor_t, critic_t;
-    float bc1, bc2;  // bias corrections of the optimiser step about to run
-    int adam_skip;   // 1: the step about to run is skipped (KL stop)
-};
 
 // ---- NCCL through dlopen: the library loads (and every single-GPU path runs)
 // on machines without NCCL.
@@ -93,6 +78,7 @@ struct mrl_ctx {
     float *actor_cache, *critic_cache, *workspace;
     int32_t* perm;
     double* stats;  // 8 doubles of reduction scratch
+    double* kl_partial;  // 256 block sums of the minibatch KL
     bool use_tc;    // precision == 1: update GEMMs on tcgen05 tensor cores in bf16
     mrl::tc::State tc;
     uint8_t* tc_workspace;
@@ -129,7 +115,8 @@ __global__ void rollout_pre_step_kernel(const float* __restrict__ logits, const 
                                         int greedy) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    uint32_t seed = (uint32_t)((unsigned long long)ctr->total_steps * 2654435761ull + (unsigned long long)t * 7919ull);
+    unsigned long long ts = (unsigned long long)ctr->total_steps + (unsigned long long)t * (unsigned long long)n;  // total_steps at step t
+    uint32_t seed = (uint32_t)(ts * 2654435761ull + (unsigned long long)t * 7919ull);
     float a, lp;
     sample_one(logits + (size_t)i * A, A, seed, i, greedy, a, lp);
     actions[i] = a;
@@ -140,68 +127,8 @@ __global__ void rollout_pre_step_kernel(const float* __restrict__ logits, const 
     for (int d = 0; d < obs_dim; ++d) r_obs[off * obs_dim + d] = obs[(size_t)i * obs_dim + d];
 }
 
-// _store_post_step_kernel + accumulate_rewards + increment_steps +
-// extract_completed_episodes + selective_reset_tracking (ppo.mojo:692-708,
-// deep_rl/gpu/rl_kernels.mojo:103-230).  Completed episodes go to a device
-// ring instead of a per-step D->H copy.
-__global__ void rollout_post_step_kernel(const float* __restrict__ rewards, const float* __restrict__ dones,
-                                         float* __restrict__ r_rewards, float* __restrict__ r_dones,
-                                         float* __restrict__ episode_rewards, float* __restrict__ episode_steps,
-                                         float* __restrict__ ring_returns, float* __restrict__ ring_lengths,
-                                         DeviceCounters* __restrict__ ctr, int t, int n) {
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    float r = rewards[i], d = dones[i];
-    size_t off = (size_t)t * n + i;
-    r_rewards[off] = r;
-    r_dones[off] = d;
-    float er = episode_rewards[i] + r;
-    float es = episode_steps[i] + 1.0f;
-    if (d > 0.5f) {
-        unsigned long long slot = atomicAdd(&ctr->ring_head, 1ull);
-        ring_returns[slot % EP_RING] = er;
-        ring_lengths[slot % EP_RING] = es;
-        atomicAdd(&ctr->completed_episodes, 1ull);
-        atomicAdd(&ctr->sum_episode_reward, (double)er);
-        atomicAdd(&ctr->sum_episode_steps, (double)es);
-        er = 0.0f;
-        es = 0.0f;
-    }
-    episode_rewards[i] = er;
-    episode_steps[i] = es;
-}
+__global__ void add_total_steps_kernel(DeviceCounters* ctr, long long n) { ctr->total_steps += n; }
 
-__global__ void add_total_steps_kernel(DeviceCounters* ctr, int n) { ctr->total_steps += n; }
-
-// Selective reset with the seed of ppo.mojo:2275, then _extract_obs_from_state
-// (ppo.mojo:712-736).  total_steps has already been advanced.
-__global__ void cartpole_auto_reset_kernel(float* __restrict__ states, float* __restrict__ dones,
-                                           float* __restrict__ obs, const DeviceCounters* __restrict__ ctr,
-                                           int t, int n) {
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    if (!(dones[i] < 0.5f)) {
-        unsigned long long seed64 = (unsigned long long)ctr->total_steps * 1013904223ull + (unsigned long long)t * 2654435761ull;
-        float s[4];
-        cartpole::reset(s, (uint32_t)((unsigned long long)i * 2654435761ull + (uint32_t)seed64));
-        float4 v = make_float4(s[0], s[1], s[2], s[3]);
-        reinterpret_cast<float4*>(states)[i] = v;
-        reinterpret_cast<float4*>(obs)[i] = v;
-        dones[i] = 0.0f;
-    }
-}
-__global__ void lunar_auto_reset_kernel(float* __restrict__ states, const float* __restrict__ dones,
-                                        float* __restrict__ obs, const DeviceCounters* __restrict__ ctr,
-                                        int t, int n) {
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    if (dones[i] > 0.5f) {
-        unsigned long long seed64 = (unsigned long long)ctr->total_steps * 1013904223ull + (unsigned long long)t * 2654435761ull;
-        float* s = states + (size_t)i * lunar::STATE_SIZE;
-        lunar::reset_row(s, lunar::combined_seed((float)seed64, i));
-        for (int d = 0; d < lunar::OBS_DIM; ++d) obs[(size_t)i * lunar::OBS_DIM + d] = s[d];
-    }
-}
 __global__ void extract_obs_kernel(const float* __restrict__ states, float* __restrict__ obs, int n,
                                    int state_size, int obs_dim) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -256,10 +183,17 @@ __global__ void begin_update_kernel(DeviceCounters* ctr) {
 
 // Sum of the per-sample KL values into grads_tail[0] (f32, like the host loop of
 // ppo.mojo:2556-2559 but tree-ordered).
-__global__ void kl_sum_kernel(const float* __restrict__ kl, int n, float* __restrict__ out) {
+__global__ void kl_partial_kernel(const float* __restrict__ kl, int n, double* __restrict__ partial) {
     __shared__ double sm[32];
     double acc = 0.0;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) acc += (double)kl[i];
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) acc += (double)kl[i];
+    acc = block_sum(acc, sm);
+    if (threadIdx.x == 0) partial[blockIdx.x] = acc;
+}
+__global__ void kl_final_kernel(const double* __restrict__ partial, int nparts, float* __restrict__ out) {
+    __shared__ double sm[32];
+    double acc = 0.0;
+    for (int i = threadIdx.x; i < nparts; i += blockDim.x) acc += partial[i];
     acc = block_sum(acc, sm);
     if (threadIdx.x == 0) out[0] = (float)acc;
 }
@@ -321,11 +255,6 @@ struct PhaseTimer {
     }
     ~PhaseTimer() { if (stop) cudaEventRecord(stop, c->stream); }
 };
-
-static int env_step_launch(mrl_ctx* c) {
-    return mrl_env_step(c->cfg.env_kind, c->cfg.n_envs, c->states, c->actions, c->rewards, c->dones, c->obs, 0,
-                        c->stream);
-}
 
 static int allreduce_f32(mrl_ctx* c, float* buf, size_t n) {
     if (c->cfg.world_size <= 1) return MRL_OK;
@@ -420,6 +349,7 @@ extern "C" int mrl_create(mrl_ctx** out, const mrl_config* cfg) {
     A_(workspace, (size_t)ws);
     A_(perm, T * N);
     A_(stats, 8);
+    A_(kl_partial, 256);
     A_(counters, 1);
     A_(tc_err, 4);
     c->use_tc = false;
@@ -545,19 +475,11 @@ extern "C" int mrl_ppo_rollout(mrl_ctx* c) {
         MRL_LAUNCH(rollout_pre_step_kernel, ceil_div(N, 128), 128, 0, st, c->logits, c->values, c->obs, c->actions,
                    c->r_obs, c->r_actions, c->r_log_probs, c->r_values, c->counters, t, N, A, c->obs_dim,
                    c->cfg.deterministic);
-        if ((rc = env_step_launch(c))) return rc;
-        MRL_LAUNCH(rollout_post_step_kernel, ceil_div(N, 128), 128, 0, st, c->rewards, c->dones, c->r_rewards,
-                   c->r_dones, c->episode_rewards, c->episode_steps, c->ring_returns, c->ring_lengths, c->counters,
-                   t, N);
-        MRL_LAUNCH(add_total_steps_kernel, 1, 1, 0, st, c->counters, N);
-        if (c->cfg.env_kind == MRL_ENV_CARTPOLE) {
-            MRL_LAUNCH(cartpole_auto_reset_kernel, ceil_div(N, 128), 128, 0, st, c->states, c->dones, c->obs,
-                       c->counters, t, N);
-        } else {
-            MRL_LAUNCH(lunar_auto_reset_kernel, ceil_div(N, 128), 128, 0, st, c->states, c->dones, c->obs,
-                       c->counters, t, N);
-        }
+        RolloutStepArgs ra{c->states, c->actions, c->rewards, c->dones, c->obs, c->r_rewards, c->r_dones,
+                           c->episode_rewards, c->episode_steps, c->ring_returns, c->ring_lengths, c->counters, t, N};
+        if ((rc = rollout_env_step(c->cfg.env_kind, ra, st))) return rc;
     }
+    MRL_LAUNCH(add_total_steps_kernel, 1, 1, 0, st, c->counters, (long long)T * N);
     return MRL_OK;
 }
 
@@ -615,7 +537,11 @@ extern "C" int mrl_ppo_update(mrl_ctx* c, float actor_lr, float critic_lr, float
                                               c->actor_cache, c->workspace, st))) return rc;
             if ((rc = mrl_ppo_actor_grad(B, A, c->mb_logits, c->mb_old_lp, c->mb_adv, c->mb_actions, cfg.clip_epsilon,
                                          entropy_coef, c->mb_grad_logits, c->mb_kl, st))) return rc;
-            MRL_LAUNCH(kl_sum_kernel, 1, 1024, 0, st, c->mb_kl, B, c->actor_grads + c->actor_p);
+            {
+                int parts = ceil_div(B, 1024) < 256 ? ceil_div(B, 1024) : 256;
+                MRL_LAUNCH(kl_partial_kernel, parts, 256, 0, st, c->mb_kl, B, c->kl_partial);
+                MRL_LAUNCH(kl_final_kernel, 1, 256, 0, st, c->kl_partial, parts, c->actor_grads + c->actor_p);
+            }
             if (c->use_tc) {
                 if ((rc = c->tc.backward(&c->actor_net, c->actor_params, c->mb_obs, c->mb_grad_logits, c->actor_grads,
                                          st))) return rc;

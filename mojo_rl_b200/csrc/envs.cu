@@ -3,6 +3,7 @@
 // Compile with -fmad=false (bit-level parity with the CPU checker).
 #include "env_cartpole.cuh"
 #include "env_lunar.cuh"
+#include "rollout.cuh"
 
 namespace mrl {
 
@@ -44,37 +45,113 @@ __global__ void cartpole_selective_reset_kernel(float* __restrict__ states, floa
 }
 
 // ------------------------------------------------------------- LunarLander
-__global__ void __launch_bounds__(ENV_TPB)
-lunar_step_rows_kernel(float* __restrict__ states, const float* __restrict__ actions,
-                       float* __restrict__ rewards, float* __restrict__ dones,
-                       float* __restrict__ obs, int n) {
-    int env = blockIdx.x * blockDim.x + threadIdx.x;
-    if (env >= n) return;
-    float* s = states + (size_t)env * lunar::STATE_SIZE;
+// The reference row is 192 floats (768 B) per environment, so a thread that
+// walks its own row issues strided, uncoalesced loads.  Each block instead
+// copies its rows into shared memory with coalesced loads (row pitch 193 floats:
+// consecutive environments fall into consecutive banks), steps every
+// environment there, and copies the rows back.
+constexpr int LUNAR_TPB = 64;
+constexpr int LUNAR_PITCH = lunar::STATE_SIZE + 1;
+constexpr int LUNAR_SMEM = LUNAR_TPB * LUNAR_PITCH * 4;
+
+__device__ __forceinline__ void lunar_rows_to_smem(const float* __restrict__ states, float* sm, int env0, int n) {
+    const int rows = min(LUNAR_TPB, n - env0);
+    const float* src = states + (size_t)env0 * lunar::STATE_SIZE;
+    for (int i = threadIdx.x; i < rows * lunar::STATE_SIZE; i += blockDim.x) {
+        int r = i / lunar::STATE_SIZE, k = i - r * lunar::STATE_SIZE;
+        sm[r * LUNAR_PITCH + k] = src[i];
+    }
+}
+__device__ __forceinline__ void lunar_rows_from_smem(float* __restrict__ states, const float* sm, int env0, int n) {
+    const int rows = min(LUNAR_TPB, n - env0);
+    float* dst = states + (size_t)env0 * lunar::STATE_SIZE;
+    for (int i = threadIdx.x; i < rows * lunar::STATE_SIZE; i += blockDim.x) {
+        int r = i / lunar::STATE_SIZE, k = i - r * lunar::STATE_SIZE;
+        dst[i] = sm[r * LUNAR_PITCH + k];
+    }
+}
+
+// One step of one environment whose row lives at s (lunar_lander_v2.mojo:1453-1517).
+__device__ __forceinline__ void lunar_step_row(float* s, int env, int action, float& reward, float& done) {
     lunar::Env e;
     lunar::load_row(s, e);
-    int action = (int)actions[env];
     lunar::apply_engines(e, env, action);
     lunar::RowEdges edges{s};
     phys::Contacts<lunar::MAX_CONTACTS> c;
     lunar::physics_step(e, edges, c);
     float o[lunar::OBS_DIM];
     bool obs_written;
-    float reward, done;
     lunar::finalize(e, edges, c, action, o, obs_written, reward, done);
     lunar::store_row(s, e);
     if (obs_written) {
 #pragma unroll
         for (int d = 0; d < lunar::OBS_DIM; ++d) s[d] = o[d];
-    } else {
-#pragma unroll
-        for (int d = 0; d < lunar::OBS_DIM; ++d) o[d] = s[d];
     }
-    float4* ob = reinterpret_cast<float4*>(obs + (size_t)env * lunar::OBS_DIM);
-    ob[0] = make_float4(o[0], o[1], o[2], o[3]);
-    ob[1] = make_float4(o[4], o[5], o[6], o[7]);
-    rewards[env] = reward;
-    dones[env] = done;
+}
+
+__global__ void __launch_bounds__(LUNAR_TPB)
+lunar_step_rows_kernel(float* __restrict__ states, const float* __restrict__ actions,
+                       float* __restrict__ rewards, float* __restrict__ dones,
+                       float* __restrict__ obs, int n) {
+    extern __shared__ float sm[];
+    const int env0 = blockIdx.x * LUNAR_TPB;
+    lunar_rows_to_smem(states, sm, env0, n);
+    __syncthreads();
+    const int env = env0 + threadIdx.x;
+    if (env < n) {
+        float* s = sm + threadIdx.x * LUNAR_PITCH;
+        float reward, done;
+        lunar_step_row(s, env, (int)actions[env], reward, done);
+        float4* ob = reinterpret_cast<float4*>(obs + (size_t)env * lunar::OBS_DIM);
+        ob[0] = make_float4(s[0], s[1], s[2], s[3]);
+        ob[1] = make_float4(s[4], s[5], s[6], s[7]);
+        rewards[env] = reward;
+        dones[env] = done;
+    }
+    __syncthreads();
+    lunar_rows_from_smem(states, sm, env0, n);
+}
+
+// Rollout step: step, store, episode tracking, selective reset, observation.
+__global__ void __launch_bounds__(LUNAR_TPB) lunar_rollout_step_kernel(RolloutStepArgs a) {
+    extern __shared__ float sm[];
+    const int env0 = blockIdx.x * LUNAR_TPB;
+    lunar_rows_to_smem(a.states, sm, env0, a.n);
+    __syncthreads();
+    const int env = env0 + threadIdx.x;
+    if (env < a.n) {
+        float* s = sm + threadIdx.x * LUNAR_PITCH;
+        float reward, done;
+        lunar_step_row(s, env, (int)a.actions[env], reward, done);
+        a.rewards[env] = reward;
+        a.dones[env] = done;  // the reference's selective reset leaves the flag set (:1643-1701)
+        track_episode(a, env, reward, done);
+        if (done > 0.5f) lunar::reset_row(s, lunar::combined_seed((float)auto_reset_seed(a), env));
+        float4* ob = reinterpret_cast<float4*>(a.obs + (size_t)env * lunar::OBS_DIM);
+        ob[0] = make_float4(s[0], s[1], s[2], s[3]);
+        ob[1] = make_float4(s[4], s[5], s[6], s[7]);
+    }
+    __syncthreads();
+    lunar_rows_from_smem(a.states, sm, env0, a.n);
+}
+
+__global__ void cartpole_rollout_step_kernel(RolloutStepArgs a) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.n) return;
+    float4 v = reinterpret_cast<float4*>(a.states)[i];
+    float s[4] = {v.x, v.y, v.z, v.w};
+    bool done = cartpole::step(s, (int)a.actions[i]);
+    float d = done ? 1.0f : 0.0f;
+    a.rewards[i] = 1.0f;
+    track_episode(a, i, 1.0f, d);
+    if (done) {  // cartpole.mojo:838-905: reset and clear the flag
+        cartpole::reset(s, (uint32_t)((unsigned long long)i * 2654435761ull + (uint32_t)auto_reset_seed(a)));
+        d = 0.0f;
+    }
+    a.dones[i] = d;
+    float4 o = make_float4(s[0], s[1], s[2], s[3]);
+    reinterpret_cast<float4*>(a.states)[i] = o;
+    reinterpret_cast<float4*>(a.obs)[i] = o;
 }
 
 __global__ void lunar_reset_rows_kernel(float* __restrict__ states, const float* __restrict__ dones,
@@ -83,6 +160,31 @@ __global__ void lunar_reset_rows_kernel(float* __restrict__ states, const float*
     if (env >= n) return;
     if (dones != nullptr && !(dones[env] > 0.5f)) return;  // dones are not cleared (:1643-1701)
     lunar::reset_row(states + (size_t)env * lunar::STATE_SIZE, lunar::combined_seed(seed_f32, env));
+}
+
+static cudaError_t ensure_lunar_smem() {
+    static bool done = false;
+    if (done) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(lunar_step_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LUNAR_SMEM);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(lunar_rollout_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LUNAR_SMEM);
+    if (e == cudaSuccess) done = true;
+    return e;
+}
+
+int rollout_env_step(int env_kind, const RolloutStepArgs& a, cudaStream_t st) {
+    switch (env_kind) {
+        case MRL_ENV_CARTPOLE:
+            MRL_LAUNCH(cartpole_rollout_step_kernel, ceil_div(a.n, 128), 128, 0, st, a);
+            return MRL_OK;
+        case MRL_ENV_LUNAR_LANDER:
+            MRL_CUDA_OK(ensure_lunar_smem());
+            MRL_LAUNCH(lunar_rollout_step_kernel, ceil_div(a.n, LUNAR_TPB), LUNAR_TPB, LUNAR_SMEM, st, a);
+            return MRL_OK;
+        default:
+            set_error("rollout: env kind %d is not built", env_kind);
+            return MRL_ERR_UNSUPPORTED;
+    }
 }
 
 }  // namespace mrl
@@ -134,7 +236,8 @@ extern "C" int mrl_env_step(int env_kind, int batch, float* states, const float*
                        dones, obs, batch);
             return MRL_OK;
         case MRL_ENV_LUNAR_LANDER:
-            MRL_LAUNCH(lunar_step_rows_kernel, ceil_div(batch, ENV_TPB), ENV_TPB, 0, st, states, actions,
+            MRL_CUDA_OK(ensure_lunar_smem());
+            MRL_LAUNCH(lunar_step_rows_kernel, ceil_div(batch, LUNAR_TPB), LUNAR_TPB, LUNAR_SMEM, st, states, actions,
                        rewards, dones, obs, batch);
             return MRL_OK;
         default:

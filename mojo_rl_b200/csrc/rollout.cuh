@@ -1,0 +1,80 @@
+// Shared between agent.cu (phase drivers) and envs.cu (fused environment
+// kernels of the rollout): the device-resident counters and the per-step
+// argument block of the fused "step + store + track + auto-reset" kernels.
+#pragma once
+#include "common.cuh"
+
+namespace mrl {
+
+constexpr int EP_RING = 1 << 16;
+
+// Device-resident counters shared by the phases.
+struct DeviceCounters {
+    long long total_steps;
+    unsigned long long completed_episodes;
+    double sum_episode_reward, sum_episode_steps;
+    unsigned long long ring_head;  // episodes ever pushed; ring index = head % EP_RING
+    int kl_stop;
+    int minibatches_done;
+    float last_mean_kl;
+    int actor_t, critic_t;
+    float bc1, bc2;  // bias corrections of the optimiser step about to run
+    int adam_skip;   // 1: the step about to run is skipped (KL stop)
+};
+
+// One rollout step after the policy has chosen actions (ppo.mojo:2147-2285):
+// env step, _store_post_step_kernel, accumulate_rewards / increment_steps /
+// extract_completed_episodes / selective_reset_tracking
+// (deep_rl/gpu/rl_kernels.mojo:103-230), selective reset with the seed of
+// ppo.mojo:2275 and _extract_obs_from_state.  total_steps in the counters is the
+// value at the start of the rollout; step t sees total_steps + t * n before and
+// + (t + 1) * n after the increment of ppo.mojo:2194.
+struct RolloutStepArgs {
+    float* states;
+    const float* actions;
+    float* rewards;
+    float* dones;
+    float* obs;
+    float* r_rewards;  // [T, n]
+    float* r_dones;
+    float* episode_rewards;
+    float* episode_steps;
+    float* ring_returns;
+    float* ring_lengths;
+    DeviceCounters* ctr;
+    int t;
+    int n;
+};
+
+// Launches the fused step kernel of `env_kind` (envs.cu).
+int rollout_env_step(int env_kind, const RolloutStepArgs& a, cudaStream_t st);
+
+// Episode bookkeeping of one environment after its step; returns the updated
+// accumulators through the pointers.
+__device__ __forceinline__ void track_episode(const RolloutStepArgs& a, int i, float r, float d) {
+    size_t off = (size_t)a.t * a.n + i;
+    a.r_rewards[off] = r;
+    a.r_dones[off] = d;
+    float er = a.episode_rewards[i] + r;
+    float es = a.episode_steps[i] + 1.0f;
+    if (d > 0.5f) {
+        unsigned long long slot = atomicAdd(&a.ctr->ring_head, 1ull);
+        a.ring_returns[slot % EP_RING] = er;
+        a.ring_lengths[slot % EP_RING] = es;
+        atomicAdd(&a.ctr->completed_episodes, 1ull);
+        atomicAdd(&a.ctr->sum_episode_reward, (double)er);
+        atomicAdd(&a.ctr->sum_episode_steps, (double)es);
+        er = 0.0f;
+        es = 0.0f;
+    }
+    a.episode_rewards[i] = er;
+    a.episode_steps[i] = es;
+}
+
+// UInt64(total_steps * 1013904223 + t * 2654435761) with total_steps already advanced (ppo.mojo:2275).
+__device__ __forceinline__ unsigned long long auto_reset_seed(const RolloutStepArgs& a) {
+    unsigned long long ts = (unsigned long long)a.ctr->total_steps + (unsigned long long)(a.t + 1) * (unsigned long long)a.n;
+    return ts * 1013904223ull + (unsigned long long)a.t * 2654435761ull;
+}
+
+}  // namespace mrl

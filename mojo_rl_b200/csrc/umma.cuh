@@ -102,9 +102,20 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(const void* smem_tile
            | (1ull << 46)           // descriptor version of sm_100
            | (2ull << 61);          // SWIZZLE_128B
 }
-// Instruction descriptor: bf16 A and B (both K-major), fp32 accumulator, M x N tile.
-__host__ __device__ constexpr uint32_t make_idesc_bf16_f32(int M, int N) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+// Shared-memory matrix descriptor of an MN-major bf16 operand: the tile is stored
+// as K rows of 64 MN-elements (128 bytes, 128-byte swizzle), i.e. what a TMA load
+// of a [k rows, 64 mn] box of a row-major [K, MN] matrix produces.  Eight k-rows
+// form one swizzle atom (1024 B apart = stride byte offset); the next 64 MN
+// elements come from another box, `mn_atom_bytes` further (leading byte offset).
+__device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(const void* smem_tile, uint32_t mn_atom_bytes) {
+    uint64_t addr = (uint64_t)(smem_u32(smem_tile) & 0x3FFFFu) >> 4;
+    return addr | ((uint64_t)(mn_atom_bytes >> 4) << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: bf16 A and B, fp32 accumulator, M x N tile; mn_major
+// sets both operands to MN-major (bits 15 and 16), otherwise both are K-major.
+__host__ __device__ constexpr uint32_t make_idesc_bf16_f32(int M, int N, bool mn_major = false) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (mn_major ? ((1u << 15) | (1u << 16)) : 0u) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 // D[tmem] (+)= A[smem] * B[smem]^T, one K=16 step.  Issued by one thread.

@@ -5,8 +5,8 @@
 //     dW1 = h0^T . g1          (backward dW, linear_relu.mojo:398-447)
 // run on tcgen05.mma with fp32 accumulators in TMEM, operands fetched by TMA
 // (128-byte swizzle); the thin layers (K = obs_dim, N = actions) and all
-// reductions stay on CUDA cores in fp32.  Activations are stored in bf16
-// (h0, h1, g1, g0) and twice where a GEMM needs them K-major (h0^T, g1^T).
+// reductions stay on CUDA cores in fp32.  Activations are stored once, in bf16
+// and row-major (h0, h1, g1, g0): the dW GEMM reads them as MN-major operands.
 // The reference has no counterpart: its matmuls are fp32 16x16 tiles.
 #include "update_bf16.cuh"
 
@@ -228,6 +228,10 @@ constexpr int K2_OP_BYTES = H * KCH * 2;              // 32768 per operand per s
 constexpr int K2_BAR_OFF = K2_STAGES * 2 * K2_OP_BYTES;
 constexpr int K2_SMEM = K2_BAR_OFF + 16 * 8 + 1024;
 
+// MN_MAJOR: the operands are the row-major activations themselves, A = X[K, 256]
+// and B = G[K, 256] (partial = X^T . G); each operand stage is then four
+// [64 k-rows, 64 columns] boxes of 8 KB.
+template <bool MN_MAJOR>
 __global__ void __launch_bounds__(NTHREADS, 1)
 k2_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int Ktot,
                  int k_per_cta, float* __restrict__ partial, int* err) {
@@ -265,13 +269,21 @@ k2_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 ok = mbar_wait(&empty[s], ph ^ 1u, err, 201);
                 if (!ok) break;
                 mbar_arrive_expect_tx(&full[s], 2 * K2_OP_BYTES);
-                tma_load_2d(smem + s * 2 * K2_OP_BYTES, &tmA, &full[s], k0 + it * KCH, 0);
-                tma_load_2d(smem + s * 2 * K2_OP_BYTES + K2_OP_BYTES, &tmB, &full[s], k0 + it * KCH, 0);
+                uint8_t* sa = smem + s * 2 * K2_OP_BYTES;
+                if (MN_MAJOR) {
+                    for (int b = 0; b < 4; ++b) {
+                        tma_load_2d(sa + b * 8192, &tmA, &full[s], b * 64, k0 + it * KCH);
+                        tma_load_2d(sa + K2_OP_BYTES + b * 8192, &tmB, &full[s], b * 64, k0 + it * KCH);
+                    }
+                } else {
+                    tma_load_2d(sa, &tmA, &full[s], k0 + it * KCH, 0);
+                    tma_load_2d(sa + K2_OP_BYTES, &tmB, &full[s], k0 + it * KCH, 0);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = make_idesc_bf16_f32(TILE_M, H);
+            const uint32_t idesc = make_idesc_bf16_f32(TILE_M, H, MN_MAJOR);
             bool ok = true;
             for (int it = 0; it < nk && ok; ++it) {
                 int s = it % K2_STAGES;
@@ -280,14 +292,24 @@ k2_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (!ok) break;
                 tc_fence_after_sync();
                 uint8_t* a = smem + s * 2 * K2_OP_BYTES;
-                uint64_t da0 = make_kmajor_sw128_desc(a);
-                uint64_t da1 = make_kmajor_sw128_desc(a + TILE_M * KCH * 2);
-                uint64_t db = make_kmajor_sw128_desc(a + K2_OP_BYTES);
+                uint64_t da0, da1, db;
+                uint32_t kstep;  // descriptor advance per K = 16 step, in 16-byte units
+                if (MN_MAJOR) {
+                    da0 = make_mnmajor_sw128_desc(a, 8192);              // columns   0..127 of X
+                    da1 = make_mnmajor_sw128_desc(a + 2 * 8192, 8192);   // columns 128..255 of X
+                    db = make_mnmajor_sw128_desc(a + K2_OP_BYTES, 8192);
+                    kstep = (16 * 128) >> 4;                             // 16 k-rows of 128 bytes
+                } else {
+                    da0 = make_kmajor_sw128_desc(a);
+                    da1 = make_kmajor_sw128_desc(a + TILE_M * KCH * 2);
+                    db = make_kmajor_sw128_desc(a + K2_OP_BYTES);
+                    kstep = 2;                                           // 16 elements = 32 bytes
+                }
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     uint32_t acc = (it | k) != 0 ? 1u : 0u;
-                    mma_bf16_ss(tmem_base, da0 + 2 * k, db + 2 * k, idesc, acc);
-                    mma_bf16_ss(tmem_base + H, da1 + 2 * k, db + 2 * k, idesc, acc);
+                    mma_bf16_ss(tmem_base, da0 + kstep * k, db + kstep * k, idesc, acc);
+                    mma_bf16_ss(tmem_base + H, da1 + kstep * k, db + kstep * k, idesc, acc);
                 }
                 mma_commit(&empty[s]);
             }
@@ -354,11 +376,11 @@ __device__ __forceinline__ void store_row32_bf16(bf16* dst, const float (&v)[32]
 }
 
 // First layer (LinearReLU[obs, 256], K = obs_dim): h0 = relu(x . W0 + b0), written
-// row-major [M, 256] and transposed [256, M].  One block = 32 rows, thread j = column j.
+// row-major [M, 256] in bf16.  One block = 32 rows, thread j = column j.
 template <int IN>
 __global__ void __launch_bounds__(H)
 l0_forward_kernel(const float* __restrict__ x, const float* __restrict__ W0, const float* __restrict__ b0,
-                  bf16* __restrict__ h0, bf16* __restrict__ h0t, int M) {
+                  bf16* __restrict__ h0, int M) {
     __shared__ float sx[32 * IN];
     const int j = threadIdx.x;
     const int r0 = blockIdx.x * 32;
@@ -371,16 +393,13 @@ l0_forward_kernel(const float* __restrict__ x, const float* __restrict__ W0, con
     for (int k = 0; k < IN; ++k) w[k] = W0[k * H + j];
     const float b = b0[j];
     __syncthreads();
-    float hv[32];
 #pragma unroll
     for (int r = 0; r < 32; ++r) {
         float acc = b;
 #pragma unroll
         for (int k = 0; k < IN; ++k) acc = fmaf(sx[r * IN + k], w[k], acc);
-        hv[r] = fmaxf(acc, 0.0f);
-        if (r0 + r < M) h0[(size_t)(r0 + r) * H + j] = __float2bfloat16_rn(hv[r]);
+        if (r0 + r < M) h0[(size_t)(r0 + r) * H + j] = __float2bfloat16_rn(fmaxf(acc, 0.0f));
     }
-    store_row32_bf16(h0t + (size_t)j * M + r0, hv);   // M % 32 == 0 on this path
 }
 
 // Head backward and everything that reduces over rows next to it:
@@ -391,7 +410,7 @@ l0_forward_kernel(const float* __restrict__ x, const float* __restrict__ W0, con
 template <int OUT>
 __global__ void __launch_bounds__(H)
 head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout, int ldd,
-                     const float* __restrict__ W2, int out_dim, bf16* __restrict__ g1, bf16* __restrict__ g1t,
+                     const float* __restrict__ W2, int out_dim, bf16* __restrict__ g1,
                      float* __restrict__ part, int M, int rows_per_block) {
     __shared__ float sd[32 * OUT];
     const int j = threadIdx.x;
@@ -408,8 +427,7 @@ head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout
             sd[i] = (r < re && a < out_dim) ? dout[(size_t)r * ldd + a] : 0.0f;
         }
         __syncthreads();
-        float gv[32];
-#pragma unroll
+#pragma unroll 8
         for (int r = 0; r < 32; ++r) {
             float h = 0.0f;
             if (r0 + r < re) h = __bfloat162float(h1[(size_t)(r0 + r) * H + j]);
@@ -421,11 +439,9 @@ head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout
                 dw2[a] = fmaf(h, d, dw2[a]);
             }
             float g = h > 0.0f ? dh : 0.0f;
-            gv[r] = g;
             db1 += g;
             if (r0 + r < re) g1[(size_t)(r0 + r) * H + j] = __float2bfloat16_rn(g);
         }
-        store_row32_bf16(g1t + (size_t)j * M + r0, gv);
         if (j < OUT) {
 #pragma unroll
             for (int r = 0; r < 32; ++r) db2 += sd[r * OUT + j];
@@ -579,18 +595,19 @@ static int launch_k1_forward(const CUtensorMap& tmA, const CUtensorMap& tmB, con
     return MRL_ERR_UNSUPPORTED;
 }
 
+template <bool MN_MAJOR>
 static int launch_k2(const CUtensorMap& tmA, const CUtensorMap& tmB, int Ktot, float* partial, int* splits_out,
                      int* err, cudaStream_t st) {
     static bool attr_set = false;
     if (!attr_set) {
-        MRL_CUDA_OK(cudaFuncSetAttribute(k2_splitk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, K2_SMEM));
+        MRL_CUDA_OK(cudaFuncSetAttribute(k2_splitk_kernel<MN_MAJOR>, cudaFuncAttributeMaxDynamicSharedMemorySize, K2_SMEM));
         attr_set = true;
     }
     int chunks = (Ktot + KCH - 1) / KCH;
     int splits = chunks < sm_count() ? chunks : sm_count();
     int k_per_cta = ((chunks + splits - 1) / splits) * KCH;
     splits = (Ktot + k_per_cta - 1) / k_per_cta;
-    k2_splitk_kernel<<<splits, NTHREADS, K2_SMEM, st>>>(tmA, tmB, Ktot, k_per_cta, partial, err);
+    k2_splitk_kernel<MN_MAJOR><<<splits, NTHREADS, K2_SMEM, st>>>(tmA, tmB, Ktot, k_per_cta, partial, err);
     count_launch();
     MRL_CUDA_OK(cudaGetLastError());
     *splits_out = splits;
@@ -601,13 +618,13 @@ int max_splits() { return sm_count(); }
 
 bool supported(const mrl_net_spec* net, int batch) {
     return net->hidden_dim == H && net->activation == MRL_ACT_RELU && net->head == MRL_HEAD_LINEAR &&
-           net->out_dim <= 8 && (net->in_dim == 4 || net->in_dim == 8 || net->in_dim == 24) && batch % 128 == 0;
+           net->out_dim <= 8 && (net->in_dim == 4 || net->in_dim == 8 || net->in_dim == 24) && batch % 32 == 0;
 }
 
 int64_t workspace_bytes(int batch) {
     int64_t act = (int64_t)batch * H * 2;                 // one bf16 activation array
     int64_t parts = (int64_t)max_splits() * H * H * 4;    // K2 partials (also reused by the small reductions)
-    return 6 * act + 2 * (int64_t)H * H * 2 + parts + 4096;
+    return 4 * act + 2 * (int64_t)H * H * 2 + parts + 4096;
 }
 
 int State::init(void* workspace, int batch_, int* err_flag) {
@@ -616,10 +633,8 @@ int State::init(void* workspace, int batch_, int* err_flag) {
     uint8_t* p = (uint8_t*)workspace;
     int64_t act = (int64_t)batch * H * 2;
     h0 = (bf16*)p; p += act;
-    h0t = (bf16*)p; p += act;
     h1 = (bf16*)p; p += act;
     g1 = (bf16*)p; p += act;
-    g1t = (bf16*)p; p += act;
     g0 = (bf16*)p; p += act;
     w1 = (bf16*)p; p += H * H * 2;
     w1t = (bf16*)p; p += H * H * 2;
@@ -629,14 +644,14 @@ int State::init(void* workspace, int batch_, int* err_flag) {
     if ((rc = make_tensor_map(&tm_g1, g1, batch, H, TILE_M))) return rc;
     if ((rc = make_tensor_map(&tm_w1t, w1t, H, H, H))) return rc;
     if ((rc = make_tensor_map(&tm_w1, w1, H, H, H))) return rc;
-    if ((rc = make_tensor_map(&tm_h0t, h0t, H, batch, H))) return rc;
-    if ((rc = make_tensor_map(&tm_g1t, g1t, H, batch, H))) return rc;
+    if ((rc = make_tensor_map(&tm_h0_mn, h0, batch, H, 64))) return rc;
+    if ((rc = make_tensor_map(&tm_g1_mn, g1, batch, H, 64))) return rc;
     return MRL_OK;
 }
 
 template <int IN>
-static int l0_forward(const float* x, const float* W0, const float* b0, bf16* h0, bf16* h0t, int M, cudaStream_t st) {
-    MRL_LAUNCH((l0_forward_kernel<IN>), M / 32, H, 0, st, x, W0, b0, h0, h0t, M);
+static int l0_forward(const float* x, const float* W0, const float* b0, bf16* h0, int M, cudaStream_t st) {
+    MRL_LAUNCH((l0_forward_kernel<IN>), (M + 31) / 32, H, 0, st, x, W0, b0, h0, M);
     return MRL_OK;
 }
 
@@ -647,9 +662,9 @@ int State::forward(const mrl_net_spec* net, const float* params, const float* x,
     const float* W2 = b1 + H; const float* b2 = W2 + (size_t)H * O;
     MRL_LAUNCH(convert_w1_kernel, dim3(H / 32, H / 32), dim3(32, 8), 0, st, W1, w1, w1t);
     int rc;
-    if (I == 4) rc = l0_forward<4>(x, W0, b0, h0, h0t, batch, st);
-    else if (I == 8) rc = l0_forward<8>(x, W0, b0, h0, h0t, batch, st);
-    else rc = l0_forward<24>(x, W0, b0, h0, h0t, batch, st);
+    if (I == 4) rc = l0_forward<4>(x, W0, b0, h0, batch, st);
+    else if (I == 8) rc = l0_forward<8>(x, W0, b0, h0, batch, st);
+    else rc = l0_forward<24>(x, W0, b0, h0, batch, st);
     if (rc) return rc;
     K1Params p{};
     p.M = batch; p.bias = b1; p.W2 = W2; p.b2 = b2; p.out_dim = O; p.h1 = h1; p.head_out = head_out; p.head_ld = O;
@@ -666,10 +681,10 @@ int State::backward(const mrl_net_spec* net, const float* params, const float* x
     const int rows_per_block = 512;
     const int nblocks = (batch + rows_per_block - 1) / rows_per_block;
     const int OUT = O <= 1 ? 1 : (O <= 2 ? 2 : (O <= 4 ? 4 : 8));
-    if (OUT == 1) { MRL_LAUNCH((head_backward_kernel<1>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, g1t, part, batch, rows_per_block); }
-    else if (OUT == 2) { MRL_LAUNCH((head_backward_kernel<2>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, g1t, part, batch, rows_per_block); }
-    else if (OUT == 4) { MRL_LAUNCH((head_backward_kernel<4>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, g1t, part, batch, rows_per_block); }
-    else { MRL_LAUNCH((head_backward_kernel<8>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, g1t, part, batch, rows_per_block); }
+    if (OUT == 1) { MRL_LAUNCH((head_backward_kernel<1>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
+    else if (OUT == 2) { MRL_LAUNCH((head_backward_kernel<2>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
+    else if (OUT == 4) { MRL_LAUNCH((head_backward_kernel<4>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
+    else { MRL_LAUNCH((head_backward_kernel<8>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
     const int hstride = (OUT + 1) * H + OUT;
     MRL_LAUNCH(reduce_head_parts_kernel, ceil_div(hstride, 256), 256, 0, st, part, nblocks, OUT, O, grads + oW2,
                grads + ob2, grads + ob1);
@@ -686,7 +701,7 @@ int State::backward(const mrl_net_spec* net, const float* params, const float* x
                grads + oW0);  // dW0 [I][256] then db0 [256] are adjacent in the gradient vector
     // dW1 = h0^T . g1 (split-K over the SMs), then the fixed-order reduction
     int splits = 0;
-    rc = launch_k2(tm_h0t, tm_g1t, batch, part, &splits, err, st);
+    rc = launch_k2<true>(tm_h0_mn, tm_g1_mn, batch, part, &splits, err, st);
     if (rc) return rc;
     MRL_LAUNCH(reduce_parts_kernel, ceil_div(H * H, 256), 256, 0, st, part, splits, H * H, H * H, grads + oW1);
     return MRL_OK;
@@ -718,7 +733,19 @@ extern "C" int mrl_bf16_splitk_gemm(int K, const void* A_bf16, const void* B_bf1
     int rc;
     if ((rc = tc::make_tensor_map(&ta, A_bf16, tc::H, (uint64_t)K, tc::H))) return rc;
     if ((rc = tc::make_tensor_map(&tb, B_bf16, tc::H, (uint64_t)K, tc::H))) return rc;
-    return tc::launch_k2(ta, tb, K, partial, splits, err_flag, as_stream(stream));
+    return tc::launch_k2<false>(ta, tb, K, partial, splits, err_flag, as_stream(stream));
+}
+
+// Same product from the row-major activations: partial slices of X^T . G with
+// X, G bf16 [K, 256] (both operands MN-major for the tensor core).
+extern "C" int mrl_bf16_splitk_gemm_tn(int K, const void* X_bf16, const void* G_bf16, float* partial, int* splits,
+                                       int* err_flag, void* stream) {
+    MRL_CHECK_ARG(K > 0 && X_bf16 && G_bf16 && partial && splits && err_flag);
+    CUtensorMap ta, tb;
+    int rc;
+    if ((rc = tc::make_tensor_map(&ta, X_bf16, (uint64_t)K, tc::H, 64))) return rc;
+    if ((rc = tc::make_tensor_map(&tb, G_bf16, (uint64_t)K, tc::H, 64))) return rc;
+    return tc::launch_k2<true>(ta, tb, K, partial, splits, err_flag, as_stream(stream));
 }
 
 extern "C" int mrl_bf16_max_splits(void) { return tc::max_splits(); }

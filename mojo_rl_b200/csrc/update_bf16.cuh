@@ -20,9 +20,9 @@ int make_tensor_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t co
 struct State {
     int batch;
     int* err;  // device word: 0, or the code of the first wait that gave up
-    __nv_bfloat16 *h0, *h0t, *h1, *g1, *g1t, *g0, *w1, *w1t;
+    __nv_bfloat16 *h0, *h1, *g1, *g0, *w1, *w1t;
     float* part;
-    CUtensorMap tm_h0, tm_g1, tm_w1t, tm_w1, tm_h0t, tm_g1t;
+    CUtensorMap tm_h0, tm_g1, tm_w1t, tm_w1, tm_h0_mn, tm_g1_mn;
 
     int init(void* workspace, int batch, int* err_flag);
     // head_out [batch, out_dim] = logits / values (fp32)

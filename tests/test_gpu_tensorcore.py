@@ -53,6 +53,28 @@ def test_splitk_gemm(K):
     assert torch.allclose(got, want, rtol=1e-3, atol=1e-4 * scale), float((got - want).abs().max())
 
 
+@pytest.mark.parametrize("K", [64, 704, 262144])
+def test_splitk_gemm_from_row_major_activations(K):
+    import torch
+    from _gpu import stream
+    from mojo_rl_b200 import _lib
+    torch.manual_seed(K + 1)
+    X = torch.randn(K, 256, device="cuda").to(torch.bfloat16)
+    G = (torch.randn(K, 256, device="cuda") / 16).to(torch.bfloat16)
+    ms = _lib.lib().mrl_bf16_max_splits()
+    part = torch.full((ms, 256, 256), float("nan"), device="cuda")
+    err = _err_flag()
+    splits = ctypes.c_int(0)
+    _lib.check(_lib.lib().mrl_bf16_splitk_gemm_tn(K, _lib.ptr(X), _lib.ptr(G), _lib.ptr(part), ctypes.byref(splits),
+                                                  _lib.ptr(err), stream()))
+    torch.cuda.synchronize()
+    assert int(err[0]) == 0 and 1 <= splits.value <= ms
+    got = part[:splits.value].sum(0)
+    want = X.float().t() @ G.float()
+    scale = float(want.abs().max())
+    assert torch.allclose(got, want, rtol=1e-3, atol=1e-4 * scale), float((got - want).abs().max())
+
+
 def test_update_precision1_matches_fp32_gradients():
     """Same rollout, same permutation, one minibatch: the bf16 tensor-core update's
     gradients agree with the fp32 path to bf16 accuracy, and training state advances."""
