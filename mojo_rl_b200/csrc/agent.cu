@@ -82,6 +82,9 @@ struct mrl_ctx {
     bool use_tc;    // precision == 1: update GEMMs on tcgen05 tensor cores in bf16
     mrl::tc::State tc;
     uint8_t* tc_workspace;
+    bool use_tc_policy;  // precision == 1 and the rollout policy kernel covers this shape
+    mrl::tc::PolicyState policy;
+    uint8_t* policy_workspace;
     int* tc_err;    // device word written by a kernel whose bounded wait gave up
     DeviceCounters* counters;
     ncclComm_t comm;
@@ -353,6 +356,7 @@ extern "C" int mrl_create(mrl_ctx** out, const mrl_config* cfg) {
     A_(counters, 1);
     A_(tc_err, 4);
     c->use_tc = false;
+    c->use_tc_policy = false;
     if (cfg->precision == 1) {
         if (!tc::supported(&c->actor_net, (int)B) || !tc::supported(&c->critic_net, (int)B)) {
             set_error("precision 1 (bf16 tensor-core update) needs hidden_dim 256, ReLU nets, obs_dim in {4, 8, 24}, "
@@ -364,6 +368,12 @@ extern "C" int mrl_create(mrl_ctx** out, const mrl_config* cfg) {
         rc = c->tc.init(c->tc_workspace, (int)B, c->tc_err);
         if (rc) { mrl_destroy(c); return rc; }
         c->use_tc = true;
+        if (tc::policy_supported(od, na, cfg->hidden_dim)) {
+            A_(policy_workspace, (size_t)tc::policy_workspace_bytes());
+            rc = c->policy.init(c->policy_workspace, c->tc_err);
+            if (rc) { mrl_destroy(c); return rc; }
+            c->use_tc_policy = true;
+        }
     } else if (cfg->precision != 0) {
         set_error("precision must be 0 (fp32) or 1 (bf16 tensor-core update)");
         mrl_destroy(c);
@@ -469,12 +479,22 @@ extern "C" int mrl_ppo_rollout(mrl_ctx* c) {
     cudaStream_t st = c->stream;
     int rc;
     PhaseTimer timer(c, 0);
+    if (c->use_tc_policy) {
+        if ((rc = c->policy.prepare(c->actor_params, c->critic_params, c->obs_dim, st))) return rc;
+    }
     for (int t = 0; t < T; ++t) {
-        if ((rc = mlp_forward_impl(&c->actor_net, N, c->obs, c->actor_params, c->logits, nullptr, c->workspace, st))) return rc;
-        if ((rc = mlp_forward_impl(&c->critic_net, N, c->obs, c->critic_params, c->values, nullptr, c->workspace, st))) return rc;
-        MRL_LAUNCH(rollout_pre_step_kernel, ceil_div(N, 128), 128, 0, st, c->logits, c->values, c->obs, c->actions,
-                   c->r_obs, c->r_actions, c->r_log_probs, c->r_values, c->counters, t, N, A, c->obs_dim,
-                   c->cfg.deterministic);
+        if (c->use_tc_policy) {
+            tc::PolicyStepArgs pa{c->obs, c->actor_params, c->critic_params, N, c->obs_dim, A, t, c->cfg.deterministic,
+                                  c->actions, c->values, c->r_obs, c->r_actions, c->r_log_probs, c->r_values,
+                                  c->counters};
+            if ((rc = c->policy.step(pa, st))) return rc;
+        } else {
+            if ((rc = mlp_forward_impl(&c->actor_net, N, c->obs, c->actor_params, c->logits, nullptr, c->workspace, st))) return rc;
+            if ((rc = mlp_forward_impl(&c->critic_net, N, c->obs, c->critic_params, c->values, nullptr, c->workspace, st))) return rc;
+            MRL_LAUNCH(rollout_pre_step_kernel, ceil_div(N, 128), 128, 0, st, c->logits, c->values, c->obs, c->actions,
+                       c->r_obs, c->r_actions, c->r_log_probs, c->r_values, c->counters, t, N, A, c->obs_dim,
+                       c->cfg.deterministic);
+        }
         RolloutStepArgs ra{c->states, c->actions, c->rewards, c->dones, c->obs, c->r_rewards, c->r_dones,
                            c->episode_rewards, c->episode_steps, c->ring_returns, c->ring_lengths, c->counters, t, N};
         if ((rc = rollout_env_step(c->cfg.env_kind, ra, st))) return rc;

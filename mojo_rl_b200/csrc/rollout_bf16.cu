@@ -1,0 +1,248 @@
+// Rollout policy step on tensor cores (precision 1, hidden width 256):
+// one launch evaluates actor and critic for every environment and finishes the
+// pre-step work of the rollout (ppo.mojo:2069-2145):
+//   actor.forward_gpu_no_cache_ws, critic.forward_gpu_no_cache_ws,
+//   _sample_actions_kernel, _store_pre_step_kernel.
+// Grid = (row tiles of 128 environments, 2 networks).  Per CTA:
+//   1. TMA brings the network's W1^T (bf16, 128 KB) into shared memory;
+//   2. meanwhile all threads compute h0 = relu(obs . W0 + b0) for the tile on CUDA
+//      cores (K = obs_dim) and write it as bf16 in the 128-byte-swizzled K-major
+//      layout the tensor core reads;
+//   3. one thread issues 16 tcgen05.mma (128 x 256 x 16) into TMEM;
+//   4. four warps read the accumulators, add b1, apply ReLU, contract with W2 in
+//      fp32 (logits / value), then the actor's threads sample the action.
+// The fp32 path (precision 0) keeps the reference's summation order instead.
+#include "rollout.cuh"
+#include "update_bf16.cuh"
+
+namespace mrl {
+namespace tc {
+
+using namespace umma;
+typedef __nv_bfloat16 bf16;
+
+constexpr int P_THREADS = 256;
+constexpr int P_TILE = 128;
+constexpr int P_B_BYTES = H * H * 2;            // 131072: W1^T as four [256 x 64] chunks
+constexpr int P_A_BYTES = P_TILE * H * 2;       // 65536: h0 tile as four [128 x 64] chunks
+constexpr int P_MAX_IN = 8;
+constexpr int P_MAX_OUT = 4;
+// fp32 parameters in shared memory: W0 [IN][256], b0, b1, W2 [256][OUT], b2
+constexpr int P_PARAM_FLOATS = P_MAX_IN * H + H + H + H * P_MAX_OUT + P_MAX_OUT;
+constexpr int P_BAR_OFF = P_B_BYTES + P_A_BYTES + P_PARAM_FLOATS * 4;
+constexpr int P_SMEM = P_BAR_OFF + 64 + 1024;
+
+struct PolicyArgs {
+    const float* obs;            // [n, IN]
+    const float* params[2];      // fp32 parameter vectors of actor, critic
+    int n, in_dim, num_actions, t, greedy;
+    float* actions;              // [n]
+    float* values;               // [n]
+    float* r_obs; float* r_actions; float* r_log_probs; float* r_values;  // [T, n, ...]
+    const DeviceCounters* ctr;
+    int* err;
+};
+
+template <int IN>
+__global__ void __launch_bounds__(P_THREADS, 1)
+rollout_policy_kernel(const __grid_constant__ CUtensorMap tm_actor_w1t,
+                      const __grid_constant__ CUtensorMap tm_critic_w1t, PolicyArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sB = smem;
+    uint8_t* sA = smem + P_B_BYTES;
+    float* sW0 = (float*)(smem + P_B_BYTES + P_A_BYTES);
+    float* sb0 = sW0 + P_MAX_IN * H;
+    float* sb1 = sb0 + H;
+    float* sW2 = sb1 + H;
+    float* sb2 = sW2 + H * P_MAX_OUT;
+    uint64_t* b_full = (uint64_t*)(smem + P_BAR_OFF);
+    uint64_t* t_full = b_full + 1;
+    uint32_t* tmem_slot = (uint32_t*)(t_full + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int net = blockIdx.y;
+    const int out_dim = net == 0 ? a.num_actions : 1;
+    const CUtensorMap* tmB = net == 0 ? &tm_actor_w1t : &tm_critic_w1t;
+    const float* prm = a.params[net];
+    const float* W0 = prm;
+    const float* b0 = W0 + IN * H;
+    const float* b1 = b0 + H + H * H;
+    const float* W2 = b1 + H;
+    const float* b2 = W2 + H * out_dim;
+    const int row0 = blockIdx.x * P_TILE;
+
+    if (threadIdx.x == 0) {
+        mbar_init(b_full, 1);
+        mbar_init(t_full, 1);
+        fence_barrier_init();
+        prefetch_tensormap(tmB);
+        mbar_arrive_expect_tx(b_full, P_B_BYTES);
+        for (int c = 0; c < 4; ++c) tma_load_2d(sB + c * (H * 64 * 2), tmB, b_full, c * 64, 0);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, 256);
+    for (int i = threadIdx.x; i < IN * H; i += P_THREADS) sW0[i] = W0[i];
+    for (int i = threadIdx.x; i < H; i += P_THREADS) { sb0[i] = b0[i]; sb1[i] = b1[i]; }
+    for (int i = threadIdx.x; i < H * P_MAX_OUT; i += P_THREADS) {
+        int j = i / P_MAX_OUT, o = i % P_MAX_OUT;
+        sW2[i] = o < out_dim ? W2[j * out_dim + o] : 0.0f;
+    }
+    if (threadIdx.x < P_MAX_OUT) sb2[threadIdx.x] = threadIdx.x < out_dim ? b2[threadIdx.x] : 0.0f;
+    __syncthreads();
+
+    // ---- h0 tile: thread -> (row, half of the 256 columns)
+    {
+        const int r = threadIdx.x & (P_TILE - 1);
+        const int half = threadIdx.x >> 7;
+        const int row = row0 + r;
+        float x[IN];
+#pragma unroll
+        for (int k = 0; k < IN; ++k) x[k] = row < a.n ? a.obs[(size_t)row * IN + k] : 0.0f;
+#pragma unroll 2
+        for (int c8 = 0; c8 < 16; ++c8) {
+            const int j0 = half * 128 + c8 * 8;
+            float h[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                float acc = sb0[j0 + u];
+#pragma unroll
+                for (int k = 0; k < IN; ++k) acc = fmaf(x[k], sW0[k * H + j0 + u], acc);
+                h[u] = fmaxf(acc, 0.0f);
+            }
+            uint32_t w[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                __nv_bfloat162 pk = __floats2bfloat162_rn(h[2 * u], h[2 * u + 1]);
+                w[u] = *reinterpret_cast<uint32_t*>(&pk);
+            }
+            // K-major, 128-byte swizzle: 64-column chunk kc, 16-byte unit (j % 64) / 8 XOR (row % 8)
+            const int kc = j0 >> 6, unit = (j0 & 63) >> 3;
+            uint8_t* dst = sA + kc * (P_TILE * 128) + r * 128 + ((unit ^ (r & 7)) << 4);
+            *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+    fence_proxy_async_smem();  // the tensor core reads sA through the async proxy
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        if (mbar_wait(b_full, 0, a.err, 301)) {
+            const uint32_t idesc = make_idesc_bf16_f32(P_TILE, H);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint64_t da = make_kmajor_sw128_desc(sA + c * (P_TILE * 128));
+                uint64_t db = make_kmajor_sw128_desc(sB + c * (H * 128));
+#pragma unroll
+                for (int k = 0; k < 4; ++k) mma_bf16_ss(tmem_base, da + 2 * k, db + 2 * k, idesc, (c | k) != 0 ? 1u : 0u);
+            }
+            mma_commit(t_full);
+        }
+    }
+    if (warp >= 4) {
+        const int q = warp & 3;
+        if (mbar_wait(t_full, 0, a.err, 302)) {
+            tc_fence_after_sync();
+            const int row = row0 + q * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+            float o[P_MAX_OUT];
+#pragma unroll
+            for (int u = 0; u < P_MAX_OUT; ++u) o[u] = sb2[u];
+#pragma unroll 1
+            for (int ch = 0; ch < 8; ++ch) {
+                float v[32];
+                tmem_ld_32x32(taddr + ch * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int j = ch * 32 + i;
+                    float hv = fmaxf(v[i] + sb1[j], 0.0f);
+#pragma unroll
+                    for (int u = 0; u < P_MAX_OUT; ++u) o[u] = fmaf(hv, sW2[j * P_MAX_OUT + u], o[u]);
+                }
+            }
+            if (row < a.n) {
+                const size_t off = (size_t)a.t * a.n + row;
+                if (net == 0) {
+                    unsigned long long ts = (unsigned long long)a.ctr->total_steps + (unsigned long long)a.t * (unsigned long long)a.n;
+                    uint32_t seed = (uint32_t)(ts * 2654435761ull + (unsigned long long)a.t * 7919ull);  // ppo.mojo:2071
+                    float act, lp;
+                    sample_one(o, a.num_actions, seed, row, a.greedy, act, lp);
+                    a.actions[row] = act;
+                    a.r_actions[off] = act;
+                    a.r_log_probs[off] = lp;
+#pragma unroll
+                    for (int k = 0; k < IN; ++k) a.r_obs[off * IN + k] = a.obs[(size_t)row * IN + k];
+                } else {
+                    a.values[row] = o[0];
+                    a.r_values[off] = o[0];
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*(volatile int*)a.err != 0)
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, 256);
+    }
+}
+
+// Critic-only variant of the same kernel body is not needed: the bootstrap value
+// of the GAE phase uses the fp32 forward (one call per rollout).
+
+bool policy_supported(int in_dim, int num_actions, int hidden) {
+    return hidden == H && (in_dim == 4 || in_dim == 8) && num_actions <= P_MAX_OUT;
+}
+
+int PolicyState::init(void* workspace, int* err_flag) {
+    err = err_flag;
+    w1t[0] = (bf16*)workspace;
+    w1t[1] = w1t[0] + H * H;
+    scratch_w1 = w1t[1] + H * H;
+    int rc;
+    if ((rc = make_tensor_map(&tm_w1t[0], w1t[0], H, H, H))) return rc;
+    if ((rc = make_tensor_map(&tm_w1t[1], w1t[1], H, H, H))) return rc;
+    return MRL_OK;
+}
+
+int64_t policy_workspace_bytes() { return 3 * (int64_t)H * H * 2 + 256; }
+
+int PolicyState::prepare(const float* actor_params, const float* critic_params, int in_dim, cudaStream_t st) {
+    const size_t oW1 = (size_t)in_dim * H + H;
+    int rc = convert_w1(actor_params + oW1, scratch_w1, w1t[0], st);
+    if (rc) return rc;
+    return convert_w1(critic_params + oW1, scratch_w1, w1t[1], st);
+}
+
+template <int IN>
+static int launch_policy(const CUtensorMap& ta, const CUtensorMap& tb, const PolicyArgs& a, cudaStream_t st) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        MRL_CUDA_OK(cudaFuncSetAttribute(rollout_policy_kernel<IN>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM));
+        attr_set = true;
+    }
+    dim3 grid((a.n + P_TILE - 1) / P_TILE, 2);
+    rollout_policy_kernel<IN><<<grid, P_THREADS, P_SMEM, st>>>(ta, tb, a);
+    count_launch();
+    MRL_CUDA_OK(cudaGetLastError());
+    return MRL_OK;
+}
+
+int PolicyState::step(const PolicyStepArgs& s, cudaStream_t st) {
+    PolicyArgs a;
+    a.obs = s.obs; a.params[0] = s.actor_params; a.params[1] = s.critic_params;
+    a.n = s.n; a.in_dim = s.in_dim; a.num_actions = s.num_actions; a.t = s.t; a.greedy = s.greedy;
+    a.actions = s.actions; a.values = s.values;
+    a.r_obs = s.r_obs; a.r_actions = s.r_actions; a.r_log_probs = s.r_log_probs; a.r_values = s.r_values;
+    a.ctr = (const DeviceCounters*)s.counters; a.err = err;
+    if (s.in_dim == 4) return launch_policy<4>(tm_w1t[0], tm_w1t[1], a, st);
+    if (s.in_dim == 8) return launch_policy<8>(tm_w1t[0], tm_w1t[1], a, st);
+    set_error("rollout policy kernel: obs_dim %d is not built", s.in_dim);
+    return MRL_ERR_UNSUPPORTED;
+}
+
+}  // namespace tc
+}  // namespace mrl

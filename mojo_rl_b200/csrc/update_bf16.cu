@@ -361,6 +361,11 @@ __global__ void convert_w1_kernel(const float* __restrict__ W1, bf16* __restrict
         w1t[(size_t)(bx + r) * H + by + threadIdx.x] = __float2bfloat16_rn(tile[threadIdx.x][r]);
 }
 
+int convert_w1(const float* W1, bf16* w1, bf16* w1t, cudaStream_t st) {
+    MRL_LAUNCH(convert_w1_kernel, dim3(H / 32, H / 32), dim3(32, 8), 0, st, W1, w1, w1t);
+    return MRL_OK;
+}
+
 __device__ __forceinline__ void store_row32_bf16(bf16* dst, const float (&v)[32]) {
     uint4* d = reinterpret_cast<uint4*>(dst);
 #pragma unroll

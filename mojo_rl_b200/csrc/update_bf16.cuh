@@ -32,5 +32,36 @@ struct State {
                  cudaStream_t st);
 };
 
+// W1 fp32 [256, 256] -> bf16 row-major copy and bf16 transposed copy.
+int convert_w1(const float* W1, __nv_bfloat16* w1, __nv_bfloat16* w1t, cudaStream_t st);
+
+// ---- rollout policy step on tensor cores (rollout_bf16.cu) ----------------------
+struct DeviceCountersFwd;  // (DeviceCounters lives in rollout.cuh)
+struct PolicyStepArgs {
+    const float* obs;
+    const float* actor_params;
+    const float* critic_params;
+    int n, in_dim, num_actions, t, greedy;
+    float* actions;
+    float* values;
+    float* r_obs; float* r_actions; float* r_log_probs; float* r_values;
+    const void* counters;  // const DeviceCounters*
+};
+
+bool policy_supported(int in_dim, int num_actions, int hidden);
+int64_t policy_workspace_bytes();
+
+struct PolicyState {
+    int* err;
+    __nv_bfloat16* w1t[2];     // bf16 W1^T of actor and critic, refreshed once per rollout
+    __nv_bfloat16* scratch_w1; // row-major bf16 copy (by-product of the conversion)
+    CUtensorMap tm_w1t[2];
+    int init(void* workspace, int* err_flag);
+    // Converts the current W1 of both networks (call once per rollout, before step 0).
+    int prepare(const float* actor_params, const float* critic_params, int in_dim, cudaStream_t st);
+    // Actor + critic forward, sampling and pre-step store for rollout step a.t.
+    int step(const PolicyStepArgs& a, cudaStream_t st);
+};
+
 }  // namespace tc
 }  // namespace mrl

@@ -121,3 +121,37 @@ def test_precision1_rejects_unsupported_shapes():
     h = ctypes.c_void_p()
     assert L.mrl_create(ctypes.byref(h), ctypes.byref(cfg)) == -4
     assert b"precision 1" in L.mrl_last_error_string()
+
+
+def test_rollout_policy_kernel_matches_fp32_policy():
+    """One rollout step: the tensor-core policy kernel (precision 1) against the fp32 forward +
+    sampler (precision 0) on the same observations, parameters and seeds."""
+    from _gpu import GpuAgent
+    from _util import NetSpec, default_config, xavier_params
+    rng = np.random.default_rng(1)
+    # moderate weights: with the reference's whole-model Xavier range the 256-term sums cancel
+    # almost completely and bf16 rounding of the operands dominates the (tiny) result
+    pa = xavier_params(NetSpec(8, 256, 4, 0, 0), rng) * 0.25
+    pc = xavier_params(NetSpec(8, 256, 1, 0, 0), rng) * 0.25
+    out = {}
+    for prec in (0, 1):
+        for det in (0, 1):
+            cfg = default_config(env_kind=2, n_envs=1024, rollout_len=2, hidden_dim=256, minibatch_size=2048,
+                                 num_epochs=1, precision=prec, deterministic=det)
+            g = GpuAgent(cfg)
+            try:
+                g.set_params(0, pa, np.zeros(2 * pa.size, np.float32))
+                g.set_params(1, pc, np.zeros(2 * pc.size, np.float32))
+                g.reset(3); g.rollout()
+                out[(prec, det)] = {k: g.buffer(i)[:1024 * (8 if k == "obs" else 1)] for k, i in
+                                    (("obs", 2), ("act", 3), ("lp", 4), ("val", 5))}
+                assert g.stats().total_steps == 2048
+            finally:
+                g.close()
+    for det in (0, 1):
+        a, b = out[(1, det)], out[(0, det)]
+        assert np.array_equal(a["obs"], b["obs"])                      # step 0 observations are the reset's
+        assert np.allclose(a["val"], b["val"], rtol=2e-2, atol=2e-2), np.abs(a["val"] - b["val"]).max()
+        agree = (a["act"] == b["act"])
+        assert agree.mean() > 0.97, agree.mean()
+        assert np.allclose(a["lp"][agree], b["lp"][agree], rtol=0, atol=3e-2)
