@@ -496,7 +496,8 @@ extern "C" int mrl_ppo_rollout(mrl_ctx* c) {
                        c->cfg.deterministic);
         }
         RolloutStepArgs ra{c->states, c->actions, c->rewards, c->dones, c->obs, c->r_rewards, c->r_dones,
-                           c->episode_rewards, c->episode_steps, c->ring_returns, c->ring_lengths, c->counters, t, N};
+                           c->episode_rewards, c->episode_steps, c->ring_returns, c->ring_lengths, c->counters, t, N,
+                           c->tc_err};
         if ((rc = rollout_env_step(c->cfg.env_kind, ra, st))) return rc;
     }
     MRL_LAUNCH(add_total_steps_kernel, 1, 1, 0, st, c->counters, (long long)T * N);

@@ -111,6 +111,10 @@ struct RowEdges {
         const float* p = s + EDGES_OFFSET + e * 6;
         x0 = p[0]; y0 = p[1]; x1 = p[2]; y1 = p[3]; nx = p[4]; ny = p[5];
     }
+    __device__ __forceinline__ void get_x(int e, float& x0, float& x1) const {
+        x0 = s[EDGES_OFFSET + e * 6];
+        x1 = s[EDGES_OFFSET + e * 6 + 2];
+    }
     __device__ __forceinline__ float y0_of(int e) const { return s[EDGES_OFFSET + e * 6 + 1]; }
     __device__ __forceinline__ float y1_of(int e) const { return s[EDGES_OFFSET + e * 6 + 3]; }
 };
@@ -166,22 +170,56 @@ __device__ __forceinline__ void physics_step(Env& e, const Edges& edges, Contact
     integrate_velocities(e.b, zero, zero, zero, gx, gy, dt);
     refresh_trig(e.b);
     // EdgeTerrainCollision.detect_single_env: body-major, vertex, edge order.
+    // Edges whose padded x-range misses the x-extent of all 14 vertices fail the
+    // reference's own range test for every vertex, so they are dropped up front
+    // (the surviving edges are still visited in ascending order per vertex).
+    constexpr int NV = 14;
+    float wxs[NV], wys[NV];
+    {
+        int idx = 0;
+#pragma unroll
+        for (int body = 0; body < NUM_BODIES; ++body) {
+#pragma unroll
+            for (int v = 0; v < 6; ++v) {
+                if (v >= shape_nverts(body)) break;
+                float lx, ly;
+                shape_vertex(body, v, lx, ly);
+                wxs[idx] = e.b.x[body] + lx * e.b.cs[body] - ly * e.b.sn[body];
+                wys[idx] = e.b.y[body] + lx * e.b.sn[body] + ly * e.b.cs[body];
+                ++idx;
+            }
+        }
+    }
+    float vmin = wxs[0], vmax = wxs[0];
+#pragma unroll
+    for (int i = 1; i < NV; ++i) { vmin = fminf(vmin, wxs[i]); vmax = fmaxf(vmax, wxs[i]); }
+    uint32_t candidates = 0;
+    for (int ed = 0; ed < MAX_TERRAIN_EDGES; ++ed) {
+        if (ed >= e.n_edges) break;
+        float x0, x1;
+        edges.get_x(ed, x0, x1);
+        float x_min = x0, x_max = x1;
+        if (x0 > x1) { x_min = x1; x_max = x0; }
+        if (!(vmax < x_min - 0.1f || vmin > x_max + 0.1f)) candidates |= 1u << ed;
+    }
     c.n = 0;
+    if (candidates != 0) {
+        int idx = 0;
 #pragma unroll
-    for (int body = 0; body < NUM_BODIES; ++body) {
-        const int nv = shape_nverts(body);
+        for (int body = 0; body < NUM_BODIES; ++body) {
 #pragma unroll
-        for (int v = 0; v < 6; ++v) {
-            if (v >= nv) break;
-            float lx, ly;
-            shape_vertex(body, v, lx, ly);
-            float wx = e.b.x[body] + lx * e.b.cs[body] - ly * e.b.sn[body];
-            float wy = e.b.y[body] + lx * e.b.sn[body] + ly * e.b.cs[body];
-            for (int ed = 0; ed < MAX_TERRAIN_EDGES; ++ed) {
-                if (ed >= e.n_edges) break;
-                float x0, y0, x1, y1, nx, ny;
-                edges.get(ed, x0, y0, x1, y1, nx, ny);
-                vertex_edge_test(c, body, wx, wy, x0, y0, x1, y1, nx, ny);
+            for (int v = 0; v < 6; ++v) {
+                if (v >= shape_nverts(body)) break;
+                const float wx = wxs[idx], wy = wys[idx];
+                ++idx;
+                uint32_t m = candidates;
+                while (m != 0) {
+                    const int ed = __ffs(m) - 1;
+                    m &= m - 1;
+                    float x0, y0, x1, y1, nx, ny;
+                    edges.get(ed, x0, y0, x1, y1, nx, ny);
+                    vertex_edge_test(c, body, wx, wy, x0, y0, x1, y1, nx, ny);
+                }
             }
         }
     }

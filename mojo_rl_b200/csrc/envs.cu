@@ -4,6 +4,7 @@
 #include "env_cartpole.cuh"
 #include "env_lunar.cuh"
 #include "rollout.cuh"
+#include "umma.cuh"
 
 namespace mrl {
 
@@ -46,28 +47,33 @@ __global__ void cartpole_selective_reset_kernel(float* __restrict__ states, floa
 
 // ------------------------------------------------------------- LunarLander
 // The reference row is 192 floats (768 B) per environment, so a thread that
-// walks its own row issues strided, uncoalesced loads.  Each block instead
-// copies its rows into shared memory with coalesced loads (row pitch 193 floats:
-// consecutive environments fall into consecutive banks), steps every
-// environment there, and copies the rows back.
+// walks its own row in global memory issues strided, uncoalesced loads.  Each
+// block instead brings its 64 rows (48 KB, contiguous) into shared memory with
+// one bulk copy (TMA), steps every environment there, and writes the rows back
+// with one bulk store.  err: device word set when the bounded wait gives up.
 constexpr int LUNAR_TPB = 64;
-constexpr int LUNAR_PITCH = lunar::STATE_SIZE + 1;
-constexpr int LUNAR_SMEM = LUNAR_TPB * LUNAR_PITCH * 4;
+constexpr int LUNAR_PITCH = lunar::STATE_SIZE;
+constexpr int LUNAR_SMEM = LUNAR_TPB * LUNAR_PITCH * 4 + 16;
 
-__device__ __forceinline__ void lunar_rows_to_smem(const float* __restrict__ states, float* sm, int env0, int n) {
+__device__ __forceinline__ bool lunar_rows_to_smem(const float* __restrict__ states, float* sm, uint64_t* bar,
+                                                   int env0, int n, int* err) {
     const int rows = min(LUNAR_TPB, n - env0);
-    const float* src = states + (size_t)env0 * lunar::STATE_SIZE;
-    for (int i = threadIdx.x; i < rows * lunar::STATE_SIZE; i += blockDim.x) {
-        int r = i / lunar::STATE_SIZE, k = i - r * lunar::STATE_SIZE;
-        sm[r * LUNAR_PITCH + k] = src[i];
+    if (threadIdx.x == 0) {
+        umma::mbar_init(bar, 1);
+        umma::fence_barrier_init();
+        umma::mbar_arrive_expect_tx(bar, rows * lunar::STATE_SIZE * 4);
+        umma::bulk_load(sm, states + (size_t)env0 * lunar::STATE_SIZE, rows * lunar::STATE_SIZE * 4, bar);
     }
+    __syncthreads();
+    return umma::mbar_wait(bar, 0, err, 401);
 }
 __device__ __forceinline__ void lunar_rows_from_smem(float* __restrict__ states, const float* sm, int env0, int n) {
     const int rows = min(LUNAR_TPB, n - env0);
-    float* dst = states + (size_t)env0 * lunar::STATE_SIZE;
-    for (int i = threadIdx.x; i < rows * lunar::STATE_SIZE; i += blockDim.x) {
-        int r = i / lunar::STATE_SIZE, k = i - r * lunar::STATE_SIZE;
-        dst[i] = sm[r * LUNAR_PITCH + k];
+    umma::fence_proxy_async_smem();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        umma::bulk_store(states + (size_t)env0 * lunar::STATE_SIZE, sm, rows * lunar::STATE_SIZE * 4);
+        umma::bulk_store_wait_read();
     }
 }
 
@@ -92,11 +98,11 @@ __device__ __forceinline__ void lunar_step_row(float* s, int env, int action, fl
 __global__ void __launch_bounds__(LUNAR_TPB)
 lunar_step_rows_kernel(float* __restrict__ states, const float* __restrict__ actions,
                        float* __restrict__ rewards, float* __restrict__ dones,
-                       float* __restrict__ obs, int n) {
-    extern __shared__ float sm[];
+                       float* __restrict__ obs, int n, int* err) {
+    extern __shared__ __align__(128) float sm[];
+    uint64_t* bar = reinterpret_cast<uint64_t*>(sm + LUNAR_TPB * LUNAR_PITCH);
     const int env0 = blockIdx.x * LUNAR_TPB;
-    lunar_rows_to_smem(states, sm, env0, n);
-    __syncthreads();
+    if (!lunar_rows_to_smem(states, sm, bar, env0, n, err)) return;
     const int env = env0 + threadIdx.x;
     if (env < n) {
         float* s = sm + threadIdx.x * LUNAR_PITCH;
@@ -108,16 +114,15 @@ lunar_step_rows_kernel(float* __restrict__ states, const float* __restrict__ act
         rewards[env] = reward;
         dones[env] = done;
     }
-    __syncthreads();
     lunar_rows_from_smem(states, sm, env0, n);
 }
 
 // Rollout step: step, store, episode tracking, selective reset, observation.
 __global__ void __launch_bounds__(LUNAR_TPB) lunar_rollout_step_kernel(RolloutStepArgs a) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(128) float sm[];
+    uint64_t* bar = reinterpret_cast<uint64_t*>(sm + LUNAR_TPB * LUNAR_PITCH);
     const int env0 = blockIdx.x * LUNAR_TPB;
-    lunar_rows_to_smem(a.states, sm, env0, a.n);
-    __syncthreads();
+    if (!lunar_rows_to_smem(a.states, sm, bar, env0, a.n, a.err)) return;
     const int env = env0 + threadIdx.x;
     if (env < a.n) {
         float* s = sm + threadIdx.x * LUNAR_PITCH;
@@ -131,7 +136,6 @@ __global__ void __launch_bounds__(LUNAR_TPB) lunar_rollout_step_kernel(RolloutSt
         ob[0] = make_float4(s[0], s[1], s[2], s[3]);
         ob[1] = make_float4(s[4], s[5], s[6], s[7]);
     }
-    __syncthreads();
     lunar_rows_from_smem(a.states, sm, env0, a.n);
 }
 
@@ -170,6 +174,23 @@ static cudaError_t ensure_lunar_smem() {
     e = cudaFuncSetAttribute(lunar_rollout_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LUNAR_SMEM);
     if (e == cudaSuccess) done = true;
     return e;
+}
+
+// Device word for the bounded waits of the stand-alone boundary kernels: a
+// file-scope variable, looked up once per device.
+static __device__ int g_boundary_err;
+static cudaError_t boundary_err_word(int** out) {
+    static int* ptr[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!ptr[dev]) {
+        e = cudaGetSymbolAddress((void**)&ptr[dev], g_boundary_err);
+        if (e != cudaSuccess) return e;
+    }
+    *out = ptr[dev];
+    return cudaSuccess;
 }
 
 int rollout_env_step(int env_kind, const RolloutStepArgs& a, cudaStream_t st) {
@@ -230,6 +251,7 @@ extern "C" int mrl_env_step(int env_kind, int batch, float* states, const float*
     MRL_CHECK_ARG(batch > 0 && states && actions && rewards && dones && obs);
     (void)rng_seed;  // neither CartPole nor LunarLander consumes the per-step seed
     cudaStream_t st = as_stream(stream);
+    int* err_word = nullptr;
     switch (env_kind) {
         case MRL_ENV_CARTPOLE:
             MRL_LAUNCH(cartpole_step_kernel, ceil_div(batch, 256), 256, 0, st, states, actions, rewards,
@@ -237,8 +259,10 @@ extern "C" int mrl_env_step(int env_kind, int batch, float* states, const float*
             return MRL_OK;
         case MRL_ENV_LUNAR_LANDER:
             MRL_CUDA_OK(ensure_lunar_smem());
+            MRL_CHECK_ARG(((uintptr_t)states & 15) == 0);
+            MRL_CUDA_OK(boundary_err_word(&err_word));
             MRL_LAUNCH(lunar_step_rows_kernel, ceil_div(batch, LUNAR_TPB), LUNAR_TPB, LUNAR_SMEM, st, states, actions,
-                       rewards, dones, obs, batch);
+                       rewards, dones, obs, batch, err_word);
             return MRL_OK;
         default:
             set_error("mrl_env_step: env kind %d is not built", env_kind);

@@ -44,6 +44,7 @@ struct RolloutStepArgs {
     DeviceCounters* ctr;
     int t;
     int n;
+    int* err;  // device word for bounded waits
 };
 
 // Launches the fused step kernel of `env_kind` (envs.cu).
