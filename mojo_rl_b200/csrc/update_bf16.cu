@@ -17,7 +17,8 @@ using namespace umma;
 typedef __nv_bfloat16 bf16;
 
 constexpr int TILE_M = 128, KCH = 64;
-constexpr int NTHREADS = 192;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
+constexpr int NTHREADS = 192;     // split-K kernel: warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 epilogue
+constexpr int K1_THREADS = 320;   // row-tile kernel: two epilogue groups (warps 2-5, 6-9), one per TMEM buffer
 
 // ---------------------------------------------------------------- K1
 // D[128-row tile, 256] = A[tile rows, 256] . B^T with B [256 (n), 256 (k)]
@@ -45,7 +46,7 @@ __device__ __forceinline__ void drain_on_error(const int* err) {
 }
 
 template <int MODE, int OUT>
-__global__ void __launch_bounds__(NTHREADS, 1)
+__global__ void __launch_bounds__(K1_THREADS, 1)
 k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, K1Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -74,8 +75,8 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (warp == 1) tmem_alloc(tmem_slot, 512);
     if (warp >= 2 && MODE == 1) {
         int t = threadIdx.x - 64;
-        for (int i = t; i < H; i += 128) sP[i] = p.bias[i];
-        for (int i = t; i < H * OUT; i += 128) {
+        for (int i = t; i < H; i += 256) sP[i] = p.bias[i];
+        for (int i = t; i < H * OUT; i += 256) {
             int j = i / OUT, a = i % OUT;
             sP[H + i] = a < p.out_dim ? p.W2[j * p.out_dim + a] : 0.0f;
         }
@@ -131,10 +132,12 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
     } else {
         const int q = warp & 3;  // TMEM lane quarter this warp may read
+        const int group = (warp - 2) >> 2;  // epilogue group = TMEM buffer it drains (tiles lt with lt % 2 == group)
         uint32_t lt = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
             int buf = lt & 1;
+            if (buf != group) continue;
             ok = mbar_wait(&t_full[buf], (lt >> 1) & 1u, p.err, 105);
             if (!ok) break;
             tc_fence_after_sync();
@@ -148,6 +151,17 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
 #pragma unroll 1
             for (int ch = 0; ch < 8; ++ch) {
+                uint4 hm[4];
+                if (MODE == 2) {  // the ReLU mask source, fetched before the accumulator read so that both latencies overlap
+                    if (in_range) {
+                        const uint4* src = reinterpret_cast<const uint4*>(p.h0 + (size_t)row * H + ch * 32);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) hm[i] = __ldg(src + i);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) hm[i] = make_uint4(0, 0, 0, 0);
+                    }
+                }
                 float v[32];
                 tmem_ld_32x32(taddr + ch * 32, v);
                 if (MODE == 0) {
@@ -172,15 +186,6 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                             packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
                         }
                     } else {
-                        uint4 hm[4];
-                        if (in_range) {
-                            const uint4* src = reinterpret_cast<const uint4*>(p.h0 + (size_t)row * H + ch * 32);
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) hm[i] = src[i];
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) hm[i] = make_uint4(0, 0, 0, 0);
-                        }
                         const uint32_t* hw = reinterpret_cast<const uint32_t*>(hm);
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
@@ -366,97 +371,137 @@ int convert_w1(const float* W1, bf16* w1, bf16* w1t, cudaStream_t st) {
     return MRL_OK;
 }
 
-__device__ __forceinline__ void store_row32_bf16(bf16* dst, const float (&v)[32]) {
-    uint4* d = reinterpret_cast<uint4*>(dst);
+// Thread mapping of the CUDA-core kernels below: a block has 256 threads =
+// 8 warps; a warp covers 4 column groups of 8 columns (16 bytes of bf16) for 8
+// rows at a time, so a block covers all 256 columns of 8 rows per iteration and
+// every access is a 16-byte vector.  Sums over rows are finished inside a warp
+// with shuffles over the 8 row lanes.
+struct VecMap {
+    int row_lane, col0;
+    __device__ __forceinline__ VecMap() {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        row_lane = lane & 7;
+        col0 = (warp * 4 + (lane >> 3)) * 8;
+    }
+};
+__device__ __forceinline__ float sum_row_lanes(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    return v;
+}
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        uint32_t w[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            __nv_bfloat162 pk = __floats2bfloat162_rn(v[8 * i + 2 * k], v[8 * i + 2 * k + 1]);
-            w[k] = *reinterpret_cast<uint32_t*>(&pk);
-        }
-        d[i] = make_uint4(w[0], w[1], w[2], w[3]);
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
     }
 }
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __nv_bfloat162 pk = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&pk);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
 
-// First layer (LinearReLU[obs, 256], K = obs_dim): h0 = relu(x . W0 + b0), written
-// row-major [M, 256] in bf16.  One block = 32 rows, thread j = column j.
+// First layer (LinearReLU[obs, 256], K = obs_dim): h0 = relu(x . W0 + b0) in bf16, row-major.
 template <int IN>
 __global__ void __launch_bounds__(H)
 l0_forward_kernel(const float* __restrict__ x, const float* __restrict__ W0, const float* __restrict__ b0,
-                  bf16* __restrict__ h0, int M) {
-    __shared__ float sx[32 * IN];
-    const int j = threadIdx.x;
-    const int r0 = blockIdx.x * 32;
-    for (int i = threadIdx.x; i < 32 * IN; i += H) {
-        int r = r0 + i / IN;
-        sx[i] = r < M ? x[(size_t)r0 * IN + i] : 0.0f;
+                  bf16* __restrict__ h0, int M, int rows_per_block) {
+    const VecMap vm;
+    float w[IN][8], b[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        b[u] = b0[vm.col0 + u];
+#pragma unroll
+        for (int k = 0; k < IN; ++k) w[k][u] = W0[k * H + vm.col0 + u];
     }
-    float w[IN];
+    const int rb = blockIdx.x * rows_per_block;
+    const int re = min(M, rb + rows_per_block);
+    for (int r = rb + vm.row_lane; r < re; r += 8) {
+        float xr[IN];
 #pragma unroll
-    for (int k = 0; k < IN; ++k) w[k] = W0[k * H + j];
-    const float b = b0[j];
-    __syncthreads();
+        for (int k = 0; k < IN; ++k) xr[k] = __ldg(x + (size_t)r * IN + k);
+        float hv[8];
 #pragma unroll
-    for (int r = 0; r < 32; ++r) {
-        float acc = b;
+        for (int u = 0; u < 8; ++u) {
+            float acc = b[u];
 #pragma unroll
-        for (int k = 0; k < IN; ++k) acc = fmaf(sx[r * IN + k], w[k], acc);
-        if (r0 + r < M) h0[(size_t)(r0 + r) * H + j] = __float2bfloat16_rn(fmaxf(acc, 0.0f));
+            for (int k = 0; k < IN; ++k) acc = fmaf(xr[k], w[k][u], acc);
+            hv[u] = fmaxf(acc, 0.0f);
+        }
+        *reinterpret_cast<uint4*>(h0 + (size_t)r * H + vm.col0) = pack8(hv);
     }
 }
 
 // Head backward and everything that reduces over rows next to it:
 //   g1[r][j]  = h1[r][j] > 0 ? sum_a dout[r][a] * W2[j][a] : 0      (dX of the head, ReLU mask of layer 1)
 //   dW2[j][a] = sum_r h1[r][j] * dout[r][a],  db2[a] = sum_r dout[r][a],  db1[j] = sum_r g1[r][j]
-// One block walks rows_per_block rows in groups of 32; thread j owns column j.
 // part layout per block: [OUT][256] dW2^T, [256] db1, [OUT] db2.
 template <int OUT>
 __global__ void __launch_bounds__(H)
 head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout, int ldd,
                      const float* __restrict__ W2, int out_dim, bf16* __restrict__ g1,
                      float* __restrict__ part, int M, int rows_per_block) {
-    __shared__ float sd[32 * OUT];
-    const int j = threadIdx.x;
-    float w2[OUT], dw2[OUT];
+    const VecMap vm;
+    float w2[OUT][8], dw2[OUT][8], db1[8], db2[OUT];
 #pragma unroll
-    for (int a = 0; a < OUT; ++a) { w2[a] = a < out_dim ? W2[j * out_dim + a] : 0.0f; dw2[a] = 0.0f; }
-    float db1 = 0.0f, db2 = 0.0f;
+    for (int a = 0; a < OUT; ++a) {
+        db2[a] = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            w2[a][u] = a < out_dim ? W2[(vm.col0 + u) * out_dim + a] : 0.0f;
+            dw2[a][u] = 0.0f;
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) db1[u] = 0.0f;
     const int rb = blockIdx.x * rows_per_block;
     const int re = min(M, rb + rows_per_block);
-    for (int r0 = rb; r0 < re; r0 += 32) {
-        __syncthreads();
-        for (int i = threadIdx.x; i < 32 * OUT; i += H) {
-            int r = r0 + i / OUT, a = i % OUT;
-            sd[i] = (r < re && a < out_dim) ? dout[(size_t)r * ldd + a] : 0.0f;
+    for (int r = rb + vm.row_lane; r < re; r += 8) {
+        float h[8], d[OUT], g[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(h1 + (size_t)r * H + vm.col0)), h);
+#pragma unroll
+        for (int a = 0; a < OUT; ++a) {
+            d[a] = a < out_dim ? __ldg(dout + (size_t)r * ldd + a) : 0.0f;
+            db2[a] += d[a];
         }
-        __syncthreads();
-#pragma unroll 8
-        for (int r = 0; r < 32; ++r) {
-            float h = 0.0f;
-            if (r0 + r < re) h = __bfloat162float(h1[(size_t)(r0 + r) * H + j]);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
             float dh = 0.0f;
 #pragma unroll
             for (int a = 0; a < OUT; ++a) {
-                float d = sd[r * OUT + a];
-                dh = fmaf(d, w2[a], dh);
-                dw2[a] = fmaf(h, d, dw2[a]);
+                dh = fmaf(d[a], w2[a][u], dh);
+                dw2[a][u] = fmaf(h[u], d[a], dw2[a][u]);
             }
-            float g = h > 0.0f ? dh : 0.0f;
-            db1 += g;
-            if (r0 + r < re) g1[(size_t)(r0 + r) * H + j] = __float2bfloat16_rn(g);
+            g[u] = h[u] > 0.0f ? dh : 0.0f;
+            db1[u] += g[u];
         }
-        if (j < OUT) {
-#pragma unroll
-            for (int r = 0; r < 32; ++r) db2 += sd[r * OUT + j];
-        }
+        *reinterpret_cast<uint4*>(g1 + (size_t)r * H + vm.col0) = pack8(g);
     }
     float* pb = part + (size_t)blockIdx.x * ((OUT + 1) * H + OUT);
 #pragma unroll
-    for (int a = 0; a < OUT; ++a) pb[a * H + j] = dw2[a];
-    pb[OUT * H + j] = db1;
-    if (j < OUT) pb[(OUT + 1) * H + j] = db2;
+    for (int a = 0; a < OUT; ++a)
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            float v = sum_row_lanes(dw2[a][u]);
+            if (vm.row_lane == 0) pb[a * H + vm.col0 + u] = v;
+        }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        float v = sum_row_lanes(db1[u]);
+        if (vm.row_lane == 0) pb[OUT * H + vm.col0 + u] = v;
+    }
+#pragma unroll
+    for (int a = 0; a < OUT; ++a) {
+        float v = sum_row_lanes(db2[a]);  // every column group sees every row: take column group 0
+        if (threadIdx.x == 0) pb[(OUT + 1) * H + a] = v;
+    }
 }
 
 // dW0[k][j] = sum_r x[r][k] * g0[r][j], db0[j] = sum_r g0[r][j]; part per block: [IN + 1][256].
@@ -464,44 +509,63 @@ template <int IN>
 __global__ void __launch_bounds__(H)
 l0_backward_kernel(const bf16* __restrict__ g0, const float* __restrict__ x, float* __restrict__ part, int M,
                    int rows_per_block) {
-    __shared__ float sx[32 * IN];
-    const int j = threadIdx.x;
-    float dw[IN];
+    const VecMap vm;
+    float dw[IN][8], db[8];
 #pragma unroll
-    for (int k = 0; k < IN; ++k) dw[k] = 0.0f;
-    float db = 0.0f;
+    for (int u = 0; u < 8; ++u) {
+        db[u] = 0.0f;
+#pragma unroll
+        for (int k = 0; k < IN; ++k) dw[k][u] = 0.0f;
+    }
     const int rb = blockIdx.x * rows_per_block;
     const int re = min(M, rb + rows_per_block);
-    for (int r0 = rb; r0 < re; r0 += 32) {
-        __syncthreads();
-        for (int i = threadIdx.x; i < 32 * IN; i += H) {
-            int r = r0 + i / IN;
-            sx[i] = r < re ? x[(size_t)r0 * IN + i] : 0.0f;
-        }
-        __syncthreads();
-#pragma unroll 8
-        for (int r = 0; r < 32; ++r) {
-            if (r0 + r >= re) break;
-            float g = __bfloat162float(g0[(size_t)(r0 + r) * H + j]);
-            db += g;
+    for (int r = rb + vm.row_lane; r < re; r += 8) {
+        float g[8], xr[IN];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(g0 + (size_t)r * H + vm.col0)), g);
 #pragma unroll
-            for (int k = 0; k < IN; ++k) dw[k] = fmaf(sx[r * IN + k], g, dw[k]);
+        for (int k = 0; k < IN; ++k) xr[k] = __ldg(x + (size_t)r * IN + k);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            db[u] += g[u];
+#pragma unroll
+            for (int k = 0; k < IN; ++k) dw[k][u] = fmaf(xr[k], g[u], dw[k][u]);
         }
     }
     float* pb = part + (size_t)blockIdx.x * (IN + 1) * H;
 #pragma unroll
-    for (int k = 0; k < IN; ++k) pb[k * H + j] = dw[k];
-    pb[IN * H + j] = db;
+    for (int k = 0; k < IN; ++k)
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            float v = sum_row_lanes(dw[k][u]);
+            if (vm.row_lane == 0) pb[k * H + vm.col0 + u] = v;
+        }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        float v = sum_row_lanes(db[u]);
+        if (vm.row_lane == 0) pb[IN * H + vm.col0 + u] = v;
+    }
 }
 
-// out[i] = sum_b part[b * stride + i]  (b ascending: deterministic)
+// sum_b p[b * stride] with four interleaved accumulators combined in a fixed order (deterministic).
+__device__ __forceinline__ float sum_parts(const float* __restrict__ p, int nblocks, int stride) {
+    float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+    int b = 0;
+    for (; b + 4 <= nblocks; b += 4) {
+        a0 += p[(size_t)b * stride];
+        a1 += p[(size_t)(b + 1) * stride];
+        a2 += p[(size_t)(b + 2) * stride];
+        a3 += p[(size_t)(b + 3) * stride];
+    }
+    for (; b < nblocks; ++b) a0 += p[(size_t)b * stride];
+    return (a0 + a1) + (a2 + a3);
+}
+
+// out[i] = sum_b part[b * stride + i]
 __global__ void reduce_parts_kernel(const float* __restrict__ part, int nblocks, int stride, int n,
                                     float* __restrict__ out) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    float acc = 0.0f;
-    for (int b = 0; b < nblocks; ++b) acc += part[(size_t)b * stride + i];
-    out[i] = acc;
+    out[i] = sum_parts(part + i, nblocks, stride);
 }
 // Head parts -> dW2 [256][out_dim] (transposed from [OUT][256]), db2, and db1.
 __global__ void reduce_head_parts_kernel(const float* __restrict__ part, int nblocks, int OUT, int out_dim,
@@ -510,8 +574,7 @@ __global__ void reduce_head_parts_kernel(const float* __restrict__ part, int nbl
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     const int stride = (OUT + 1) * H + OUT;
     if (i >= stride) return;
-    float acc = 0.0f;
-    for (int b = 0; b < nblocks; ++b) acc += part[(size_t)b * stride + i];
+    float acc = sum_parts(part + i, nblocks, stride);
     if (i < OUT * H) {
         int a = i / H, j = i % H;
         if (a < out_dim) dW2[j * out_dim + a] = acc;
@@ -585,7 +648,7 @@ static int launch_k1(const CUtensorMap& tmA, const CUtensorMap& tmB, const K1Par
     }
     int tiles = (p.M + TILE_M - 1) / TILE_M;
     int grid = tiles < sm_count() ? tiles : sm_count();
-    k1_rowtile_kernel<MODE, OUT><<<grid, NTHREADS, K1_SMEM, st>>>(tmA, tmB, p);
+    k1_rowtile_kernel<MODE, OUT><<<grid, K1_THREADS, K1_SMEM, st>>>(tmA, tmB, p);
     count_launch();
     MRL_CUDA_OK(cudaGetLastError());
     return MRL_OK;
@@ -656,7 +719,9 @@ int State::init(void* workspace, int batch_, int* err_flag) {
 
 template <int IN>
 static int l0_forward(const float* x, const float* W0, const float* b0, bf16* h0, int M, cudaStream_t st) {
-    MRL_LAUNCH((l0_forward_kernel<IN>), (M + 31) / 32, H, 0, st, x, W0, b0, h0, M);
+    const int rows_per_block = 64;
+    MRL_LAUNCH((l0_forward_kernel<IN>), (M + rows_per_block - 1) / rows_per_block, H, 0, st, x, W0, b0, h0, M,
+               rows_per_block);
     return MRL_OK;
 }
 
@@ -683,7 +748,9 @@ int State::backward(const mrl_net_spec* net, const float* params, const float* x
     const size_t oW0 = 0, ob0 = (size_t)I * H, oW1 = ob0 + H, ob1 = oW1 + (size_t)H * H, oW2 = ob1 + H,
                  ob2 = oW2 + (size_t)H * O;
     const float* W2 = params + oW2;
-    const int rows_per_block = 512;
+    // two blocks per SM, each walking a contiguous slab of rows (multiple of 8)
+    int rows_per_block = ((batch + 2 * sm_count() - 1) / (2 * sm_count()) + 7) & ~7;
+    if (rows_per_block < 64) rows_per_block = 64;
     const int nblocks = (batch + rows_per_block - 1) / rows_per_block;
     const int OUT = O <= 1 ? 1 : (O <= 2 ? 2 : (O <= 4 ? 4 : 8));
     if (OUT == 1) { MRL_LAUNCH((head_backward_kernel<1>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
