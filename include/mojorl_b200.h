@@ -311,6 +311,12 @@ int mrl_drain_episodes(mrl_ctx* ctx, float* returns_host, float* lengths_host, i
  * counts into calls_host[0..2], and clears them.  Synchronises the stream. */
 int mrl_get_timers(mrl_ctx* ctx, float ms_host[3], int calls_host[3]);
 
+/* Per-kernel CUDA-event timing of the precision-1 update (diagnostics; off by
+ * default).  mrl_profile_report synchronises the device, writes one text line per
+ * kernel group (calls, total ms, average us) into buf and returns the length. */
+int mrl_profile_enable(int on);
+int mrl_profile_report(char* buf_host, int buf_size);
+
 /* The stream all fused phases run on (cudaStream_t as void*). */
 void* mrl_stream(mrl_ctx* ctx);
 

@@ -88,6 +88,8 @@ SIGNATURES = {
     "mrl_get_stats": (ctypes.c_int, [c_void_p, ctypes.POINTER(Stats)]),
     "mrl_drain_episodes": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_int]),
     "mrl_get_timers": (ctypes.c_int, [c_void_p, c_void_p, c_void_p]),
+    "mrl_profile_enable": (ctypes.c_int, [ctypes.c_int]),
+    "mrl_profile_report": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int]),
     "mrl_stream": (c_void_p, [c_void_p]),
     "mrl_kernel_launch_count": (ctypes.c_int64, []),
 }

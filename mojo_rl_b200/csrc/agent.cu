@@ -7,6 +7,7 @@
 #include <stdarg.h>
 #include <string.h>
 #include <atomic>
+#include <string>
 #include <vector>
 #include "env_cartpole.cuh"
 #include "env_lunar.cuh"
@@ -51,6 +52,18 @@ struct NcclApi {
     }
 };
 static NcclApi g_nccl;
+// ---- per-kernel profiler (see common.cuh)
+struct ProfMark { const char* name; cudaEvent_t ev; };
+static bool g_prof_on = false;
+static std::vector<ProfMark> g_prof;
+void prof_mark(const char* name, cudaStream_t st) {
+    if (!g_prof_on || g_prof.size() > 200000) return;
+    cudaEvent_t e;
+    if (cudaEventCreate(&e) != cudaSuccess) return;
+    cudaEventRecord(e, st);
+    g_prof.push_back({name, e});
+}
+
 constexpr int NCCL_FLOAT32 = 7, NCCL_FLOAT64 = 8, NCCL_SUM = 0;
 
 }  // namespace mrl
@@ -300,6 +313,35 @@ extern "C" void mrl_config_defaults(mrl_config* cfg) {
     cfg->adam_beta1 = 0.9f;
     cfg->adam_beta2 = 0.999f;
     cfg->adam_eps = 1e-8f;
+}
+
+extern "C" int mrl_profile_enable(int on) {
+    g_prof_on = on != 0;
+    return MRL_OK;
+}
+
+extern "C" int mrl_profile_report(char* buf, int buf_size) {
+    MRL_CHECK_ARG(buf && buf_size > 0);
+    MRL_CUDA_OK(cudaDeviceSynchronize());
+    std::vector<std::pair<std::string, std::pair<double, int>>> agg;
+    for (size_t i = 1; i < g_prof.size(); ++i) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, g_prof[i - 1].ev, g_prof[i].ev) != cudaSuccess) continue;
+        std::string name = g_prof[i].name;
+        bool found = false;
+        for (auto& a : agg) if (a.first == name) { a.second.first += ms; a.second.second += 1; found = true; break; }
+        if (!found) agg.push_back({name, {ms, 1}});
+    }
+    for (auto& m : g_prof) cudaEventDestroy(m.ev);
+    g_prof.clear();
+    int off = 0;
+    for (auto& a : agg) {
+        int n = snprintf(buf + off, buf_size - off, "%-28s calls %6d total %10.3f ms avg %9.2f us\n", a.first.c_str(),
+                         a.second.second, a.second.first, 1e3 * a.second.first / a.second.second);
+        if (n < 0 || n >= buf_size - off) break;
+        off += n;
+    }
+    return off;
 }
 
 extern "C" const char* mrl_last_error_string(void) { return g_error; }

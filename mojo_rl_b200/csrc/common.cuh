@@ -41,6 +41,11 @@ void count_launch(int n = 1);
         MRL_CUDA_OK(cudaGetLastError());                                               \
     } while (0)
 
+// Optional per-kernel timing of the update path: when enabled, prof_mark(name)
+// records a CUDA event after the launches it follows; mrl_profile_report sums
+// the device time between consecutive marks by name.  Off by default.
+void prof_mark(const char* name, cudaStream_t st);
+
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 

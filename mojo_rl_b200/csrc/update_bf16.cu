@@ -23,8 +23,8 @@ constexpr int K1_THREADS = 320;   // row-tile kernel: two epilogue groups (warps
 // ---------------------------------------------------------------- K1
 // D[128-row tile, 256] = A[tile rows, 256] . B^T with B [256 (n), 256 (k)]
 // resident in shared memory for the CTA's lifetime; A tiles stream through a
-// 4-deep ring; two TMEM accumulators overlap the epilogue with the next tile.
-constexpr int K1_STAGES = 4;
+// 5-deep ring; two TMEM accumulators overlap the epilogue with the next tile.
+constexpr int K1_STAGES = 5;
 constexpr int K1_B_BYTES = 4 * H * KCH * 2;           // 131072
 constexpr int K1_A_STAGE = TILE_M * KCH * 2;          // 16384
 constexpr int K1_PARAM_FLOATS = H + H * 8 + 8;        // bias, W2 (up to 8 outputs), b2
@@ -639,6 +639,14 @@ static int sm_count() {
     return g_sm_count;
 }
 
+// Rows per block of the CUDA-core kernels: four blocks per SM, each walking a
+// contiguous slab of rows (a multiple of 8, at least 64).
+static int slab_rows(int M) {
+    int blocks = 4 * sm_count();
+    int r = ((M + blocks - 1) / blocks + 7) & ~7;
+    return r < 64 ? 64 : r;
+}
+
 template <int MODE, int OUT>
 static int launch_k1(const CUtensorMap& tmA, const CUtensorMap& tmB, const K1Params& p, cudaStream_t st) {
     static bool attr_set = false;
@@ -719,7 +727,7 @@ int State::init(void* workspace, int batch_, int* err_flag) {
 
 template <int IN>
 static int l0_forward(const float* x, const float* W0, const float* b0, bf16* h0, int M, cudaStream_t st) {
-    const int rows_per_block = 64;
+    const int rows_per_block = slab_rows(M);
     MRL_LAUNCH((l0_forward_kernel<IN>), (M + rows_per_block - 1) / rows_per_block, H, 0, st, x, W0, b0, h0, M,
                rows_per_block);
     return MRL_OK;
@@ -730,16 +738,21 @@ int State::forward(const mrl_net_spec* net, const float* params, const float* x,
     const float* W0 = params; const float* b0 = W0 + (size_t)I * H;
     const float* W1 = b0 + H; const float* b1 = W1 + (size_t)H * H;
     const float* W2 = b1 + H; const float* b2 = W2 + (size_t)H * O;
+    prof_mark("(other)", st);
     MRL_LAUNCH(convert_w1_kernel, dim3(H / 32, H / 32), dim3(32, 8), 0, st, W1, w1, w1t);
+    prof_mark("convert_w1", st);
     int rc;
     if (I == 4) rc = l0_forward<4>(x, W0, b0, h0, batch, st);
     else if (I == 8) rc = l0_forward<8>(x, W0, b0, h0, batch, st);
     else rc = l0_forward<24>(x, W0, b0, h0, batch, st);
     if (rc) return rc;
+    prof_mark("l0_forward", st);
     K1Params p{};
     p.M = batch; p.bias = b1; p.W2 = W2; p.b2 = b2; p.out_dim = O; p.h1 = h1; p.head_out = head_out; p.head_ld = O;
     p.err = err;
-    return launch_k1_forward(tm_h0, tm_w1t, p, st);
+    rc = launch_k1_forward(tm_h0, tm_w1t, p, st);
+    prof_mark("k1_forward_gemm", st);
+    return rc;
 }
 
 int State::backward(const mrl_net_spec* net, const float* params, const float* x, const float* dout, float* grads,
@@ -748,34 +761,39 @@ int State::backward(const mrl_net_spec* net, const float* params, const float* x
     const size_t oW0 = 0, ob0 = (size_t)I * H, oW1 = ob0 + H, ob1 = oW1 + (size_t)H * H, oW2 = ob1 + H,
                  ob2 = oW2 + (size_t)H * O;
     const float* W2 = params + oW2;
-    // two blocks per SM, each walking a contiguous slab of rows (multiple of 8)
-    int rows_per_block = ((batch + 2 * sm_count() - 1) / (2 * sm_count()) + 7) & ~7;
-    if (rows_per_block < 64) rows_per_block = 64;
+    const int rows_per_block = slab_rows(batch);
     const int nblocks = (batch + rows_per_block - 1) / rows_per_block;
     const int OUT = O <= 1 ? 1 : (O <= 2 ? 2 : (O <= 4 ? 4 : 8));
     if (OUT == 1) { MRL_LAUNCH((head_backward_kernel<1>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
     else if (OUT == 2) { MRL_LAUNCH((head_backward_kernel<2>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
     else if (OUT == 4) { MRL_LAUNCH((head_backward_kernel<4>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
     else { MRL_LAUNCH((head_backward_kernel<8>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
+    prof_mark("head_backward", st);
     const int hstride = (OUT + 1) * H + OUT;
     MRL_LAUNCH(reduce_head_parts_kernel, ceil_div(hstride, 256), 256, 0, st, part, nblocks, OUT, O, grads + oW2,
                grads + ob2, grads + ob1);
+    prof_mark("reduce_head", st);
     // dh0 = g1 . W1^T, masked by h0 > 0 -> g0
     K1Params p{};
     p.M = batch; p.h0 = h0; p.g0 = g0; p.err = err;
     int rc = launch_k1<2, 1>(tm_g1, tm_w1, p, st);
     if (rc) return rc;
+    prof_mark("k1_dx_gemm", st);
     // dW0, db0
     if (I == 4) { MRL_LAUNCH((l0_backward_kernel<4>), nblocks, H, 0, st, g0, x, part, batch, rows_per_block); }
     else if (I == 8) { MRL_LAUNCH((l0_backward_kernel<8>), nblocks, H, 0, st, g0, x, part, batch, rows_per_block); }
     else { MRL_LAUNCH((l0_backward_kernel<24>), nblocks, H, 0, st, g0, x, part, batch, rows_per_block); }
+    prof_mark("l0_backward", st);
     MRL_LAUNCH(reduce_parts_kernel, ceil_div((I + 1) * H, 256), 256, 0, st, part, nblocks, (I + 1) * H, (I + 1) * H,
                grads + oW0);  // dW0 [I][256] then db0 [256] are adjacent in the gradient vector
+    prof_mark("reduce_l0", st);
     // dW1 = h0^T . g1 (split-K over the SMs), then the fixed-order reduction
     int splits = 0;
     rc = launch_k2<true>(tm_h0_mn, tm_g1_mn, batch, part, &splits, err, st);
     if (rc) return rc;
+    prof_mark("k2_dw_gemm", st);
     MRL_LAUNCH(reduce_parts_kernel, ceil_div(H * H, 256), 256, 0, st, part, splits, H * H, H * H, grads + oW1);
+    prof_mark("reduce_dw1", st);
     return MRL_OK;
 }
 
