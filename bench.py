@@ -178,7 +178,10 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     L = _lib.lib()
     agent = make_params(w, seed=0)   # same seed on every rank: replicas start identical
-    agent.precision = args.precision if args.precision is not None else int(os.environ.get("MRL_PRECISION", "0"))
+    # BASELINE.json: LunarLander "update matmuls in bf16"; the hidden-64 configs stay fp32 (launch-bound)
+    default_precision = 1 if w["hidden"] == 256 else 0
+    agent.precision = args.precision if args.precision is not None else int(
+        os.environ.get("MRL_PRECISION", str(default_precision)))
     h = agent.create_context(w["kind"], world_size=world, rank=rank)
     if world > 1:
         idt = torch.zeros(128, dtype=torch.uint8)

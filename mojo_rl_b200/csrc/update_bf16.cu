@@ -423,10 +423,14 @@ l0_forward_kernel(const float* __restrict__ x, const float* __restrict__ W0, con
     }
     const int rb = blockIdx.x * rows_per_block;
     const int re = min(M, rb + rows_per_block);
+    extern __shared__ float s_rows[];  // the slab's x rows: (re - rb) * IN floats
+    for (int i = threadIdx.x; i < (re - rb) * IN; i += H) s_rows[i] = x[(size_t)rb * IN + i];
+    __syncthreads();
+#pragma unroll 2
     for (int r = rb + vm.row_lane; r < re; r += 8) {
         float xr[IN];
 #pragma unroll
-        for (int k = 0; k < IN; ++k) xr[k] = __ldg(x + (size_t)r * IN + k);
+        for (int k = 0; k < IN; ++k) xr[k] = s_rows[(r - rb) * IN + k];
         float hv[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
@@ -463,26 +467,44 @@ head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout
     for (int u = 0; u < 8; ++u) db1[u] = 0.0f;
     const int rb = blockIdx.x * rows_per_block;
     const int re = min(M, rb + rows_per_block);
-    for (int r = rb + vm.row_lane; r < re; r += 8) {
-        float h[8], d[OUT], g[8];
-        unpack8(__ldg(reinterpret_cast<const uint4*>(h1 + (size_t)r * H + vm.col0)), h);
+    extern __shared__ float s_rows[];  // the slab's dout rows: (re - rb) * OUT floats
+    for (int i = threadIdx.x; i < (re - rb) * OUT; i += H) {
+        int rr = i / OUT, a = i % OUT;
+        s_rows[i] = a < out_dim ? dout[(size_t)(rb + rr) * ldd + a] : 0.0f;
+    }
+    __syncthreads();
+    constexpr int UNR = 4;  // independent 16-byte loads in flight per thread
+    for (int r0 = rb + vm.row_lane; r0 < re; r0 += 8 * UNR) {
+        uint4 raw[UNR];
 #pragma unroll
-        for (int a = 0; a < OUT; ++a) {
-            d[a] = a < out_dim ? __ldg(dout + (size_t)r * ldd + a) : 0.0f;
-            db2[a] += d[a];
+        for (int i = 0; i < UNR; ++i) {
+            const int r = r0 + 8 * i;
+            raw[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(h1 + (size_t)r * H + vm.col0)) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            float dh = 0.0f;
+        for (int i = 0; i < UNR; ++i) {
+            const int r = r0 + 8 * i;
+            if (r >= re) break;
+            float h[8], d[OUT], g[8];
+            unpack8(raw[i], h);
 #pragma unroll
             for (int a = 0; a < OUT; ++a) {
-                dh = fmaf(d[a], w2[a][u], dh);
-                dw2[a][u] = fmaf(h[u], d[a], dw2[a][u]);
+                d[a] = s_rows[(r - rb) * OUT + a];
+                db2[a] += d[a];
             }
-            g[u] = h[u] > 0.0f ? dh : 0.0f;
-            db1[u] += g[u];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                float dh = 0.0f;
+#pragma unroll
+                for (int a = 0; a < OUT; ++a) {
+                    dh = fmaf(d[a], w2[a][u], dh);
+                    dw2[a][u] = fmaf(h[u], d[a], dw2[a][u]);
+                }
+                g[u] = h[u] > 0.0f ? dh : 0.0f;
+                db1[u] += g[u];
+            }
+            *reinterpret_cast<uint4*>(g1 + (size_t)r * H + vm.col0) = pack8(g);
         }
-        *reinterpret_cast<uint4*>(g1 + (size_t)r * H + vm.col0) = pack8(g);
     }
     float* pb = part + (size_t)blockIdx.x * ((OUT + 1) * H + OUT);
 #pragma unroll
@@ -519,16 +541,31 @@ l0_backward_kernel(const bf16* __restrict__ g0, const float* __restrict__ x, flo
     }
     const int rb = blockIdx.x * rows_per_block;
     const int re = min(M, rb + rows_per_block);
-    for (int r = rb + vm.row_lane; r < re; r += 8) {
-        float g[8], xr[IN];
-        unpack8(__ldg(reinterpret_cast<const uint4*>(g0 + (size_t)r * H + vm.col0)), g);
+    extern __shared__ float s_rows[];  // the slab's x rows
+    for (int i = threadIdx.x; i < (re - rb) * IN; i += H) s_rows[i] = x[(size_t)rb * IN + i];
+    __syncthreads();
+    constexpr int UNR = 4;
+    for (int r0 = rb + vm.row_lane; r0 < re; r0 += 8 * UNR) {
+        uint4 raw[UNR];
 #pragma unroll
-        for (int k = 0; k < IN; ++k) xr[k] = __ldg(x + (size_t)r * IN + k);
+        for (int i = 0; i < UNR; ++i) {
+            const int r = r0 + 8 * i;
+            raw[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(g0 + (size_t)r * H + vm.col0)) : make_uint4(0, 0, 0, 0);
+        }
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            db[u] += g[u];
+        for (int i = 0; i < UNR; ++i) {
+            const int r = r0 + 8 * i;
+            if (r >= re) break;
+            float g[8];
+            unpack8(raw[i], g);
 #pragma unroll
-            for (int k = 0; k < IN; ++k) dw[k][u] = fmaf(xr[k], g[u], dw[k][u]);
+            for (int u = 0; u < 8; ++u) db[u] += g[u];
+#pragma unroll
+            for (int k = 0; k < IN; ++k) {
+                const float xk = s_rows[(r - rb) * IN + k];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) dw[k][u] = fmaf(xk, g[u], dw[k][u]);
+            }
         }
     }
     float* pb = part + (size_t)blockIdx.x * (IN + 1) * H;
@@ -560,21 +597,46 @@ __device__ __forceinline__ float sum_parts(const float* __restrict__ p, int nblo
     return (a0 + a1) + (a2 + a3);
 }
 
-// out[i] = sum_b part[b * stride + i]
+// Sum over partials for 32 consecutive outputs per block: lane = output, warp w
+// takes partials w, w + 8, ...; the eight warp sums are added in warp order.
+__device__ __forceinline__ float block_sum_parts(const float* __restrict__ part, int nblocks, int stride, int i,
+                                                 bool valid) {
+    __shared__ float sm[8][33];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    float a0 = 0.0f, a1 = 0.0f;
+    if (valid) {
+        int b = w;
+        for (; b + 8 < nblocks; b += 16) {
+            a0 += part[(size_t)b * stride + i];
+            a1 += part[(size_t)(b + 8) * stride + i];
+        }
+        if (b < nblocks) a0 += part[(size_t)b * stride + i];
+    }
+    sm[w][lane] = a0 + a1;
+    __syncthreads();
+    float acc = 0.0f;
+    if (w == 0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc += sm[k][lane];
+    }
+    return acc;  // valid in warp 0
+}
+
+// out[i] = sum_b part[b * stride + i]; grid = ceil(n / 32) blocks of 256 threads
 __global__ void reduce_parts_kernel(const float* __restrict__ part, int nblocks, int stride, int n,
                                     float* __restrict__ out) {
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    out[i] = sum_parts(part + i, nblocks, stride);
+    const int i = blockIdx.x * 32 + (threadIdx.x & 31);
+    float acc = block_sum_parts(part, nblocks, stride, i, i < n);
+    if ((threadIdx.x >> 5) == 0 && i < n) out[i] = acc;
 }
 // Head parts -> dW2 [256][out_dim] (transposed from [OUT][256]), db2, and db1.
 __global__ void reduce_head_parts_kernel(const float* __restrict__ part, int nblocks, int OUT, int out_dim,
                                          float* __restrict__ dW2, float* __restrict__ db2,
                                          float* __restrict__ db1) {
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int i = blockIdx.x * 32 + (threadIdx.x & 31);
     const int stride = (OUT + 1) * H + OUT;
-    if (i >= stride) return;
-    float acc = sum_parts(part + i, nblocks, stride);
+    float acc = block_sum_parts(part, nblocks, stride, i, i < stride);
+    if ((threadIdx.x >> 5) != 0 || i >= stride) return;
     if (i < OUT * H) {
         int a = i / H, j = i % H;
         if (a < out_dim) dW2[j * out_dim + a] = acc;
@@ -641,9 +703,12 @@ static int sm_count() {
 
 // Rows per block of the CUDA-core kernels: four blocks per SM, each walking a
 // contiguous slab of rows (a multiple of 8, at least 64).
-static int slab_rows(int M) {
+// The per-row fp32 operand of a slab (floats_per_row each) is staged in at most 40 KB of shared memory.
+static int slab_rows(int M, int floats_per_row) {
     int blocks = 4 * sm_count();
     int r = ((M + blocks - 1) / blocks + 7) & ~7;
+    int cap = (40960 / (4 * floats_per_row)) & ~7;
+    if (r > cap) r = cap;
     return r < 64 ? 64 : r;
 }
 
@@ -727,9 +792,9 @@ int State::init(void* workspace, int batch_, int* err_flag) {
 
 template <int IN>
 static int l0_forward(const float* x, const float* W0, const float* b0, bf16* h0, int M, cudaStream_t st) {
-    const int rows_per_block = slab_rows(M);
-    MRL_LAUNCH((l0_forward_kernel<IN>), (M + rows_per_block - 1) / rows_per_block, H, 0, st, x, W0, b0, h0, M,
-               rows_per_block);
+    const int rows_per_block = slab_rows(M, IN);
+    MRL_LAUNCH((l0_forward_kernel<IN>), (M + rows_per_block - 1) / rows_per_block, H, rows_per_block * IN * 4, st, x,
+               W0, b0, h0, M, rows_per_block);
     return MRL_OK;
 }
 
@@ -761,16 +826,16 @@ int State::backward(const mrl_net_spec* net, const float* params, const float* x
     const size_t oW0 = 0, ob0 = (size_t)I * H, oW1 = ob0 + H, ob1 = oW1 + (size_t)H * H, oW2 = ob1 + H,
                  ob2 = oW2 + (size_t)H * O;
     const float* W2 = params + oW2;
-    const int rows_per_block = slab_rows(batch);
+    const int rows_per_block = slab_rows(batch, I > 8 ? I : 8);
     const int nblocks = (batch + rows_per_block - 1) / rows_per_block;
     const int OUT = O <= 1 ? 1 : (O <= 2 ? 2 : (O <= 4 ? 4 : 8));
-    if (OUT == 1) { MRL_LAUNCH((head_backward_kernel<1>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
-    else if (OUT == 2) { MRL_LAUNCH((head_backward_kernel<2>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
-    else if (OUT == 4) { MRL_LAUNCH((head_backward_kernel<4>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
-    else { MRL_LAUNCH((head_backward_kernel<8>), nblocks, H, 0, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
+    if (OUT == 1) { MRL_LAUNCH((head_backward_kernel<1>), nblocks, H, rows_per_block * 1 * 4, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
+    else if (OUT == 2) { MRL_LAUNCH((head_backward_kernel<2>), nblocks, H, rows_per_block * 2 * 4, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
+    else if (OUT == 4) { MRL_LAUNCH((head_backward_kernel<4>), nblocks, H, rows_per_block * 4 * 4, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
+    else { MRL_LAUNCH((head_backward_kernel<8>), nblocks, H, rows_per_block * 8 * 4, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
     prof_mark("head_backward", st);
     const int hstride = (OUT + 1) * H + OUT;
-    MRL_LAUNCH(reduce_head_parts_kernel, ceil_div(hstride, 256), 256, 0, st, part, nblocks, OUT, O, grads + oW2,
+    MRL_LAUNCH(reduce_head_parts_kernel, ceil_div(hstride, 32), 256, 0, st, part, nblocks, OUT, O, grads + oW2,
                grads + ob2, grads + ob1);
     prof_mark("reduce_head", st);
     // dh0 = g1 . W1^T, masked by h0 > 0 -> g0
@@ -780,11 +845,11 @@ int State::backward(const mrl_net_spec* net, const float* params, const float* x
     if (rc) return rc;
     prof_mark("k1_dx_gemm", st);
     // dW0, db0
-    if (I == 4) { MRL_LAUNCH((l0_backward_kernel<4>), nblocks, H, 0, st, g0, x, part, batch, rows_per_block); }
-    else if (I == 8) { MRL_LAUNCH((l0_backward_kernel<8>), nblocks, H, 0, st, g0, x, part, batch, rows_per_block); }
-    else { MRL_LAUNCH((l0_backward_kernel<24>), nblocks, H, 0, st, g0, x, part, batch, rows_per_block); }
+    if (I == 4) { MRL_LAUNCH((l0_backward_kernel<4>), nblocks, H, rows_per_block * 4 * 4, st, g0, x, part, batch, rows_per_block); }
+    else if (I == 8) { MRL_LAUNCH((l0_backward_kernel<8>), nblocks, H, rows_per_block * 8 * 4, st, g0, x, part, batch, rows_per_block); }
+    else { MRL_LAUNCH((l0_backward_kernel<24>), nblocks, H, rows_per_block * 24 * 4, st, g0, x, part, batch, rows_per_block); }
     prof_mark("l0_backward", st);
-    MRL_LAUNCH(reduce_parts_kernel, ceil_div((I + 1) * H, 256), 256, 0, st, part, nblocks, (I + 1) * H, (I + 1) * H,
+    MRL_LAUNCH(reduce_parts_kernel, ceil_div((I + 1) * H, 32), 256, 0, st, part, nblocks, (I + 1) * H, (I + 1) * H,
                grads + oW0);  // dW0 [I][256] then db0 [256] are adjacent in the gradient vector
     prof_mark("reduce_l0", st);
     // dW1 = h0^T . g1 (split-K over the SMs), then the fixed-order reduction
@@ -792,7 +857,7 @@ int State::backward(const mrl_net_spec* net, const float* params, const float* x
     rc = launch_k2<true>(tm_h0_mn, tm_g1_mn, batch, part, &splits, err, st);
     if (rc) return rc;
     prof_mark("k2_dw_gemm", st);
-    MRL_LAUNCH(reduce_parts_kernel, ceil_div(H * H, 256), 256, 0, st, part, splits, H * H, H * H, grads + oW1);
+    MRL_LAUNCH(reduce_parts_kernel, ceil_div(H * H, 32), 256, 0, st, part, splits, H * H, H * H, grads + oW1);
     prof_mark("reduce_dw1", st);
     return MRL_OK;
 }
