@@ -200,6 +200,61 @@ int mrl_ppo_critic_grad(int batch, const float* values, const float* old_values,
 int mrl_grad_clip(int n, float* grads, float max_grad_norm, float* scratch, void* stream);
 
 /* ------------------------------------------------------------------------
+ * Gaussian policy of DeepPPOContinuousAgent (deep_agents/ppo/ppo_continuous.mojo,
+ * deep_agents/ppo/kernels.mojo).  actor_output rows are [mean(A) | log_std(A)],
+ * the StochasticActor layout (deep_rl/model/stochastic_actor.mojo:25-80).
+ * action_dim <= 16.
+ * ---------------------------------------------------------------------- */
+
+/* _sample_continuous_actions_kernel (kernels.mojo:12-98): one Philox stream
+ * per (env, dim) seeded Int(seed) + env * action_dim + dim, Box-Muller noise,
+ * log_std clamped to [-5, 2]; log_probs[env] sums the per-dim Gaussian
+ * log-densities.  greedy != 0 returns the mean (evaluation policy). */
+int mrl_sample_continuous_actions(int n_envs, int action_dim, const float* actor_output, float* actions,
+                                  float* log_probs, uint32_t seed, int greedy, void* stream);
+
+/* ppo_continuous_gather_minibatch_kernel (kernels.mojo:161-226):
+ * actions are action_dim floats per sample. */
+int mrl_ppo_gather_minibatch_continuous(int batch, int obs_dim, int action_dim, const int32_t* indices,
+                                        const float* rollout_obs, const float* rollout_actions,
+                                        const float* advantages, const float* returns,
+                                        const float* rollout_log_probs, const float* rollout_values,
+                                        float* mb_obs, float* mb_actions, float* mb_advantages,
+                                        float* mb_returns, float* mb_old_log_probs, float* mb_old_values,
+                                        void* stream);
+
+/* ppo_continuous_actor_grad_kernel (kernels.mojo:230-412): grad_output is
+ * [batch, 2 * action_dim]; zero where the clipped objective is the smaller one;
+ * each entry clipped to [-10, 10]; kl = (ratio - 1) - log ratio in [0, 100]. */
+int mrl_ppo_continuous_actor_grad(int batch, int action_dim, const float* actor_output,
+                                  const float* old_log_probs, const float* advantages, const float* actions,
+                                  float clip_epsilon, float entropy_coef, float* grad_output,
+                                  float* kl_divergences, void* stream);
+
+/* ppo_critic_grad_kernel / ppo_critic_grad_clipped_kernel of kernels.mojo:416-486
+ * (no value-loss coefficient). */
+int mrl_ppo_continuous_critic_grad(int batch, const float* values, const float* old_values,
+                                   const float* returns, float clip_epsilon, int clip_value,
+                                   float* grad_values, void* stream);
+
+/* clamp_log_std_params_kernel (kernels.mojo:842-873): clamps the state-independent
+ * log_std parameters (the last action_dim floats of the actor) to [-5, 2]. */
+int mrl_clamp_log_std(int action_dim, float* log_std_params, void* stream);
+
+/* RunningMeanStd.update followed by RunningMeanStd.normalize
+ * (core/utils/normalization.mojo:188-292) over one rollout of rewards.
+ * state3: {count, mean, var_sum} as three doubles of device memory, zero before
+ * the first call; scratch2: two doubles of device memory.  The reference runs
+ * this on the host (ppo_continuous.mojo:2867-2871). */
+int mrl_reward_rms_update_normalize(int64_t n, const float* rewards, float* normalized, double* state3,
+                                    double* scratch2, void* stream);
+
+/* Global advantage normalisation of the continuous agent
+ * (ppo_continuous.mojo:2906-2923): as mrl_normalize_advantages, but the square
+ * root is taken in double precision.  scratch: 4 floats, 8-byte aligned. */
+int mrl_normalize_advantages_f64sqrt(int64_t n, float* advantages, float* scratch, void* stream);
+
+/* ------------------------------------------------------------------------
  * L4 fused path: the three phases of DeepPPOAgent.train_gpu
  * (ppo.mojo:1558-2840) with every buffer resident in HBM and no host crossing
  * inside a phase.
@@ -218,6 +273,8 @@ typedef struct mrl_config {
     int32_t deterministic;   /* 1: greedy actions in the rollout (evaluation / parity) */
     int32_t world_size;      /* data-parallel ranks; gradients are averaged over them  */
     int32_t rank;
+    int32_t normalize_rewards; /* continuous agent only: RunningMeanStd reward normalisation before GAE
+                                  (ppo_continuous.mojo:2867-2871)                                    */
     double gamma;            /* Float64 in the reference; cast to f32 where it does    */
     double gae_lambda;       /* (gamma * gae_lambda is formed in f64, ppo.mojo:2319)   */
     float clip_epsilon;

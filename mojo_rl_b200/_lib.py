@@ -27,6 +27,7 @@ class Config(ctypes.Structure):
                 ("precision", ctypes.c_int32), ("normalize_advantages", ctypes.c_int32),
                 ("norm_adv_per_minibatch", ctypes.c_int32), ("clip_value", ctypes.c_int32),
                 ("deterministic", ctypes.c_int32), ("world_size", ctypes.c_int32), ("rank", ctypes.c_int32),
+                ("normalize_rewards", ctypes.c_int32),
                 ("gamma", ctypes.c_double), ("gae_lambda", ctypes.c_double), ("clip_epsilon", ctypes.c_float),
                 ("value_loss_coef", ctypes.c_float), ("target_kl", ctypes.c_float),
                 ("max_grad_norm", ctypes.c_float), ("adam_beta1", ctypes.c_float), ("adam_beta2", ctypes.c_float),
@@ -69,6 +70,13 @@ SIGNATURES = {
     "mrl_ppo_actor_grad": (ctypes.c_int, [ctypes.c_int, ctypes.c_int] + [c_void_p] * 4 + [ctypes.c_float, ctypes.c_float] + [c_void_p] * 3),
     "mrl_ppo_critic_grad": (ctypes.c_int, [ctypes.c_int] + [c_void_p] * 3 + [ctypes.c_float, ctypes.c_float, ctypes.c_int, c_void_p, c_void_p]),
     "mrl_grad_clip": (ctypes.c_int, [ctypes.c_int, c_void_p, ctypes.c_float, c_void_p, c_void_p]),
+    "mrl_sample_continuous_actions": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, c_void_p, c_void_p, c_void_p, ctypes.c_uint32, ctypes.c_int, c_void_p]),
+    "mrl_ppo_gather_minibatch_continuous": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int] + [c_void_p] * 14),
+    "mrl_ppo_continuous_actor_grad": (ctypes.c_int, [ctypes.c_int, ctypes.c_int] + [c_void_p] * 4 + [ctypes.c_float, ctypes.c_float] + [c_void_p] * 3),
+    "mrl_ppo_continuous_critic_grad": (ctypes.c_int, [ctypes.c_int] + [c_void_p] * 3 + [ctypes.c_float, ctypes.c_int, c_void_p, c_void_p]),
+    "mrl_clamp_log_std": (ctypes.c_int, [ctypes.c_int, c_void_p, c_void_p]),
+    "mrl_reward_rms_update_normalize": (ctypes.c_int, [ctypes.c_int64] + [c_void_p] * 5),
+    "mrl_normalize_advantages_f64sqrt": (ctypes.c_int, [ctypes.c_int64, c_void_p, c_void_p, c_void_p]),
     "mrl_config_defaults": (None, [ctypes.POINTER(Config)]),
     "mrl_create": (ctypes.c_int, [ctypes.POINTER(c_void_p), ctypes.POINTER(Config)]),
     "mrl_destroy": (ctypes.c_int, [c_void_p]),

@@ -73,6 +73,11 @@ using namespace mrl;
 struct mrl_ctx {
     mrl_config cfg;
     int state_size, obs_dim, num_actions, action_dim;
+    bool continuous;  // Gaussian policy (DeepPPOContinuousAgent): actions are action_dim floats per env
+    int act_w;        // floats per stored action
+    int head_w;       // columns of the actor output
+    float* r_rewards_norm;  // normalised copy of the rollout rewards (continuous agent)
+    double* rms_state;      // RunningMeanStd of the rewards: {count, mean, var_sum}
     mrl_net_spec actor_net, critic_net;
     int actor_p, critic_p;
     cudaStream_t stream;
@@ -138,6 +143,32 @@ __global__ void rollout_pre_step_kernel(const float* __restrict__ logits, const 
     actions[i] = a;
     size_t off = (size_t)t * n + i;
     r_actions[off] = a;
+    r_log_probs[off] = lp;
+    r_values[off] = values[i];
+    for (int d = 0; d < obs_dim; ++d) r_obs[off * obs_dim + d] = obs[(size_t)i * obs_dim + d];
+}
+
+// _sample_continuous_actions_kernel + _store_pre_step_kernel of the continuous
+// agent (ppo_continuous.mojo:2640-2690); same seed formula (:2620).
+__global__ void rollout_pre_step_continuous_kernel(const float* __restrict__ actor_out,
+                                                   const float* __restrict__ values, const float* __restrict__ obs,
+                                                   float* __restrict__ actions, float* __restrict__ r_obs,
+                                                   float* __restrict__ r_actions, float* __restrict__ r_log_probs,
+                                                   float* __restrict__ r_values,
+                                                   const DeviceCounters* __restrict__ ctr, int t, int n, int A,
+                                                   int obs_dim, int greedy) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    unsigned long long ts = (unsigned long long)ctr->total_steps + (unsigned long long)t * (unsigned long long)n;
+    uint32_t seed = (uint32_t)(ts * 2654435761ull + (unsigned long long)t * 7919ull);
+    float act[MAX_ACTIONS];
+    float lp;
+    sample_continuous_one(actor_out + (size_t)i * 2 * A, A, seed, i, greedy, act, lp);
+    size_t off = (size_t)t * n + i;
+    for (int j = 0; j < A; ++j) {
+        actions[(size_t)i * A + j] = act[j];
+        r_actions[off * A + j] = act[j];
+    }
     r_log_probs[off] = lp;
     r_values[off] = values[i];
     for (int d = 0; d < obs_dim; ++d) r_obs[off * obs_dim + d] = obs[(size_t)i * obs_dim + d];
@@ -272,6 +303,8 @@ struct PhaseTimer {
     ~PhaseTimer() { if (stop) cudaEventRecord(stop, c->stream); }
 };
 
+void launch_clamp_log_std(float* log_std, int A, const int* skip, cudaStream_t st);  // ppo_kernels.cu
+
 static int allreduce_f32(mrl_ctx* c, float* buf, size_t n) {
     if (c->cfg.world_size <= 1) return MRL_OK;
     if (!c->comm) { set_error("world_size > 1 but mrl_comm_init was not called"); return MRL_ERR_NCCL; }
@@ -304,6 +337,7 @@ extern "C" void mrl_config_defaults(mrl_config* cfg) {
     cfg->deterministic = 0;
     cfg->world_size = 1;
     cfg->rank = 0;
+    cfg->normalize_rewards = 1;  // ppo_continuous.mojo:258
     cfg->gamma = 0.99;
     cfg->gae_lambda = 0.95;
     cfg->clip_epsilon = 0.2f;
@@ -359,14 +393,24 @@ extern "C" int mrl_create(mrl_ctx** out, const mrl_config* cfg) {
     int ss, od, na, ad;
     int rc = mrl_env_info(cfg->env_kind, &ss, &od, &na, &ad);
     if (rc) return rc;
-    if (na == 0) { set_error("continuous-action envs are not built into the fused path yet"); return MRL_ERR_UNSUPPORTED; }
+    MRL_CHECK_ARG(na <= MAX_ACTIONS && ad <= MAX_ACTIONS);
     const int64_t total = (int64_t)cfg->n_envs * cfg->rollout_len;
     MRL_CHECK_ARG(cfg->minibatch_size <= total && total < (1ll << 31));
     mrl_ctx* c = new mrl_ctx();
     c->cfg = *cfg;
     c->state_size = ss; c->obs_dim = od; c->num_actions = na; c->action_dim = ad;
-    c->actor_net = mrl_net_spec{od, cfg->hidden_dim, na, MRL_ACT_RELU, MRL_HEAD_LINEAR};   // ppo.mojo:807-818
-    c->critic_net = mrl_net_spec{od, cfg->hidden_dim, 1, MRL_ACT_RELU, MRL_HEAD_LINEAR};   // ppo.mojo:820-830
+    c->continuous = ad > 0;
+    if (c->continuous) {  // ppo_continuous.mojo:171-194: tanh trunk, StochasticActor head
+        c->actor_net = mrl_net_spec{od, cfg->hidden_dim, ad, MRL_ACT_TANH, MRL_HEAD_STOCHASTIC_ACTOR};
+        c->critic_net = mrl_net_spec{od, cfg->hidden_dim, 1, MRL_ACT_TANH, MRL_HEAD_LINEAR};
+        c->act_w = ad;
+        c->head_w = 2 * ad;
+    } else {
+        c->actor_net = mrl_net_spec{od, cfg->hidden_dim, na, MRL_ACT_RELU, MRL_HEAD_LINEAR};   // ppo.mojo:807-818
+        c->critic_net = mrl_net_spec{od, cfg->hidden_dim, 1, MRL_ACT_RELU, MRL_HEAD_LINEAR};   // ppo.mojo:820-830
+        c->act_w = 1;
+        c->head_w = na;
+    }
     c->actor_p = mrl_net_param_size(&c->actor_net);
     c->critic_p = mrl_net_param_size(&c->critic_net);
     c->comm = nullptr;
@@ -380,15 +424,17 @@ extern "C" int mrl_create(mrl_ctx** out, const mrl_config* cfg) {
     const size_t N = cfg->n_envs, T = cfg->rollout_len, B = cfg->minibatch_size;
     int64_t ws = mlp_workspace_floats(&c->actor_net, (int)(B > N ? B : N));
 #define A_(p, n) do { rc = dalloc(c, &c->p, (n)); if (rc) { mrl_destroy(c); return rc; } } while (0)
-    A_(states, N * ss); A_(obs, N * od); A_(actions, N); A_(log_probs, N); A_(values, N);
-    A_(rewards, N); A_(dones, N); A_(logits, N * na); A_(episode_rewards, N); A_(episode_steps, N);
-    A_(r_obs, T * N * od); A_(r_actions, T * N); A_(r_log_probs, T * N); A_(r_values, T * N);
+    const size_t AW = c->act_w, HW = c->head_w;
+    A_(states, N * ss); A_(obs, N * od); A_(actions, N * AW); A_(log_probs, N); A_(values, N);
+    A_(rewards, N); A_(dones, N); A_(logits, N * HW); A_(episode_rewards, N); A_(episode_steps, N);
+    A_(r_obs, T * N * od); A_(r_actions, T * N * AW); A_(r_log_probs, T * N); A_(r_values, T * N);
     A_(r_rewards, T * N); A_(r_dones, T * N); A_(advantages, T * N); A_(returns, T * N); A_(bootstrap, N);
     A_(ring_returns, EP_RING); A_(ring_lengths, EP_RING);
     A_(actor_params, c->actor_p); A_(actor_state, 2 * (size_t)c->actor_p); A_(actor_grads, c->actor_p + 4);
     A_(critic_params, c->critic_p); A_(critic_state, 2 * (size_t)c->critic_p); A_(critic_grads, c->critic_p + 4);
-    A_(mb_obs, B * od); A_(mb_actions, B); A_(mb_adv, B); A_(mb_ret, B); A_(mb_old_lp, B); A_(mb_old_v, B);
-    A_(mb_kl, B); A_(mb_logits, B * na); A_(mb_grad_logits, B * na); A_(mb_values, B); A_(mb_grad_values, B);
+    A_(r_rewards_norm, c->continuous ? T * N : 1); A_(rms_state, 4);
+    A_(mb_obs, B * od); A_(mb_actions, B * AW); A_(mb_adv, B); A_(mb_ret, B); A_(mb_old_lp, B); A_(mb_old_v, B);
+    A_(mb_kl, B); A_(mb_logits, B * HW); A_(mb_grad_logits, B * HW); A_(mb_values, B); A_(mb_grad_values, B);
     A_(actor_cache, B * (size_t)mrl_net_cache_per_sample(&c->actor_net));
     A_(critic_cache, B * (size_t)mrl_net_cache_per_sample(&c->critic_net));
     A_(workspace, (size_t)ws);
@@ -401,7 +447,8 @@ extern "C" int mrl_create(mrl_ctx** out, const mrl_config* cfg) {
     c->use_tc_policy = false;
     if (cfg->precision == 1) {
         if (!tc::supported(&c->actor_net, (int)B) || !tc::supported(&c->critic_net, (int)B)) {
-            set_error("precision 1 (bf16 tensor-core update) needs hidden_dim 256, ReLU nets, obs_dim in {4, 8, 24}, "
+            set_error("precision 1 (bf16 tensor-core update) needs hidden_dim 256, ReLU nets with linear heads "
+                      "(the discrete agent), obs_dim in {4, 8, 24}, "
                       "head width <= 8 and a minibatch that is a multiple of 128; use precision 0");
             mrl_destroy(c);
             return MRL_ERR_UNSUPPORTED;
@@ -410,7 +457,7 @@ extern "C" int mrl_create(mrl_ctx** out, const mrl_config* cfg) {
         rc = c->tc.init(c->tc_workspace, (int)B, c->tc_err);
         if (rc) { mrl_destroy(c); return rc; }
         c->use_tc = true;
-        if (tc::policy_supported(od, na, cfg->hidden_dim)) {
+        if (!c->continuous && tc::policy_supported(od, na, cfg->hidden_dim)) {
             A_(policy_workspace, (size_t)tc::policy_workspace_bytes());
             rc = c->policy.init(c->policy_workspace, c->tc_err);
             if (rc) { mrl_destroy(c); return rc; }
@@ -533,9 +580,15 @@ extern "C" int mrl_ppo_rollout(mrl_ctx* c) {
         } else {
             if ((rc = mlp_forward_impl(&c->actor_net, N, c->obs, c->actor_params, c->logits, nullptr, c->workspace, st))) return rc;
             if ((rc = mlp_forward_impl(&c->critic_net, N, c->obs, c->critic_params, c->values, nullptr, c->workspace, st))) return rc;
-            MRL_LAUNCH(rollout_pre_step_kernel, ceil_div(N, 128), 128, 0, st, c->logits, c->values, c->obs, c->actions,
-                       c->r_obs, c->r_actions, c->r_log_probs, c->r_values, c->counters, t, N, A, c->obs_dim,
-                       c->cfg.deterministic);
+            if (c->continuous) {
+                MRL_LAUNCH(rollout_pre_step_continuous_kernel, ceil_div(N, 128), 128, 0, st, c->logits, c->values,
+                           c->obs, c->actions, c->r_obs, c->r_actions, c->r_log_probs, c->r_values, c->counters, t, N,
+                           c->action_dim, c->obs_dim, c->cfg.deterministic);
+            } else {
+                MRL_LAUNCH(rollout_pre_step_kernel, ceil_div(N, 128), 128, 0, st, c->logits, c->values, c->obs,
+                           c->actions, c->r_obs, c->r_actions, c->r_log_probs, c->r_values, c->counters, t, N, A,
+                           c->obs_dim, c->cfg.deterministic);
+            }
         }
         RolloutStepArgs ra{c->states, c->actions, c->rewards, c->dones, c->obs, c->r_rewards, c->r_dones,
                            c->episode_rewards, c->episode_steps, c->ring_returns, c->ring_lengths, c->counters, t, N,
@@ -553,10 +606,15 @@ extern "C" int mrl_ppo_gae(mrl_ctx* c) {
     int rc;
     PhaseTimer timer(c, 1);
     if ((rc = mlp_forward_impl(&c->critic_net, N, c->obs, c->critic_params, c->bootstrap, nullptr, c->workspace, st))) return rc;
-    if ((rc = mrl_gae(T, N, c->r_rewards, c->r_values, c->r_dones, c->bootstrap, c->cfg.gamma, c->cfg.gae_lambda,
+    const float* rewards = c->r_rewards;
+    if (c->continuous && c->cfg.normalize_rewards) {  // ppo_continuous.mojo:2867-2871
+        if ((rc = reward_rms_impl((int64_t)T * N, c->r_rewards, c->r_rewards_norm, c->rms_state, c->stats, st))) return rc;
+        rewards = c->r_rewards_norm;
+    }
+    if ((rc = mrl_gae(T, N, rewards, c->r_values, c->r_dones, c->bootstrap, c->cfg.gamma, c->cfg.gae_lambda,
                       c->advantages, c->returns, st))) return rc;
     if (c->cfg.normalize_advantages) {
-        if ((rc = normalize_advantages_impl((int64_t)T * N, c->advantages, c->stats, st))) return rc;
+        if ((rc = normalize_advantages_impl((int64_t)T * N, c->advantages, c->stats, st, c->continuous))) return rc;
     }
     return MRL_OK;
 }
@@ -587,7 +645,7 @@ extern "C" int mrl_ppo_update(mrl_ctx* c, float actor_lr, float critic_lr, float
                 MRL_LAUNCH(make_indices_kernel, ceil_div(B, 256), 256, 0, st, idx, B, (uint32_t)mb * (uint32_t)B, total,
                            half, key);
             }
-            if ((rc = mrl_ppo_gather_minibatch(B, c->obs_dim, idx, c->r_obs, c->r_actions, c->advantages, c->returns,
+            if ((rc = mrl_ppo_gather_minibatch_continuous(B, c->obs_dim, c->act_w, idx, c->r_obs, c->r_actions, c->advantages, c->returns,
                                                c->r_log_probs, c->r_values, c->mb_obs, c->mb_actions, c->mb_adv,
                                                c->mb_ret, c->mb_old_lp, c->mb_old_v, st))) return rc;
             if (cfg.norm_adv_per_minibatch) {
@@ -598,8 +656,12 @@ extern "C" int mrl_ppo_update(mrl_ctx* c, float actor_lr, float critic_lr, float
                 if ((rc = c->tc.forward(&c->actor_net, c->actor_params, c->mb_obs, c->mb_logits, st))) return rc;
             } else if ((rc = mlp_forward_impl(&c->actor_net, B, c->mb_obs, c->actor_params, c->mb_logits,
                                               c->actor_cache, c->workspace, st))) return rc;
-            if ((rc = mrl_ppo_actor_grad(B, A, c->mb_logits, c->mb_old_lp, c->mb_adv, c->mb_actions, cfg.clip_epsilon,
-                                         entropy_coef, c->mb_grad_logits, c->mb_kl, st))) return rc;
+            if (c->continuous) {
+                if ((rc = mrl_ppo_continuous_actor_grad(B, c->action_dim, c->mb_logits, c->mb_old_lp, c->mb_adv,
+                                                        c->mb_actions, cfg.clip_epsilon, entropy_coef,
+                                                        c->mb_grad_logits, c->mb_kl, st))) return rc;
+            } else if ((rc = mrl_ppo_actor_grad(B, A, c->mb_logits, c->mb_old_lp, c->mb_adv, c->mb_actions,
+                                                cfg.clip_epsilon, entropy_coef, c->mb_grad_logits, c->mb_kl, st))) return rc;
             {
                 int parts = ceil_div(B, 1024) < 256 ? ceil_div(B, 1024) : 256;
                 MRL_LAUNCH(kl_partial_kernel, parts, 256, 0, st, c->mb_kl, B, c->kl_partial);
@@ -622,13 +684,21 @@ extern "C" int mrl_ppo_update(mrl_ctx* c, float actor_lr, float critic_lr, float
             }
             MRL_LAUNCH(adam_ctx_kernel, ceil_div(c->actor_p, 256), 256, 0, st, c->actor_params, c->actor_grads,
                        c->actor_state, c->actor_p, actor_lr, cfg.adam_beta1, cfg.adam_beta2, cfg.adam_eps, c->counters);
+            if (c->continuous) {  // clamp_log_std_params_kernel after the actor step (ppo_continuous.mojo:3151-3171)
+                launch_clamp_log_std(c->actor_params + c->actor_p - c->action_dim, c->action_dim,
+                                     &c->counters->adam_skip, st);
+                MRL_CUDA_OK(cudaGetLastError());
+            }
             // ---- critic (ppo.mojo:2626-2728)
             if (c->use_tc) {
                 if ((rc = c->tc.forward(&c->critic_net, c->critic_params, c->mb_obs, c->mb_values, st))) return rc;
             } else if ((rc = mlp_forward_impl(&c->critic_net, B, c->mb_obs, c->critic_params, c->mb_values,
                                               c->critic_cache, c->workspace, st))) return rc;
-            if ((rc = mrl_ppo_critic_grad(B, c->mb_values, c->mb_old_v, c->mb_ret, cfg.value_loss_coef,
-                                          cfg.clip_epsilon, cfg.clip_value, c->mb_grad_values, st))) return rc;
+            if (c->continuous) {
+                if ((rc = mrl_ppo_continuous_critic_grad(B, c->mb_values, c->mb_old_v, c->mb_ret, cfg.clip_epsilon,
+                                                         cfg.clip_value, c->mb_grad_values, st))) return rc;
+            } else if ((rc = mrl_ppo_critic_grad(B, c->mb_values, c->mb_old_v, c->mb_ret, cfg.value_loss_coef,
+                                                 cfg.clip_epsilon, cfg.clip_value, c->mb_grad_values, st))) return rc;
             if (c->use_tc) {
                 if ((rc = c->tc.backward(&c->critic_net, c->critic_params, c->mb_obs, c->mb_grad_values,
                                          c->critic_grads, st))) return rc;
@@ -661,7 +731,7 @@ extern "C" int mrl_get_buffer(mrl_ctx* c, int which, float** device_ptr, int64_t
         case MRL_BUF_STATES: p = c->states; n = N * c->state_size; break;
         case MRL_BUF_OBS: p = c->obs; n = N * c->obs_dim; break;
         case MRL_BUF_ROLLOUT_OBS: p = c->r_obs; n = T * N * c->obs_dim; break;
-        case MRL_BUF_ROLLOUT_ACTIONS: p = c->r_actions; n = T * N; break;
+        case MRL_BUF_ROLLOUT_ACTIONS: p = c->r_actions; n = T * N * c->act_w; break;
         case MRL_BUF_ROLLOUT_LOG_PROBS: p = c->r_log_probs; n = T * N; break;
         case MRL_BUF_ROLLOUT_VALUES: p = c->r_values; n = T * N; break;
         case MRL_BUF_ROLLOUT_REWARDS: p = c->r_rewards; n = T * N; break;

@@ -3,6 +3,8 @@
 // Compile with -fmad=false (bit-level parity with the CPU checker).
 #include "env_cartpole.cuh"
 #include "env_lunar.cuh"
+#include "env_pendulum.cuh"
+#include "env_cheetah.cuh"
 #include "rollout.cuh"
 #include "umma.cuh"
 
@@ -43,6 +45,59 @@ __global__ void cartpole_selective_reset_kernel(float* __restrict__ states, floa
     cartpole::reset(s, (uint32_t)((uint64_t)i * 2654435761ull + seed32));
     reinterpret_cast<float4*>(states)[i] = make_float4(s[0], s[1], s[2], s[3]);
     dones[i] = 0.0f;
+}
+
+// ---------------------------------------------------------------- Pendulum
+__global__ void pendulum_step_kernel(float* __restrict__ states, const float* __restrict__ actions,
+                                     float* __restrict__ rewards, float* __restrict__ dones,
+                                     float* __restrict__ obs, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float s[8];
+    pendulum::load_row(states + (size_t)i * 8, s);
+    float r, d;
+    pendulum::step(s, actions[i], r, d);
+    pendulum::store_row(states + (size_t)i * 8, s);
+    rewards[i] = r;
+    dones[i] = d;
+    obs[(size_t)i * 3 + 0] = s[0];
+    obs[(size_t)i * 3 + 1] = s[1];
+    obs[(size_t)i * 3 + 2] = s[2];
+}
+
+// dones == nullptr: reset every environment; otherwise only where done > 0.5,
+// clearing the flag (pendulum_v2.mojo:381-392).
+__global__ void pendulum_reset_kernel(float* __restrict__ states, float* __restrict__ dones, float seed_f32,
+                                      int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    if (dones != nullptr) {
+        if (!(dones[i] > 0.5f)) return;
+        dones[i] = 0.0f;
+    }
+    float s[8];
+    pendulum::reset(s, pendulum::combined_seed(seed_f32, i));
+    pendulum::store_row(states + (size_t)i * 8, s);
+}
+
+__global__ void pendulum_rollout_step_kernel(RolloutStepArgs a) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.n) return;
+    float s[8];
+    pendulum::load_row(a.states + (size_t)i * 8, s);
+    float r, d;
+    pendulum::step(s, a.actions[i], r, d);
+    a.rewards[i] = r;
+    track_episode(a, i, r, d);
+    if (d > 0.5f) {
+        pendulum::reset(s, pendulum::combined_seed((float)auto_reset_seed(a), i));
+        d = 0.0f;
+    }
+    a.dones[i] = d;
+    pendulum::store_row(a.states + (size_t)i * 8, s);
+    a.obs[(size_t)i * 3 + 0] = s[0];
+    a.obs[(size_t)i * 3 + 1] = s[1];
+    a.obs[(size_t)i * 3 + 2] = s[2];
 }
 
 // ------------------------------------------------------------- LunarLander
@@ -139,6 +194,114 @@ __global__ void __launch_bounds__(LUNAR_TPB) lunar_rollout_step_kernel(RolloutSt
     lunar_rows_from_smem(a.states, sm, env0, a.n);
 }
 
+// ------------------------------------------------------------ HalfCheetah
+// 253-float rows: a block stages its rows in shared memory like the lander
+// kernels.  A bulk copy moves multiples of 16 bytes, i.e. groups of four rows
+// (4 x 1012 B); the up to three rows left in the last block move with plain
+// loads.  The odd row pitch keeps the per-thread row accesses free of bank
+// conflicts.
+constexpr int CHEETAH_TPB = 64;
+constexpr int CHEETAH_ROW = cheetah::STATE_SIZE;
+constexpr int CHEETAH_SMEM = CHEETAH_TPB * CHEETAH_ROW * 4 + 16;
+
+template <int ROW, int TPB>
+__device__ __forceinline__ bool rows_to_smem(const float* __restrict__ states, float* sm, uint64_t* bar, int env0,
+                                             int n, int* err, int code) {
+    const int rows = min(TPB, n - env0);
+    const int bulk_rows = (ROW % 4 == 0) ? rows : (rows & ~3);
+    if (threadIdx.x == 0 && bulk_rows > 0) {
+        umma::mbar_init(bar, 1);
+        umma::fence_barrier_init();
+        umma::mbar_arrive_expect_tx(bar, bulk_rows * ROW * 4);
+        umma::bulk_load(sm, states + (size_t)env0 * ROW, bulk_rows * ROW * 4, bar);
+    }
+    for (int i = bulk_rows * ROW + threadIdx.x; i < rows * ROW; i += TPB) sm[i] = states[(size_t)env0 * ROW + i];
+    __syncthreads();
+    if (bulk_rows == 0) return true;
+    return umma::mbar_wait(bar, 0, err, code);
+}
+template <int ROW, int TPB>
+__device__ __forceinline__ void rows_from_smem(float* __restrict__ states, const float* sm, int env0, int n) {
+    const int rows = min(TPB, n - env0);
+    const int bulk_rows = (ROW % 4 == 0) ? rows : (rows & ~3);
+    umma::fence_proxy_async_smem();
+    __syncthreads();
+    if (threadIdx.x == 0 && bulk_rows > 0) {
+        umma::bulk_store(states + (size_t)env0 * ROW, sm, bulk_rows * ROW * 4);
+        umma::bulk_store_wait_read();
+    }
+    for (int i = bulk_rows * ROW + threadIdx.x; i < rows * ROW; i += TPB) states[(size_t)env0 * ROW + i] = sm[i];
+}
+
+__global__ void __launch_bounds__(CHEETAH_TPB)
+cheetah_step_rows_kernel(float* __restrict__ states, const float* __restrict__ actions,
+                         float* __restrict__ rewards, float* __restrict__ dones, float* __restrict__ obs, int n,
+                         int* err) {
+    extern __shared__ __align__(128) float sm[];
+    uint64_t* bar = reinterpret_cast<uint64_t*>(sm + CHEETAH_TPB * CHEETAH_ROW);
+    const int env0 = blockIdx.x * CHEETAH_TPB;
+    if (!rows_to_smem<CHEETAH_ROW, CHEETAH_TPB>(states, sm, bar, env0, n, err, 402)) return;
+    const int env = env0 + threadIdx.x;
+    if (env < n) {
+        float o[cheetah::OBS_DIM], reward, done;
+        cheetah::step_row(sm + threadIdx.x * CHEETAH_ROW, actions + (size_t)env * cheetah::ACTION_DIM, o, reward,
+                          done);
+        rewards[env] = reward;
+        dones[env] = done;
+#pragma unroll
+        for (int d = 0; d < cheetah::OBS_DIM; ++d) obs[(size_t)env * cheetah::OBS_DIM + d] = o[d];
+    }
+    rows_from_smem<CHEETAH_ROW, CHEETAH_TPB>(states, sm, env0, n);
+}
+
+__global__ void __launch_bounds__(CHEETAH_TPB) cheetah_rollout_step_kernel(RolloutStepArgs a) {
+    extern __shared__ __align__(128) float sm[];
+    uint64_t* bar = reinterpret_cast<uint64_t*>(sm + CHEETAH_TPB * CHEETAH_ROW);
+    const int env0 = blockIdx.x * CHEETAH_TPB;
+    if (!rows_to_smem<CHEETAH_ROW, CHEETAH_TPB>(a.states, sm, bar, env0, a.n, a.err, 403)) return;
+    const int env = env0 + threadIdx.x;
+    if (env < a.n) {
+        float* s = sm + threadIdx.x * CHEETAH_ROW;
+        float o[cheetah::OBS_DIM], reward, done;
+        cheetah::step_row(s, a.actions + (size_t)env * cheetah::ACTION_DIM, o, reward, done);
+        a.rewards[env] = reward;
+        track_episode(a, env, reward, done);
+        if (done > 0.5f) {  // cheetah_planar_v2.mojo:1121-1167: reset and clear the flag
+            cheetah::reset_row(s, cheetah::combined_seed((float)auto_reset_seed(a), env));
+            done = 0.0f;
+#pragma unroll
+            for (int d = 0; d < cheetah::OBS_DIM; ++d) o[d] = s[d];
+        }
+        a.dones[env] = done;
+#pragma unroll
+        for (int d = 0; d < cheetah::OBS_DIM; ++d) a.obs[(size_t)env * cheetah::OBS_DIM + d] = o[d];
+    }
+    rows_from_smem<CHEETAH_ROW, CHEETAH_TPB>(a.states, sm, env0, a.n);
+}
+
+// dones == nullptr: reset every environment; otherwise only where done > 0.5, clearing the flag.
+__global__ void cheetah_reset_rows_kernel(float* __restrict__ states, float* __restrict__ dones, float seed_f32,
+                                          int n) {
+    int env = blockIdx.x * blockDim.x + threadIdx.x;
+    if (env >= n) return;
+    if (dones != nullptr) {
+        if (!(dones[env] > 0.5f)) return;
+        dones[env] = 0.0f;
+    }
+    cheetah::reset_row(states + (size_t)env * CHEETAH_ROW, cheetah::combined_seed(seed_f32, env));
+}
+
+static cudaError_t ensure_cheetah_smem() {
+    static bool done = false;
+    if (done) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(cheetah_step_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         CHEETAH_SMEM);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(cheetah_rollout_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CHEETAH_SMEM);
+    if (e == cudaSuccess) done = true;
+    return e;
+}
+
 __global__ void cartpole_rollout_step_kernel(RolloutStepArgs a) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= a.n) return;
@@ -198,6 +361,13 @@ int rollout_env_step(int env_kind, const RolloutStepArgs& a, cudaStream_t st) {
         case MRL_ENV_CARTPOLE:
             MRL_LAUNCH(cartpole_rollout_step_kernel, ceil_div(a.n, 128), 128, 0, st, a);
             return MRL_OK;
+        case MRL_ENV_PENDULUM:
+            MRL_LAUNCH(pendulum_rollout_step_kernel, ceil_div(a.n, 128), 128, 0, st, a);
+            return MRL_OK;
+        case MRL_ENV_HALF_CHEETAH:
+            MRL_CUDA_OK(ensure_cheetah_smem());
+            MRL_LAUNCH(cheetah_rollout_step_kernel, ceil_div(a.n, CHEETAH_TPB), CHEETAH_TPB, CHEETAH_SMEM, st, a);
+            return MRL_OK;
         case MRL_ENV_LUNAR_LANDER:
             MRL_CUDA_OK(ensure_lunar_smem());
             MRL_LAUNCH(lunar_rollout_step_kernel, ceil_div(a.n, LUNAR_TPB), LUNAR_TPB, LUNAR_SMEM, st, a);
@@ -218,6 +388,8 @@ extern "C" int mrl_env_info(int env_kind, int* state_size, int* obs_dim, int* nu
     switch (env_kind) {
         case MRL_ENV_CARTPOLE: ss = 4; od = 4; na = 2; ad = 0; break;
         case MRL_ENV_LUNAR_LANDER: ss = lunar::STATE_SIZE; od = 8; na = 4; ad = 0; break;
+        case MRL_ENV_PENDULUM: ss = 8; od = 3; na = 0; ad = 1; break;
+        case MRL_ENV_HALF_CHEETAH: ss = cheetah::STATE_SIZE; od = 17; na = 0; ad = 6; break;
         default:
             set_error("mrl_env_info: env kind %d is not built", env_kind);
             return MRL_ERR_UNSUPPORTED;
@@ -240,6 +412,14 @@ extern "C" int mrl_env_reset(int env_kind, int batch, float* states, uint64_t rn
             MRL_LAUNCH(lunar_reset_rows_kernel, ceil_div(batch, ENV_TPB), ENV_TPB, 0, st, states,
                        (const float*)nullptr, (float)rng_seed, batch);
             return MRL_OK;
+        case MRL_ENV_PENDULUM:
+            MRL_LAUNCH(pendulum_reset_kernel, ceil_div(batch, 256), 256, 0, st, states, (float*)nullptr,
+                       (float)rng_seed, batch);
+            return MRL_OK;
+        case MRL_ENV_HALF_CHEETAH:
+            MRL_LAUNCH(cheetah_reset_rows_kernel, ceil_div(batch, ENV_TPB), ENV_TPB, 0, st, states, (float*)nullptr,
+                       (float)rng_seed, batch);
+            return MRL_OK;
         default:
             set_error("mrl_env_reset: env kind %d is not built", env_kind);
             return MRL_ERR_UNSUPPORTED;
@@ -249,13 +429,25 @@ extern "C" int mrl_env_reset(int env_kind, int batch, float* states, uint64_t rn
 extern "C" int mrl_env_step(int env_kind, int batch, float* states, const float* actions,
                             float* rewards, float* dones, float* obs, uint64_t rng_seed, void* stream) {
     MRL_CHECK_ARG(batch > 0 && states && actions && rewards && dones && obs);
-    (void)rng_seed;  // neither CartPole nor LunarLander consumes the per-step seed
+    (void)rng_seed;  // none of the built environments consumes the per-step seed
     cudaStream_t st = as_stream(stream);
     int* err_word = nullptr;
     switch (env_kind) {
         case MRL_ENV_CARTPOLE:
             MRL_LAUNCH(cartpole_step_kernel, ceil_div(batch, 256), 256, 0, st, states, actions, rewards,
                        dones, obs, batch);
+            return MRL_OK;
+        case MRL_ENV_PENDULUM:
+            MRL_CHECK_ARG(((uintptr_t)states & 15) == 0);
+            MRL_LAUNCH(pendulum_step_kernel, ceil_div(batch, 256), 256, 0, st, states, actions, rewards, dones, obs,
+                       batch);
+            return MRL_OK;
+        case MRL_ENV_HALF_CHEETAH:
+            MRL_CUDA_OK(ensure_cheetah_smem());
+            MRL_CHECK_ARG(((uintptr_t)states & 15) == 0);
+            MRL_CUDA_OK(boundary_err_word(&err_word));
+            MRL_LAUNCH(cheetah_step_rows_kernel, ceil_div(batch, CHEETAH_TPB), CHEETAH_TPB, CHEETAH_SMEM, st, states,
+                       actions, rewards, dones, obs, batch, err_word);
             return MRL_OK;
         case MRL_ENV_LUNAR_LANDER:
             MRL_CUDA_OK(ensure_lunar_smem());
@@ -282,6 +474,14 @@ extern "C" int mrl_env_selective_reset(int env_kind, int batch, float* states, f
         case MRL_ENV_LUNAR_LANDER:
             MRL_LAUNCH(lunar_reset_rows_kernel, ceil_div(batch, ENV_TPB), ENV_TPB, 0, st, states,
                        (const float*)dones, (float)rng_seed, batch);
+            return MRL_OK;
+        case MRL_ENV_PENDULUM:
+            MRL_LAUNCH(pendulum_reset_kernel, ceil_div(batch, 256), 256, 0, st, states, dones, (float)rng_seed,
+                       batch);
+            return MRL_OK;
+        case MRL_ENV_HALF_CHEETAH:
+            MRL_LAUNCH(cheetah_reset_rows_kernel, ceil_div(batch, ENV_TPB), ENV_TPB, 0, st, states, dones,
+                       (float)rng_seed, batch);
             return MRL_OK;
         default:
             set_error("mrl_env_selective_reset: env kind %d is not built", env_kind);

@@ -7,7 +7,9 @@
 // the bias - the summation order of the reference's 16x16 tiled kernels
 // (linear.mojo:167-225) - so forward results are bit-identical to the CPU
 // checker.  Batch reductions (dW, db) are split over CTAs and summed in a fixed
-// order (deterministic, but not the reference's serial order).
+// order (deterministic, but not the reference's serial order); their running
+// sums are kept in double precision (fp32 products folded in every 16 rows),
+// so that one update stays within 1e-5 of a serial double-precision sum.
 #include "common.cuh"
 
 namespace mrl {
@@ -33,6 +35,15 @@ gemm_kernel(int M, int N, int K, int k_chunk, ALoad aload, BLoad bload, Epi epi)
     for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = epi.init(m0 + tm + i, n0 + tn + j, M, N);
+
+    // Epi::WIDE: the fp32 accumulators are folded into double ones after every k tile
+    double wide[Epi::WIDE ? 4 : 1][Epi::WIDE ? 4 : 1];
+    if constexpr (Epi::WIDE) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wide[i][j] = 0.0;
+    }
 
     for (int kt = k_begin; kt < k_end; kt += BK) {
         // A tile: BM x BK = 1024 elements, 4 per thread
@@ -64,7 +75,19 @@ gemm_kernel(int M, int N, int K, int k_chunk, ALoad aload, BLoad bload, Epi epi)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
         }
+        if constexpr (Epi::WIDE) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { wide[i][j] += (double)acc[i][j]; acc[i][j] = 0.0f; }
+        }
         __syncthreads();
+    }
+    if constexpr (Epi::WIDE) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = (float)wide[i][j];
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i)
@@ -119,6 +142,7 @@ struct MaskedGrad {
 };
 
 struct ForwardEpi {
+    static constexpr bool WIDE = false;
     const float* bias; float* y; int ldy; float* cache; int ldc; int in_dim; int act;  // act: 0 relu, 1 tanh, -1 none
     __device__ __forceinline__ float init(int, int n, int, int N) const { return n < N ? bias[n] : 0.0f; }
     __device__ __forceinline__ void store(int m, int n, float acc, int) const {
@@ -134,11 +158,13 @@ struct ForwardEpi {
     }
 };
 struct PlainEpi {
+    static constexpr bool WIDE = false;
     float* c; int ldc;
     __device__ __forceinline__ float init(int, int, int, int) const { return 0.0f; }
     __device__ __forceinline__ void store(int m, int n, float acc, int) const { c[(size_t)m * ldc + n] = acc; }
 };
-struct SplitEpi {  // partial[split][m][n]
+struct SplitEpi {  // partial[split][m][n]; a batch reduction
+    static constexpr bool WIDE = true;
     float* partial; int M, N;
     __device__ __forceinline__ float init(int, int, int, int) const { return 0.0f; }
     __device__ __forceinline__ void store(int m, int n, float acc, int split) const {
@@ -151,9 +177,9 @@ __global__ void reduce_splits_kernel(const float* __restrict__ partial, float* _
                                      int splits) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    float acc = 0.0f;
-    for (int s = 0; s < splits; ++s) acc += partial[(size_t)s * n + i];
-    out[i] = acc;
+    double acc = 0.0;
+    for (int s = 0; s < splits; ++s) acc += (double)partial[(size_t)s * n + i];
+    out[i] = (float)acc;
 }
 
 // Copies the layer input into its cache block (cache row = [input | ...]).
@@ -172,9 +198,9 @@ __global__ void colsum_kernel(G g, int rows, int cols, int rows_per_chunk, float
     int chunk = blockIdx.y;
     if (col >= cols) return;
     int r0 = chunk * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
-    float acc = 0.0f;
-    for (int r = r0; r < r1; ++r) acc += g.at(r, col);
-    partial[(size_t)chunk * cols + col] = acc;
+    double acc = 0.0;
+    for (int r = r0; r < r1; ++r) acc += (double)g.at(r, col);
+    partial[(size_t)chunk * cols + col] = (float)acc;
 }
 
 // stochastic_actor.mojo:386-575: out[:, A + j] = clamp(log_std[j], -5, 2).

@@ -65,16 +65,43 @@ __global__ void sqdev_kernel(const float* __restrict__ x, int64_t n, const doubl
     if (threadIdx.x == 0) atomicAdd(out, acc);
 }
 // x = (x - mean) / (sqrt(var + 1e-8) + 1e-8) with f32 mean / var (ppo.mojo:2363-2371)
-__global__ void normalize_apply_kernel(float* __restrict__ x, int64_t n, const double* __restrict__ stats) {
+__global__ void normalize_apply_kernel(float* __restrict__ x, int64_t n, const double* __restrict__ stats,
+                                       int f64_sqrt) {
     float mean = (float)(stats[0] / (double)n);
     float variance = (float)(stats[1] / (double)n);
-    float stdv = sqrtf(variance + 1e-8f);
+    float stdv = f64_sqrt ? (float)sqrt((double)variance + 1e-8) : sqrtf(variance + 1e-8f);
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
         x[i] = (x[i] - mean) / (stdv + 1e-8f);
 }
 
-// ppo_gather_minibatch_kernel, ppo.mojo:135-191
-__global__ void gather_minibatch_kernel(int batch, int obs_dim, const int32_t* __restrict__ indices,
+// RunningMeanStd.update with the batch sums in stats2 = {sum, squared deviations}.
+__global__ void rms_update_kernel(double* __restrict__ state3, const double* __restrict__ stats2, int64_t n) {
+    double count = state3[0], mean = state3[1], var_sum = state3[2];
+    double batch_mean = stats2[0] / (double)n;
+    double batch_var = stats2[1] / (double)n;
+    double new_count = count + (double)n;
+    if (count == 0.0) {
+        mean = batch_mean;
+        var_sum = batch_var * (double)n;
+    } else {
+        double delta = batch_mean - mean;
+        double new_mean = mean + delta * (double)n / new_count;
+        var_sum = var_sum + batch_var * (double)n + delta * delta * count * (double)n / new_count;
+        mean = new_mean;
+    }
+    state3[0] = new_count; state3[1] = mean; state3[2] = var_sum;
+}
+__global__ void rms_normalize_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t n,
+                                     const double* __restrict__ state3) {
+    double count = state3[0], mean = state3[1];
+    double variance = count < 2.0 ? 1.0 : state3[2] / count;
+    double s = sqrt(variance + 1e-8);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = (float)(((double)in[i] - mean) / (s + 1e-8));
+}
+
+// ppo_gather_minibatch_kernel, ppo.mojo:135-191 (actions are act_w floats per sample)
+__global__ void gather_minibatch_kernel(int batch, int obs_dim, int act_w, const int32_t* __restrict__ indices,
                                         const float* __restrict__ r_obs, const float* __restrict__ r_actions,
                                         const float* __restrict__ adv, const float* __restrict__ ret,
                                         const float* __restrict__ r_lp, const float* __restrict__ r_val,
@@ -85,7 +112,7 @@ __global__ void gather_minibatch_kernel(int batch, int obs_dim, const int32_t* _
     if (i >= batch) return;
     size_t src = (size_t)indices[i];
     for (int d = 0; d < obs_dim; ++d) mb_obs[(size_t)i * obs_dim + d] = r_obs[src * obs_dim + d];
-    mb_actions[i] = r_actions[src];
+    for (int d = 0; d < act_w; ++d) mb_actions[(size_t)i * act_w + d] = r_actions[src * act_w + d];
     mb_adv[i] = adv[src];
     mb_ret[i] = ret[src];
     mb_lp[i] = r_lp[src];
@@ -117,6 +144,52 @@ __global__ void critic_grad_kernel(int batch, const float* __restrict__ values,
     if (b >= batch) return;
     grad_values[b] = critic_grad_one(values[b], old_values ? old_values[b] : 0.0f, returns[b], value_loss_coef,
                                      clip_epsilon, clip_value, batch_div);
+}
+
+// _sample_continuous_actions_kernel, deep_agents/ppo/kernels.mojo:12-98
+__global__ void sample_continuous_kernel(const float* __restrict__ actor_out, float* __restrict__ actions,
+                                         float* __restrict__ log_probs, uint32_t seed, int n, int A, int greedy) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float lp;
+    sample_continuous_one(actor_out + (size_t)i * 2 * A, A, seed, i, greedy, actions + (size_t)i * A, lp);
+    log_probs[i] = lp;
+}
+// ppo_continuous_actor_grad_kernel, kernels.mojo:230-412
+__global__ void continuous_actor_grad_kernel(int batch, int A, const float* __restrict__ actor_out,
+                                             const float* __restrict__ old_log_probs,
+                                             const float* __restrict__ advantages,
+                                             const float* __restrict__ actions, float clip_epsilon,
+                                             float entropy_coef, float batch_div, float* __restrict__ grad_out,
+                                             float* __restrict__ kl) {
+    int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= batch) return;
+    float g[2 * MAX_ACTIONS];
+    float klv;
+    continuous_actor_grad_one(actor_out + (size_t)b * 2 * A, A, old_log_probs[b], advantages[b],
+                              actions + (size_t)b * A, clip_epsilon, entropy_coef, batch_div, g, klv);
+    for (int a = 0; a < 2 * A; ++a) grad_out[(size_t)b * 2 * A + a] = g[a];
+    kl[b] = klv;
+}
+// kernels.mojo:416-486
+__global__ void continuous_critic_grad_kernel(int batch, const float* __restrict__ values,
+                                              const float* __restrict__ old_values,
+                                              const float* __restrict__ returns, float clip_epsilon, int clip_value,
+                                              float batch_div, float* __restrict__ grad_values) {
+    int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= batch) return;
+    grad_values[b] = continuous_critic_grad_one(values[b], old_values ? old_values[b] : 0.0f, returns[b],
+                                                clip_epsilon, clip_value, batch_div);
+}
+// clamp_log_std_params_kernel, kernels.mojo:842-873
+__global__ void clamp_log_std_kernel(float* __restrict__ log_std, int A, const int* __restrict__ skip) {
+    int i = threadIdx.x;
+    if (i >= A) return;
+    if (skip != nullptr && *skip != 0) return;
+    float v = log_std[i];
+    if (v < -5.0f) v = -5.0f;
+    else if (v > 2.0f) v = 2.0f;
+    log_std[i] = v;
 }
 
 // gradient_norm_kernel, ppo.mojo:382-430 (sum of squares; accumulated in f64)
@@ -173,15 +246,30 @@ extern "C" int mrl_gae(int rollout_len, int n_envs, const float* rewards, const 
 }
 
 namespace mrl {
-int normalize_advantages_impl(int64_t n, float* adv, double* stats2, cudaStream_t st) {
+int normalize_advantages_impl(int64_t n, float* adv, double* stats2, cudaStream_t st, bool f64_sqrt) {
     MRL_CUDA_OK(cudaMemsetAsync(stats2, 0, 2 * sizeof(double), st));
     int blocks = (int)((n + 1023) / 1024);
     if (blocks > 592) blocks = 592;
     if (blocks < 1) blocks = 1;
     MRL_LAUNCH(sum_kernel, blocks, 256, 0, st, adv, n, stats2);
     MRL_LAUNCH(sqdev_kernel, blocks, 256, 0, st, adv, n, stats2, stats2 + 1);
-    MRL_LAUNCH(normalize_apply_kernel, blocks, 256, 0, st, adv, n, stats2);
+    MRL_LAUNCH(normalize_apply_kernel, blocks, 256, 0, st, adv, n, stats2, f64_sqrt ? 1 : 0);
     return MRL_OK;
+}
+int reward_rms_impl(int64_t n, const float* in, float* out, double* state3, double* scratch2, cudaStream_t st) {
+    MRL_CUDA_OK(cudaMemsetAsync(scratch2, 0, 2 * sizeof(double), st));
+    int blocks = (int)((n + 1023) / 1024);
+    if (blocks > 592) blocks = 592;
+    if (blocks < 1) blocks = 1;
+    MRL_LAUNCH(sum_kernel, blocks, 256, 0, st, in, n, scratch2);
+    MRL_LAUNCH(sqdev_kernel, blocks, 256, 0, st, in, n, scratch2, scratch2 + 1);
+    MRL_LAUNCH(rms_update_kernel, 1, 1, 0, st, state3, scratch2, n);
+    MRL_LAUNCH(rms_normalize_kernel, blocks, 256, 0, st, in, out, n, state3);
+    return MRL_OK;
+}
+void launch_clamp_log_std(float* log_std, int A, const int* skip, cudaStream_t st) {
+    clamp_log_std_kernel<<<1, 32, 0, st>>>(log_std, A, skip);
+    count_launch();
 }
 int grad_clip_impl(int n, float* grads, float max_norm, double* sumsq, float* report, cudaStream_t st) {
     MRL_CUDA_OK(cudaMemsetAsync(sumsq, 0, sizeof(double), st));
@@ -209,7 +297,7 @@ extern "C" int mrl_ppo_gather_minibatch(int batch, int obs_dim, const int32_t* i
     MRL_CHECK_ARG(batch > 0 && obs_dim > 0 && indices && rollout_obs && rollout_actions && advantages &&
                   returns && rollout_log_probs && rollout_values && mb_obs && mb_actions && mb_advantages &&
                   mb_returns && mb_old_log_probs && mb_old_values);
-    MRL_LAUNCH(gather_minibatch_kernel, ceil_div(batch, 256), 256, 0, as_stream(stream), batch, obs_dim,
+    MRL_LAUNCH(gather_minibatch_kernel, ceil_div(batch, 256), 256, 0, as_stream(stream), batch, obs_dim, 1,
                indices, rollout_obs, rollout_actions, advantages, returns, rollout_log_probs, rollout_values,
                mb_obs, mb_actions, mb_advantages, mb_returns, mb_old_log_probs, mb_old_values);
     return MRL_OK;
@@ -241,4 +329,70 @@ extern "C" int mrl_grad_clip(int n, float* grads, float max_grad_norm, float* sc
     // scratch: [0..1] report (squared norm, scale), [2..3] one double accumulator
     return grad_clip_impl(n, grads, max_grad_norm, reinterpret_cast<double*>(scratch + 2), scratch,
                           as_stream(stream));
+}
+
+// ---- Gaussian policy entry points -------------------------------------------
+
+extern "C" int mrl_normalize_advantages_f64sqrt(int64_t n, float* advantages, float* scratch, void* stream) {
+    MRL_CHECK_ARG(n > 0 && advantages && scratch);
+    MRL_CHECK_ARG(((uintptr_t)scratch & 7) == 0);
+    return normalize_advantages_impl(n, advantages, reinterpret_cast<double*>(scratch), as_stream(stream), true);
+}
+
+extern "C" int mrl_reward_rms_update_normalize(int64_t n, const float* rewards, float* normalized,
+                                               double* state3, double* scratch2, void* stream) {
+    MRL_CHECK_ARG(n > 0 && rewards && normalized && state3 && scratch2);
+    return reward_rms_impl(n, rewards, normalized, state3, scratch2, as_stream(stream));
+}
+
+extern "C" int mrl_ppo_gather_minibatch_continuous(int batch, int obs_dim, int action_dim, const int32_t* indices,
+                                                   const float* rollout_obs, const float* rollout_actions,
+                                                   const float* advantages, const float* returns,
+                                                   const float* rollout_log_probs, const float* rollout_values,
+                                                   float* mb_obs, float* mb_actions, float* mb_advantages,
+                                                   float* mb_returns, float* mb_old_log_probs,
+                                                   float* mb_old_values, void* stream) {
+    MRL_CHECK_ARG(batch > 0 && obs_dim > 0 && action_dim > 0 && indices && rollout_obs && rollout_actions &&
+                  advantages && returns && rollout_log_probs && rollout_values && mb_obs && mb_actions &&
+                  mb_advantages && mb_returns && mb_old_log_probs && mb_old_values);
+    MRL_LAUNCH(gather_minibatch_kernel, ceil_div(batch, 256), 256, 0, as_stream(stream), batch, obs_dim, action_dim,
+               indices, rollout_obs, rollout_actions, advantages, returns, rollout_log_probs, rollout_values,
+               mb_obs, mb_actions, mb_advantages, mb_returns, mb_old_log_probs, mb_old_values);
+    return MRL_OK;
+}
+
+extern "C" int mrl_sample_continuous_actions(int n_envs, int action_dim, const float* actor_output, float* actions,
+                                             float* log_probs, uint32_t seed, int greedy, void* stream) {
+    MRL_CHECK_ARG(n_envs > 0 && action_dim > 0 && action_dim <= MAX_ACTIONS && actor_output && actions && log_probs);
+    MRL_LAUNCH(sample_continuous_kernel, ceil_div(n_envs, 256), 256, 0, as_stream(stream), actor_output, actions,
+               log_probs, seed, n_envs, action_dim, greedy);
+    return MRL_OK;
+}
+
+extern "C" int mrl_ppo_continuous_actor_grad(int batch, int action_dim, const float* actor_output,
+                                             const float* old_log_probs, const float* advantages,
+                                             const float* actions, float clip_epsilon, float entropy_coef,
+                                             float* grad_output, float* kl_divergences, void* stream) {
+    MRL_CHECK_ARG(batch > 0 && action_dim > 0 && action_dim <= MAX_ACTIONS && actor_output && old_log_probs &&
+                  advantages && actions && grad_output && kl_divergences);
+    MRL_LAUNCH(continuous_actor_grad_kernel, ceil_div(batch, 256), 256, 0, as_stream(stream), batch, action_dim,
+               actor_output, old_log_probs, advantages, actions, clip_epsilon, entropy_coef, (float)batch,
+               grad_output, kl_divergences);
+    return MRL_OK;
+}
+
+extern "C" int mrl_ppo_continuous_critic_grad(int batch, const float* values, const float* old_values,
+                                              const float* returns, float clip_epsilon, int clip_value,
+                                              float* grad_values, void* stream) {
+    MRL_CHECK_ARG(batch > 0 && values && returns && grad_values && (!clip_value || old_values));
+    MRL_LAUNCH(continuous_critic_grad_kernel, ceil_div(batch, 256), 256, 0, as_stream(stream), batch, values,
+               old_values, returns, clip_epsilon, clip_value, (float)batch, grad_values);
+    return MRL_OK;
+}
+
+extern "C" int mrl_clamp_log_std(int action_dim, float* log_std_params, void* stream) {
+    MRL_CHECK_ARG(action_dim > 0 && action_dim <= 32 && log_std_params);
+    launch_clamp_log_std(log_std_params, action_dim, nullptr, as_stream(stream));
+    MRL_CUDA_OK(cudaGetLastError());
+    return MRL_OK;
 }

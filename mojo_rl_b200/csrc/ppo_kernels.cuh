@@ -85,8 +85,115 @@ __device__ __forceinline__ float critic_grad_one(float v_new, float v_old, float
     return value_loss_coef * grad / batch_div;
 }
 
+// ---------------------------------------------------------------------------
+// Gaussian policy (deep_agents/ppo/kernels.mojo, ppo_continuous.mojo).  The
+// actor output row is [mean(A) | log_std(A)].
+// ---------------------------------------------------------------------------
+
+// _sample_continuous_actions_kernel body (kernels.mojo:12-98): one Philox
+// stream per (env, dim) with seed Int(rng_seed) + i * A + j and offset 0,
+// Box-Muller (cosine branch), log_std clamped to [-5, 2].  greedy: action = mean.
+__device__ __forceinline__ void sample_continuous_one(const float* __restrict__ row, int A, uint32_t rng_seed,
+                                                      int i, int greedy, float* __restrict__ actions_row,
+                                                      float& log_prob_out) {
+    const float EPS = 1e-6f, LOG_2PI = 1.8378770664093453f;
+    float total = 0.0f;
+    for (int j = 0; j < A; ++j) {
+        float mean = row[j];
+        float log_std = row[A + j];
+        if (log_std < -5.0f) log_std = -5.0f;
+        else if (log_std > 2.0f) log_std = 2.0f;
+        Philox ph((uint64_t)((int64_t)rng_seed + (int64_t)i * A + j), 0);
+        float r[4];
+        ph.step_uniform(r);
+        float u1 = r[0] + 1e-8f, u2 = r[1];
+        float mag = sqrtf(-2.0f * mrl_logf(u1));
+        float noise = mag * mrl_cosf(u2 * 6.283185307179586f);
+        if (greedy) noise = 0.0f;
+        float stdv = mrl_expf(log_std);
+        float action = mean + stdv * noise;
+        actions_row[j] = action;
+        float an = (action - mean) / (stdv + EPS);
+        float lg = -0.5f * (LOG_2PI + 2.0f * log_std + an * an);
+        total = total + lg;
+    }
+    log_prob_out = total;
+}
+
+// ppo_continuous_actor_grad_kernel body (kernels.mojo:230-412).  g has 2A entries.
+__device__ __forceinline__ void continuous_actor_grad_one(const float* __restrict__ row, int A, float old_lp,
+                                                          float advantage, const float* __restrict__ act,
+                                                          float clip_epsilon, float entropy_coef, float batch_div,
+                                                          float* g, float& kl_out) {
+    const float eps = 1e-6f, log_2pi = 1.8378770664093453f;
+    float new_lp = 0.0f;
+    float sv[MAX_ACTIONS];
+    for (int j = 0; j < A; ++j) {
+        float mean = row[j];
+        float log_std = row[A + j];
+        if (log_std < -5.0f) log_std = -5.0f;
+        else if (log_std > 2.0f) log_std = 2.0f;
+        float stdv = mrl_expf(log_std);
+        sv[j] = stdv;
+        float an = (act[j] - mean) / (stdv + eps);
+        float lg = -0.5f * (log_2pi + 2.0f * log_std + an * an);
+        new_lp = new_lp + lg;
+    }
+    float diff = new_lp - old_lp;
+    if (diff > 20.0f) diff = 20.0f;
+    else if (diff < -20.0f) diff = -20.0f;
+    float ratio = mrl_expf(diff);
+    float kl = (ratio - 1.0f) - diff;
+    if (kl < 0.0f) kl = 0.0f;
+    else if (kl > 100.0f) kl = 100.0f;
+    kl_out = kl;
+    float clipped = ratio;
+    if (clipped < 1.0f - clip_epsilon) clipped = 1.0f - clip_epsilon;
+    else if (clipped > 1.0f + clip_epsilon) clipped = 1.0f + clip_epsilon;
+    bool is_clipped = clipped * advantage < ratio * advantage;
+    for (int j = 0; j < A; ++j) {
+        if (is_clipped) { g[j] = 0.0f; g[A + j] = 0.0f; continue; }
+        float an = (act[j] - row[j]) / (sv[j] + eps);
+        float d_mean = an / (sv[j] + eps);
+        float d_log_std = an * an - 1.0f;
+        float grad_mean = (-advantage * ratio * d_mean) / batch_div;
+        float grad_log_std = (-advantage * ratio * d_log_std - entropy_coef * 1.0f) / batch_div;
+        if (grad_mean > 10.0f) grad_mean = 10.0f;
+        else if (grad_mean < -10.0f) grad_mean = -10.0f;
+        if (grad_log_std > 10.0f) grad_log_std = 10.0f;
+        else if (grad_log_std < -10.0f) grad_log_std = -10.0f;
+        g[j] = grad_mean;
+        g[A + j] = grad_log_std;
+    }
+}
+
+// ppo_critic_grad_kernel / ppo_critic_grad_clipped_kernel of kernels.mojo:416-486
+// (the continuous agent applies no value-loss coefficient).
+__device__ __forceinline__ float continuous_critic_grad_one(float value, float old_value, float target,
+                                                            float clip_epsilon, int clip_value, float batch_div) {
+    if (!clip_value) return (value - target) / batch_div;
+    float d = value - old_value;
+    float dc = d < clip_epsilon ? d : clip_epsilon;
+    dc = dc > -clip_epsilon ? dc : -clip_epsilon;
+    float value_clipped = old_value + dc;
+    float loss_unclipped = (value - target) * (value - target);
+    float loss_clipped = (value_clipped - target) * (value_clipped - target);
+    if (loss_clipped > loss_unclipped) {
+        float clip_sign = 1.0f;
+        if (value - old_value > clip_epsilon) clip_sign = 0.0f;
+        else if (value - old_value < -clip_epsilon) clip_sign = 0.0f;
+        return clip_sign * (value_clipped - target) / batch_div;
+    }
+    return (value - target) / batch_div;
+}
+
 // Host-side launchers shared with the fused agent (defined in ppo_kernels.cu / mlp.cu).
-int normalize_advantages_impl(int64_t n, float* adv, double* stats2, cudaStream_t st);
+// f64_sqrt: the square root of the variance is taken in double precision
+// (the continuous agent's global normalisation, ppo_continuous.mojo:2906-2923).
+int normalize_advantages_impl(int64_t n, float* adv, double* stats2, cudaStream_t st, bool f64_sqrt = false);
+// RunningMeanStd.update + normalize (core/utils/normalization.mojo:188-292):
+// state3 = {count, mean, var_sum} on the device, scratch2 two doubles.
+int reward_rms_impl(int64_t n, const float* in, float* out, double* state3, double* scratch2, cudaStream_t st);
 int grad_clip_impl(int n, float* grads, float max_norm, double* sumsq, float* report, cudaStream_t st);
 int mlp_forward_impl(const mrl_net_spec* net, int batch, const float* in, const float* params, float* out,
                      float* cache, float* workspace, cudaStream_t st);

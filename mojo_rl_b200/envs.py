@@ -1,4 +1,4 @@
-"""GPUDiscreteEnv implementors (reference: core/env_traits.mojo:230-310).
+"""GPUDiscreteEnv / GPUContinuousEnv implementors (reference: core/env_traits.mojo:230-397).
 
 Each class mirrors the static trait methods of the reference struct of the same
 name; buffers are torch CUDA float32 tensors standing in for DeviceBuffer, and
@@ -76,3 +76,21 @@ class LunarLanderV2(_GPUDiscreteEnv):
     """envs/lunar_lander/lunar_lander_v2.mojo: STATE_SIZE 192, OBS_DIM 8, NUM_ACTIONS 4."""
     KIND = ENV_KINDS["lunar_lander"]
     STATE_SIZE, OBS_DIM, NUM_ACTIONS = 192, 8, 4
+
+
+class _GPUContinuousEnv(_GPUDiscreteEnv):
+    """GPUContinuousEnv (core/env_traits.mojo:313-397): actions are [BATCH_SIZE, ACTION_DIM] floats."""
+    NUM_ACTIONS = 0
+    ACTION_DIM = None
+
+
+class PendulumV2(_GPUContinuousEnv):
+    """envs/pendulum/pendulum_v2.mojo: STATE_SIZE 8, OBS_DIM 3, ACTION_DIM 1 (torque = 2 * action, clamped)."""
+    KIND = ENV_KINDS["pendulum"]
+    STATE_SIZE, OBS_DIM, ACTION_DIM = 8, 3, 1
+
+
+class HalfCheetahPlanarV2(_GPUContinuousEnv):
+    """envs/half_cheetah/cheetah_planar_v2.mojo: STATE_SIZE 253, OBS_DIM 17, ACTION_DIM 6 (joint torques in [-1, 1])."""
+    KIND = ENV_KINDS["half_cheetah"]
+    STATE_SIZE, OBS_DIM, ACTION_DIM = 253, 17, 6

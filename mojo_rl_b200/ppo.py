@@ -9,7 +9,7 @@ import ctypes
 import numpy as np
 
 from . import _lib
-from .model import Adam, Linear, LinearReLU, Network, Xavier, seq
+from .model import Adam, Kaiming, Linear, LinearReLU, LinearTanh, Network, StochasticActor, Xavier, seq
 
 
 class EpisodeMetrics:
@@ -224,3 +224,54 @@ class DeepPPOAgent:
                 setattr(self, k, int(meta[k]))
         if "normalize_advantages" in meta:
             self.normalize_advantages = meta["normalize_advantages"] == "True"
+
+
+class DeepPPOContinuousAgent(DeepPPOAgent):
+    """DeepPPOContinuousAgent[obs_dim, action_dim, hidden_dim, rollout_len, n_envs, gpu_minibatch_size]
+    with the constructor defaults of ppo_continuous.mojo:232-266: tanh trunk, StochasticActor head
+    (state-independent log_std), Kaiming init with a small mean head and log_std = -0.5, reward
+    normalisation by a running mean / std, no value-loss coefficient in the critic gradient.
+    Observation noise (obs_noise_std, default 0 in the reference) is not built."""
+
+    def __init__(self, obs_dim, action_dim, hidden_dim=64, rollout_len=128, n_envs=1024, gpu_minibatch_size=256,
+                 gamma=0.99, gae_lambda=0.95, clip_epsilon=0.2, actor_lr=0.0003, critic_lr=0.001,
+                 entropy_coef=0.01, value_loss_coef=0.5, num_epochs=10, normalize_advantages=True, target_kl=0.02,
+                 max_grad_norm=0.5, anneal_lr=True, anneal_entropy=False, target_total_steps=0,
+                 norm_adv_per_minibatch=True, action_scale=1.0, action_bias=0.0, checkpoint_every=0,
+                 checkpoint_path="", normalize_rewards=True, clip_value=True, precision=0, seed=0):
+        super().__init__(obs_dim, action_dim, hidden_dim, rollout_len, n_envs, gpu_minibatch_size, gamma, gae_lambda,
+                         clip_epsilon, actor_lr, critic_lr, entropy_coef, value_loss_coef, num_epochs, 64,
+                         normalize_advantages, target_kl, max_grad_norm, anneal_lr, anneal_entropy,
+                         target_total_steps, clip_value, norm_adv_per_minibatch, checkpoint_every, checkpoint_path,
+                         precision, seed)
+        self.action_scale, self.action_bias, self.normalize_rewards = action_scale, action_bias, normalize_rewards
+        rng = np.random.default_rng(seed)
+        # ppo_continuous.mojo:171-194, :296-343
+        self.actor = Network(seq(LinearTanh(obs_dim, hidden_dim), LinearTanh(hidden_dim, hidden_dim),
+                                 StochasticActor(hidden_dim, action_dim)), Adam(lr=actor_lr), Kaiming(), rng)
+        self.critic = Network(seq(LinearTanh(obs_dim, hidden_dim), LinearTanh(hidden_dim, hidden_dim),
+                                  Linear(hidden_dim, 1)), Adam(lr=critic_lr), Kaiming(), rng)
+        # StochasticActor.init_params_small (stochastic_actor.mojo:94-137): mean weights +-0.01, zero mean
+        # bias, log_std = -0.5
+        head = hidden_dim * action_dim + 2 * action_dim
+        p = self.actor.params
+        off = p.size - head
+        p[off:off + hidden_dim * action_dim] = ((rng.random(hidden_dim * action_dim) * 2.0 - 1.0) * 0.01).astype(np.float32)
+        p[off + hidden_dim * action_dim:off + hidden_dim * action_dim + action_dim] = 0.0
+        p[p.size - action_dim:] = -0.5
+
+    def make_config(self, env_kind, deterministic=False, world_size=1, rank=0):
+        cfg = super().make_config(env_kind, deterministic, world_size, rank)
+        cfg.normalize_rewards = int(self.normalize_rewards)
+        return cfg
+
+    def train_gpu(self, EnvType, ctx=None, num_episodes=100, verbose=False, print_every=10, max_rollouts=None):
+        """train_gpu[EnvType](ctx, num_episodes, verbose, print_every) (ppo_continuous.mojo:2111-3400);
+        annealing target num_episodes * 500 (:2575-2577)."""
+        saved = self.target_total_steps
+        if not saved:
+            self.target_total_steps = num_episodes * 500
+        try:
+            return super().train_gpu(EnvType, ctx, num_episodes, verbose, print_every, max_rollouts)
+        finally:
+            self.target_total_steps = saved

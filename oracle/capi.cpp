@@ -123,6 +123,29 @@ void orc_ppo_critic_grad(int batch, const float* values, const float* old_values
     ppo::critic_grad(values, old_values, returns, batch, value_loss_coef, clip_epsilon, clip_value != 0,
                      (float)batch, grad_values);
 }
+void orc_sample_continuous_actions(int n, int A, const float* actor_out, float* actions, float* log_probs,
+                                   uint32_t seed, int greedy) {
+    ppo::sample_continuous_actions(actor_out, n, A, seed, greedy, actions, log_probs);
+}
+void orc_ppo_continuous_actor_grad(int batch, int A, const float* actor_out, const float* old_log_probs,
+                                   const float* advantages, const float* actions, float clip_epsilon,
+                                   float entropy_coef, float* grad_out, float* kl) {
+    ppo::continuous_actor_grad(actor_out, old_log_probs, advantages, actions, batch, A, clip_epsilon, entropy_coef,
+                               (float)batch, grad_out, kl);
+}
+void orc_ppo_continuous_critic_grad(int batch, const float* values, const float* old_values, const float* returns,
+                                    float clip_epsilon, int clip_value, float* grad_values) {
+    ppo::continuous_critic_grad(values, old_values, returns, batch, clip_epsilon, clip_value != 0, (float)batch,
+                                grad_values);
+}
+// RunningMeanStd over successive batches; state = {count, mean, var_sum}
+void orc_rms_update_normalize(double* state3, const float* in, float* out, int64_t n) {
+    ppo::RunningMeanStd r;
+    r.count = state3[0]; r.mean = state3[1]; r.var_sum = state3[2];
+    r.update(in, (size_t)n);
+    r.normalize(in, out, (size_t)n);
+    state3[0] = r.count; state3[1] = r.mean; state3[2] = r.var_sum;
+}
 float orc_grad_clip(int n, float* grads, float max_norm, int acc64) {
     return acc64 ? ppo::clip_grad_norm<double>(grads, n, max_norm)
                  : ppo::clip_grad_norm<float>(grads, n, max_norm);

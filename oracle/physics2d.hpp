@@ -189,7 +189,7 @@ inline int edge_terrain_detect(const float* s, const float* shapes, int num_bodi
 }
 
 // physics2d/collision/flat_terrain.mojo:456-580 is restated next to its only
-// caller (the planar cheetah) in half_cheetah.cpp.
+// caller (the planar cheetah) in half_cheetah.hpp.
 
 // physics2d/solvers/impulse.mojo:419-628
 inline void solve_velocity_contacts(float* s, int bodies_off, float* contacts, int contact_count,

@@ -10,6 +10,7 @@
 // (linear.mojo:167-225).  Whether the Mojo compiler fuses is unknown; fmaf is
 // this build's documented choice on both sides.
 #pragma once
+#include <cmath>
 #include <vector>
 #include "physics2d.hpp"
 
@@ -370,6 +371,175 @@ inline void adam_step(float* params, const float* grads, float* state_mv, int n,
         float v_hat = v_new / bc2;
         params[i] = params[i] - lr * m_hat / (sqrtf(v_hat) + eps);
     }
+}
+
+// ---------------------------------------------------------------------------
+// Continuous-action (Gaussian) PPO: deep_agents/ppo/kernels.mojo,
+// ppo_continuous.mojo, core/utils/normalization.mojo.
+// ---------------------------------------------------------------------------
+
+// _sample_continuous_actions_kernel, kernels.mojo:12-98.  actor_out is
+// [n, 2A] = [mean | log_std].  One Philox stream per (env, dim):
+// seed = Int(rng_seed) + i * A + j, offset 0; Box-Muller, cosine branch.
+// greedy: the action is the mean (evaluation policy, ppo_continuous.mojo:703-976).
+inline void sample_continuous_actions(const float* actor_out, int n, int A, uint32_t rng_seed, int greedy,
+                                      float* actions, float* log_probs) {
+    const float EPS = 1e-6f, LOG_STD_MIN = -5.0f, LOG_STD_MAX = 2.0f, LOG_2PI = 1.8378770664093453f;
+    for (int i = 0; i < n; ++i) {
+        float total = 0.0f;
+        for (int j = 0; j < A; ++j) {
+            float mean = actor_out[(size_t)i * 2 * A + j];
+            float log_std = actor_out[(size_t)i * 2 * A + A + j];
+            if (log_std < LOG_STD_MIN) log_std = LOG_STD_MIN;
+            else if (log_std > LOG_STD_MAX) log_std = LOG_STD_MAX;
+            Philox ph((uint64_t)((int64_t)rng_seed + (int64_t)i * A + j), 0);
+            float r[4];
+            ph.step_uniform(r);
+            float u1 = r[0] + 1e-8f, u2 = r[1];
+            float mag = sqrtf(-2.0f * mrl_logf(u1));
+            float noise = mag * mrl_cosf(u2 * 6.283185307179586f);
+            if (greedy) noise = 0.0f;
+            float stdv = mrl_expf(log_std);
+            float action = mean + stdv * noise;
+            actions[(size_t)i * A + j] = action;
+            float an = (action - mean) / (stdv + EPS);
+            float lg = -0.5f * (LOG_2PI + 2.0f * log_std + an * an);
+            total = total + lg;
+        }
+        log_probs[i] = total;
+    }
+}
+
+// ppo_continuous_actor_grad_kernel, kernels.mojo:230-412.  grad_out is [batch, 2A].
+inline void continuous_actor_grad(const float* actor_out, const float* old_log_probs, const float* advantages,
+                                  const float* actions, int batch, int A, float clip_epsilon,
+                                  float entropy_coef, float batch_div, float* grad_out, float* kl_out) {
+    const float eps = 1e-6f, log_2pi = 1.8378770664093453f;
+    for (int b = 0; b < batch; ++b) {
+        float advantage = advantages[b], old_lp = old_log_probs[b];
+        float new_lp = 0.0f, entropy_sum = 0.0f;
+        float av[16], mv[16], sv[16];
+        for (int j = 0; j < A; ++j) {
+            float mean = actor_out[(size_t)b * 2 * A + j];
+            float log_std = actor_out[(size_t)b * 2 * A + A + j];
+            float act = actions[(size_t)b * A + j];
+            if (log_std < -5.0f) log_std = -5.0f;
+            else if (log_std > 2.0f) log_std = 2.0f;
+            float stdv = mrl_expf(log_std);
+            float an = (act - mean) / (stdv + eps);
+            av[j] = act; mv[j] = mean; sv[j] = stdv;
+            float lg = -0.5f * (log_2pi + 2.0f * log_std + an * an);
+            new_lp = new_lp + lg;
+            entropy_sum = entropy_sum + 0.5f * (log_2pi + 1.0f + 2.0f * log_std);
+        }
+        (void)entropy_sum;
+        float diff = new_lp - old_lp;
+        if (diff > 20.0f) diff = 20.0f;
+        else if (diff < -20.0f) diff = -20.0f;
+        float ratio = mrl_expf(diff);
+        float kl = (ratio - 1.0f) - diff;
+        if (kl < 0.0f) kl = 0.0f;
+        else if (kl > 100.0f) kl = 100.0f;
+        kl_out[b] = kl;
+        float clipped = ratio;
+        if (clipped < 1.0f - clip_epsilon) clipped = 1.0f - clip_epsilon;
+        else if (clipped > 1.0f + clip_epsilon) clipped = 1.0f + clip_epsilon;
+        bool is_clipped = clipped * advantage < ratio * advantage;
+        for (int j = 0; j < A; ++j) {
+            float* gm = grad_out + (size_t)b * 2 * A + j;
+            float* gs = grad_out + (size_t)b * 2 * A + A + j;
+            if (is_clipped) { *gm = 0.0f; *gs = 0.0f; continue; }
+            float an = (av[j] - mv[j]) / (sv[j] + eps);
+            float d_mean = an / (sv[j] + eps);
+            float d_log_std = an * an - 1.0f;
+            float grad_mean = (-advantage * ratio * d_mean) / batch_div;
+            float grad_log_std = (-advantage * ratio * d_log_std - entropy_coef * 1.0f) / batch_div;
+            if (grad_mean > 10.0f) grad_mean = 10.0f;
+            else if (grad_mean < -10.0f) grad_mean = -10.0f;
+            if (grad_log_std > 10.0f) grad_log_std = 10.0f;
+            else if (grad_log_std < -10.0f) grad_log_std = -10.0f;
+            *gm = grad_mean;
+            *gs = grad_log_std;
+        }
+    }
+}
+
+// ppo_critic_grad_kernel / ppo_critic_grad_clipped_kernel of kernels.mojo:416-486 (no value-loss coefficient).
+inline void continuous_critic_grad(const float* values, const float* old_values, const float* returns, int batch,
+                                   float clip_epsilon, bool clip_value, float batch_div, float* grad_values) {
+    for (int b = 0; b < batch; ++b) {
+        float value = values[b], target = returns[b];
+        if (!clip_value) { grad_values[b] = (value - target) / batch_div; continue; }
+        float old_value = old_values[b];
+        float d = value - old_value;
+        float dc = d < clip_epsilon ? d : clip_epsilon;        // min(value - old, eps)
+        dc = dc > -clip_epsilon ? dc : -clip_epsilon;           // max(.., -eps)
+        float value_clipped = old_value + dc;
+        float loss_unclipped = (value - target) * (value - target);
+        float loss_clipped = (value_clipped - target) * (value_clipped - target);
+        if (loss_clipped > loss_unclipped) {
+            float clip_sign = 1.0f;
+            if (value - old_value > clip_epsilon) clip_sign = 0.0f;
+            else if (value - old_value < -clip_epsilon) clip_sign = 0.0f;
+            grad_values[b] = clip_sign * (value_clipped - target) / batch_div;
+        } else {
+            grad_values[b] = (value - target) / batch_div;
+        }
+    }
+}
+
+// clamp_log_std_params_kernel, kernels.mojo:842-873
+inline void clamp_log_std(float* log_std, int A) {
+    for (int i = 0; i < A; ++i) {
+        if (log_std[i] < -5.0f) log_std[i] = -5.0f;
+        else if (log_std[i] > 2.0f) log_std[i] = 2.0f;
+    }
+}
+
+// core/utils/normalization.mojo:188-292
+struct RunningMeanStd {
+    double count = 0.0, mean = 0.0, var_sum = 0.0;
+    double variance() const { return count < 2 ? 1.0 : var_sum / count; }
+    double stdev() const { return std::sqrt(variance() + 1e-8); }
+    void update(const float* buf, size_t n) {
+        if (n == 0) return;
+        double batch_mean = 0.0;
+        for (size_t i = 0; i < n; ++i) batch_mean += (double)buf[i];
+        batch_mean /= (double)n;
+        double batch_var = 0.0;
+        for (size_t i = 0; i < n; ++i) { double d = (double)buf[i] - batch_mean; batch_var += d * d; }
+        batch_var /= (double)n;
+        double new_count = count + (double)n;
+        if (count == 0) {
+            mean = batch_mean;
+            var_sum = batch_var * (double)n;
+        } else {
+            double delta = batch_mean - mean;
+            double new_mean = mean + delta * (double)n / new_count;
+            var_sum = var_sum + batch_var * (double)n + delta * delta * count * (double)n / new_count;
+            mean = new_mean;
+        }
+        count = new_count;
+    }
+    void normalize(const float* in, float* out, size_t n) const {
+        double s = stdev();
+        for (size_t i = 0; i < n; ++i) out[i] = (float)(((double)in[i] - mean) / (s + 1e-8));
+    }
+};
+
+// Global advantage normalisation of the continuous agent (ppo_continuous.mojo:2906-2923):
+// like normalize_advantages but the square root is taken in f64.
+template <typename ACC>
+inline void normalize_advantages_f64sqrt(float* adv, size_t n) {
+    ACC mean = 0;
+    for (size_t i = 0; i < n; ++i) mean += (ACC)adv[i];
+    mean /= (ACC)n;
+    ACC var_sum = 0;
+    for (size_t i = 0; i < n; ++i) { ACC d = (ACC)adv[i] - mean; var_sum += d * d; }
+    float meanf = (float)mean;
+    float variance = (float)(var_sum / (ACC)n);
+    float stdv = (float)std::sqrt((double)variance + 1e-8);
+    for (size_t i = 0; i < n; ++i) adv[i] = (adv[i] - meanf) / (stdv + 1e-8f);
 }
 
 inline void adam_bias_corrections(double beta1, double beta2, int t, float* bc1, float* bc2) {

@@ -11,6 +11,8 @@
 #include "../include/mojorl_b200.h"
 #include "cartpole.hpp"
 #include "lunar_lander.hpp"
+#include "pendulum.hpp"
+#include "half_cheetah.hpp"
 #include "ppo.hpp"
 
 namespace oracle {
@@ -19,6 +21,8 @@ inline bool env_dims(int kind, int* state_size, int* obs_dim, int* num_actions, 
     switch (kind) {
         case MRL_ENV_CARTPOLE: *state_size = 4; *obs_dim = 4; *num_actions = 2; *action_dim = 0; return true;
         case MRL_ENV_LUNAR_LANDER: *state_size = lunar::STATE_SIZE; *obs_dim = 8; *num_actions = 4; *action_dim = 0; return true;
+        case MRL_ENV_PENDULUM: *state_size = 8; *obs_dim = 3; *num_actions = 0; *action_dim = 1; return true;
+        case MRL_ENV_HALF_CHEETAH: *state_size = cheetah::STATE_SIZE; *obs_dim = 17; *num_actions = 0; *action_dim = 6; return true;
         default: return false;
     }
 }
@@ -26,16 +30,22 @@ inline bool env_dims(int kind, int* state_size, int* obs_dim, int* num_actions, 
 inline void env_reset(int kind, float* states, int n, uint64_t seed) {
     if (kind == MRL_ENV_CARTPOLE) cartpole::reset_all(states, n);
     else if (kind == MRL_ENV_LUNAR_LANDER) lunar::reset_all(states, n, seed);
+    else if (kind == MRL_ENV_PENDULUM) pendulum::reset_all(states, n, seed);
+    else if (kind == MRL_ENV_HALF_CHEETAH) cheetah::reset_all(states, n, seed);
 }
 inline void env_step(int kind, float* states, const float* actions, float* rewards, float* dones,
                      float* obs, int n, uint64_t seed) {
     (void)seed;
     if (kind == MRL_ENV_CARTPOLE) cartpole::step_all(states, actions, rewards, dones, obs, n);
     else if (kind == MRL_ENV_LUNAR_LANDER) lunar::step_all(states, actions, rewards, dones, obs, n);
+    else if (kind == MRL_ENV_PENDULUM) pendulum::step_all(states, actions, rewards, dones, obs, n);
+    else if (kind == MRL_ENV_HALF_CHEETAH) cheetah::step_all(states, actions, rewards, dones, obs, n);
 }
 inline void env_selective_reset(int kind, float* states, float* dones, int n, uint64_t seed) {
     if (kind == MRL_ENV_CARTPOLE) cartpole::selective_reset(states, dones, n, seed);
     else if (kind == MRL_ENV_LUNAR_LANDER) lunar::selective_reset(states, dones, n, seed);
+    else if (kind == MRL_ENV_PENDULUM) pendulum::selective_reset(states, dones, n, seed);
+    else if (kind == MRL_ENV_HALF_CHEETAH) cheetah::selective_reset(states, dones, n, seed);
 }
 
 struct Agent {
@@ -54,11 +64,21 @@ struct Agent {
     std::vector<float> advantages, returns, bootstrap;
     int minibatches_done = 0, kl_early_stop = 0;
     float last_mean_kl = 0;
+    bool continuous = false;   // Gaussian policy (DeepPPOContinuousAgent, ppo_continuous.mojo)
+    int act_w = 1;             // floats per stored action
+    ppo::RunningMeanStd reward_rms;
 
     explicit Agent(const mrl_config& c) : cfg(c) {
         env_dims(c.env_kind, &state_size, &obs_dim, &num_actions, &action_dim);
-        actor_net = {obs_dim, c.hidden_dim, num_actions, ppo::ACT_RELU, ppo::HEAD_LINEAR};
-        critic_net = {obs_dim, c.hidden_dim, 1, ppo::ACT_RELU, ppo::HEAD_LINEAR};
+        continuous = action_dim > 0;
+        if (continuous) {  // ppo_continuous.mojo:171-194
+            act_w = action_dim;
+            actor_net = {obs_dim, c.hidden_dim, action_dim, ppo::ACT_TANH, ppo::HEAD_STOCHASTIC};
+            critic_net = {obs_dim, c.hidden_dim, 1, ppo::ACT_TANH, ppo::HEAD_LINEAR};
+        } else {           // ppo.mojo:807-830
+            actor_net = {obs_dim, c.hidden_dim, num_actions, ppo::ACT_RELU, ppo::HEAD_LINEAR};
+            critic_net = {obs_dim, c.hidden_dim, 1, ppo::ACT_RELU, ppo::HEAD_LINEAR};
+        }
         const size_t N = c.n_envs, T = c.rollout_len;
         actor_params.assign(actor_net.param_size(), 0.f);
         critic_params.assign(critic_net.param_size(), 0.f);
@@ -68,11 +88,11 @@ struct Agent {
         critic_grads.assign(critic_params.size(), 0.f);
         states.assign(N * state_size, 0.f);
         obs.assign(N * obs_dim, 0.f);
-        actions.assign(N, 0.f); log_probs.assign(N, 0.f); values.assign(N, 0.f);
+        actions.assign(N * act_w, 0.f); log_probs.assign(N, 0.f); values.assign(N, 0.f);
         rewards.assign(N, 0.f); dones.assign(N, 0.f);
         episode_rewards.assign(N, 0.f); episode_steps.assign(N, 0.f);
         r_obs.assign(T * N * obs_dim, 0.f);
-        r_actions.assign(T * N, 0.f); r_log_probs.assign(T * N, 0.f); r_values.assign(T * N, 0.f);
+        r_actions.assign(T * N * act_w, 0.f); r_log_probs.assign(T * N, 0.f); r_values.assign(T * N, 0.f);
         r_rewards.assign(T * N, 0.f); r_dones.assign(T * N, 0.f);
         advantages.assign(T * N, 0.f); returns.assign(T * N, 0.f); bootstrap.assign(N, 0.f);
     }
@@ -91,12 +111,15 @@ struct Agent {
     // Phase 1, ppo.mojo:2069-2286
     void rollout() {
         const int N = cfg.n_envs, T = cfg.rollout_len;
-        std::vector<float> logits((size_t)N * num_actions);
+        std::vector<float> logits((size_t)N * actor_net.out_cols());
         for (int t = 0; t < T; ++t) {
             uint32_t rng_seed = (uint32_t)((uint64_t)total_steps * 2654435761ull + (uint64_t)t * 7919ull);
             ppo::mlp_forward(actor_net, N, obs.data(), actor_params.data(), logits.data(), nullptr);
             ppo::mlp_forward(critic_net, N, obs.data(), critic_params.data(), values.data(), nullptr);
-            if (cfg.deterministic) {
+            if (continuous) {
+                ppo::sample_continuous_actions(logits.data(), N, action_dim, rng_seed, cfg.deterministic,
+                                               actions.data(), log_probs.data());
+            } else if (cfg.deterministic) {
                 ppo::argmax_actions(logits.data(), N, num_actions, actions.data());
                 // log-prob of the greedy action, same formula as the sampler
                 for (int i = 0; i < N; ++i) {
@@ -112,7 +135,7 @@ struct Agent {
             }
             size_t off = (size_t)t * N;
             std::memcpy(&r_obs[off * obs_dim], obs.data(), sizeof(float) * N * obs_dim);
-            std::memcpy(&r_actions[off], actions.data(), sizeof(float) * N);
+            std::memcpy(&r_actions[off * act_w], actions.data(), sizeof(float) * N * act_w);
             std::memcpy(&r_log_probs[off], log_probs.data(), sizeof(float) * N);
             std::memcpy(&r_values[off], values.data(), sizeof(float) * N);
             uint64_t env_step_seed = (uint64_t)total_steps * 1103515245ull + (uint64_t)t * 12345ull;
@@ -146,9 +169,20 @@ struct Agent {
         ppo::mlp_forward(critic_net, N, obs.data(), critic_params.data(), bootstrap.data(), nullptr);
         float gamma = (float)cfg.gamma;
         float decay = (float)(cfg.gamma * cfg.gae_lambda);
-        ppo::gae(r_rewards.data(), r_values.data(), r_dones.data(), bootstrap.data(), T, N, gamma,
+        const float* rew = r_rewards.data();
+        std::vector<float> norm_rewards;
+        if (continuous && cfg.normalize_rewards) {  // ppo_continuous.mojo:2867-2871 (host copy only)
+            norm_rewards.resize((size_t)T * N);
+            reward_rms.update(r_rewards.data(), (size_t)T * N);
+            reward_rms.normalize(r_rewards.data(), norm_rewards.data(), (size_t)T * N);
+            rew = norm_rewards.data();
+        }
+        ppo::gae(rew, r_values.data(), r_dones.data(), bootstrap.data(), T, N, gamma,
                  decay, advantages.data(), returns.data());
-        if (cfg.normalize_advantages) ppo::normalize_advantages<ACC>(advantages.data(), (size_t)T * N);
+        if (cfg.normalize_advantages) {
+            if (continuous) ppo::normalize_advantages_f64sqrt<ACC>(advantages.data(), (size_t)T * N);
+            else ppo::normalize_advantages<ACC>(advantages.data(), (size_t)T * N);
+        }
     }
 
     // Phase 3, ppo.mojo:2386-2728.  perms: [num_epochs, T*N].
@@ -157,9 +191,10 @@ struct Agent {
         const int N = cfg.n_envs, T = cfg.rollout_len, B = cfg.minibatch_size;
         const size_t total = (size_t)T * N;
         const int num_minibatches = (int)(total / B);
-        std::vector<float> mb_obs((size_t)B * obs_dim), mb_actions(B), mb_adv(B), mb_ret(B),
+        const int oc = actor_net.out_cols();
+        std::vector<float> mb_obs((size_t)B * obs_dim), mb_actions((size_t)B * act_w), mb_adv(B), mb_ret(B),
             mb_old_lp(B), mb_old_v(B), kl(B);
-        std::vector<float> logits((size_t)B * num_actions), grad_logits((size_t)B * num_actions);
+        std::vector<float> logits((size_t)B * oc), grad_logits((size_t)B * oc);
         std::vector<float> vals(B), grad_vals(B);
         std::vector<float> actor_cache((size_t)B * actor_net.cache_per_sample());
         std::vector<float> critic_cache((size_t)B * critic_net.cache_per_sample());
@@ -173,7 +208,7 @@ struct Agent {
                 for (int i = 0; i < B; ++i) {
                     size_t src = (size_t)perm[(size_t)mb * B + i];
                     for (int d = 0; d < obs_dim; ++d) mb_obs[(size_t)i * obs_dim + d] = r_obs[src * obs_dim + d];
-                    mb_actions[i] = r_actions[src];
+                    for (int d = 0; d < act_w; ++d) mb_actions[(size_t)i * act_w + d] = r_actions[src * act_w + d];
                     mb_adv[i] = advantages[src];
                     mb_ret[i] = returns[src];
                     mb_old_lp[i] = r_log_probs[src];
@@ -181,9 +216,14 @@ struct Agent {
                 }
                 if (cfg.norm_adv_per_minibatch) ppo::normalize_advantages<ACC>(mb_adv.data(), B);
                 ppo::mlp_forward(actor_net, B, mb_obs.data(), actor_params.data(), logits.data(), actor_cache.data());
-                ppo::actor_grad_with_kl(logits.data(), mb_old_lp.data(), mb_adv.data(), mb_actions.data(), B,
-                                        num_actions, cfg.clip_epsilon, entropy_coef, (float)B,
-                                        grad_logits.data(), kl.data());
+                if (continuous)
+                    ppo::continuous_actor_grad(logits.data(), mb_old_lp.data(), mb_adv.data(), mb_actions.data(), B,
+                                               action_dim, cfg.clip_epsilon, entropy_coef, (float)B,
+                                               grad_logits.data(), kl.data());
+                else
+                    ppo::actor_grad_with_kl(logits.data(), mb_old_lp.data(), mb_adv.data(), mb_actions.data(), B,
+                                            num_actions, cfg.clip_epsilon, entropy_coef, (float)B,
+                                            grad_logits.data(), kl.data());
                 if (cfg.target_kl > 0.0f) {
                     ACC kl_sum = 0;
                     for (int i = 0; i < B; ++i) kl_sum += (ACC)kl[i];
@@ -201,9 +241,15 @@ struct Agent {
                 ppo::adam_step(actor_params.data(), actor_grads.data(), actor_state.data(),
                                (int)actor_params.size(), actor_lr, cfg.adam_beta1, cfg.adam_beta2,
                                cfg.adam_eps, bc1, bc2);
+                if (continuous)  // ppo_continuous.mojo:3151-3171
+                    ppo::clamp_log_std(actor_params.data() + actor_params.size() - action_dim, action_dim);
                 ppo::mlp_forward(critic_net, B, mb_obs.data(), critic_params.data(), vals.data(), critic_cache.data());
-                ppo::critic_grad(vals.data(), mb_old_v.data(), mb_ret.data(), B, cfg.value_loss_coef,
-                                 cfg.clip_epsilon, cfg.clip_value != 0, (float)B, grad_vals.data());
+                if (continuous)
+                    ppo::continuous_critic_grad(vals.data(), mb_old_v.data(), mb_ret.data(), B, cfg.clip_epsilon,
+                                                cfg.clip_value != 0, (float)B, grad_vals.data());
+                else
+                    ppo::critic_grad(vals.data(), mb_old_v.data(), mb_ret.data(), B, cfg.value_loss_coef,
+                                     cfg.clip_epsilon, cfg.clip_value != 0, (float)B, grad_vals.data());
                 ppo::mlp_backward<ACC>(critic_net, B, grad_vals.data(), critic_params.data(),
                                        critic_cache.data(), nullptr, critic_grads.data());
                 if (cfg.max_grad_norm > 0.0f)

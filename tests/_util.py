@@ -39,6 +39,11 @@ _SIGS = {
     "orc_normalize_advantages": (None, [ctypes.c_int64, F, ctypes.c_int]),
     "orc_ppo_actor_grad": (None, [ctypes.c_int, ctypes.c_int, F, F, F, F, ctypes.c_float, ctypes.c_float, F, F]),
     "orc_ppo_critic_grad": (None, [ctypes.c_int, F, F, F, ctypes.c_float, ctypes.c_float, ctypes.c_int, F]),
+    "orc_sample_continuous_actions": (None, [ctypes.c_int, ctypes.c_int, F, F, F, ctypes.c_uint32, ctypes.c_int]),
+    "orc_ppo_continuous_actor_grad": (None, [ctypes.c_int, ctypes.c_int, F, F, F, F, ctypes.c_float, ctypes.c_float,
+                                             F, F]),
+    "orc_ppo_continuous_critic_grad": (None, [ctypes.c_int, F, F, F, ctypes.c_float, ctypes.c_int, F]),
+    "orc_rms_update_normalize": (None, [ctypes.POINTER(ctypes.c_double), F, F, ctypes.c_int64]),
     "orc_grad_clip": (ctypes.c_float, [ctypes.c_int, F, ctypes.c_float, ctypes.c_int]),
     "orc_agent_create": (ctypes.c_void_p, [ctypes.POINTER(Config)]),
     "orc_agent_destroy": (None, [ctypes.c_void_p]),
@@ -88,7 +93,7 @@ def default_config(lib_defaults=None, **kw):
     cfg.env_kind, cfg.n_envs, cfg.rollout_len, cfg.hidden_dim = 2, 1024, 128, 64
     cfg.minibatch_size, cfg.num_epochs, cfg.precision = 256, 4, 0
     cfg.normalize_advantages, cfg.norm_adv_per_minibatch, cfg.clip_value, cfg.deterministic = 1, 1, 1, 0
-    cfg.world_size, cfg.rank = 1, 0
+    cfg.world_size, cfg.rank, cfg.normalize_rewards = 1, 0, 1
     cfg.gamma, cfg.gae_lambda, cfg.clip_epsilon, cfg.value_loss_coef = 0.99, 0.95, 0.2, 0.5
     cfg.target_kl, cfg.max_grad_norm = 0.015, 0.5
     cfg.adam_beta1, cfg.adam_beta2, cfg.adam_eps = 0.9, 0.999, 1e-8

@@ -9,15 +9,20 @@ pytestmark = pytest.mark.gpu
 
 BUF = dict(states=0, obs=1, r_obs=2, r_actions=3, r_log_probs=4, r_values=5, r_rewards=6, r_dones=7,
            advantages=8, returns=9, actor_params=10, critic_params=11, actor_grads=12, critic_grads=13, dones=14)
-OBS = {0: 4, 2: 8}
+OBS = {0: 4, 1: 3, 2: 8, 4: 17}
 NACT = {0: 2, 2: 4}
+ADIM = {1: 1, 4: 6}
 
 
 def _pair(cfg, seed=0):
     from _gpu import GpuAgent
     rng = np.random.default_rng(seed)
-    a_spec = NetSpec(OBS[cfg.env_kind], cfg.hidden_dim, NACT[cfg.env_kind], 0, 0)
-    c_spec = NetSpec(OBS[cfg.env_kind], cfg.hidden_dim, 1, 0, 0)
+    if cfg.env_kind in ADIM:   # tanh trunk + StochasticActor head (ppo_continuous.mojo:171-194)
+        a_spec = NetSpec(OBS[cfg.env_kind], cfg.hidden_dim, ADIM[cfg.env_kind], 1, 1)
+        c_spec = NetSpec(OBS[cfg.env_kind], cfg.hidden_dim, 1, 1, 0)
+    else:
+        a_spec = NetSpec(OBS[cfg.env_kind], cfg.hidden_dim, NACT[cfg.env_kind], 0, 0)
+        c_spec = NetSpec(OBS[cfg.env_kind], cfg.hidden_dim, 1, 0, 0)
     # a little larger than Xavier so that actions are not all identical
     pa, pc = xavier_params(a_spec, rng) * 3, xavier_params(c_spec, rng)
     o, g = OracleAgent(cfg), GpuAgent(cfg)
@@ -31,16 +36,17 @@ def _rel(a, b, floor=1e-3):
     return float(np.max(np.abs(a - b) / np.maximum(np.abs(b), floor)))
 
 
-@pytest.mark.parametrize("kind,det", [(0, 1), (2, 1), (0, 0), (2, 0)])
+@pytest.mark.parametrize("kind,det", [(0, 1), (2, 1), (0, 0), (2, 0), (1, 0), (1, 1), (4, 0)])
 def test_rollout_100_steps(kind, det):
-    cfg = default_config(env_kind=kind, n_envs=512, rollout_len=100, hidden_dim=64, minibatch_size=512,
+    cfg = default_config(env_kind=kind, n_envs=512, rollout_len=100 if kind != 1 else 230, hidden_dim=64, minibatch_size=512,
                          deterministic=det)
     o, g = _pair(cfg, seed=kind)
     try:
         o.o.orc_agent_reset(o.h, 0); g.reset(0)
         assert np.array_equal(g.buffer(BUF["states"]), o.buffer(BUF["states"]))
         o.o.orc_agent_rollout(o.h); g.rollout()
-        # action indices and done/reset flags: bit-exact over the 100 steps
+        # action indices and done/reset flags: bit-exact over the 100 steps (Gaussian actions are
+        # floats computed by the same IEEE operations, so they are compared the same way)
         assert np.array_equal(g.buffer(BUF["r_actions"]), o.buffer(BUF["r_actions"]))
         assert np.array_equal(g.buffer(BUF["r_dones"]), o.buffer(BUF["r_dones"]))
         # per-env state after 100 steps: 1e-4 relative
@@ -48,18 +54,18 @@ def test_rollout_100_steps(kind, det):
         for k in ("r_obs", "r_log_probs", "r_values", "r_rewards"):
             assert np.allclose(g.buffer(BUF[k]), o.buffer(BUF[k]), rtol=1e-4, atol=1e-6), k
         so, sg = o.stats(), g.stats()
-        assert sg.total_steps == so.total_steps == 512 * 100
+        assert sg.total_steps == so.total_steps == 512 * cfg.rollout_len
         assert sg.completed_episodes == so.completed_episodes
         assert abs(sg.sum_episode_reward - so.sum_episode_reward) <= 1e-3 * max(1.0, abs(so.sum_episode_reward))
         rg, lg = g.drain()
         assert len(rg) == so.completed_episodes
-        if kind == 0:
+        if kind in (0, 1):
             assert so.completed_episodes > 0
     finally:
         o.close(); g.close()
 
 
-@pytest.mark.parametrize("kind", [0, 2])
+@pytest.mark.parametrize("kind", [0, 1, 2, 4])
 def test_gae_and_one_update(kind):
     cfg = default_config(env_kind=kind, n_envs=256, rollout_len=32, hidden_dim=64, minibatch_size=1024,
                          num_epochs=2, target_kl=0.0)
@@ -87,8 +93,9 @@ def test_gae_and_one_update(kind):
         o.close(); g.close()
 
 
-def test_kl_early_stop_matches():
-    cfg = default_config(env_kind=0, n_envs=128, rollout_len=32, hidden_dim=64, minibatch_size=512,
+@pytest.mark.parametrize("kind", [0, 1])
+def test_kl_early_stop_matches(kind):
+    cfg = default_config(env_kind=kind, n_envs=128, rollout_len=32, hidden_dim=64, minibatch_size=512,
                          num_epochs=4, target_kl=1e-4)
     o, g = _pair(cfg, seed=3)
     try:
@@ -131,3 +138,17 @@ def test_device_side_shuffle_is_a_permutation_and_training_runs():
     assert m.num_episodes() > 0 and np.isfinite(agent.actor.params).all()
     assert not np.array_equal(before, agent.actor.params)
     assert agent.actor.optimizer.t > 0
+
+
+def test_continuous_agent_trains_on_pendulum():
+    """DeepPPOContinuousAgent.train_gpu through the Python mirror: parameters move, log_std stays in its band."""
+    from mojo_rl_b200 import DeepPPOContinuousAgent, PendulumV2
+    agent = DeepPPOContinuousAgent(3, 1, hidden_dim=64, rollout_len=200, n_envs=256, gpu_minibatch_size=2048,
+                                   num_epochs=4)
+    assert agent.actor.params.size == 3 * 64 + 64 + 64 * 64 + 64 + 64 + 1 + 1 and agent.actor.params[-1] == -0.5
+    before = agent.actor.params.copy()
+    m = agent.train_gpu(PendulumV2, None, num_episodes=10 ** 9, max_rollouts=4)
+    assert m.num_episodes() == 4 * 256                     # every episode truncates at 200 steps
+    assert np.isfinite(agent.actor.params).all() and not np.array_equal(before, agent.actor.params)
+    assert -5.0 <= agent.actor.params[-1] <= 2.0
+    assert -1800.0 < m.mean_reward() < -600.0              # a near-random policy on Pendulum

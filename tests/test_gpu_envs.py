@@ -7,10 +7,11 @@ from _util import fp, oracle
 
 pytestmark = pytest.mark.gpu
 
-CARTPOLE, LUNAR = 0, 2
-STATE = {CARTPOLE: 4, LUNAR: 192}
-OBS = {CARTPOLE: 4, LUNAR: 8}
+CARTPOLE, PENDULUM, LUNAR, CHEETAH = 0, 1, 2, 4
+STATE = {CARTPOLE: 4, PENDULUM: 8, LUNAR: 192, CHEETAH: 253}
+OBS = {CARTPOLE: 4, PENDULUM: 3, LUNAR: 8, CHEETAH: 17}
 NACT = {CARTPOLE: 2, LUNAR: 4}
+ADIM = {PENDULUM: 1, CHEETAH: 6}
 
 
 def _run_both(kind, n, steps, seed, policy):
@@ -46,12 +47,14 @@ def _run_both(kind, n, steps, seed, policy):
         o.orc_env_selective_reset(kind, n, fp(st_c), fp(done_c), rs)
         call("mrl_env_selective_reset", kind, n, st_g, done_g, rs, stream())
         assert np.array_equal(host(st_g), st_c) and np.array_equal(host(done_g), done_c)
-        if kind == LUNAR:
+        if kind in (LUNAR, PENDULUM, CHEETAH):   # the row starts with the observation
             obs_c[:] = st_c[:, :O]
     return n_done, worst
 
 
 def _random_policy(kind):
+    if kind in ADIM:  # beyond [-1, 1] so that the action clamp is exercised
+        return lambda rng, obs, n: (rng.standard_normal((n, ADIM[kind])) * 0.8).astype(np.float32)
     return lambda rng, obs, n: rng.integers(0, NACT[kind], n).astype(np.float32)
 
 
@@ -59,6 +62,11 @@ def _deterministic_policy(kind):
     # a fixed function of the observation (stands in for argmax of a frozen net)
     if kind == CARTPOLE:
         return lambda rng, obs, n: (obs[:, 2] + 0.5 * obs[:, 3] > 0).astype(np.float32)
+    if kind == CHEETAH:   # a gait-like feedback on joint angles and velocities
+        return lambda rng, obs, n: np.ascontiguousarray(
+            np.tanh(2.0 * np.sin(3.0 * obs[:, 2:8]) - 0.1 * obs[:, 11:17] + obs[:, 8:9]), np.float32)
+    if kind == PENDULUM:  # energy-pumping torque, a smooth function of the observation
+        return lambda rng, obs, n: np.ascontiguousarray(np.tanh(obs[:, 2:3] * obs[:, 0:1] + obs[:, 1:2]), np.float32)
     def pol(rng, obs, n):
         a = np.zeros(n, np.float32)
         a[obs[:, 3] < -0.4] = 2.0
@@ -68,7 +76,7 @@ def _deterministic_policy(kind):
     return pol
 
 
-@pytest.mark.parametrize("kind", [CARTPOLE, LUNAR])
+@pytest.mark.parametrize("kind", [CARTPOLE, PENDULUM, LUNAR, CHEETAH])
 @pytest.mark.parametrize("n", [1, 33, 1024])
 def test_100_steps_deterministic_policy(kind, n):
     n_done, worst = _run_both(kind, n, 100, 0, _deterministic_policy(kind))
@@ -76,11 +84,18 @@ def test_100_steps_deterministic_policy(kind, n):
     assert worst <= 1e-4
 
 
-@pytest.mark.parametrize("kind", [CARTPOLE, LUNAR])
+@pytest.mark.parametrize("kind", [CARTPOLE, PENDULUM, LUNAR])
 def test_400_steps_random_policy_with_resets(kind):
     n_done, worst = _run_both(kind, 512, 400, 7, _random_policy(kind))
     assert n_done > 100           # crashes / landings / time-outs and their resets were exercised
     assert worst <= 1e-4
+
+
+def test_cheetah_1005_steps_random_policy_bitwise_with_truncation():
+    """Random torques over more than one episode (MAX_STEPS = 1000): ground contacts of every body, joint limits,
+    the truncation and its reset; the kernels evaluate the oracle's IEEE operations, so equality is expected."""
+    n_done, worst = _run_both(CHEETAH, 67, 1005, 11, _random_policy(CHEETAH))
+    assert n_done == 67 and worst == 0.0
 
 
 def test_lunar_bitwise_identity():

@@ -141,3 +141,67 @@ def test_normalise_gather_grads_clip():
         call("mrl_grad_clip", g.size, gg, 0.5, scratch, stream())
         assert np.allclose(host(gg), gc, rtol=1e-6, atol=1e-12)
         assert abs(np.sqrt(host(scratch)[0]) - norm) < 1e-5 * max(norm, 1.0)
+
+
+def test_gaussian_policy_kernels_bitwise():
+    """Sampler, loss gradients and log_std clamp of the continuous agent: the same IEEE operations as the
+    oracle, so equality; the reward statistics reduce in a different order, so closeness."""
+    import torch
+    from _gpu import call, dev, host, stream
+    o = oracle()
+    rng = np.random.default_rng(4)
+    for n, A in ((1, 1), (4096, 1), (1000, 6), (33, 16)):
+        out = rng.standard_normal((n, 2 * A)).astype(np.float32)
+        out[:, A:] *= 3.0                                   # log_std beyond [-5, 2] on some rows
+        a_c, lp_c = np.empty((n, A), np.float32), np.empty(n, np.float32)
+        a_g, lp_g = torch.zeros(n, A, device="cuda"), torch.zeros(n, device="cuda")
+        for seed, greedy in ((0, 0), (0xdeadbeef, 0), (7, 1)):
+            o.orc_sample_continuous_actions(n, A, fp(out), fp(a_c), fp(lp_c), seed, greedy)
+            call("mrl_sample_continuous_actions", n, A, dev(out), a_g, lp_g, seed, greedy, stream())
+            assert np.array_equal(host(a_g), a_c) and np.array_equal(host(lp_g), lp_c)
+        adv = rng.standard_normal(n).astype(np.float32)
+        old_lp = (lp_c + 0.2 * rng.standard_normal(n)).astype(np.float32)
+        g_c, kl_c = np.empty((n, 2 * A), np.float32), np.empty(n, np.float32)
+        o.orc_ppo_continuous_actor_grad(n, A, fp(out), fp(old_lp), fp(adv), fp(a_c), 0.2, 0.01, fp(g_c), fp(kl_c))
+        g_g, kl_g = torch.zeros(n, 2 * A, device="cuda"), torch.zeros(n, device="cuda")
+        call("mrl_ppo_continuous_actor_grad", n, A, dev(out), dev(old_lp), dev(adv), dev(a_c), 0.2, 0.01, g_g, kl_g,
+             stream())
+        assert np.array_equal(host(g_g), g_c) and np.array_equal(host(kl_g), kl_c)
+        assert (g_c == 0).all(1).sum() > 0 or n < 10          # the clipped branch was taken
+    Bn = 4096
+    v = rng.standard_normal(Bn).astype(np.float32); vo = (v + 0.3 * rng.standard_normal(Bn)).astype(np.float32)
+    ret = rng.standard_normal(Bn).astype(np.float32)
+    for clip in (0, 1):
+        gv_c = np.empty(Bn, np.float32)
+        o.orc_ppo_continuous_critic_grad(Bn, fp(v), fp(vo), fp(ret), 0.2, clip, fp(gv_c))
+        gv_g = torch.zeros(Bn, device="cuda")
+        call("mrl_ppo_continuous_critic_grad", Bn, dev(v), dev(vo), dev(ret), 0.2, clip, gv_g, stream())
+        assert np.array_equal(host(gv_g), gv_c)
+    ls = dev(np.array([-7.0, -5.0, 0.3, 2.0, 2.5, -4.9], np.float32))
+    call("mrl_clamp_log_std", 6, ls, stream())
+    assert np.array_equal(host(ls), np.array([-5.0, -5.0, 0.3, 2.0, 2.0, -4.9], np.float32))
+    # wide gather
+    total, B, OBS, A = 3000, 500, 3, 6
+    idx = rng.permutation(total)[:B].astype(np.int32)
+    src = [rng.standard_normal((total, OBS)).astype(np.float32), rng.standard_normal((total, A)).astype(np.float32)] + \
+          [rng.standard_normal(total).astype(np.float32) for _ in range(4)]
+    outs = [torch.zeros(B, OBS, device="cuda"), torch.zeros(B, A, device="cuda")] + \
+           [torch.zeros(B, device="cuda") for _ in range(4)]
+    call("mrl_ppo_gather_minibatch_continuous", B, OBS, A, dev(idx), *[dev(x) for x in src], *outs, stream())
+    for x, og in zip(src, outs):
+        assert np.array_equal(host(og), x[idx])
+    # reward statistics over three rollouts, then the f64-sqrt advantage normalisation
+    st_c = np.zeros(3, np.float64)
+    st_g = torch.zeros(3, dtype=torch.float64, device="cuda"); scr = torch.zeros(2, dtype=torch.float64, device="cuda")
+    for k in range(3):
+        r = (rng.standard_normal(1 << 16) * (k + 1) - 4.0).astype(np.float32)
+        out_c = np.empty_like(r)
+        o.orc_rms_update_normalize(st_c.ctypes.data_as(ctypes.POINTER(ctypes.c_double)), fp(r), fp(out_c), r.size)
+        out_g = torch.zeros(r.size, device="cuda")
+        call("mrl_reward_rms_update_normalize", r.size, dev(r), out_g, st_g, scr, stream())
+        assert np.allclose(st_g.cpu().numpy(), st_c, rtol=1e-12)
+        assert np.allclose(host(out_g), out_c, rtol=1e-6, atol=1e-6)
+    x = (rng.standard_normal(100000) * 3 + 1).astype(np.float32)
+    xg = dev(x); scratch = torch.zeros(8, device="cuda")
+    call("mrl_normalize_advantages_f64sqrt", x.size, xg, scratch, stream())
+    assert abs(host(xg).mean()) < 1e-5 and abs(host(xg).std() - 1.0) < 1e-4
