@@ -30,10 +30,63 @@ import numpy as np  # noqa: E402
 # n_envs per GPU, rollout_len, hidden, epochs, minibatches per epoch (BASELINE.json configs)
 WORKLOADS = {
     "lunar_lander": dict(env="lunar_lander", kind=2, obs=8, act=4, n_envs=8192, T=128, hidden=256, epochs=4, mbs=4,
-                         step_bytes=256, label="LunarLander discrete PPO, 8192 envs/GPU x 128 steps, 8-256-256-{4,1}"),
+                         step_bytes=256, row_bytes=768, label="LunarLander discrete PPO, 8192 envs/GPU x 128 steps, 8-256-256-{4,1}"),
     "cartpole": dict(env="cartpole", kind=0, obs=4, act=2, n_envs=4096, T=128, hidden=64, epochs=4, mbs=4,
-                     step_bytes=60, label="CartPole PPO, 4096 envs x 128 steps, 4-64-64-{2,1}"),
+                     step_bytes=60, row_bytes=16, label="CartPole PPO, 4096 envs x 128 steps, 4-64-64-{2,1}"),
+    # continuous-action configs (Gaussian policy, tanh nets; fp32 update)
+    "pendulum": dict(env="pendulum", kind=1, obs=3, act=1, continuous=True, n_envs=16384, T=200, hidden=64, epochs=10,
+                     mbs=16, step_bytes=48, row_bytes=32,
+                     label="Pendulum continuous PPO, 16384 envs x 200 steps, 3-64-64-{(1,log_std),1}"),
+    "half_cheetah": dict(env="half_cheetah", kind=4, obs=17, act=6, continuous=True, n_envs=8192, T=512, hidden=512,
+                         epochs=4, mbs=16, step_bytes=452, row_bytes=1012,
+                         label="planar HalfCheetah continuous PPO, 8192 envs/GPU x 512 steps, 17-512-512-{(6,log_std),1}"),
 }
+
+
+def kernel_algorithmic_bytes(w, total):
+    """Algorithmic bytes one launch of each profiled kernel must move (its operands read or written once).
+
+    Rollout kernels process the n_envs environments of one step: the step kernel's per-env figure is the
+    dynamic body state, live metadata, terrain heights, action, observation, reward and done
+    (`step_bytes`; the reference's AoS row is `row_bytes` each way on top of the same outputs).  Update
+    kernels process one minibatch of B = total / mbs rows with bf16 activations [B, H]."""
+    i, h, n, B = w["obs"], w["hidden"], w["n_envs"], total // w["mbs"]
+    act_out = (w["act"] + 1) / 2.0   # actor and critic launches averaged
+    return {
+        "rollout_env_step": n * w["step_bytes"],
+        "rollout_policy": n * (8 * i + 20),
+        "l0_forward": B * (4 * i + 2 * h),
+        "k1_forward_gemm": B * (4 * h + 4 * act_out),
+        "head_backward": B * (4 * h + 4 * act_out),
+        "k1_dx_gemm": B * 6 * h,
+        "l0_backward": B * (2 * h + 4 * i),
+        "k2_dw_gemm": B * 4 * h,
+    }
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures of the same
+# kernels at this workload's sizes (profiles/); not measured live - a profiler never runs inside the bench.
+NCU_TRAFFIC = {
+    "lunar_lander": {"rollout_env_step": 6.49e6, "k1_dx_gemm": 268.6e6 + 97.5e6, "k1_forward_gemm": 134.4e6 + 83.8e6,
+                     "head_backward": 136.9e6 + 95.2e6},
+}
+
+
+def profile_kernels(L, one_iteration, iters):
+    """Per-kernel device time over `iters` further iterations: CUDA events recorded on the library's
+    stream after every launch group (mrl_profile_enable); returns {name: (calls, total_ms)}."""
+    L.mrl_profile_enable(1)
+    for _ in range(iters):
+        one_iteration()
+    buf = ctypes.create_string_buffer(1 << 15)
+    L.mrl_profile_report(buf, 1 << 15)
+    L.mrl_profile_enable(0)
+    out = {}
+    for ln in buf.value.decode().splitlines():
+        parts = ln.split()
+        if len(parts) >= 8 and parts[1] == "calls":
+            out[parts[0]] = (int(parts[2]), float(parts[4]))
+    return out
 
 
 def mlp_flops_per_env_step(w):
@@ -79,8 +132,12 @@ class ClockSampler:
 
 
 def make_params(w, seed):
-    from mojo_rl_b200 import DeepPPOAgent
+    from mojo_rl_b200 import DeepPPOAgent, DeepPPOContinuousAgent
     total = w["n_envs"] * w["T"]
+    if w.get("continuous"):
+        return DeepPPOContinuousAgent(w["obs"], w["act"], hidden_dim=w["hidden"], rollout_len=w["T"],
+                                      n_envs=w["n_envs"], gpu_minibatch_size=total // w["mbs"],
+                                      num_epochs=w["epochs"], actor_lr=3e-4, critic_lr=3e-4, target_kl=0.0, seed=seed)
     agent = DeepPPOAgent(w["obs"], w["act"], hidden_dim=w["hidden"], rollout_len=w["T"], n_envs=w["n_envs"],
                          gpu_minibatch_size=total // w["mbs"], num_epochs=w["epochs"], actor_lr=3e-4, critic_lr=3e-4,
                          target_kl=0.0, seed=seed)
@@ -102,8 +159,9 @@ def cpu_baseline(w, seconds_budget=20.0, path=None):
                                minibatch_size=total // w["mbs"], num_epochs=w["epochs"], target_kl=0.0)
     rng = np.random.default_rng(0)
     h = o.orc_agent_create(ctypes.byref(cfg))
+    cont = 1 if w.get("continuous") else 0
     for which, out in ((0, w["act"]), (1, 1)):
-        spec = _util.NetSpec(w["obs"], w["hidden"], out, 0, 0)
+        spec = _util.NetSpec(w["obs"], w["hidden"], out, cont, cont if which == 0 else 0)
         p = _util.xavier_params(spec, rng)
         o.orc_agent_set_params(h, which, _util.fp(p), _util.fp(np.zeros(2 * p.size, np.float32)))
     o.orc_agent_reset(h, 0)
@@ -179,7 +237,7 @@ def main():
     L = _lib.lib()
     agent = make_params(w, seed=0)   # same seed on every rank: replicas start identical
     # BASELINE.json: LunarLander "update matmuls in bf16"; the hidden-64 configs stay fp32 (launch-bound)
-    default_precision = 1 if w["hidden"] == 256 else 0
+    default_precision = 1 if w["hidden"] == 256 and not w.get("continuous") else 0
     agent.precision = args.precision if args.precision is not None else int(
         os.environ.get("MRL_PRECISION", str(default_precision)))
     h = agent.create_context(w["kind"], world_size=world, rank=rank)
@@ -236,6 +294,16 @@ def main():
         ms = float(t.item())
     value = world * total * args.steps / (ms * 1e-3)
 
+    # ---- per-kernel durations for the roofline: the same iterations again with an event after every launch
+    prof, prof_iters, prof_ms = {}, max(1, min(args.steps, 3)), 0.0
+    if rank == 0 or world > 1:
+        pe0, pe1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        pe0.record(stream)
+        prof = profile_kernels(L, one_iteration, prof_iters)
+        pe1.record(stream)
+        torch.cuda.synchronize()
+        prof_ms = pe0.elapsed_time(pe1)
+
     # ---- end to end through the public API: every step uploads parameters and optimiser state from
     # pinned host memory, runs one PPO iteration, and reads back parameters, state and episode metrics.
     pa, pc = L.mrl_param_size(h, 0), L.mrl_param_size(h, 1)
@@ -281,10 +349,40 @@ def main():
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
         except Exception:
             pass
-        tf_peak = peaks.get("bf16_tflops_sustained", 1400.0)
+        hbm_peak = peaks.get("hbm_gbs", 6650.0)
         peak_src = "measured" if peaks else "fallback"
-        flops_update = mlp_flops_per_env_step(w) * total * (3.0 * w["epochs"]) / (1 + 3.0 * w["epochs"])
-        achieved = flops_update / (phase_ms[2] * 1e-3) / 1e12 if phase_ms[2] > 0 else 0.0
+        # dominant kernel = the largest share of the profiled iterations; its roofline is HBM (the update GEMMs
+        # have K = N = hidden, below the machine balance; the step kernel moves rows, no tensor work)
+        algo = kernel_algorithmic_bytes(w, total)
+        prof_total = sum(v[1] for v in prof.values()) or 1.0
+        kernels = []
+        for name, (calls, tot_ms) in sorted(prof.items(), key=lambda kv: -kv[1][1]):
+            us = 1e3 * tot_ms / max(1, calls)
+            ent = {"kernel": name, "launches": calls // prof_iters, "avg_us": round(us, 2),
+                   "share": round(tot_ms / prof_total, 4)}
+            if name in algo and us > 0:
+                ent["algorithmic_bytes"] = int(algo[name])
+                ent["achieved_gbs"] = round(algo[name] / (us * 1e-6) / 1e9, 1)
+                ent["frac"] = round(ent["achieved_gbs"] / hbm_peak, 4)
+            kernels.append(ent)
+        top = next((k for k in kernels if "algorithmic_bytes" in k), None)
+        roofline = None
+        if top is not None:
+            roofline = {"bound": "hbm", "kernel": top["kernel"], "achieved": top["achieved_gbs"], "peak": hbm_peak,
+                        "unit": "GB/s", "frac": top["frac"], "peak_source": f"hbm_gbs of {peak_src}",
+                        "algorithmic_bytes_per_launch": top["algorithmic_bytes"], "avg_launch_us": top["avg_us"],
+                        "share_of_iteration": top["share"],
+                        "traffic": NCU_TRAFFIC.get(args.workload, {}).get(top["kernel"]),
+                        "timing": f"CUDA events on the launch stream around every launch, {prof_iters} further "
+                                  f"iterations of the timed workload ({prof_ms / prof_iters:.2f} ms each with the "
+                                  f"events in place)",
+                        "kernels": kernels}
+            if top["kernel"] == "rollout_env_step":
+                ref_bytes = w["n_envs"] * (2 * w["row_bytes"] + w["step_bytes"])
+                roofline["reference_layout_bytes_per_launch"] = ref_bytes
+                roofline["reference_layout_gbs"] = round(ref_bytes / (top["avg_us"] * 1e-6) / 1e9, 1)
+                roofline["note"] = ("one thread per environment: latency-bound at this environment count, "
+                                    "not bandwidth-bound")
         line = {
             "metric": "ppo_env_steps_per_sec_incl_update", "value": value, "unit": "env-steps/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
@@ -297,9 +395,7 @@ def main():
             "e2e": {"value": e2e_value, "unit": "env-steps/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches),
             "clocks": clk,
-            "roofline": {"bound": "tensor", "kernel": "update-phase MLP GEMMs (fwd + dX + dW, actor and critic)",
-                         "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s", "frac": achieved / tf_peak,
-                         "peak_source": f"bf16_tflops_sustained of {peak_src}", "traffic": None},
+            "roofline": roofline,
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(w)[0]

@@ -571,6 +571,7 @@ extern "C" int mrl_ppo_rollout(mrl_ctx* c) {
     if (c->use_tc_policy) {
         if ((rc = c->policy.prepare(c->actor_params, c->critic_params, c->obs_dim, st))) return rc;
     }
+    prof_mark("(other)", st);
     for (int t = 0; t < T; ++t) {
         if (c->use_tc_policy) {
             tc::PolicyStepArgs pa{c->obs, c->actor_params, c->critic_params, N, c->obs_dim, A, t, c->cfg.deterministic,
@@ -590,10 +591,12 @@ extern "C" int mrl_ppo_rollout(mrl_ctx* c) {
                            c->obs_dim, c->cfg.deterministic);
             }
         }
+        prof_mark("rollout_policy", st);
         RolloutStepArgs ra{c->states, c->actions, c->rewards, c->dones, c->obs, c->r_rewards, c->r_dones,
                            c->episode_rewards, c->episode_steps, c->ring_returns, c->ring_lengths, c->counters, t, N,
                            c->tc_err};
         if ((rc = rollout_env_step(c->cfg.env_kind, ra, st))) return rc;
+        prof_mark("rollout_env_step", st);
     }
     MRL_LAUNCH(add_total_steps_kernel, 1, 1, 0, st, c->counters, (long long)T * N);
     return MRL_OK;
@@ -605,6 +608,7 @@ extern "C" int mrl_ppo_gae(mrl_ctx* c) {
     cudaStream_t st = c->stream;
     int rc;
     PhaseTimer timer(c, 1);
+    prof_mark("(other)", st);
     if ((rc = mlp_forward_impl(&c->critic_net, N, c->obs, c->critic_params, c->bootstrap, nullptr, c->workspace, st))) return rc;
     const float* rewards = c->r_rewards;
     if (c->continuous && c->cfg.normalize_rewards) {  // ppo_continuous.mojo:2867-2871
@@ -616,6 +620,7 @@ extern "C" int mrl_ppo_gae(mrl_ctx* c) {
     if (c->cfg.normalize_advantages) {
         if ((rc = normalize_advantages_impl((int64_t)T * N, c->advantages, c->stats, st, c->continuous))) return rc;
     }
+    prof_mark("gae_phase", st);
     return MRL_OK;
 }
 
@@ -651,11 +656,15 @@ extern "C" int mrl_ppo_update(mrl_ctx* c, float actor_lr, float critic_lr, float
             if (cfg.norm_adv_per_minibatch) {
                 if ((rc = normalize_advantages_impl(B, c->mb_adv, c->stats, st))) return rc;
             }
+            prof_mark("gather_normalize", st);
             // ---- actor (ppo.mojo:2513-2624)
             if (c->use_tc) {
                 if ((rc = c->tc.forward(&c->actor_net, c->actor_params, c->mb_obs, c->mb_logits, st))) return rc;
-            } else if ((rc = mlp_forward_impl(&c->actor_net, B, c->mb_obs, c->actor_params, c->mb_logits,
-                                              c->actor_cache, c->workspace, st))) return rc;
+            } else {
+                if ((rc = mlp_forward_impl(&c->actor_net, B, c->mb_obs, c->actor_params, c->mb_logits, c->actor_cache,
+                                           c->workspace, st))) return rc;
+                prof_mark("fp32_mlp_forward", st);
+            }
             if (c->continuous) {
                 if ((rc = mrl_ppo_continuous_actor_grad(B, c->action_dim, c->mb_logits, c->mb_old_lp, c->mb_adv,
                                                         c->mb_actions, cfg.clip_epsilon, entropy_coef,
@@ -670,8 +679,12 @@ extern "C" int mrl_ppo_update(mrl_ctx* c, float actor_lr, float critic_lr, float
             if (c->use_tc) {
                 if ((rc = c->tc.backward(&c->actor_net, c->actor_params, c->mb_obs, c->mb_grad_logits, c->actor_grads,
                                          st))) return rc;
-            } else if ((rc = mlp_backward_impl(&c->actor_net, B, c->mb_grad_logits, c->actor_params, c->actor_cache,
-                                               nullptr, c->actor_grads, c->workspace, st))) return rc;
+            } else {
+                prof_mark("loss_grad", st);
+                if ((rc = mlp_backward_impl(&c->actor_net, B, c->mb_grad_logits, c->actor_params, c->actor_cache,
+                                            nullptr, c->actor_grads, c->workspace, st))) return rc;
+                prof_mark("fp32_mlp_backward", st);
+            }
             if (cfg.world_size > 1) {
                 if ((rc = allreduce_f32(c, c->actor_grads, (size_t)c->actor_p + 1))) return rc;
                 MRL_LAUNCH(scale_kernel, ceil_div(c->actor_p, 256), 256, 0, st, c->actor_grads, c->actor_p,
@@ -692,8 +705,12 @@ extern "C" int mrl_ppo_update(mrl_ctx* c, float actor_lr, float critic_lr, float
             // ---- critic (ppo.mojo:2626-2728)
             if (c->use_tc) {
                 if ((rc = c->tc.forward(&c->critic_net, c->critic_params, c->mb_obs, c->mb_values, st))) return rc;
-            } else if ((rc = mlp_forward_impl(&c->critic_net, B, c->mb_obs, c->critic_params, c->mb_values,
-                                              c->critic_cache, c->workspace, st))) return rc;
+            } else {
+                prof_mark("clip_adam", st);
+                if ((rc = mlp_forward_impl(&c->critic_net, B, c->mb_obs, c->critic_params, c->mb_values,
+                                           c->critic_cache, c->workspace, st))) return rc;
+                prof_mark("fp32_mlp_forward", st);
+            }
             if (c->continuous) {
                 if ((rc = mrl_ppo_continuous_critic_grad(B, c->mb_values, c->mb_old_v, c->mb_ret, cfg.clip_epsilon,
                                                          cfg.clip_value, c->mb_grad_values, st))) return rc;
@@ -702,8 +719,12 @@ extern "C" int mrl_ppo_update(mrl_ctx* c, float actor_lr, float critic_lr, float
             if (c->use_tc) {
                 if ((rc = c->tc.backward(&c->critic_net, c->critic_params, c->mb_obs, c->mb_grad_values,
                                          c->critic_grads, st))) return rc;
-            } else if ((rc = mlp_backward_impl(&c->critic_net, B, c->mb_grad_values, c->critic_params, c->critic_cache,
-                                               nullptr, c->critic_grads, c->workspace, st))) return rc;
+            } else {
+                prof_mark("loss_grad", st);
+                if ((rc = mlp_backward_impl(&c->critic_net, B, c->mb_grad_values, c->critic_params, c->critic_cache,
+                                            nullptr, c->critic_grads, c->workspace, st))) return rc;
+                prof_mark("fp32_mlp_backward", st);
+            }
             if (cfg.world_size > 1) {
                 if ((rc = allreduce_f32(c, c->critic_grads, (size_t)c->critic_p))) return rc;
                 MRL_LAUNCH(scale_kernel, ceil_div(c->critic_p, 256), 256, 0, st, c->critic_grads, c->critic_p,
@@ -716,6 +737,7 @@ extern "C" int mrl_ppo_update(mrl_ctx* c, float actor_lr, float critic_lr, float
             }
             MRL_LAUNCH(adam_ctx_kernel, ceil_div(c->critic_p, 256), 256, 0, st, c->critic_params, c->critic_grads,
                        c->critic_state, c->critic_p, critic_lr, cfg.adam_beta1, cfg.adam_beta2, cfg.adam_eps, c->counters);
+            prof_mark("clip_adam", st);
         }
     }
     c->update_count += 1;
