@@ -242,15 +242,8 @@ def main():
         os.environ.get("MRL_PRECISION", str(default_precision)))
     h = agent.create_context(w["kind"], world_size=world, rank=rank)
     if world > 1:
-        idt = torch.zeros(128, dtype=torch.uint8)
-        if rank == 0:
-            buf = (ctypes.c_uint8 * 128)()
-            _lib.check(L.mrl_comm_unique_id(buf))
-            idt = torch.tensor(list(buf), dtype=torch.uint8)
-        idt = idt.cuda()
-        dist.broadcast(idt, 0)
-        idb = (ctypes.c_uint8 * 128)(*idt.cpu().tolist())
-        _lib.check(L.mrl_comm_init(h, idb))
+        from mojo_rl_b200 import dist as mdist
+        mdist.init_comm(L, h, dist, device=torch.device("cuda", local_rank))
     stream = torch.cuda.ExternalStream(L.mrl_stream(h))
     total = w["n_envs"] * w["T"]
     _lib.check(L.mrl_ppo_reset(h, rank))

@@ -1,0 +1,76 @@
+"""Host-side plumbing of the data-parallel path: one process per GPU.
+
+Environments are independent, so each rank owns n_envs environments, its own
+rollout slab, GAE and minibatch sampling; the only exchange is the sum of the
+gradients (and of the minibatch KL) once per network per minibatch, done by
+NCCL inside `mrl_ppo_update`.  What remains for the host is to hand every
+rank the same NCCL unique id, to give ranks different environment seeds, and
+to add up episode statistics for reporting.  `torch.distributed` carries the
+id (any backend: NCCL on the GPU box, gloo in the CPU tests).
+"""
+import ctypes
+
+import numpy as np
+
+UNIQUE_ID_BYTES = 128
+
+
+def shard_envs(total_envs, world_size, rank):
+    """(count, first) of the environments rank owns when a job-wide count is split evenly
+    (e.g. 65 536 HalfCheetah environments over 8 GPUs); the remainder goes to the low ranks."""
+    if world_size < 1 or not 0 <= rank < world_size:
+        raise ValueError("rank outside the world")
+    base, rem = divmod(int(total_envs), world_size)
+    count = base + (1 if rank < rem else 0)
+    first = rank * base + min(rank, rem)
+    return count, first
+
+
+def exchange_unique_id(dist, make_id, device=None):
+    """Rank 0 calls make_id() -> 128 bytes; every rank returns rank 0's bytes."""
+    import torch
+    t = torch.zeros(UNIQUE_ID_BYTES, dtype=torch.uint8)
+    if dist.get_rank() == 0:
+        raw = bytes(make_id())
+        if len(raw) != UNIQUE_ID_BYTES:
+            raise ValueError("a communicator id is 128 bytes")
+        t = torch.tensor(list(raw), dtype=torch.uint8)
+    if device is not None:
+        t = t.to(device)
+    dist.broadcast(t, 0)
+    return bytes(t.cpu().tolist())
+
+
+def init_comm(lib, handle, dist, device=None):
+    """mrl_comm_unique_id on rank 0, broadcast, mrl_comm_init on every rank."""
+    from . import _lib
+
+    def make_id():
+        buf = (ctypes.c_uint8 * UNIQUE_ID_BYTES)()
+        _lib.check(lib.mrl_comm_unique_id(buf))
+        return bytes(buf)
+
+    raw = exchange_unique_id(dist, make_id, device)
+    idb = (ctypes.c_uint8 * UNIQUE_ID_BYTES)(*raw)
+    _lib.check(lib.mrl_comm_init(handle, idb))
+
+
+def reset_seed(base_seed, rank):
+    """Seed of mrl_ppo_reset on this rank: ranks must not replay each other's environments."""
+    return int(base_seed) + int(rank)
+
+
+def aggregate_stats(dist, stats):
+    """Job-wide totals of the per-rank counters (mrl_stats): steps, episodes and the reward / length sums."""
+    import torch
+    v = torch.tensor([float(stats.total_steps), float(stats.completed_episodes), float(stats.sum_episode_reward),
+                      float(stats.sum_episode_steps)], dtype=torch.float64)
+    if dist is not None and dist.is_initialized() and dist.get_world_size() > 1:
+        if dist.get_backend() == "nccl":
+            v = v.cuda()
+        dist.all_reduce(v)
+        v = v.cpu()
+    steps, eps, rsum, lsum = (float(x) for x in v)
+    return {"total_steps": int(steps), "completed_episodes": int(eps),
+            "mean_episode_reward": rsum / eps if eps > 0 else float("nan"),
+            "mean_episode_length": lsum / eps if eps > 0 else float("nan")}

@@ -186,6 +186,10 @@ void orc_agent_update(void* h, float actor_lr, float critic_lr, float entropy_co
     if (acc64) ((Agent*)h)->update<double>(actor_lr, critic_lr, entropy_coef, perms);
     else ((Agent*)h)->update<float>(actor_lr, critic_lr, entropy_coef, perms);
 }
+void orc_agent_set_allreduce(void* h, void (*fn)(float*, int64_t, void*), void* user) {
+    ((Agent*)h)->allreduce = fn;
+    ((Agent*)h)->allreduce_user = user;
+}
 // which follows mrl_buffer
 int orc_agent_get_buffer(void* h, int which, float** ptr, int64_t* n) {
     Agent* a = (Agent*)h;

@@ -64,6 +64,11 @@ struct Agent {
     std::vector<float> advantages, returns, bootstrap;
     int minibatches_done = 0, kl_early_stop = 0;
     float last_mean_kl = 0;
+    // world_size > 1: sum over ranks of a float buffer, supplied by the test (gloo all-reduce or an
+    // in-process stand-in).  Gradients are averaged once per network per minibatch and the KL sum
+    // rides in the float after the actor gradients, as the device path does it.
+    void (*allreduce)(float* buf, int64_t n, void* user) = nullptr;
+    void* allreduce_user = nullptr;
     bool continuous = false;   // Gaussian policy (DeepPPOContinuousAgent, ppo_continuous.mojo)
     int act_w = 1;             // floats per stored action
     ppo::RunningMeanStd reward_rms;
@@ -224,15 +229,32 @@ struct Agent {
                     ppo::actor_grad_with_kl(logits.data(), mb_old_lp.data(), mb_adv.data(), mb_actions.data(), B,
                                             num_actions, cfg.clip_epsilon, entropy_coef, (float)B,
                                             grad_logits.data(), kl.data());
-                if (cfg.target_kl > 0.0f) {
+                const bool multi = cfg.world_size > 1 && allreduce != nullptr;
+                if (cfg.target_kl > 0.0f || multi) {
                     ACC kl_sum = 0;
                     for (int i = 0; i < B; ++i) kl_sum += (ACC)kl[i];
-                    double mean_kl = (double)(float)kl_sum / (double)B;
-                    last_mean_kl = (float)mean_kl;
-                    if (mean_kl > (double)cfg.target_kl) { kl_early_stop = 1; break; }
+                    float kl_sum_f = (float)kl_sum;
+                    double count = (double)B;
+                    if (multi) {  // gradients and KL sum of every rank, then the same decision everywhere
+                        ppo::mlp_backward<ACC>(actor_net, B, grad_logits.data(), actor_params.data(),
+                                               actor_cache.data(), nullptr, actor_grads.data());
+                        std::vector<float> buf(actor_grads.begin(), actor_grads.end());
+                        buf.push_back(kl_sum_f);
+                        allreduce(buf.data(), (int64_t)buf.size(), allreduce_user);
+                        const float inv_world = 1.0f / (float)cfg.world_size;
+                        for (size_t i = 0; i < actor_grads.size(); ++i) actor_grads[i] = buf[i] * inv_world;
+                        kl_sum_f = buf.back();
+                        count = (double)((float)B * (float)cfg.world_size);
+                    }
+                    if (cfg.target_kl > 0.0f) {
+                        double mean_kl = (double)kl_sum_f / count;
+                        last_mean_kl = (float)mean_kl;
+                        if (mean_kl > (double)cfg.target_kl) { kl_early_stop = 1; break; }
+                    }
                 }
-                ppo::mlp_backward<ACC>(actor_net, B, grad_logits.data(), actor_params.data(),
-                                       actor_cache.data(), nullptr, actor_grads.data());
+                if (!multi)
+                    ppo::mlp_backward<ACC>(actor_net, B, grad_logits.data(), actor_params.data(),
+                                           actor_cache.data(), nullptr, actor_grads.data());
                 if (cfg.max_grad_norm > 0.0f)
                     ppo::clip_grad_norm<ACC>(actor_grads.data(), (int)actor_grads.size(), cfg.max_grad_norm);
                 actor_t += 1;
@@ -252,6 +274,11 @@ struct Agent {
                                      cfg.clip_epsilon, cfg.clip_value != 0, (float)B, grad_vals.data());
                 ppo::mlp_backward<ACC>(critic_net, B, grad_vals.data(), critic_params.data(),
                                        critic_cache.data(), nullptr, critic_grads.data());
+                if (multi) {
+                    allreduce(critic_grads.data(), (int64_t)critic_grads.size(), allreduce_user);
+                    const float inv_world = 1.0f / (float)cfg.world_size;
+                    for (float& g : critic_grads) g = g * inv_world;
+                }
                 if (cfg.max_grad_norm > 0.0f)
                     ppo::clip_grad_norm<ACC>(critic_grads.data(), (int)critic_grads.size(), cfg.max_grad_norm);
                 critic_t += 1;

@@ -54,6 +54,7 @@ _SIGS = {
     "orc_agent_rollout": (None, [ctypes.c_void_p]),
     "orc_agent_gae": (None, [ctypes.c_void_p, ctypes.c_int]),
     "orc_agent_update": (None, [ctypes.c_void_p, ctypes.c_float, ctypes.c_float, ctypes.c_float, I32, ctypes.c_int]),
+    "orc_agent_set_allreduce": (None, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "orc_agent_get_buffer": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(F),
                                             ctypes.POINTER(ctypes.c_int64)]),
     "orc_agent_get_stats": (None, [ctypes.c_void_p, ctypes.POINTER(Stats)]),
@@ -75,6 +76,9 @@ def oracle(path=ORACLE_SO):
             return l
         _oracle = l
     return _oracle
+
+
+ALLREDUCE_FN = ctypes.CFUNCTYPE(None, F, ctypes.c_int64, ctypes.c_void_p)
 
 
 def fp(a):

@@ -1,0 +1,77 @@
+"""Two NCCL ranks (one process per GPU) against the oracle's two-rank update.  Needs two GPUs; skipped otherwise."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _worker(rank, port, q):
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, HERE)
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=2, device_id=torch.device("cuda", rank))
+    try:
+        import test_multi_rank_cpu as m
+        from _gpu import GpuAgent
+        from _util import NetSpec, default_config, xavier_params
+        from mojo_rl_b200 import _lib, dist as mdist
+        cfg = default_config(world_size=2, rank=rank, **m.CFG)
+        g = GpuAgent(cfg)
+        rng = np.random.default_rng(0)
+        pa, pc = xavier_params(NetSpec(4, 32, 2, 0, 0), rng) * 3, xavier_params(NetSpec(4, 32, 1, 0, 0), rng)
+        g.set_params(0, pa, np.zeros(2 * pa.size, np.float32))
+        g.set_params(1, pc, np.zeros(2 * pc.size, np.float32))
+        mdist.init_comm(_lib.lib(), g.h, dist, device=torch.device("cuda", rank))
+        total = m.CFG["n_envs"] * m.CFG["rollout_len"]
+        prng = np.random.default_rng(100 + rank)
+        g.reset(rank)
+        for _ in range(rank):
+            g.rollout()
+        for _ in range(2):
+            g.rollout(); g.gae()
+            perms = np.stack([prng.permutation(total) for _ in range(m.CFG["num_epochs"])]).astype(np.int32)
+            g.update(3e-4, 1e-3, 0.01, perms)
+        a, _ = g.get_params(0)
+        c, _ = g.get_params(1)
+        st = g.stats()
+        q.put((rank, a, c, (st.minibatches_done, st.kl_early_stop, st.actor_adam_t, st.critic_adam_t)))
+        g.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(600)
+def test_two_nccl_ranks_match_the_oracle_ranks():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    import test_multi_rank_cpu as m
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = m._free_port()
+    procs = [ctx.Process(target=_worker, args=(r, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(2):
+        item = q.get(timeout=500)
+        res[item[0]] = item[1:]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    ref = m._run_threads()
+    for r in range(2):
+        a, c, counters = res[r]
+        assert counters == ref[r][2]
+        for got, want in ((a, ref[r][0]), (c, ref[r][1])):
+            rel = np.max(np.abs(got - want) / np.maximum(np.abs(want), 1e-2))
+            assert rel <= 1e-5
+    assert np.array_equal(res[0][0], res[1][0]) and np.array_equal(res[0][1], res[1][1])   # replicas identical

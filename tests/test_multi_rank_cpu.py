@@ -1,0 +1,178 @@
+"""Data-parallel path on CPU: two `gloo` ranks.
+
+Covers the host-side plumbing (communicator-id hand-out, environment sharding,
+statistics roll-up) and the semantics of the gradient exchange: the oracle's
+PPO update with world_size = 2, its all-reduce supplied by `torch.distributed`
+over gloo, against the same two ranks run as threads of one process with an
+in-process sum.  The CUDA path implements the same exchange with NCCL.
+"""
+import ctypes
+import os
+import socket
+import sys
+import threading
+
+import numpy as np
+import pytest
+
+from _util import ALLREDUCE_FN, NetSpec, OracleAgent, Stats, default_config, ip, xavier_params
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+WORLD = 2
+CFG = dict(env_kind=0, n_envs=64, rollout_len=32, hidden_dim=32, minibatch_size=512, num_epochs=2, target_kl=0.05)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _make_agent(rank, world, allreduce_cb):
+    cfg = default_config(world_size=world, rank=rank, **CFG)
+    a = OracleAgent(cfg)
+    rng = np.random.default_rng(0)                      # every rank starts from the same parameters
+    pa, pc = xavier_params(NetSpec(4, 32, 2, 0, 0), rng) * 3, xavier_params(NetSpec(4, 32, 1, 0, 0), rng)
+    a.set_params(0, pa, np.zeros(2 * pa.size, np.float32))
+    a.set_params(1, pc, np.zeros(2 * pc.size, np.float32))
+    if allreduce_cb is not None:
+        a.o.orc_agent_set_allreduce(a.h, ctypes.cast(allreduce_cb, ctypes.c_void_p), None)
+    return a
+
+
+def _train(a, rank, iterations=2):
+    """Rank-specific environments (CartPole's selective reset is seeded per call), shared permutation."""
+    total = CFG["n_envs"] * CFG["rollout_len"]
+    prng = np.random.default_rng(100 + rank)            # ranks shuffle independently
+    a.o.orc_agent_reset(a.h, rank)
+    # decorrelate the ranks' environments: CartPole's reset ignores the seed, so step rank r by r extra rollouts
+    for _ in range(rank):
+        a.o.orc_agent_rollout(a.h)
+    for _ in range(iterations):
+        a.o.orc_agent_rollout(a.h)
+        a.o.orc_agent_gae(a.h, 1)
+        perms = np.stack([prng.permutation(total) for _ in range(CFG["num_epochs"])]).astype(np.int32)
+        a.o.orc_agent_update(a.h, 3e-4, 1e-3, 0.01, ip(perms), 1)
+    pa, _ = a.get_params(0)
+    pc, _ = a.get_params(1)
+    st = a.stats()
+    return pa, pc, (st.minibatches_done, st.kl_early_stop, st.actor_adam_t, st.critic_adam_t)
+
+
+def _run_threads():
+    """Both ranks in one process; the all-reduce is a barrier-synchronised sum."""
+    barrier = threading.Barrier(WORLD)
+    slots = [None] * WORLD
+    out = [None] * WORLD
+
+    def make_cb(rank):
+        def cb(buf, n, _user):
+            arr = np.ctypeslib.as_array(buf, shape=(n,))
+            slots[rank] = arr.copy()
+            barrier.wait()
+            total = slots[0] + slots[1]                 # rank order, like a two-rank ring
+            barrier.wait()
+            arr[:] = total
+        return ALLREDUCE_FN(cb)
+
+    cbs = [make_cb(r) for r in range(WORLD)]
+
+    def work(rank):
+        a = _make_agent(rank, WORLD, cbs[rank])
+        try:
+            out[rank] = _train(a, rank)
+        finally:
+            a.close()
+
+    ts = [threading.Thread(target=work, args=(r,)) for r in range(WORLD)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join(timeout=120)
+    assert all(o is not None for o in out)
+    return out
+
+
+def _gloo_worker(rank, port, q):
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, HERE)
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    try:
+        from mojo_rl_b200 import dist as mdist
+        # 1. communicator id: every rank ends up with rank 0's bytes
+        mine = bytes([(rank * 37 + i) % 251 for i in range(128)])
+        got = mdist.exchange_unique_id(dist, lambda: mine)
+        id_ok = got == bytes([i % 251 for i in range(128)])
+        # 2. sharding of a job-wide environment count
+        shard = mdist.shard_envs(65536 + 1, WORLD, rank)
+        # 3. statistics roll-up
+        st = Stats()
+        st.total_steps, st.completed_episodes = 1000 * (rank + 1), 10 * (rank + 1)
+        st.sum_episode_reward, st.sum_episode_steps = 50.0 * (rank + 1), 200.0 * (rank + 1)
+        agg = mdist.aggregate_stats(dist, st)
+
+        # 4. the PPO update with gradients summed over gloo
+        def cb(buf, n, _user):
+            arr = np.ctypeslib.as_array(buf, shape=(n,))
+            t = torch.from_numpy(arr)                  # shares memory with the oracle's buffer
+            dist.all_reduce(t)
+        cb_c = ALLREDUCE_FN(cb)
+        a = _make_agent(rank, WORLD, cb_c)
+        try:
+            pa, pc, counters = _train(a, rank)
+        finally:
+            a.close()
+        q.put((rank, id_ok, shard, agg, pa, pc, counters, mdist.reset_seed(7, rank)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_two_gloo_ranks_match_in_process_ranks():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gloo_worker, args=(r, port, q)) for r in range(WORLD)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(WORLD):
+        item = q.get(timeout=240)
+        res[item[0]] = item[1:]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    ref = _run_threads()
+    for r in range(WORLD):
+        id_ok, shard, agg, pa, pc, counters, seed = res[r]
+        assert id_ok
+        assert shard == ((32769, 0) if r == 0 else (32768, 32769))
+        assert agg == {"total_steps": 3000, "completed_episodes": 30, "mean_episode_reward": 5.0,
+                       "mean_episode_length": 20.0}
+        assert seed == 7 + r
+        # gloo ranks == in-process ranks, bit for bit (a two-rank sum has one order)
+        assert np.array_equal(pa, ref[r][0]) and np.array_equal(pc, ref[r][1]) and counters == ref[r][2]
+    # replicas stay identical: same averaged gradient, same Adam step, same KL decision
+    assert np.array_equal(res[0][3], res[1][3]) and np.array_equal(res[0][4], res[1][4])
+    assert res[0][5] == res[1][5]
+    # and the exchange matters: a rank trained alone ends elsewhere
+    solo = _make_agent(0, 1, None)
+    try:
+        pa_solo, _, _ = _train(solo, 0)
+    finally:
+        solo.close()
+    assert not np.array_equal(pa_solo, res[0][3])
+
+
+def test_shard_envs_edges():
+    from mojo_rl_b200.dist import shard_envs
+    assert [shard_envs(10, 4, r) for r in range(4)] == [(3, 0), (3, 3), (2, 6), (2, 8)]
+    assert shard_envs(8, 1, 0) == (8, 0)
+    assert sum(shard_envs(65536, 8, r)[0] for r in range(8)) == 65536
+    with pytest.raises(ValueError):
+        shard_envs(8, 2, 2)
