@@ -37,6 +37,9 @@ WORKLOADS = {
     "pendulum": dict(env="pendulum", kind=1, obs=3, act=1, continuous=True, n_envs=16384, T=200, hidden=64, epochs=10,
                      mbs=16, step_bytes=48, row_bytes=32,
                      label="Pendulum continuous PPO, 16384 envs x 200 steps, 3-64-64-{(1,log_std),1}"),
+    "bipedal_walker": dict(env="bipedal_walker", kind=3, obs=24, act=4, continuous=True, n_envs=4096, T=256,
+                           hidden=256, epochs=10, mbs=32, step_bytes=916, row_bytes=3800,
+                           label="BipedalWalker continuous PPO, 4096 envs/GPU x 256 steps, 24-256-256-{(4,log_std),1}"),
     "half_cheetah": dict(env="half_cheetah", kind=4, obs=17, act=6, continuous=True, n_envs=8192, T=512, hidden=512,
                          epochs=4, mbs=16, step_bytes=452, row_bytes=1012,
                          label="planar HalfCheetah continuous PPO, 8192 envs/GPU x 512 steps, 17-512-512-{(6,log_std),1}"),

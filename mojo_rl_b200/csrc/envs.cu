@@ -5,6 +5,7 @@
 #include "env_lunar.cuh"
 #include "env_pendulum.cuh"
 #include "env_cheetah.cuh"
+#include "env_bipedal.cuh"
 #include "rollout.cuh"
 #include "umma.cuh"
 
@@ -302,6 +303,57 @@ static cudaError_t ensure_cheetah_smem() {
     return e;
 }
 
+// ---------------------------------------------------------- BipedalWalker
+// 950-float rows, 768 of them terrain that a step only reads: the kernels work
+// on the row in place (the dynamic fields are ~180 floats read once and written
+// once; the terrain stays in L2 between steps).  One warp per block spreads the
+// 4096 environments of the benchmark config over 128 SMs.
+constexpr int BIPEDAL_TPB = 32;
+
+__global__ void __launch_bounds__(BIPEDAL_TPB)
+bipedal_step_kernel(float* __restrict__ states, const float* __restrict__ actions, float* __restrict__ rewards,
+                    float* __restrict__ dones, float* __restrict__ obs, int n) {
+    const int env = blockIdx.x * BIPEDAL_TPB + threadIdx.x;
+    if (env >= n) return;
+    float o[bipedal::OBS_DIM], reward, done;
+    bipedal::step_row(states + (size_t)env * bipedal::STATE_SIZE, actions + (size_t)env * bipedal::ACTION_DIM, o,
+                      reward, done);
+    rewards[env] = reward;
+    dones[env] = done;
+#pragma unroll
+    for (int d = 0; d < bipedal::OBS_DIM; ++d) obs[(size_t)env * bipedal::OBS_DIM + d] = o[d];
+}
+
+__global__ void __launch_bounds__(BIPEDAL_TPB) bipedal_rollout_step_kernel(RolloutStepArgs a) {
+    const int env = blockIdx.x * BIPEDAL_TPB + threadIdx.x;
+    if (env >= a.n) return;
+    float* s = a.states + (size_t)env * bipedal::STATE_SIZE;
+    float o[bipedal::OBS_DIM], reward, done;
+    bipedal::step_row(s, a.actions + (size_t)env * bipedal::ACTION_DIM, o, reward, done);
+    a.rewards[env] = reward;
+    track_episode(a, env, reward, done);
+    if (done > 0.5f) {  // bipedal_walker_v2.mojo:1456-1505: reset and clear the flag
+        bipedal::reset_row(s, bipedal::combined_seed((float)auto_reset_seed(a), env), o);
+        done = 0.0f;
+    }
+    a.dones[env] = done;
+#pragma unroll
+    for (int d = 0; d < bipedal::OBS_DIM; ++d) a.obs[(size_t)env * bipedal::OBS_DIM + d] = o[d];
+}
+
+// dones == nullptr: reset every environment; otherwise only where done > 0.5, clearing the flag.
+__global__ void __launch_bounds__(BIPEDAL_TPB)
+bipedal_reset_rows_kernel(float* __restrict__ states, float* __restrict__ dones, float seed_f32, int n) {
+    const int env = blockIdx.x * BIPEDAL_TPB + threadIdx.x;
+    if (env >= n) return;
+    if (dones != nullptr) {
+        if (!(dones[env] > 0.5f)) return;
+        dones[env] = 0.0f;
+    }
+    float o[bipedal::OBS_DIM];
+    bipedal::reset_row(states + (size_t)env * bipedal::STATE_SIZE, bipedal::combined_seed(seed_f32, env), o);
+}
+
 __global__ void cartpole_rollout_step_kernel(RolloutStepArgs a) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= a.n) return;
@@ -364,6 +416,9 @@ int rollout_env_step(int env_kind, const RolloutStepArgs& a, cudaStream_t st) {
         case MRL_ENV_PENDULUM:
             MRL_LAUNCH(pendulum_rollout_step_kernel, ceil_div(a.n, 128), 128, 0, st, a);
             return MRL_OK;
+        case MRL_ENV_BIPEDAL_WALKER:
+            MRL_LAUNCH(bipedal_rollout_step_kernel, ceil_div(a.n, BIPEDAL_TPB), BIPEDAL_TPB, 0, st, a);
+            return MRL_OK;
         case MRL_ENV_HALF_CHEETAH:
             MRL_CUDA_OK(ensure_cheetah_smem());
             MRL_LAUNCH(cheetah_rollout_step_kernel, ceil_div(a.n, CHEETAH_TPB), CHEETAH_TPB, CHEETAH_SMEM, st, a);
@@ -390,6 +445,7 @@ extern "C" int mrl_env_info(int env_kind, int* state_size, int* obs_dim, int* nu
         case MRL_ENV_LUNAR_LANDER: ss = lunar::STATE_SIZE; od = 8; na = 4; ad = 0; break;
         case MRL_ENV_PENDULUM: ss = 8; od = 3; na = 0; ad = 1; break;
         case MRL_ENV_HALF_CHEETAH: ss = cheetah::STATE_SIZE; od = 17; na = 0; ad = 6; break;
+        case MRL_ENV_BIPEDAL_WALKER: ss = bipedal::STATE_SIZE; od = 24; na = 0; ad = 4; break;
         default:
             set_error("mrl_env_info: env kind %d is not built", env_kind);
             return MRL_ERR_UNSUPPORTED;
@@ -420,6 +476,10 @@ extern "C" int mrl_env_reset(int env_kind, int batch, float* states, uint64_t rn
             MRL_LAUNCH(cheetah_reset_rows_kernel, ceil_div(batch, ENV_TPB), ENV_TPB, 0, st, states, (float*)nullptr,
                        (float)rng_seed, batch);
             return MRL_OK;
+        case MRL_ENV_BIPEDAL_WALKER:
+            MRL_LAUNCH(bipedal_reset_rows_kernel, ceil_div(batch, BIPEDAL_TPB), BIPEDAL_TPB, 0, st, states,
+                       (float*)nullptr, (float)rng_seed, batch);
+            return MRL_OK;
         default:
             set_error("mrl_env_reset: env kind %d is not built", env_kind);
             return MRL_ERR_UNSUPPORTED;
@@ -441,6 +501,10 @@ extern "C" int mrl_env_step(int env_kind, int batch, float* states, const float*
             MRL_CHECK_ARG(((uintptr_t)states & 15) == 0);
             MRL_LAUNCH(pendulum_step_kernel, ceil_div(batch, 256), 256, 0, st, states, actions, rewards, dones, obs,
                        batch);
+            return MRL_OK;
+        case MRL_ENV_BIPEDAL_WALKER:
+            MRL_LAUNCH(bipedal_step_kernel, ceil_div(batch, BIPEDAL_TPB), BIPEDAL_TPB, 0, st, states, actions, rewards,
+                       dones, obs, batch);
             return MRL_OK;
         case MRL_ENV_HALF_CHEETAH:
             MRL_CUDA_OK(ensure_cheetah_smem());
@@ -481,6 +545,10 @@ extern "C" int mrl_env_selective_reset(int env_kind, int batch, float* states, f
             return MRL_OK;
         case MRL_ENV_HALF_CHEETAH:
             MRL_LAUNCH(cheetah_reset_rows_kernel, ceil_div(batch, ENV_TPB), ENV_TPB, 0, st, states, dones,
+                       (float)rng_seed, batch);
+            return MRL_OK;
+        case MRL_ENV_BIPEDAL_WALKER:
+            MRL_LAUNCH(bipedal_reset_rows_kernel, ceil_div(batch, BIPEDAL_TPB), BIPEDAL_TPB, 0, st, states, dones,
                        (float)rng_seed, batch);
             return MRL_OK;
         default:

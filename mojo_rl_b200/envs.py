@@ -94,3 +94,10 @@ class HalfCheetahPlanarV2(_GPUContinuousEnv):
     """envs/half_cheetah/cheetah_planar_v2.mojo: STATE_SIZE 253, OBS_DIM 17, ACTION_DIM 6 (joint torques in [-1, 1])."""
     KIND = ENV_KINDS["half_cheetah"]
     STATE_SIZE, OBS_DIM, ACTION_DIM = 253, 17, 6
+
+
+class BipedalWalkerV2(_GPUContinuousEnv):
+    """envs/bipedal_walker/bipedal_walker_v2.mojo: STATE_SIZE 950, OBS_DIM 24 (14 body terms + 10 lidar),
+    ACTION_DIM 4 (hip / knee motors of both legs in [-1, 1])."""
+    KIND = ENV_KINDS["bipedal_walker"]
+    STATE_SIZE, OBS_DIM, ACTION_DIM = 950, 24, 4

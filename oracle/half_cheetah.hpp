@@ -234,7 +234,9 @@ inline void step_env(float* s, const float* shapes, const float* action, float* 
 inline void step_all(float* states, const float* actions, float* rewards, float* dones, float* obs, int n) {
     float shapes[NUM_SHAPES * SHAPE_MAX_SIZE];
     init_shapes(shapes);
+#ifdef _OPENMP
 #pragma omp parallel for schedule(static)
+#endif
     for (int env = 0; env < n; ++env) {
         float* s = states + (size_t)env * STATE_SIZE;
         step_env(s, shapes, actions + (size_t)env * ACTION_DIM, &rewards[env], &dones[env]);

@@ -7,11 +7,11 @@ from _util import fp, oracle
 
 pytestmark = pytest.mark.gpu
 
-CARTPOLE, PENDULUM, LUNAR, CHEETAH = 0, 1, 2, 4
-STATE = {CARTPOLE: 4, PENDULUM: 8, LUNAR: 192, CHEETAH: 253}
-OBS = {CARTPOLE: 4, PENDULUM: 3, LUNAR: 8, CHEETAH: 17}
+CARTPOLE, PENDULUM, LUNAR, BIPEDAL, CHEETAH = 0, 1, 2, 3, 4
+STATE = {CARTPOLE: 4, PENDULUM: 8, LUNAR: 192, BIPEDAL: 950, CHEETAH: 253}
+OBS = {CARTPOLE: 4, PENDULUM: 3, LUNAR: 8, BIPEDAL: 24, CHEETAH: 17}
 NACT = {CARTPOLE: 2, LUNAR: 4}
-ADIM = {PENDULUM: 1, CHEETAH: 6}
+ADIM = {PENDULUM: 1, BIPEDAL: 4, CHEETAH: 6}
 
 
 def _run_both(kind, n, steps, seed, policy):
@@ -47,7 +47,7 @@ def _run_both(kind, n, steps, seed, policy):
         o.orc_env_selective_reset(kind, n, fp(st_c), fp(done_c), rs)
         call("mrl_env_selective_reset", kind, n, st_g, done_g, rs, stream())
         assert np.array_equal(host(st_g), st_c) and np.array_equal(host(done_g), done_c)
-        if kind in (LUNAR, PENDULUM, CHEETAH):   # the row starts with the observation
+        if kind in (LUNAR, PENDULUM, CHEETAH, BIPEDAL):   # the row starts with the observation
             obs_c[:] = st_c[:, :O]
     return n_done, worst
 
@@ -62,6 +62,15 @@ def _deterministic_policy(kind):
     # a fixed function of the observation (stands in for argmax of a frozen net)
     if kind == CARTPOLE:
         return lambda rng, obs, n: (obs[:, 2] + 0.5 * obs[:, 3] > 0).astype(np.float32)
+    if kind == BIPEDAL:   # keeps the hull up for a while: hips follow the hull tilt, knees stay bent
+        def walker(rng, obs, n):
+            a = np.zeros((n, 4), np.float32)
+            a[:, 0] = np.tanh(3.0 * obs[:, 0] - 2.0 * obs[:, 4])
+            a[:, 2] = np.tanh(3.0 * obs[:, 0] - 2.0 * obs[:, 9] + 0.3)
+            a[:, 1] = np.tanh(-1.0 - 2.0 * obs[:, 6])
+            a[:, 3] = np.tanh(-1.0 - 2.0 * obs[:, 11])
+            return a
+        return walker
     if kind == CHEETAH:   # a gait-like feedback on joint angles and velocities
         return lambda rng, obs, n: np.ascontiguousarray(
             np.tanh(2.0 * np.sin(3.0 * obs[:, 2:8]) - 0.1 * obs[:, 11:17] + obs[:, 8:9]), np.float32)
@@ -76,7 +85,7 @@ def _deterministic_policy(kind):
     return pol
 
 
-@pytest.mark.parametrize("kind", [CARTPOLE, PENDULUM, LUNAR, CHEETAH])
+@pytest.mark.parametrize("kind", [CARTPOLE, PENDULUM, LUNAR, BIPEDAL, CHEETAH])
 @pytest.mark.parametrize("n", [1, 33, 1024])
 def test_100_steps_deterministic_policy(kind, n):
     n_done, worst = _run_both(kind, n, 100, 0, _deterministic_policy(kind))
@@ -84,7 +93,7 @@ def test_100_steps_deterministic_policy(kind, n):
     assert worst <= 1e-4
 
 
-@pytest.mark.parametrize("kind", [CARTPOLE, PENDULUM, LUNAR])
+@pytest.mark.parametrize("kind", [CARTPOLE, PENDULUM, LUNAR, BIPEDAL])
 def test_400_steps_random_policy_with_resets(kind):
     n_done, worst = _run_both(kind, 512, 400, 7, _random_policy(kind))
     assert n_done > 100           # crashes / landings / time-outs and their resets were exercised

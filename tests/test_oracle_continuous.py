@@ -318,3 +318,101 @@ def test_cheetah_motor_limits_truncation_and_penalty():
     dd = d.copy()
     o.orc_env_selective_reset(CHEETAH, 4, fp(s), fp(dd), 77)
     assert np.all(dd == 0) and np.all(s[:, META] == 0) and np.allclose(s[:, B0 + 1], 0.7)
+
+
+# ---------------------------------------------------------------- BipedalWalker
+BIPEDAL = 3
+BW_B0, BW_J0, BW_E0, BW_EC, BW_META = 24, 104, 173, 941, 942   # BipedalWalkerLayout (physics2d/layout.mojo:268-277)
+
+
+def _walker(n, seed=0):
+    o = oracle()
+    s = np.zeros((n, 950), np.float32)
+    o.orc_env_reset(BIPEDAL, n, fp(s), seed)
+    return s
+
+
+def _wstep(s, a):
+    o = oracle()
+    n = s.shape[0]
+    r, d, ob = np.zeros(n, np.float32), np.zeros(n, np.float32), np.zeros((n, 24), np.float32)
+    o.orc_env_step(BIPEDAL, n, fp(s), fp(np.ascontiguousarray(a, np.float32)), fp(r), fp(d), fp(ob), 0)
+    return r, d, ob
+
+
+def test_bipedal_reset_terrain_bodies_and_lidar():
+    o = oracle()
+    dims = [ctypes.c_int() for _ in range(4)]
+    assert o.orc_env_info(BIPEDAL, *[ctypes.byref(x) for x in dims]) == 0
+    assert [x.value for x in dims] == [950, 24, 0, 4]
+    s = _walker(32, seed=2)
+    assert np.all(s[:, BW_EC] == 128)                       # min(TERRAIN_LENGTH - 1, MAX_TERRAIN_EDGES)
+    edges = s[:, BW_E0:BW_E0 + 768].reshape(32, 128, 6)
+    step = np.float32(14.0 / 30.0)
+    assert np.array_equal(edges[0, :, 0], np.arange(128, dtype=np.float32) * step)
+    assert np.array_equal(edges[:, 1:, 0], edges[:, :-1, 2]) and np.array_equal(edges[:, 1:, 1], edges[:, :-1, 3])
+    assert np.allclose(np.hypot(edges[:, :, 4], edges[:, :, 5]), 1.0, atol=1e-6) and np.all(edges[:, :, 5] > 0)
+    # the start pad (edges 0..20) is the same deterministic ripple in every environment; the rest is random
+    assert np.array_equal(edges[0, :21], edges[7, :21]) and not np.array_equal(edges[0, 21:], edges[7, 21:])
+    assert np.all(np.abs(edges[:, :21, 3] - 10.0 / 3.0) < 0.05)
+    body = s[:, BW_B0:BW_B0 + 65].reshape(32, 5, 13)
+    leg_h = 34.0 / 30.0
+    assert np.allclose(body[:, :, 0], 20 * 14.0 / 30.0) and np.allclose(body[:, 0, 1], 10.0 / 3.0 + 2 * leg_h)
+    assert np.allclose(body[:, 1, 1], body[:, 0, 1] - 8.0 / 30.0 - leg_h / 2, atol=1e-6)
+    assert np.allclose(body[:, 2, 1], body[:, 1, 1] - leg_h, atol=1e-6)
+    assert np.array_equal(body[:, 1, :2], body[:, 3, :2]) and np.array_equal(body[:, 2, :2], body[:, 4, :2])
+    assert np.allclose(body[:, :, 10], [0.2, 1.25, 2.0, 1.25, 2.0]) and np.allclose(body[:, :, 11], [0.5, 10, 20, 10, 20])
+    joints = s[:, BW_J0:BW_J0 + 68].reshape(32, 4, 17)
+    assert np.array_equal(joints[0, :, 1], [0, 1, 0, 3]) and np.array_equal(joints[0, :, 2], [1, 2, 3, 4])
+    assert np.allclose(joints[0, :, 8], [-0.8, -1.6, -0.8, -1.6]) and np.allclose(joints[0, :, 9], [1.1, -0.1, 1.1, -0.1])
+    assert np.all(joints[:, :, 10] == 80.0) and np.all(joints[:, :, 14] == 3)
+    # lidar: ray 0 points straight down from the hull centre: height above the pad over the range
+    h = body[:, 0, 1] - edges[:, 20, 1]
+    assert np.allclose(s[:, 14], h / (160.0 / 30.0), atol=2e-3)
+    assert np.all(np.diff(s[:, 14:24], axis=1) >= -1e-6)    # flatter rays travel farther over near-flat ground
+    assert np.all(s[:, 22:24] == 1.0)                       # the last rays (>= 1.33 rad from vertical) miss
+    assert np.all(s[:, 0:2] == 0) and np.all(s[:, 4:14] == 0)
+    assert np.array_equal(s[:, BW_META + 1], body[:, 0, 0]) and np.all(s[:, BW_META + 2:BW_META + 8] == 0)
+
+
+def test_bipedal_step_rewards_and_terminations():
+    s = _walker(16, seed=4)
+    x0 = s[:, BW_B0].copy()
+    a = np.tile(np.array([[0.5, -2.0, -0.25, 1.0]], np.float32), (16, 1))
+    r, d, ob = _wstep(s, a)
+    joints = s[:, BW_J0:BW_J0 + 68].reshape(16, 4, 17)
+    assert np.array_equal(joints[0, :, 11], [4.0, -6.0, -4.0, 6.0])            # SPEED_HIP / SPEED_KNEE with the sign
+    assert np.allclose(joints[0, :, 10], [40.0, 80.0, 20.0, 80.0])             # MOTORS_TORQUE * |clamped action|
+    assert np.array_equal(ob, s[:, :24]) and np.all(d == 0) and np.all(s[:, BW_META] == 1)
+    hull = s[:, BW_B0:BW_B0 + 13]
+    vel_x = hull[:, 3] * np.float32(600.0 / 30.0 / 50.0)
+    want = (130.0 / 30.0) * (hull[:, 0] - x0) - 5.0 * np.abs(hull[:, 2]) - 0.00035 * 80.0 * (0.5 + 2.0 + 0.25 + 1.0)
+    want = want + np.where(vel_x > 0, 3.0 * vel_x, 5.0 * vel_x)                # energy uses the unclamped actions
+    assert np.allclose(r, want, atol=1e-4)
+    assert np.array_equal(s[:, BW_META + 1], hull[:, 0])                        # prev_x follows the hull
+    # limp motors: the walker sinks until the hull is lower than TERRAIN_HEIGHT + 1.2 LEG_H -> done, reward -50
+    s = _walker(16, seed=5)
+    seen = np.zeros(16, bool)
+    for t in range(200):
+        r, d, ob = _wstep(s, np.zeros((16, 4), np.float32))
+        newly = (d > 0.5) & ~seen
+        if newly.any():
+            crit = 10.0 / 3.0 + 1.2 * 34.0 / 30.0
+            low = s[newly, BW_B0 + 1] < crit
+            assert np.all(np.where(low, r[newly] == -50.0, r[newly] == -100.0))
+        seen |= d > 0.5
+        if seen.all():
+            break
+    assert seen.all() and t < 150
+    # foot contacts reach the observation and the metadata
+    assert np.array_equal(ob[:, 8], s[:, BW_META + 5]) and np.array_equal(ob[:, 13], s[:, BW_META + 6])
+    # time limit: a state parked at step 1999 terminates on the next step
+    s = _walker(2, seed=6)
+    s[:, BW_META] = 1999
+    r, d, ob = _wstep(s, np.zeros((2, 4), np.float32))
+    assert np.all(d == 1.0) and np.all(s[:, BW_META] == 2000)
+    # leaving the terrain to the left is a crash
+    s = _walker(2, seed=6)
+    s[:, BW_B0:BW_B0 + 65:13] = -0.5      # every body, so that the joints stay satisfied
+    r, d, ob = _wstep(s, np.zeros((2, 4), np.float32))
+    assert np.all(d == 1.0) and np.all(r == -100.0)
