@@ -255,6 +255,24 @@ int mrl_reward_rms_update_normalize(int64_t n, const float* rewards, float* norm
 int mrl_normalize_advantages_f64sqrt(int64_t n, float* advantages, float* scratch, void* stream);
 
 /* ------------------------------------------------------------------------
+ * Fused training step of a hidden-64 network (the CartPole / Pendulum configs):
+ * Model.forward_gpu_ws, the PPO loss-gradient kernel and Model.backward_gpu_ws
+ * (sequential.mojo:537-865; ppo.mojo:285-378, :538-633; kernels.mojo:230-486)
+ * in one launch, activations never leaving the SM.  mode: 0 discrete actor,
+ * 1 Gaussian actor, 2 critic (discrete agent: with value_loss_coef), 3 critic
+ * (continuous agent).  grads receives the gradient of every parameter (not
+ * accumulated), kl_sum (nullable) the sum over rows of the per-sample KL term.
+ * scratch: mrl_fused_train_scratch_doubles(net, batch) doubles of device memory.
+ * Needs hidden_dim 64, in_dim <= 8, out_dim <= 4; MRL_ERR_UNSUPPORTED otherwise.
+ * ---------------------------------------------------------------------- */
+int64_t mrl_fused_train_scratch_doubles(const mrl_net_spec* net, int batch);
+int mrl_fused_train_step(const mrl_net_spec* net, int mode, int batch, const float* params, const float* obs,
+                         const float* actions, const float* advantages, const float* returns,
+                         const float* old_log_probs, const float* old_values, float clip_epsilon,
+                         float entropy_coef, float value_loss_coef, int clip_value, double* scratch, float* grads,
+                         float* kl_sum, void* stream);
+
+/* ------------------------------------------------------------------------
  * L4 fused path: the three phases of DeepPPOAgent.train_gpu
  * (ppo.mojo:1558-2840) with every buffer resident in HBM and no host crossing
  * inside a phase.

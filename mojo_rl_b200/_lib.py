@@ -77,6 +77,9 @@ SIGNATURES = {
     "mrl_clamp_log_std": (ctypes.c_int, [ctypes.c_int, c_void_p, c_void_p]),
     "mrl_reward_rms_update_normalize": (ctypes.c_int, [ctypes.c_int64] + [c_void_p] * 5),
     "mrl_normalize_advantages_f64sqrt": (ctypes.c_int, [ctypes.c_int64, c_void_p, c_void_p, c_void_p]),
+    "mrl_fused_train_scratch_doubles": (ctypes.c_int64, [ctypes.POINTER(NetSpec), ctypes.c_int]),
+    "mrl_fused_train_step": (ctypes.c_int, [ctypes.POINTER(NetSpec), ctypes.c_int, ctypes.c_int] + [c_void_p] * 7
+                             + [ctypes.c_float] * 3 + [ctypes.c_int] + [c_void_p] * 4),
     "mrl_config_defaults": (None, [ctypes.POINTER(Config)]),
     "mrl_create": (ctypes.c_int, [ctypes.POINTER(c_void_p), ctypes.POINTER(Config)]),
     "mrl_destroy": (ctypes.c_int, [c_void_p]),

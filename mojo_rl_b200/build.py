@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmojorl_b200.so")
-SOURCES = ["envs.cu", "mlp.cu", "ppo_kernels.cu", "update_bf16.cu", "rollout_bf16.cu", "agent.cu"]
+SOURCES = ["envs.cu", "mlp.cu", "ppo_kernels.cu", "update_bf16.cu", "small_mlp.cu", "rollout_bf16.cu", "agent.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-fmad=false", "-Xcompiler", "-fPIC", "-Xcompiler", "-O2",

@@ -14,6 +14,7 @@
 #include "ppo_kernels.cuh"
 #include "rollout.cuh"
 #include "update_bf16.cuh"
+#include "small_mlp.cuh"
 
 namespace mrl {
 
@@ -97,6 +98,8 @@ struct mrl_ctx {
     int32_t* perm;
     double* stats;  // 8 doubles of reduction scratch
     double* kl_partial;  // 256 block sums of the minibatch KL
+    bool use_small; // precision == 0 and both nets fit the fused hidden-64 kernel
+    double* small_partial;
     bool use_tc;    // precision == 1: update GEMMs on tcgen05 tensor cores in bf16
     mrl::tc::State tc;
     uint8_t* tc_workspace;
@@ -445,6 +448,13 @@ extern "C" int mrl_create(mrl_ctx** out, const mrl_config* cfg) {
     A_(tc_err, 4);
     c->use_tc = false;
     c->use_tc_policy = false;
+    c->use_small = false;
+    if (cfg->precision == 0 && small::supported(&c->actor_net) && small::supported(&c->critic_net)) {
+        int64_t pa = small::partial_doubles(&c->actor_net, (int)B, c->actor_p);
+        int64_t pc = small::partial_doubles(&c->critic_net, (int)B, c->critic_p);
+        A_(small_partial, (size_t)(pa > pc ? pa : pc));
+        c->use_small = true;
+    }
     if (cfg->precision == 1) {
         if (!tc::supported(&c->actor_net, (int)B) || !tc::supported(&c->critic_net, (int)B)) {
             set_error("precision 1 (bf16 tensor-core update) needs hidden_dim 256, ReLU nets with linear heads "
@@ -658,32 +668,41 @@ extern "C" int mrl_ppo_update(mrl_ctx* c, float actor_lr, float critic_lr, float
             }
             prof_mark("gather_normalize", st);
             // ---- actor (ppo.mojo:2513-2624)
-            if (c->use_tc) {
-                if ((rc = c->tc.forward(&c->actor_net, c->actor_params, c->mb_obs, c->mb_logits, st))) return rc;
+            if (c->use_small) {
+                if ((rc = small::train_step(&c->actor_net, c->continuous ? small::ACTOR_GAUSSIAN : small::ACTOR_DISCRETE,
+                                            c->actor_params, c->actor_p, c->mb_obs, c->mb_actions, c->mb_adv, c->mb_ret,
+                                            c->mb_old_lp, c->mb_old_v, B, cfg.clip_epsilon, entropy_coef,
+                                            cfg.value_loss_coef, cfg.clip_value, c->small_partial, c->actor_grads,
+                                            c->actor_grads + c->actor_p, st))) return rc;
+                prof_mark("small_train_step", st);
             } else {
-                if ((rc = mlp_forward_impl(&c->actor_net, B, c->mb_obs, c->actor_params, c->mb_logits, c->actor_cache,
-                                           c->workspace, st))) return rc;
-                prof_mark("fp32_mlp_forward", st);
-            }
-            if (c->continuous) {
-                if ((rc = mrl_ppo_continuous_actor_grad(B, c->action_dim, c->mb_logits, c->mb_old_lp, c->mb_adv,
-                                                        c->mb_actions, cfg.clip_epsilon, entropy_coef,
-                                                        c->mb_grad_logits, c->mb_kl, st))) return rc;
-            } else if ((rc = mrl_ppo_actor_grad(B, A, c->mb_logits, c->mb_old_lp, c->mb_adv, c->mb_actions,
-                                                cfg.clip_epsilon, entropy_coef, c->mb_grad_logits, c->mb_kl, st))) return rc;
-            {
-                int parts = ceil_div(B, 1024) < 256 ? ceil_div(B, 1024) : 256;
-                MRL_LAUNCH(kl_partial_kernel, parts, 256, 0, st, c->mb_kl, B, c->kl_partial);
-                MRL_LAUNCH(kl_final_kernel, 1, 256, 0, st, c->kl_partial, parts, c->actor_grads + c->actor_p);
-            }
-            if (c->use_tc) {
-                if ((rc = c->tc.backward(&c->actor_net, c->actor_params, c->mb_obs, c->mb_grad_logits, c->actor_grads,
-                                         st))) return rc;
-            } else {
-                prof_mark("loss_grad", st);
-                if ((rc = mlp_backward_impl(&c->actor_net, B, c->mb_grad_logits, c->actor_params, c->actor_cache,
-                                            nullptr, c->actor_grads, c->workspace, st))) return rc;
-                prof_mark("fp32_mlp_backward", st);
+                if (c->use_tc) {
+                    if ((rc = c->tc.forward(&c->actor_net, c->actor_params, c->mb_obs, c->mb_logits, st))) return rc;
+                } else {
+                    if ((rc = mlp_forward_impl(&c->actor_net, B, c->mb_obs, c->actor_params, c->mb_logits, c->actor_cache,
+                                               c->workspace, st))) return rc;
+                    prof_mark("fp32_mlp_forward", st);
+                }
+                if (c->continuous) {
+                    if ((rc = mrl_ppo_continuous_actor_grad(B, c->action_dim, c->mb_logits, c->mb_old_lp, c->mb_adv,
+                                                            c->mb_actions, cfg.clip_epsilon, entropy_coef,
+                                                            c->mb_grad_logits, c->mb_kl, st))) return rc;
+                } else if ((rc = mrl_ppo_actor_grad(B, A, c->mb_logits, c->mb_old_lp, c->mb_adv, c->mb_actions,
+                                                    cfg.clip_epsilon, entropy_coef, c->mb_grad_logits, c->mb_kl, st))) return rc;
+                {
+                    int parts = ceil_div(B, 1024) < 256 ? ceil_div(B, 1024) : 256;
+                    MRL_LAUNCH(kl_partial_kernel, parts, 256, 0, st, c->mb_kl, B, c->kl_partial);
+                    MRL_LAUNCH(kl_final_kernel, 1, 256, 0, st, c->kl_partial, parts, c->actor_grads + c->actor_p);
+                }
+                if (c->use_tc) {
+                    if ((rc = c->tc.backward(&c->actor_net, c->actor_params, c->mb_obs, c->mb_grad_logits, c->actor_grads,
+                                             st))) return rc;
+                } else {
+                    prof_mark("loss_grad", st);
+                    if ((rc = mlp_backward_impl(&c->actor_net, B, c->mb_grad_logits, c->actor_params, c->actor_cache,
+                                                nullptr, c->actor_grads, c->workspace, st))) return rc;
+                    prof_mark("fp32_mlp_backward", st);
+                }
             }
             if (cfg.world_size > 1) {
                 if ((rc = allreduce_f32(c, c->actor_grads, (size_t)c->actor_p + 1))) return rc;
@@ -703,27 +722,37 @@ extern "C" int mrl_ppo_update(mrl_ctx* c, float actor_lr, float critic_lr, float
                 MRL_CUDA_OK(cudaGetLastError());
             }
             // ---- critic (ppo.mojo:2626-2728)
-            if (c->use_tc) {
-                if ((rc = c->tc.forward(&c->critic_net, c->critic_params, c->mb_obs, c->mb_values, st))) return rc;
+            if (c->use_small) {
+                if ((rc = small::train_step(&c->critic_net,
+                                            c->continuous ? small::CRITIC_CONTINUOUS : small::CRITIC_DISCRETE,
+                                            c->critic_params, c->critic_p, c->mb_obs, c->mb_actions, c->mb_adv,
+                                            c->mb_ret, c->mb_old_lp, c->mb_old_v, B, cfg.clip_epsilon, entropy_coef,
+                                            cfg.value_loss_coef, cfg.clip_value, c->small_partial, c->critic_grads,
+                                            nullptr, st))) return rc;
+                prof_mark("small_train_step", st);
             } else {
-                prof_mark("clip_adam", st);
-                if ((rc = mlp_forward_impl(&c->critic_net, B, c->mb_obs, c->critic_params, c->mb_values,
-                                           c->critic_cache, c->workspace, st))) return rc;
-                prof_mark("fp32_mlp_forward", st);
-            }
-            if (c->continuous) {
-                if ((rc = mrl_ppo_continuous_critic_grad(B, c->mb_values, c->mb_old_v, c->mb_ret, cfg.clip_epsilon,
-                                                         cfg.clip_value, c->mb_grad_values, st))) return rc;
-            } else if ((rc = mrl_ppo_critic_grad(B, c->mb_values, c->mb_old_v, c->mb_ret, cfg.value_loss_coef,
-                                                 cfg.clip_epsilon, cfg.clip_value, c->mb_grad_values, st))) return rc;
-            if (c->use_tc) {
-                if ((rc = c->tc.backward(&c->critic_net, c->critic_params, c->mb_obs, c->mb_grad_values,
-                                         c->critic_grads, st))) return rc;
-            } else {
-                prof_mark("loss_grad", st);
-                if ((rc = mlp_backward_impl(&c->critic_net, B, c->mb_grad_values, c->critic_params, c->critic_cache,
-                                            nullptr, c->critic_grads, c->workspace, st))) return rc;
-                prof_mark("fp32_mlp_backward", st);
+                if (c->use_tc) {
+                    if ((rc = c->tc.forward(&c->critic_net, c->critic_params, c->mb_obs, c->mb_values, st))) return rc;
+                } else {
+                    prof_mark("clip_adam", st);
+                    if ((rc = mlp_forward_impl(&c->critic_net, B, c->mb_obs, c->critic_params, c->mb_values,
+                                               c->critic_cache, c->workspace, st))) return rc;
+                    prof_mark("fp32_mlp_forward", st);
+                }
+                if (c->continuous) {
+                    if ((rc = mrl_ppo_continuous_critic_grad(B, c->mb_values, c->mb_old_v, c->mb_ret, cfg.clip_epsilon,
+                                                             cfg.clip_value, c->mb_grad_values, st))) return rc;
+                } else if ((rc = mrl_ppo_critic_grad(B, c->mb_values, c->mb_old_v, c->mb_ret, cfg.value_loss_coef,
+                                                     cfg.clip_epsilon, cfg.clip_value, c->mb_grad_values, st))) return rc;
+                if (c->use_tc) {
+                    if ((rc = c->tc.backward(&c->critic_net, c->critic_params, c->mb_obs, c->mb_grad_values,
+                                             c->critic_grads, st))) return rc;
+                } else {
+                    prof_mark("loss_grad", st);
+                    if ((rc = mlp_backward_impl(&c->critic_net, B, c->mb_grad_values, c->critic_params, c->critic_cache,
+                                                nullptr, c->critic_grads, c->workspace, st))) return rc;
+                    prof_mark("fp32_mlp_backward", st);
+                }
             }
             if (cfg.world_size > 1) {
                 if ((rc = allreduce_f32(c, c->critic_grads, (size_t)c->critic_p))) return rc;

@@ -1,0 +1,20 @@
+// Fused fp32 kernels for the hidden-64 networks (small_mlp.cu).
+#pragma once
+#include "common.cuh"
+
+namespace mrl {
+namespace small {
+
+enum Mode { ACTOR_DISCRETE = 0, ACTOR_GAUSSIAN = 1, CRITIC_DISCRETE = 2, CRITIC_CONTINUOUS = 3 };
+
+// hidden 64, at most 8 inputs and 4 outputs (action dims for the Gaussian head)
+bool supported(const mrl_net_spec* net);
+// doubles of scratch for the per-block partial sums of one train_step
+int64_t partial_doubles(const mrl_net_spec* net, int batch, int param_size);
+int train_step(const mrl_net_spec* net, int mode, const float* params, int param_size, const float* x,
+               const float* actions, const float* adv, const float* ret, const float* old_lp, const float* old_v,
+               int batch, float clip_eps, float entropy_coef, float value_loss_coef, int clip_value, double* partial,
+               float* grads, float* kl_out, cudaStream_t st);
+
+}  // namespace small
+}  // namespace mrl

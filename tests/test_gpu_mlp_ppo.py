@@ -205,3 +205,68 @@ def test_gaussian_policy_kernels_bitwise():
     xg = dev(x); scratch = torch.zeros(8, device="cuda")
     call("mrl_normalize_advantages_f64sqrt", x.size, xg, scratch, stream())
     assert abs(host(xg).mean()) < 1e-5 and abs(host(xg).std() - 1.0) < 1e-4
+
+
+@pytest.mark.parametrize("case", [("actor", 4, 2, 0, 0), ("critic", 4, 1, 0, 0), ("gauss", 3, 1, 1, 1),
+                                  ("critic_c", 3, 1, 1, 0), ("actor", 8, 4, 0, 0), ("gauss", 8, 4, 1, 1)])
+@pytest.mark.parametrize("batch", [1, 200, 4096 + 37])
+def test_fused_train_step_matches_layerwise_oracle(case, batch):
+    """Forward + loss gradient + backward in one kernel against the oracle's layer-by-layer functions."""
+    import torch
+    from _gpu import call, dev, host, stream
+    from mojo_rl_b200 import _lib
+    kind, I, O, act, head = case
+    o = oracle()
+    L = _lib.lib()
+    rng = np.random.default_rng(batch + I + O)
+    spec = NetSpec(I, 64, O, act, head)
+    p = xavier_params(spec, rng) * 2
+    if head == 1:
+        p[-O:] = rng.uniform(-1.0, 0.5, O).astype(np.float32)
+    oc = O * (2 if head else 1)
+    x = rng.standard_normal((batch, I)).astype(np.float32)
+    out = np.empty((batch, oc), np.float32)
+    cache = np.empty(batch * o.orc_net_cache_per_sample(spec), np.float32)
+    o.orc_mlp_forward(spec, batch, fp(x), fp(p), fp(out), fp(cache))
+    adv = rng.standard_normal(batch).astype(np.float32)
+    ret = rng.standard_normal(batch).astype(np.float32)
+    old_v = (out[:, 0] + 0.3 * rng.standard_normal(batch)).astype(np.float32)
+    g_out, kl = np.zeros((batch, oc), np.float32), np.zeros(batch, np.float32)
+    if kind == "actor":
+        actions = rng.integers(0, O, batch).astype(np.float32)
+        lp = out - out.max(1, keepdims=True)
+        lp = lp - np.log(np.exp(lp).sum(1, keepdims=True))
+        old_lp = (lp[np.arange(batch), actions.astype(int)] + 0.15 * rng.standard_normal(batch)).astype(np.float32)
+        o.orc_ppo_actor_grad(batch, O, fp(out), fp(old_lp), fp(adv), fp(actions), 0.2, 0.01, fp(g_out), fp(kl))
+        mode = 0
+    elif kind == "gauss":
+        actions = (out[:, :O] + np.exp(out[:, O:]) * rng.standard_normal((batch, O))).astype(np.float32)
+        z = (actions - out[:, :O]) / np.exp(out[:, O:])
+        old_lp = ((-0.5 * (1.8378770664093453 + 2 * out[:, O:] + z * z)).sum(1)
+                  + 0.15 * rng.standard_normal(batch)).astype(np.float32)
+        o.orc_ppo_continuous_actor_grad(batch, O, fp(out), fp(old_lp), fp(adv), fp(actions), 0.2, 0.01, fp(g_out),
+                                        fp(kl))
+        mode = 1
+    elif kind == "critic":
+        actions, old_lp = np.zeros(batch, np.float32), np.zeros(batch, np.float32)
+        o.orc_ppo_critic_grad(batch, fp(out.reshape(-1).copy()), fp(old_v), fp(ret), 0.5, 0.2, 1, fp(g_out.reshape(-1)))
+        mode = 2
+    else:
+        actions, old_lp = np.zeros(batch, np.float32), np.zeros(batch, np.float32)
+        o.orc_ppo_continuous_critic_grad(batch, fp(out.reshape(-1).copy()), fp(old_v), fp(ret), 0.2, 1,
+                                         fp(g_out.reshape(-1)))
+        mode = 3
+    grads_c, gin = np.empty_like(p), np.empty((batch, I), np.float32)
+    o.orc_mlp_backward(spec, batch, fp(g_out), fp(p), fp(cache), fp(gin), fp(grads_c), 1)
+    n_scr = L.mrl_fused_train_scratch_doubles(spec, batch)
+    assert n_scr > 0
+    scratch = torch.zeros(n_scr, dtype=torch.float64, device="cuda")
+    grads_g = torch.full((p.size,), 7.0, device="cuda")
+    kl_g = torch.zeros(1, device="cuda")
+    call("mrl_fused_train_step", spec, mode, batch, dev(p), dev(x), dev(actions), dev(adv), dev(ret), dev(old_lp),
+         dev(old_v), 0.2, 0.01, 0.5, 1, scratch, grads_g, kl_g, stream())
+    scale = max(float(np.abs(grads_c).max()), 1e-6)
+    assert np.allclose(host(grads_g), grads_c, rtol=2e-5, atol=2e-6 * scale), np.abs(host(grads_g) - grads_c).max() / scale
+    if mode < 2:
+        assert abs(float(kl_g.item()) - float(kl.astype(np.float64).sum())) <= 1e-5 * max(1.0, abs(float(kl.sum())))
+    assert L.mrl_fused_train_scratch_doubles(NetSpec(24, 64, 4, 0, 0), batch) == -1
