@@ -58,6 +58,7 @@ def kernel_algorithmic_bytes(w, total):
     return {
         "rollout_env_step": n * w["step_bytes"],
         "rollout_policy": n * (8 * i + 20),
+        "rollout_persistent": w["T"] * n * (w["step_bytes"] + 8 * i + 20),
         "l0_forward": B * (4 * i + 2 * h),
         "k1_forward_gemm": B * (4 * h + 4 * act_out),
         "head_backward": B * (4 * h + 4 * act_out),

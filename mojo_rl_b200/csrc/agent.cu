@@ -99,6 +99,7 @@ struct mrl_ctx {
     double* stats;  // 8 doubles of reduction scratch
     double* kl_partial;  // 256 block sums of the minibatch KL
     bool use_small; // precision == 0 and both nets fit the fused hidden-64 kernel
+    bool use_small_rollout;  // ... and the environment is one the persistent rollout kernel steps
     double* small_partial;
     bool use_tc;    // precision == 1: update GEMMs on tcgen05 tensor cores in bf16
     mrl::tc::State tc;
@@ -449,11 +450,13 @@ extern "C" int mrl_create(mrl_ctx** out, const mrl_config* cfg) {
     c->use_tc = false;
     c->use_tc_policy = false;
     c->use_small = false;
+    c->use_small_rollout = false;
     if (cfg->precision == 0 && small::supported(&c->actor_net) && small::supported(&c->critic_net)) {
         int64_t pa = small::partial_doubles(&c->actor_net, (int)B, c->actor_p);
         int64_t pc = small::partial_doubles(&c->critic_net, (int)B, c->critic_p);
         A_(small_partial, (size_t)(pa > pc ? pa : pc));
         c->use_small = true;
+        c->use_small_rollout = small::rollout_supported(cfg->env_kind, &c->actor_net, &c->critic_net);
     }
     if (cfg->precision == 1) {
         if (!tc::supported(&c->actor_net, (int)B) || !tc::supported(&c->critic_net, (int)B)) {
@@ -582,6 +585,17 @@ extern "C" int mrl_ppo_rollout(mrl_ctx* c) {
         if ((rc = c->policy.prepare(c->actor_params, c->critic_params, c->obs_dim, st))) return rc;
     }
     prof_mark("(other)", st);
+    if (c->use_small_rollout) {
+        RolloutStepArgs ra{c->states, c->actions, c->rewards, c->dones, c->obs, c->r_rewards, c->r_dones,
+                           c->episode_rewards, c->episode_steps, c->ring_returns, c->ring_lengths, c->counters, 0, N,
+                           c->tc_err};
+        if ((rc = small::rollout(c->cfg.env_kind, &c->actor_net, c->actor_params, c->critic_params, T,
+                                 c->cfg.deterministic, c->actions, c->values, c->r_obs, c->r_actions, c->r_log_probs,
+                                 c->r_values, ra, st))) return rc;
+        prof_mark("rollout_persistent", st);
+        MRL_LAUNCH(add_total_steps_kernel, 1, 1, 0, st, c->counters, (long long)T * N);
+        return MRL_OK;
+    }
     for (int t = 0; t < T; ++t) {
         if (c->use_tc_policy) {
             tc::PolicyStepArgs pa{c->obs, c->actor_params, c->critic_params, N, c->obs_dim, A, t, c->cfg.deterministic,

@@ -16,7 +16,10 @@
 // Reductions over rows are kept in double precision per block and summed
 // over blocks in a fixed order (deterministic; not the serial order of the
 // reference's kernels).  Compile with -fmad=false.
+#include "env_cartpole.cuh"
+#include "env_pendulum.cuh"
 #include "ppo_kernels.cuh"
+#include "rollout.cuh"
 #include "small_mlp.cuh"
 
 namespace mrl {
@@ -48,7 +51,7 @@ __device__ __forceinline__ float act_bwd(float g, float y, int act) {
 
 // dst[row][col0..col0+3] = epilogue(init + A[row][:] . W[:][col0..col0+3]) for the thread's eight rows
 // rg, rg + 16, ..., rg + 112.  A: [TM][PITCH] in shared memory, W: [64][64] k-major in shared memory.
-template <class Epi>
+template <int ROWSTEP = 16, class Epi>
 __device__ __forceinline__ void tile_gemm64(const float* __restrict__ A, const float* __restrict__ W, int rg, int c0,
                                             const float (&init)[4], Epi epi) {
     float acc[8][4];
@@ -60,7 +63,7 @@ __device__ __forceinline__ void tile_gemm64(const float* __restrict__ A, const f
     for (int k = 0; k < H; k += 4) {
         float4 a[8], w[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) a[i] = *reinterpret_cast<const float4*>(A + (rg + 16 * i) * PITCH + k);
+        for (int i = 0; i < 8; ++i) a[i] = *reinterpret_cast<const float4*>(A + (rg + ROWSTEP * i) * PITCH + k);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) w[kk] = *reinterpret_cast<const float4*>(W + (k + kk) * H + c0);
 #pragma unroll
@@ -76,7 +79,7 @@ __device__ __forceinline__ void tile_gemm64(const float* __restrict__ A, const f
         }
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) epi(rg + 16 * i, c0, acc[i]);
+    for (int i = 0; i < 8; ++i) epi(rg + ROWSTEP * i, c0, acc[i]);
 }
 
 __global__ void __launch_bounds__(THREADS, 1) fused_train_kernel(TrainArgs p) {
@@ -353,6 +356,270 @@ __global__ void reduce_partials_kernel(const double* __restrict__ partial, int n
         for (int b = 0; b < nblocks; ++b) acc += partial[(size_t)b * pstride + pstride - 1];
         kl_out[0] = (float)acc;
     }
+}
+
+// ---------------------------------------------------------------------------
+// Persistent rollout of the hidden-64 configs: environments are independent and
+// the parameters are fixed during a rollout, so one launch runs all T steps.  A
+// block owns 32 environments; warps 0-1 evaluate the actor, warps 2-3 the critic
+// (both weight sets stay in shared memory), then lanes of warp 0 sample, store
+// the pre-step data, step their environment, do the episode bookkeeping and the
+// selective reset, and write the next observation back to shared memory.
+// Per step this is _sample_actions_kernel / _sample_continuous_actions_kernel,
+// the store kernels, EnvType.step_kernel_gpu, the tracking kernels and
+// selective_reset_kernel_gpu (ppo.mojo:2056-2285; ppo_continuous.mojo:2618-2836).
+// ---------------------------------------------------------------------------
+constexpr int RT = 32, RTHREADS = 128;
+
+struct RolloutArgs {
+    const float* actor_params;
+    const float* critic_params;
+    int in_dim, out_dim, act, gaussian, greedy;
+    int T;
+    float* logits_unused;
+    float* actions;      // [n, act_w] (last step's)
+    float* values;       // [n]
+    float* r_obs; float* r_actions; float* r_log_probs; float* r_values;
+    RolloutStepArgs env;  // t is set per step inside the kernel
+};
+
+struct NetSmem {
+    float W1s[H * H];
+    float W0s[MAX_IN * H];
+    float b0s[H], b1s[H];
+    float W2s[H * MAX_OUT];
+    float b2s[MAX_OUT], lss[MAX_OUT];
+    float S0[RT * PITCH], S1[RT * PITCH];
+};
+
+__device__ __forceinline__ void load_net(NetSmem& m, const float* params, int I, int O, bool gaussian, int lt, int nt) {
+    const float* W0 = params;
+    const float* b0 = W0 + I * H;
+    const float* W1 = b0 + H;
+    const float* b1 = W1 + H * H;
+    const float* W2 = b1 + H;
+    const float* b2 = W2 + H * O;
+    const float* ls = b2 + O;
+    for (int i = lt; i < H * H; i += nt) m.W1s[i] = W1[i];
+    for (int i = lt; i < MAX_IN * H; i += nt) m.W0s[i] = i < I * H ? W0[i] : 0.0f;
+    for (int i = lt; i < H; i += nt) { m.b0s[i] = b0[i]; m.b1s[i] = b1[i]; }
+    for (int i = lt; i < H * MAX_OUT; i += nt) {
+        int k = i / MAX_OUT, o = i % MAX_OUT;
+        m.W2s[i] = o < O ? W2[k * O + o] : 0.0f;
+    }
+    if (lt < MAX_OUT) {
+        m.b2s[lt] = lt < O ? b2[lt] : 0.0f;
+        float l = (gaussian && lt < O) ? ls[lt] : 0.0f;
+        if (l < -5.0f) l = -5.0f;
+        else if (l > 2.0f) l = 2.0f;
+        m.lss[lt] = l;
+    }
+}
+
+template <int ENV>  // 0 CartPole, 1 Pendulum
+__global__ void __launch_bounds__(RTHREADS, 1) fused_rollout_kernel(RolloutArgs p) {
+    extern __shared__ __align__(16) unsigned char raw[];
+    NetSmem* nets = reinterpret_cast<NetSmem*>(raw);                 // [2]
+    float* xs = reinterpret_cast<float*>(raw + 2 * sizeof(NetSmem)); // [RT][MAX_IN]
+    float* heads = xs + RT * MAX_IN;                                 // [RT][MAX_OUT + 1]: actor outputs, value
+    constexpr int SS = ENV == 0 ? 4 : 8, OD = ENV == 0 ? 4 : 3;
+
+    const int tid = threadIdx.x;
+    const int net = tid >> 6, lt = tid & 63;      // network of this thread, thread index inside it
+    const int I = p.in_dim, act = p.act, n = p.env.n;
+    const int O = net == 0 ? p.out_dim : 1;
+    NetSmem& m = nets[net];
+    load_net(m, net == 0 ? p.actor_params : p.critic_params, I, O, net == 0 && p.gaussian, lt, 64);
+    const int env0 = blockIdx.x * RT;
+    const int env = env0 + tid;                   // environment of lanes 0..31 of warp 0
+    const bool env_thread = tid < RT && env < n;
+    float st[SS];
+    float ep_r = 0.0f, ep_s = 0.0f;
+    if (tid < RT) {
+#pragma unroll
+        for (int k = 0; k < MAX_IN; ++k) xs[tid * MAX_IN + k] = 0.0f;
+    }
+    if (env_thread) {
+#pragma unroll
+        for (int k = 0; k < SS; ++k) st[k] = p.env.states[(size_t)env * SS + k];
+#pragma unroll
+        for (int k = 0; k < OD; ++k) xs[tid * MAX_IN + k] = p.env.obs[(size_t)env * OD + k];
+        ep_r = p.env.episode_rewards[env];
+        ep_s = p.env.episode_steps[env];
+    }
+    __syncthreads();
+
+    const int rg = lt >> 4, c0 = (lt & 15) * 4;   // rows rg, rg + 4, ..., rg + 28; columns c0..c0+3
+    const long long total_steps0 = p.env.ctr->total_steps;
+    for (int t = 0; t < p.T; ++t) {
+        // h0 = act(x W0 + b0)
+        {
+            float acc[8][4];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = m.b0s[c0 + j];
+            for (int k = 0; k < I; ++k) {
+                const float4 w = *reinterpret_cast<const float4*>(m.W0s + k * H + c0);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float a = xs[(rg + 4 * i) * MAX_IN + k];
+                    acc[i][0] = fmaf(a, w.x, acc[i][0]);
+                    acc[i][1] = fmaf(a, w.y, acc[i][1]);
+                    acc[i][2] = fmaf(a, w.z, acc[i][2]);
+                    acc[i][3] = fmaf(a, w.w, acc[i][3]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                *reinterpret_cast<float4*>(m.S0 + (rg + 4 * i) * PITCH + c0) =
+                    make_float4(act_fwd(acc[i][0], act), act_fwd(acc[i][1], act), act_fwd(acc[i][2], act),
+                                act_fwd(acc[i][3], act));
+        }
+        __syncthreads();
+        {
+            const float init[4] = {m.b1s[c0], m.b1s[c0 + 1], m.b1s[c0 + 2], m.b1s[c0 + 3]};
+            tile_gemm64<4>(m.S0, m.W1s, rg, c0, init, [&](int r, int c, const float (&v)[4]) {
+                *reinterpret_cast<float4*>(m.S1 + r * PITCH + c) =
+                    make_float4(act_fwd(v[0], act), act_fwd(v[1], act), act_fwd(v[2], act), act_fwd(v[3], act));
+            });
+        }
+        __syncthreads();
+        // heads: first warp of each network, one row per lane
+        if (lt < RT) {
+            float out[MAX_OUT];
+#pragma unroll
+            for (int o = 0; o < MAX_OUT; ++o) out[o] = m.b2s[o];
+            for (int k = 0; k < H; ++k) {
+                const float hv = m.S1[lt * PITCH + k];
+                const float4 w = *reinterpret_cast<const float4*>(m.W2s + k * MAX_OUT);
+                out[0] = fmaf(hv, w.x, out[0]);
+                out[1] = fmaf(hv, w.y, out[1]);
+                out[2] = fmaf(hv, w.z, out[2]);
+                out[3] = fmaf(hv, w.w, out[3]);
+            }
+            if (net == 0) {
+#pragma unroll
+                for (int o = 0; o < MAX_OUT; ++o) heads[lt * (MAX_OUT + 1) + o] = out[o];
+            } else {
+                heads[lt * (MAX_OUT + 1) + MAX_OUT] = out[0];
+            }
+        }
+        __syncthreads();
+        if (env_thread) {
+            const unsigned long long ts = (unsigned long long)total_steps0 + (unsigned long long)t * (unsigned long long)n;
+            const uint32_t seed = (uint32_t)(ts * 2654435761ull + (unsigned long long)t * 7919ull);
+            const size_t off = (size_t)t * n + env;
+            float a_out[MAX_OUT], lp;
+            const int A = p.out_dim;
+            if (p.gaussian) {
+                float row[2 * MAX_OUT];
+                for (int o = 0; o < A; ++o) { row[o] = heads[tid * (MAX_OUT + 1) + o]; row[A + o] = nets[0].lss[o]; }
+                sample_continuous_one(row, A, seed, env, p.greedy, a_out, lp);
+                for (int o = 0; o < A; ++o) p.r_actions[off * A + o] = a_out[o];
+            } else {
+                float row[MAX_OUT];
+#pragma unroll
+                for (int o = 0; o < MAX_OUT; ++o) row[o] = heads[tid * (MAX_OUT + 1) + o];
+                sample_one(row, A, seed, env, p.greedy, a_out[0], lp);
+                p.r_actions[off] = a_out[0];
+            }
+            const float value = heads[tid * (MAX_OUT + 1) + MAX_OUT];
+            p.r_log_probs[off] = lp;
+            p.r_values[off] = value;
+#pragma unroll
+            for (int k = 0; k < OD; ++k) p.r_obs[off * OD + k] = xs[tid * MAX_IN + k];
+            // environment step, bookkeeping, selective reset
+            RolloutStepArgs a = p.env;
+            a.t = t;
+            float reward, done;
+            if (ENV == 0) {
+                float s4[4] = {st[0], st[1], st[2], st[3]};
+                bool d = cartpole::step(s4, (int)a_out[0]);
+                reward = 1.0f;
+                done = d ? 1.0f : 0.0f;
+                st[0] = s4[0]; st[1] = s4[1]; st[2] = s4[2]; st[3] = s4[3];
+            } else {
+                float s8[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) s8[k] = st[k % SS];
+                pendulum::step(s8, a_out[0], reward, done);
+#pragma unroll
+                for (int k = 0; k < SS; ++k) st[k] = s8[k];
+            }
+            a.r_rewards[off] = reward;
+            a.r_dones[off] = done;
+            ep_r = ep_r + reward;
+            ep_s = ep_s + 1.0f;
+            if (done > 0.5f) {
+                unsigned long long slot = atomicAdd(&a.ctr->ring_head, 1ull);
+                a.ring_returns[slot % EP_RING] = ep_r;
+                a.ring_lengths[slot % EP_RING] = ep_s;
+                atomicAdd(&a.ctr->completed_episodes, 1ull);
+                atomicAdd(&a.ctr->sum_episode_reward, (double)ep_r);
+                atomicAdd(&a.ctr->sum_episode_steps, (double)ep_s);
+                ep_r = 0.0f;
+                ep_s = 0.0f;
+                const unsigned long long rs = auto_reset_seed(a);
+                if (ENV == 0) {
+                    float s4[4];
+                    cartpole::reset(s4, (uint32_t)((unsigned long long)env * 2654435761ull + (uint32_t)rs));
+                    st[0] = s4[0]; st[1] = s4[1]; st[2] = s4[2]; st[3] = s4[3];
+                } else {
+                    float s8[8];
+                    pendulum::reset(s8, pendulum::combined_seed((float)rs, env));
+#pragma unroll
+                    for (int k = 0; k < SS; ++k) st[k] = s8[k];
+                }
+                done = 0.0f;   // both environments clear the flag in their selective reset
+            }
+            if (t == p.T - 1) {
+                a.rewards[env] = reward;
+                a.dones[env] = done;
+                a.episode_rewards[env] = ep_r;
+                a.episode_steps[env] = ep_s;
+                p.values[env] = value;
+                for (int o = 0; o < (p.gaussian ? A : 1); ++o) p.actions[(size_t)env * (p.gaussian ? A : 1) + o] = a_out[o];
+#pragma unroll
+                for (int k = 0; k < SS; ++k) a.states[(size_t)env * SS + k] = st[k];
+#pragma unroll
+                for (int k = 0; k < OD; ++k) a.obs[(size_t)env * OD + k] = st[k];
+            }
+#pragma unroll
+            for (int k = 0; k < OD; ++k) xs[tid * MAX_IN + k] = st[k];
+        }
+        __syncthreads();
+    }
+}
+
+constexpr int ROLLOUT_SMEM = 2 * (int)sizeof(NetSmem) + (RT * MAX_IN + RT * (MAX_OUT + 1)) * 4;
+
+bool rollout_supported(int env_kind, const mrl_net_spec* actor, const mrl_net_spec* critic) {
+    return (env_kind == MRL_ENV_CARTPOLE || env_kind == MRL_ENV_PENDULUM) && supported(actor) && supported(critic) &&
+           critic->out_dim == 1;
+}
+
+int rollout(int env_kind, const mrl_net_spec* actor, const float* actor_params, const float* critic_params, int T,
+            int greedy, float* actions, float* values, float* r_obs, float* r_actions, float* r_log_probs,
+            float* r_values, const RolloutStepArgs& env, cudaStream_t st) {
+    static bool attr_done = false;
+    if (!attr_done) {
+        MRL_CUDA_OK(cudaFuncSetAttribute(fused_rollout_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ROLLOUT_SMEM));
+        MRL_CUDA_OK(cudaFuncSetAttribute(fused_rollout_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ROLLOUT_SMEM));
+        attr_done = true;
+    }
+    RolloutArgs a{};
+    a.actor_params = actor_params; a.critic_params = critic_params;
+    a.in_dim = actor->in_dim; a.out_dim = actor->out_dim; a.act = actor->activation == MRL_ACT_RELU ? 0 : 1;
+    a.gaussian = actor->head == MRL_HEAD_STOCHASTIC_ACTOR ? 1 : 0;
+    a.greedy = greedy; a.T = T;
+    a.actions = actions; a.values = values;
+    a.r_obs = r_obs; a.r_actions = r_actions; a.r_log_probs = r_log_probs; a.r_values = r_values;
+    a.env = env;
+    const int grid = ceil_div(env.n, RT);
+    if (env_kind == MRL_ENV_CARTPOLE) { MRL_LAUNCH(fused_rollout_kernel<0>, grid, RTHREADS, ROLLOUT_SMEM, st, a); }
+    else { MRL_LAUNCH(fused_rollout_kernel<1>, grid, RTHREADS, ROLLOUT_SMEM, st, a); }
+    return MRL_OK;
 }
 
 constexpr int SMEM_FLOATS = 2 * H * H + 3 * TM * PITCH + MAX_IN * H + 2 * H + H * MAX_OUT + 2 * MAX_OUT + TM * MAX_IN +

@@ -1,6 +1,7 @@
 // Fused fp32 kernels for the hidden-64 networks (small_mlp.cu).
 #pragma once
 #include "common.cuh"
+#include "rollout.cuh"
 
 namespace mrl {
 namespace small {
@@ -15,6 +16,13 @@ int train_step(const mrl_net_spec* net, int mode, const float* params, int param
                const float* actions, const float* adv, const float* ret, const float* old_lp, const float* old_v,
                int batch, float clip_eps, float entropy_coef, float value_loss_coef, int clip_value, double* partial,
                float* grads, float* kl_out, cudaStream_t st);
+
+// All T steps of a rollout in one launch (policy, sampling, stores, env step, episode bookkeeping,
+// selective reset) for CartPole / Pendulum with hidden-64 networks.  env.t is ignored.
+bool rollout_supported(int env_kind, const mrl_net_spec* actor, const mrl_net_spec* critic);
+int rollout(int env_kind, const mrl_net_spec* actor, const float* actor_params, const float* critic_params, int T,
+            int greedy, float* actions, float* values, float* r_obs, float* r_actions, float* r_log_probs,
+            float* r_values, const RolloutStepArgs& env, cudaStream_t st);
 
 }  // namespace small
 }  // namespace mrl
