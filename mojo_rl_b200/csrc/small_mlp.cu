@@ -25,7 +25,8 @@
 namespace mrl {
 namespace small {
 
-constexpr int H = 64, TM = 128, THREADS = 256, PITCH = 68, MAX_IN = 8, MAX_OUT = 4;
+constexpr int H = 64, PITCH = 68, MAX_IN = 8, MAX_OUT = 4;
+constexpr int TRAIN_THREADS = 128, TRAIN_TM = TRAIN_THREADS / 2;
 
 struct TrainArgs {
     const float* params;
@@ -47,6 +48,92 @@ __device__ __forceinline__ float act_fwd(float v, int act) { return act == 0 ? (
 // derivative applied to an upstream gradient, from the stored activation y
 __device__ __forceinline__ float act_bwd(float g, float y, int act) {
     return act == 0 ? (y > 0.0f ? g : 0.0f) : g * (1.0f - y * y);
+}
+
+// The loss gradients of ppo_kernels.cuh with every loop unrolled over MAX_OUT and predicated, so that the
+// per-row arrays stay in registers (same operations in the same order).
+__device__ __forceinline__ void actor_grad_small(const float (&l)[MAX_OUT], int A, float old_log_prob, float advantage,
+                                                 int action, float clip_epsilon, float entropy_coef, float batch_div,
+                                                 float (&g)[2 * MAX_OUT], float& kl) {
+    float max_logit = l[0];
+#pragma unroll
+    for (int a = 1; a < MAX_OUT; ++a) if (a < A && l[a] > max_logit) max_logit = l[a];
+    float e[MAX_OUT];
+    float sum_exp = 0.0f;
+#pragma unroll
+    for (int a = 0; a < MAX_OUT; ++a)
+        if (a < A) { e[a] = mrl_expf(l[a] - max_logit); sum_exp = sum_exp + e[a]; }
+    float probs[MAX_OUT];
+    float p_action = 0.0f;
+#pragma unroll
+    for (int a = 0; a < MAX_OUT; ++a)
+        if (a < A) { probs[a] = e[a] / sum_exp; if (a == action) p_action = probs[a]; }
+    float new_log_prob = mrl_logf(p_action + 1e-8f);
+    kl = old_log_prob - new_log_prob;
+    float ratio = mrl_expf(new_log_prob - old_log_prob);
+    bool is_clipped = (ratio < 1.0f - clip_epsilon) || (ratio > 1.0f + clip_epsilon);
+#pragma unroll
+    for (int a = 0; a < MAX_OUT; ++a) {
+        if (a >= A) continue;
+        if (is_clipped) { g[a] = 0.0f; continue; }
+        float d_log_prob = a == action ? 1.0f - probs[a] : -probs[a];
+        float log_prob_ent = mrl_logf(probs[a] + 1e-8f);
+        float d_entropy = -probs[a] * (1.0f + log_prob_ent);
+        g[a] = (-advantage * ratio * d_log_prob - entropy_coef * d_entropy) / batch_div;
+    }
+}
+
+__device__ __forceinline__ void gauss_grad_small(const float (&mean)[MAX_OUT], const float* __restrict__ log_std_clamped,
+                                                 const float (&act)[MAX_OUT], int A, float old_lp, float advantage,
+                                                 float clip_epsilon, float entropy_coef, float batch_div,
+                                                 float (&g)[2 * MAX_OUT], float& kl_out) {
+    const float eps = 1e-6f, log_2pi = 1.8378770664093453f;
+    float new_lp = 0.0f;
+    float sv[MAX_OUT];
+#pragma unroll
+    for (int j = 0; j < MAX_OUT; ++j) {
+        if (j >= A) continue;
+        float log_std = log_std_clamped[j];   // already inside [-5, 2]: the clamp of the reference is the identity
+        float stdv = mrl_expf(log_std);
+        sv[j] = stdv;
+        float an = (act[j] - mean[j]) / (stdv + eps);
+        float lg = -0.5f * (log_2pi + 2.0f * log_std + an * an);
+        new_lp = new_lp + lg;
+    }
+    float diff = new_lp - old_lp;
+    if (diff > 20.0f) diff = 20.0f;
+    else if (diff < -20.0f) diff = -20.0f;
+    float ratio = mrl_expf(diff);
+    float kl = (ratio - 1.0f) - diff;
+    if (kl < 0.0f) kl = 0.0f;
+    else if (kl > 100.0f) kl = 100.0f;
+    kl_out = kl;
+    float clipped = ratio;
+    if (clipped < 1.0f - clip_epsilon) clipped = 1.0f - clip_epsilon;
+    else if (clipped > 1.0f + clip_epsilon) clipped = 1.0f + clip_epsilon;
+    bool is_clipped = clipped * advantage < ratio * advantage;
+#pragma unroll
+    for (int j = 0; j < MAX_OUT; ++j) {
+        if (j >= A) continue;
+        float gm = 0.0f, gs = 0.0f;
+        if (!is_clipped) {
+            float an = (act[j] - mean[j]) / (sv[j] + eps);
+            float d_mean = an / (sv[j] + eps);
+            float d_log_std = an * an - 1.0f;
+            gm = (-advantage * ratio * d_mean) / batch_div;
+            gs = (-advantage * ratio * d_log_std - entropy_coef * 1.0f) / batch_div;
+            if (gm > 10.0f) gm = 10.0f;
+            else if (gm < -10.0f) gm = -10.0f;
+            if (gs > 10.0f) gs = 10.0f;
+            else if (gs < -10.0f) gs = -10.0f;
+        }
+        // g[j] = mean gradient, g[A + j] = log_std gradient
+#pragma unroll
+        for (int q = 0; q < 2 * MAX_OUT; ++q) {
+            if (q == j) g[q] = gm;
+            if (q == A + j) g[q] = gs;
+        }
+    }
 }
 
 // dst[row][col0..col0+3] = epilogue(init + A[row][:] . W[:][col0..col0+3]) for the thread's eight rows
@@ -82,12 +169,16 @@ __device__ __forceinline__ void tile_gemm64(const float* __restrict__ A, const f
     for (int i = 0; i < 8; ++i) epi(rg + ROWSTEP * i, c0, acc[i]);
 }
 
-__global__ void __launch_bounds__(THREADS, 1) fused_train_kernel(TrainArgs p) {
+template <int THREADS, int MODE, int ACT>
+__global__ void __launch_bounds__(THREADS, 256 / THREADS) fused_train_kernel(TrainArgs p) {
+    constexpr int TM = THREADS / 2;        // rows per tile: every thread owns 8 rows x 4 columns
+    constexpr int RG = THREADS / 16;       // row groups; thread rows are rg, rg + RG, ..., rg + 7 RG
+    constexpr int WI = 64 / RG;            // rows of the thread's dW1 tile (WI x 4)
     extern __shared__ __align__(16) float smem[];
     float* W1s = smem;                    // [k][j]
-    float* W1t = W1s + H * H;             // [j][k]: W1t[j * 64 + i] = W1[i][j]
+    float* W1t = W1s + H * H;             // [j][i] = W1[i][j]
     float* S0 = W1t + H * H;              // h0 [TM][PITCH]
-    float* S1 = S0 + TM * PITCH;          // h1, later g0
+    float* S1 = S0 + TM * PITCH;          // h1
     float* G1 = S1 + TM * PITCH;          // g1
     float* W0s = G1 + TM * PITCH;         // [MAX_IN][64]
     float* b0s = W0s + MAX_IN * H;
@@ -100,8 +191,9 @@ __global__ void __launch_bounds__(THREADS, 1) fused_train_kernel(TrainArgs p) {
     __shared__ double kl_sm[32];
 
     const int tid = threadIdx.x;
-    const int I = p.in_dim, O = p.out_dim, act = p.act;
-    const bool gaussian = p.mode == ACTOR_GAUSSIAN;
+    const int I = p.in_dim, O = p.out_dim;
+    constexpr int act = ACT;
+    constexpr bool gaussian = MODE == ACTOR_GAUSSIAN;
     const float* W0 = p.params;
     const float* b0 = W0 + I * H;
     const float* W1 = b0 + H;
@@ -130,16 +222,27 @@ __global__ void __launch_bounds__(THREADS, 1) fused_train_kernel(TrainArgs p) {
     __syncthreads();
 
     const int rg = tid >> 4, c0 = (tid & 15) * 4;     // 8 x 4 output tile of the row-tile GEMMs
-    const int wi0 = (tid >> 4) * 4, wj0 = (tid & 15) * 4;  // 4 x 4 tile of dW1
-    double dW1[4][4];
+    const int wi0 = (tid >> 4) * WI, wj0 = (tid & 15) * 4;  // WI x 4 tile of dW1
+    // Weight-gradient sums of this thread's rows.  dW1 is a proper 4 x 4 tile; the others are partial sums over
+    // the thread's eight rows per tile (columns c0..c0+3), combined across the 16 row groups at the end.
+    double dW1[WI][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < WI; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) dW1[i][j] = 0.0;
-    double dW0a = 0.0, dW0b = 0.0;          // entries tid and tid + 256 of dW0 [I][64]
-    double db0 = 0.0, db1 = 0.0;            // threads < 64
-    double dW2 = 0.0;                       // entry (k = tid / 4, o = tid % 4)
-    double db2 = 0.0, dls = 0.0;            // threads < MAX_OUT
+    float db1p[4] = {0.0f, 0.0f, 0.0f, 0.0f}, db0p[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float dW2p[4][MAX_OUT], dW0p[MAX_IN][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int o = 0; o < MAX_OUT; ++o) dW2p[j][o] = 0.0f;
+#pragma unroll
+    for (int k = 0; k < MAX_IN; ++k)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dW0p[k][j] = 0.0f;
+    float dheadp[2 * MAX_OUT];              // threads < TM: sums of their rows' head gradients (db2 | dlog_std)
+#pragma unroll
+    for (int o = 0; o < 2 * MAX_OUT; ++o) dheadp[o] = 0.0f;
     double kl_acc = 0.0;                    // threads < TM
 
     const int n_tiles = (p.B + TM - 1) / TM;
@@ -148,6 +251,23 @@ __global__ void __launch_bounds__(THREADS, 1) fused_train_kernel(TrainArgs p) {
         for (int i = tid; i < TM * MAX_IN; i += THREADS) {
             int r = i / MAX_IN, k = i % MAX_IN;
             xs[i] = (row0 + r < p.B && k < I) ? p.x[(size_t)(row0 + r) * I + k] : 0.0f;
+        }
+        // per-row loss inputs, fetched now and used after the two forward GEMMs
+        float in_adv = 0.0f, in_old_lp = 0.0f, in_ret = 0.0f, in_old_v = 0.0f, in_act[MAX_OUT] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (tid < TM && row0 + tid < p.B) {
+            const int row = row0 + tid;
+            if (MODE == ACTOR_DISCRETE || MODE == ACTOR_GAUSSIAN) {
+                in_adv = p.adv[row];
+                in_old_lp = p.old_lp[row];
+                if (MODE == ACTOR_DISCRETE) in_act[0] = p.actions[row];
+                else {
+#pragma unroll
+                    for (int o = 0; o < MAX_OUT; ++o) if (o < O) in_act[o] = p.actions[(size_t)row * O + o];
+                }
+            } else {
+                in_ret = p.ret[row];
+                in_old_v = p.old_v ? p.old_v[row] : 0.0f;
+            }
         }
         __syncthreads();
         // h0 = act(x W0 + b0)
@@ -161,7 +281,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_train_kernel(TrainArgs p) {
                 const float4 w = *reinterpret_cast<const float4*>(W0s + k * H + c0);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const float a = xs[(rg + 16 * i) * MAX_IN + k];
+                    const float a = xs[(rg + RG * i) * MAX_IN + k];
                     acc[i][0] = fmaf(a, w.x, acc[i][0]);
                     acc[i][1] = fmaf(a, w.y, acc[i][1]);
                     acc[i][2] = fmaf(a, w.z, acc[i][2]);
@@ -170,7 +290,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_train_kernel(TrainArgs p) {
             }
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-                *reinterpret_cast<float4*>(S0 + (rg + 16 * i) * PITCH + c0) =
+                *reinterpret_cast<float4*>(S0 + (rg + RG * i) * PITCH + c0) =
                     make_float4(act_fwd(acc[i][0], act), act_fwd(acc[i][1], act), act_fwd(acc[i][2], act),
                                 act_fwd(acc[i][3], act));
         }
@@ -178,7 +298,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_train_kernel(TrainArgs p) {
         // h1 = act(h0 W1 + b1)
         {
             const float init[4] = {b1s[c0], b1s[c0 + 1], b1s[c0 + 2], b1s[c0 + 3]};
-            tile_gemm64(S0, W1s, rg, c0, init, [&](int r, int c, const float (&v)[4]) {
+            tile_gemm64<RG>(S0, W1s, rg, c0, init, [&](int r, int c, const float (&v)[4]) {
                 *reinterpret_cast<float4*>(S1 + r * PITCH + c) =
                     make_float4(act_fwd(v[0], act), act_fwd(v[1], act), act_fwd(v[2], act), act_fwd(v[3], act));
             });
@@ -191,153 +311,180 @@ __global__ void __launch_bounds__(THREADS, 1) fused_train_kernel(TrainArgs p) {
 #pragma unroll
             for (int o = 0; o < 2 * MAX_OUT; ++o) dout[o] = 0.0f;
             if (row < p.B) {
-                float out[2 * MAX_OUT];
+                float out[MAX_OUT];
 #pragma unroll
                 for (int o = 0; o < MAX_OUT; ++o) out[o] = b2s[o];
-                for (int k = 0; k < H; ++k) {
-                    const float hv = S1[r * PITCH + k];
-                    const float4 w = *reinterpret_cast<const float4*>(W2s + k * MAX_OUT);
-                    out[0] = fmaf(hv, w.x, out[0]);
-                    out[1] = fmaf(hv, w.y, out[1]);
-                    out[2] = fmaf(hv, w.z, out[2]);
-                    out[3] = fmaf(hv, w.w, out[3]);
+#pragma unroll 4
+                for (int k = 0; k < H; k += 4) {
+                    const float4 hv = *reinterpret_cast<const float4*>(S1 + r * PITCH + k);
+                    const float h4[4] = {hv.x, hv.y, hv.z, hv.w};
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const float4 w = *reinterpret_cast<const float4*>(W2s + (k + kk) * MAX_OUT);
+                        out[0] = fmaf(h4[kk], w.x, out[0]);
+                        out[1] = fmaf(h4[kk], w.y, out[1]);
+                        out[2] = fmaf(h4[kk], w.z, out[2]);
+                        out[3] = fmaf(h4[kk], w.w, out[3]);
+                    }
                 }
                 const float bdiv = (float)p.B;
-                if (p.mode == ACTOR_DISCRETE) {
+                if (MODE == ACTOR_DISCRETE) {
                     float klv;
-                    actor_grad_one(out, O, p.old_lp[row], p.adv[row], (int)p.actions[row], p.clip_eps, p.entropy_coef,
-                                   bdiv, dout, klv);
+                    const float l4[MAX_OUT] = {out[0], out[1], out[2], out[3]};
+                    actor_grad_small(l4, O, in_old_lp, in_adv, (int)in_act[0], p.clip_eps, p.entropy_coef, bdiv, dout,
+                                     klv);
                     kl_acc += (double)klv;
-                } else if (p.mode == ACTOR_GAUSSIAN) {
-                    float row_out[2 * MAX_OUT], a[MAX_OUT], klv;
-                    for (int o = 0; o < O; ++o) {
-                        row_out[o] = out[o];
-                        row_out[O + o] = lss[o];
-                        a[o] = p.actions[(size_t)row * O + o];
-                    }
-                    continuous_actor_grad_one(row_out, O, p.old_lp[row], p.adv[row], a, p.clip_eps, p.entropy_coef,
-                                              bdiv, dout, klv);
+                } else if (MODE == ACTOR_GAUSSIAN) {
+                    float klv;
+                    const float m4[MAX_OUT] = {out[0], out[1], out[2], out[3]};
+                    gauss_grad_small(m4, lss, in_act, O, in_old_lp, in_adv, p.clip_eps, p.entropy_coef, bdiv, dout, klv);
                     kl_acc += (double)klv;
-                } else if (p.mode == CRITIC_DISCRETE) {
-                    dout[0] = critic_grad_one(out[0], p.old_v ? p.old_v[row] : 0.0f, p.ret[row], p.value_loss_coef,
-                                              p.clip_eps, p.clip_value, bdiv);
+                } else if (MODE == CRITIC_DISCRETE) {
+                    dout[0] = critic_grad_one(out[0], in_old_v, in_ret, p.value_loss_coef, p.clip_eps, p.clip_value, bdiv);
                 } else {
-                    dout[0] = continuous_critic_grad_one(out[0], p.old_v ? p.old_v[row] : 0.0f, p.ret[row], p.clip_eps,
-                                                         p.clip_value, bdiv);
+                    dout[0] = continuous_critic_grad_one(out[0], in_old_v, in_ret, p.clip_eps, p.clip_value, bdiv);
                 }
             }
 #pragma unroll
-            for (int o = 0; o < 2 * MAX_OUT; ++o) douts[r * 2 * MAX_OUT + o] = dout[o];
+            for (int o = 0; o < 2 * MAX_OUT; ++o) {
+                douts[r * 2 * MAX_OUT + o] = dout[o];
+                dheadp[o] += dout[o];
+            }
         }
         __syncthreads();
-        // g1 = (dout W2^T) * act'(h1); head gradients
+        // g1 = (dout W2^T) * act'(h1) -> G1; this thread's share of db1 and dW2 (= h1^T dout) on the way
         {
+            float w2r[4][MAX_OUT];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 w = *reinterpret_cast<const float4*>(W2s + (c0 + j) * MAX_OUT);
+                w2r[j][0] = w.x; w2r[j][1] = w.y; w2r[j][2] = w.z; w2r[j][3] = w.w;
+            }
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const int r = rg + 16 * i;
+                const int r = rg + RG * i;
                 const float4 y = *reinterpret_cast<const float4*>(S1 + r * PITCH + c0);
-                const float yv[4] = {y.x, y.y, y.z, y.w};
+                const float4 d4 = *reinterpret_cast<const float4*>(douts + r * 2 * MAX_OUT);
+                const float yv[4] = {y.x, y.y, y.z, y.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
                 float g[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     float acc = 0.0f;
-                    for (int o = 0; o < O; ++o) acc = fmaf(douts[r * 2 * MAX_OUT + o], W2s[(c0 + j) * MAX_OUT + o], acc);
+#pragma unroll
+                    for (int o = 0; o < MAX_OUT; ++o)
+                        if (o < O) acc = fmaf(dv[o], w2r[j][o], acc);
                     g[j] = act_bwd(acc, yv[j], act);
+                    db1p[j] += g[j];
+#pragma unroll
+                    for (int o = 0; o < MAX_OUT; ++o) dW2p[j][o] = fmaf(yv[j], dv[o], dW2p[j][o]);
                 }
                 *reinterpret_cast<float4*>(G1 + r * PITCH + c0) = make_float4(g[0], g[1], g[2], g[3]);
             }
-            // dW2[k][o] += sum_r h1[r][k] dout[r][o]
-            {
-                const int k = tid >> 2, o = tid & 3;
-                float acc = 0.0f;
-                if (o < O)
-                    for (int r = 0; r < TM; ++r) acc = fmaf(S1[r * PITCH + k], douts[r * 2 * MAX_OUT + o], acc);
-                dW2 += (double)acc;
-            }
-            if (tid < MAX_OUT && tid < O) {
-                float acc = 0.0f, accl = 0.0f;
-                for (int r = 0; r < TM; ++r) {
-                    acc += douts[r * 2 * MAX_OUT + tid];
-                    if (gaussian) accl += douts[r * 2 * MAX_OUT + O + tid];
-                }
-                db2 += (double)acc;
-                dls += (double)accl;
-            }
         }
         __syncthreads();
-        // dW1 += h0^T g1, db1 += sum g1
+        // dW1 += h0^T g1
         {
-            float acc[4][4];
+            float acc[WI][4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < WI; ++i)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
 #pragma unroll 4
             for (int r = 0; r < TM; ++r) {
-                const float4 a = *reinterpret_cast<const float4*>(S0 + r * PITCH + wi0);
-                const float4 b = *reinterpret_cast<const float4*>(G1 + r * PITCH + wj0);
-                const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+                float av[WI];
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
+                for (int q = 0; q < WI / 4; ++q) {
+                    const float4 a = *reinterpret_cast<const float4*>(S0 + r * PITCH + wi0 + 4 * q);
+                    av[4 * q] = a.x; av[4 * q + 1] = a.y; av[4 * q + 2] = a.z; av[4 * q + 3] = a.w;
+                }
+                const float4 b = *reinterpret_cast<const float4*>(G1 + r * PITCH + wj0);
+                const float bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int i = 0; i < WI; ++i)
 #pragma unroll
                     for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
             }
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < WI; ++i)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) dW1[i][j] += (double)acc[i][j];
-            if (tid < H) {
-                float s = 0.0f;
-                for (int r = 0; r < TM; ++r) s += G1[r * PITCH + tid];
-                db1 += (double)s;
-            }
         }
-        // g0 = (g1 W1^T) * act'(h0), written over h1 (no longer needed: the head gradients above are done
-        // before the barrier that precedes this block)
+        // g0 = (g1 W1^T) * act'(h0), consumed from registers: this thread's share of db0 and dW0 (= x^T g0)
         {
             const float init[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            tile_gemm64(G1, W1t, rg, c0, init, [&](int r, int c, const float (&v)[4]) {
+            tile_gemm64<RG>(G1, W1t, rg, c0, init, [&](int r, int c, const float (&v)[4]) {
                 const float4 y = *reinterpret_cast<const float4*>(S0 + r * PITCH + c);
-                *reinterpret_cast<float4*>(S1 + r * PITCH + c) =
-                    make_float4(act_bwd(v[0], y.x, act), act_bwd(v[1], y.y, act), act_bwd(v[2], y.z, act),
-                                act_bwd(v[3], y.w, act));
+                const float g[4] = {act_bwd(v[0], y.x, act), act_bwd(v[1], y.y, act), act_bwd(v[2], y.z, act),
+                                    act_bwd(v[3], y.w, act)};
+                const float4 xa = *reinterpret_cast<const float4*>(xs + r * MAX_IN);
+                const float4 xb = *reinterpret_cast<const float4*>(xs + r * MAX_IN + 4);
+                const float xv[MAX_IN] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    db0p[j] += g[j];
+#pragma unroll
+                    for (int k = 0; k < MAX_IN; ++k) dW0p[k][j] = fmaf(xv[k], g[j], dW0p[k][j]);
+                }
             });
-        }
-        __syncthreads();
-        // dW0 += x^T g0, db0 += sum g0
-        {
-            for (int e = tid, slot = 0; e < I * H; e += THREADS, ++slot) {
-                const int k = e / H, i = e % H;
-                float acc = 0.0f;
-                for (int r = 0; r < TM; ++r) acc = fmaf(xs[r * MAX_IN + k], S1[r * PITCH + i], acc);
-                if (slot == 0) dW0a += (double)acc; else dW0b += (double)acc;
-            }
-            if (tid < H) {
-                float s = 0.0f;
-                for (int r = 0; r < TM; ++r) s += S1[r * PITCH + tid];
-                db0 += (double)s;
-            }
         }
         __syncthreads();
     }
 
-    // per-block partial sums, parameter order: W0 b0 W1 b1 W2 b2 [log_std], then the KL sum
+    // ---- per-block sums -> partial[blockIdx], parameter order: W0 b0 W1 b1 W2 b2 [log_std], then the KL sum
     double* out = p.partial + (size_t)blockIdx.x * p.pstride;
     const int oW0 = 0, ob0 = I * H, oW1 = ob0 + H, ob1 = oW1 + H * H, oW2 = ob1 + H, ob2 = oW2 + H * O, ols = ob2 + O;
-    if (tid < I * H) out[oW0 + tid] = dW0a;
-    if (tid + THREADS < I * H) out[oW0 + tid + THREADS] = dW0b;
-    if (tid < H) { out[ob0 + tid] = db0; out[ob1 + tid] = db1; }
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < WI; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) out[oW1 + (wi0 + i) * H + wj0 + j] = dW1[i][j];
-    {
-        const int k = tid >> 2, o = tid & 3;
-        if (o < O) out[oW2 + k * O + o] = dW2;
+    // The per-thread shares go through shared memory (the activation buffers are free now) and are added
+    // over the row groups in ascending order.
+    float* scr = S0;                                    // needs RG * (64 + 64 + 256 + 512) + TM * 8 floats
+    float* s_db1 = scr;                                 // [16][64]
+    float* s_db0 = s_db1 + RG * H;                      // [16][64]
+    float* s_dW2 = s_db0 + RG * H;                      // [16][64][MAX_OUT]
+    float* s_dW0 = s_dW2 + RG * H * MAX_OUT;            // [16][MAX_IN][64]
+    float* s_head = s_dW0 + RG * MAX_IN * H;            // [TM][2 * MAX_OUT]
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        s_db1[rg * H + c0 + j] = db1p[j];
+        s_db0[rg * H + c0 + j] = db0p[j];
+#pragma unroll
+        for (int o = 0; o < MAX_OUT; ++o) s_dW2[(rg * H + c0 + j) * MAX_OUT + o] = dW2p[j][o];
+#pragma unroll
+        for (int k = 0; k < MAX_IN; ++k) s_dW0[(rg * MAX_IN + k) * H + c0 + j] = dW0p[k][j];
     }
-    if (tid < O) {
-        out[ob2 + tid] = db2;
-        if (gaussian) out[ols + tid] = dls;
+    if (tid < TM) {
+#pragma unroll
+        for (int o = 0; o < 2 * MAX_OUT; ++o) s_head[tid * 2 * MAX_OUT + o] = dheadp[o];
+    }
+    __syncthreads();
+    if (tid < H) {
+        double a1 = 0.0, a0 = 0.0;
+        for (int g = 0; g < RG; ++g) { a1 += (double)s_db1[g * H + tid]; a0 += (double)s_db0[g * H + tid]; }
+        out[ob1 + tid] = a1;
+        out[ob0 + tid] = a0;
+    }
+    for (int e = tid; e < H * MAX_OUT; e += THREADS) {   // dW2[k][o]
+        const int k = e >> 2, o = e & 3;
+        if (o < O) {
+            double a = 0.0;
+            for (int g = 0; g < RG; ++g) a += (double)s_dW2[(g * H + k) * MAX_OUT + o];
+            out[oW2 + k * O + o] = a;
+        }
+    }
+    for (int e = tid; e < I * H; e += THREADS) {         // dW0[k][i]
+        const int k = e / H, i = e % H;
+        double a = 0.0;
+        for (int g = 0; g < RG; ++g) a += (double)s_dW0[(g * MAX_IN + k) * H + i];
+        out[oW0 + e] = a;
+    }
+    if (tid < 2 * MAX_OUT) {
+        const int o = tid;
+        double a = 0.0;
+        for (int r = 0; r < TM; ++r) a += (double)s_head[r * 2 * MAX_OUT + o];
+        if (o < O) out[ob2 + o] = a;
+        else if (gaussian && o < 2 * O) out[ols + (o - O)] = a;
     }
     kl_acc = block_sum(kl_acc, kl_sm);
     if (tid == 0) out[p.pstride - 1] = kl_acc;
@@ -622,8 +769,10 @@ int rollout(int env_kind, const mrl_net_spec* actor, const float* actor_params, 
     return MRL_OK;
 }
 
+constexpr int TM = TRAIN_TM;
 constexpr int SMEM_FLOATS = 2 * H * H + 3 * TM * PITCH + MAX_IN * H + 2 * H + H * MAX_OUT + 2 * MAX_OUT + TM * MAX_IN +
                             TM * 2 * MAX_OUT;
+static_assert(3 * TM * PITCH >= (TRAIN_THREADS / 16) * (64 + 64 + 256 + 512) + TM * 8, "end-of-kernel scratch");
 constexpr int SMEM_BYTES = SMEM_FLOATS * 4;
 
 bool supported(const mrl_net_spec* net) {
@@ -640,7 +789,8 @@ int grid_blocks(int batch) {
         if (sms <= 0) sms = 148;
     }
     int tiles = (batch + TM - 1) / TM;
-    return tiles < sms ? tiles : sms;
+    int blocks = sms * (256 / TRAIN_THREADS);
+    return tiles < blocks ? tiles : blocks;
 }
 
 int64_t partial_doubles(const mrl_net_spec* net, int batch, int param_size) {
@@ -654,9 +804,17 @@ int train_step(const mrl_net_spec* net, int mode, const float* params, int param
                const float* actions, const float* adv, const float* ret, const float* old_lp, const float* old_v,
                int batch, float clip_eps, float entropy_coef, float value_loss_coef, int clip_value, double* partial,
                float* grads, float* kl_out, cudaStream_t st) {
+    using KernelFn = void (*)(TrainArgs);
+    static const KernelFn table[4][2] = {
+        {fused_train_kernel<TRAIN_THREADS, 0, 0>, fused_train_kernel<TRAIN_THREADS, 0, 1>},
+        {fused_train_kernel<TRAIN_THREADS, 1, 0>, fused_train_kernel<TRAIN_THREADS, 1, 1>},
+        {fused_train_kernel<TRAIN_THREADS, 2, 0>, fused_train_kernel<TRAIN_THREADS, 2, 1>},
+        {fused_train_kernel<TRAIN_THREADS, 3, 0>, fused_train_kernel<TRAIN_THREADS, 3, 1>}};
     static bool attr_done = false;
     if (!attr_done) {
-        MRL_CUDA_OK(cudaFuncSetAttribute(fused_train_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        for (int m = 0; m < 4; ++m)
+            for (int q = 0; q < 2; ++q)
+                MRL_CUDA_OK(cudaFuncSetAttribute(table[m][q], cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         attr_done = true;
     }
     TrainArgs a{};
@@ -669,7 +827,7 @@ int train_step(const mrl_net_spec* net, int mode, const float* params, int param
     a.partial = partial;
     a.pstride = param_size + 1;
     const int grid = grid_blocks(batch);
-    MRL_LAUNCH(fused_train_kernel, grid, THREADS, SMEM_BYTES, st, a);
+    MRL_LAUNCH(table[mode][a.act], grid, TRAIN_THREADS, SMEM_BYTES, st, a);
     MRL_LAUNCH(reduce_partials_kernel, ceil_div(param_size + 1, 128), 128, 0, st, partial, grid, a.pstride, param_size,
                grads, kl_out);
     return MRL_OK;
