@@ -37,8 +37,16 @@ struct K1Params {
     const float* bias;              // mode 1: b1
     const float* W2; const float* b2; int out_dim; bf16* h1; float* head_out; int head_ld;
     const bf16* h0; bf16* g0;       // mode 2: mask source and masked output
+    int act;                        // modes 1, 2: 0 ReLU, 1 tanh (derivative 1 - y^2 from the stored bf16 y)
     int* err;
 };
+
+// Hardware tanh (MUFU, ~2^-11 relative error): the result is rounded to bf16 (2^-9) right away.
+__device__ __forceinline__ float tanh_fast(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 __device__ __forceinline__ void drain_on_error(const int* err) {
     if (*(volatile const int*)err != 0)
@@ -176,7 +184,9 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
                             int j = ch * 32 + i;
-                            float h_lo = fmaxf(v[i] + sP[j], 0.0f), h_hi = fmaxf(v[i + 1] + sP[j + 1], 0.0f);
+                            float h_lo = v[i] + sP[j], h_hi = v[i + 1] + sP[j + 1];
+                            if (p.act == 0) { h_lo = fmaxf(h_lo, 0.0f); h_hi = fmaxf(h_hi, 0.0f); }
+                            else { h_lo = tanh_fast(h_lo); h_hi = tanh_fast(h_hi); }
 #pragma unroll
                             for (int a = 0; a < OUT; ++a) {
                                 o[a] = fmaf(h_lo, sP[H + j * OUT + a], o[a]);
@@ -191,9 +201,18 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                         for (int i = 0; i < 32; i += 2) {
                             uint32_t w = hw[i >> 1];
                             // bf16 > 0  <=>  sign bit clear and magnitude non-zero
-                            bool lo_pos = (w & 0x8000u) == 0 && (w & 0x7FFFu) != 0;
-                            bool hi_pos = (w & 0x80000000u) == 0 && (w & 0x7FFF0000u) != 0;
-                            __nv_bfloat162 pk = __floats2bfloat162_rn(lo_pos ? v[i] : 0.0f, hi_pos ? v[i + 1] : 0.0f);
+                            float g_lo, g_hi;
+                            if (p.act == 0) {
+                                bool lo_pos = (w & 0x8000u) == 0 && (w & 0x7FFFu) != 0;
+                                bool hi_pos = (w & 0x80000000u) == 0 && (w & 0x7FFF0000u) != 0;
+                                g_lo = lo_pos ? v[i] : 0.0f;
+                                g_hi = hi_pos ? v[i + 1] : 0.0f;
+                            } else {
+                                const float y_lo = __uint_as_float(w << 16), y_hi = __uint_as_float(w & 0xFFFF0000u);
+                                g_lo = v[i] * (1.0f - y_lo * y_lo);
+                                g_hi = v[i + 1] * (1.0f - y_hi * y_hi);
+                            }
+                            __nv_bfloat162 pk = __floats2bfloat162_rn(g_lo, g_hi);
                             packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
                         }
                     }
@@ -408,11 +427,11 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// First layer (LinearReLU[obs, 256], K = obs_dim): h0 = relu(x . W0 + b0) in bf16, row-major.
+// First layer (LinearReLU / LinearTanh[obs, 256], K = obs_dim): h0 = act(x . W0 + b0) in bf16, row-major.
 template <int IN>
 __global__ void __launch_bounds__(H)
 l0_forward_kernel(const float* __restrict__ x, const float* __restrict__ W0, const float* __restrict__ b0,
-                  bf16* __restrict__ h0, int M, int rows_per_block) {
+                  bf16* __restrict__ h0, int M, int rows_per_block, int act) {
     const VecMap vm;
     float w[IN][8], b[8];
 #pragma unroll
@@ -437,21 +456,21 @@ l0_forward_kernel(const float* __restrict__ x, const float* __restrict__ W0, con
             float acc = b[u];
 #pragma unroll
             for (int k = 0; k < IN; ++k) acc = fmaf(xr[k], w[k][u], acc);
-            hv[u] = fmaxf(acc, 0.0f);
+            hv[u] = act == 0 ? fmaxf(acc, 0.0f) : tanh_fast(acc);
         }
         *reinterpret_cast<uint4*>(h0 + (size_t)r * H + vm.col0) = pack8(hv);
     }
 }
 
 // Head backward and everything that reduces over rows next to it:
-//   g1[r][j]  = h1[r][j] > 0 ? sum_a dout[r][a] * W2[j][a] : 0      (dX of the head, ReLU mask of layer 1)
+//   g1[r][j]  = act'(h1[r][j]) * sum_a dout[r][a] * W2[j][a]        (dX of the head; ReLU mask or 1 - h1^2)
 //   dW2[j][a] = sum_r h1[r][j] * dout[r][a],  db2[a] = sum_r dout[r][a],  db1[j] = sum_r g1[r][j]
 // part layout per block: [OUT][256] dW2^T, [256] db1, [OUT] db2.
 template <int OUT>
 __global__ void __launch_bounds__(H)
 head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout, int ldd,
                      const float* __restrict__ W2, int out_dim, bf16* __restrict__ g1,
-                     float* __restrict__ part, int M, int rows_per_block) {
+                     float* __restrict__ part, int M, int rows_per_block, int act) {
     const VecMap vm;
     float w2[OUT][8], dw2[OUT][8], db1[8], db2[OUT];
 #pragma unroll
@@ -500,7 +519,7 @@ head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout
                     dh = fmaf(d[a], w2[a][u], dh);
                     dw2[a][u] = fmaf(h[u], d[a], dw2[a][u]);
                 }
-                g[u] = h[u] > 0.0f ? dh : 0.0f;
+                g[u] = act == 0 ? (h[u] > 0.0f ? dh : 0.0f) : dh * (1.0f - h[u] * h[u]);
                 db1[u] += g[u];
             }
             *reinterpret_cast<uint4*>(g1 + (size_t)r * H + vm.col0) = pack8(g);
@@ -758,8 +777,8 @@ static int launch_k2(const CUtensorMap& tmA, const CUtensorMap& tmB, int Ktot, f
 int max_splits() { return sm_count(); }
 
 bool supported(const mrl_net_spec* net, int batch) {
-    return net->hidden_dim == H && net->activation == MRL_ACT_RELU && net->head == MRL_HEAD_LINEAR &&
-           net->out_dim <= 8 && (net->in_dim == 4 || net->in_dim == 8 || net->in_dim == 24) && batch % 32 == 0;
+    return net->hidden_dim == H && (net->activation == MRL_ACT_RELU || net->activation == MRL_ACT_TANH) &&
+           (net->head == MRL_HEAD_LINEAR || net->head == MRL_HEAD_STOCHASTIC_ACTOR) && net->out_dim <= 8 && (net->in_dim == 4 || net->in_dim == 8 || net->in_dim == 24) && batch % 32 == 0;
 }
 
 int64_t workspace_bytes(int batch) {
@@ -790,11 +809,30 @@ int State::init(void* workspace, int batch_, int* err_flag) {
     return MRL_OK;
 }
 
+__global__ void fill_log_std_cols_kernel(const float* __restrict__ log_std, float* __restrict__ out, int batch, int A) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= batch * A) return;
+    int r = i / A, j = i % A;
+    float ls = log_std[j];
+    if (ls < -5.0f) ls = -5.0f;
+    else if (ls > 2.0f) ls = 2.0f;
+    out[(size_t)r * 2 * A + A + j] = ls;
+}
+// One block per action dimension: column sum of dout[:, A + j] in double.
+__global__ void log_std_grad_kernel(const float* __restrict__ dout, int ldd, int A, int batch, float* __restrict__ out) {
+    __shared__ double sm[32];
+    const int j = blockIdx.x;
+    double acc = 0.0;
+    for (int r = threadIdx.x; r < batch; r += blockDim.x) acc += (double)dout[(size_t)r * ldd + A + j];
+    acc = block_sum(acc, sm);
+    if (threadIdx.x == 0) out[j] = (float)acc;
+}
+
 template <int IN>
-static int l0_forward(const float* x, const float* W0, const float* b0, bf16* h0, int M, cudaStream_t st) {
+static int l0_forward(const float* x, const float* W0, const float* b0, bf16* h0, int M, int act, cudaStream_t st) {
     const int rows_per_block = slab_rows(M, IN);
     MRL_LAUNCH((l0_forward_kernel<IN>), (M + rows_per_block - 1) / rows_per_block, H, rows_per_block * IN * 4, st, x,
-               W0, b0, h0, M, rows_per_block);
+               W0, b0, h0, M, rows_per_block, act);
     return MRL_OK;
 }
 
@@ -807,15 +845,23 @@ int State::forward(const mrl_net_spec* net, const float* params, const float* x,
     MRL_LAUNCH(convert_w1_kernel, dim3(H / 32, H / 32), dim3(32, 8), 0, st, W1, w1, w1t);
     prof_mark("convert_w1", st);
     int rc;
-    if (I == 4) rc = l0_forward<4>(x, W0, b0, h0, batch, st);
-    else if (I == 8) rc = l0_forward<8>(x, W0, b0, h0, batch, st);
-    else rc = l0_forward<24>(x, W0, b0, h0, batch, st);
+    const int act = net->activation == MRL_ACT_RELU ? 0 : 1;
+    const bool gaussian = net->head == MRL_HEAD_STOCHASTIC_ACTOR;
+    if (I == 4) rc = l0_forward<4>(x, W0, b0, h0, batch, act, st);
+    else if (I == 8) rc = l0_forward<8>(x, W0, b0, h0, batch, act, st);
+    else rc = l0_forward<24>(x, W0, b0, h0, batch, act, st);
     if (rc) return rc;
     prof_mark("l0_forward", st);
     K1Params p{};
-    p.M = batch; p.bias = b1; p.W2 = W2; p.b2 = b2; p.out_dim = O; p.h1 = h1; p.head_out = head_out; p.head_ld = O;
+    p.M = batch; p.bias = b1; p.W2 = W2; p.b2 = b2; p.out_dim = O; p.h1 = h1; p.head_out = head_out;
+    p.head_ld = gaussian ? 2 * O : O;
+    p.act = act;
     p.err = err;
     rc = launch_k1_forward(tm_h0, tm_w1t, p, st);
+    if (rc) return rc;
+    if (gaussian) {  // columns O..2O-1 carry the clamped state-independent log_std (stochastic_actor.mojo:386-575)
+        MRL_LAUNCH(fill_log_std_cols_kernel, ceil_div((int64_t)batch * O, 256), 256, 0, st, b2 + O, head_out, batch, O);
+    }
     prof_mark("k1_forward_gemm", st);
     return rc;
 }
@@ -826,21 +872,27 @@ int State::backward(const mrl_net_spec* net, const float* params, const float* x
     const size_t oW0 = 0, ob0 = (size_t)I * H, oW1 = ob0 + H, ob1 = oW1 + (size_t)H * H, oW2 = ob1 + H,
                  ob2 = oW2 + (size_t)H * O;
     const float* W2 = params + oW2;
+    const int act = net->activation == MRL_ACT_RELU ? 0 : 1;
+    const bool gaussian = net->head == MRL_HEAD_STOCHASTIC_ACTOR;
+    const int ldd = gaussian ? 2 * O : O;   // columns O..2O-1 of a Gaussian head's gradient belong to log_std
     const int rows_per_block = slab_rows(batch, I > 8 ? I : 8);
     const int nblocks = (batch + rows_per_block - 1) / rows_per_block;
     const int OUT = O <= 1 ? 1 : (O <= 2 ? 2 : (O <= 4 ? 4 : 8));
-    if (OUT == 1) { MRL_LAUNCH((head_backward_kernel<1>), nblocks, H, rows_per_block * 1 * 4, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
-    else if (OUT == 2) { MRL_LAUNCH((head_backward_kernel<2>), nblocks, H, rows_per_block * 2 * 4, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
-    else if (OUT == 4) { MRL_LAUNCH((head_backward_kernel<4>), nblocks, H, rows_per_block * 4 * 4, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
-    else { MRL_LAUNCH((head_backward_kernel<8>), nblocks, H, rows_per_block * 8 * 4, st, h1, dout, O, W2, O, g1, part, batch, rows_per_block); }
+    if (OUT == 1) { MRL_LAUNCH((head_backward_kernel<1>), nblocks, H, rows_per_block * 1 * 4, st, h1, dout, ldd, W2, O, g1, part, batch, rows_per_block, act); }
+    else if (OUT == 2) { MRL_LAUNCH((head_backward_kernel<2>), nblocks, H, rows_per_block * 2 * 4, st, h1, dout, ldd, W2, O, g1, part, batch, rows_per_block, act); }
+    else if (OUT == 4) { MRL_LAUNCH((head_backward_kernel<4>), nblocks, H, rows_per_block * 4 * 4, st, h1, dout, ldd, W2, O, g1, part, batch, rows_per_block, act); }
+    else { MRL_LAUNCH((head_backward_kernel<8>), nblocks, H, rows_per_block * 8 * 4, st, h1, dout, ldd, W2, O, g1, part, batch, rows_per_block, act); }
     prof_mark("head_backward", st);
     const int hstride = (OUT + 1) * H + OUT;
     MRL_LAUNCH(reduce_head_parts_kernel, ceil_div(hstride, 32), 256, 0, st, part, nblocks, OUT, O, grads + oW2,
                grads + ob2, grads + ob1);
+    if (gaussian) {  // dlog_std[j] = sum over rows of dout[:, O + j] (stochastic_actor.mojo:727-966)
+        MRL_LAUNCH(log_std_grad_kernel, O, 256, 0, st, dout, ldd, O, batch, grads + ob2 + O);
+    }
     prof_mark("reduce_head", st);
-    // dh0 = g1 . W1^T, masked by h0 > 0 -> g0
+    // dh0 = g1 . W1^T times the activation derivative at h0 -> g0
     K1Params p{};
-    p.M = batch; p.h0 = h0; p.g0 = g0; p.err = err;
+    p.M = batch; p.h0 = h0; p.g0 = g0; p.act = act; p.err = err;
     int rc = launch_k1<2, 1>(tm_g1, tm_w1, p, st);
     if (rc) return rc;
     prof_mark("k1_dx_gemm", st);

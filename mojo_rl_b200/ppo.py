@@ -170,6 +170,46 @@ class DeepPPOAgent:
             L.mrl_destroy(h)
         return metrics
 
+    def evaluate_gpu(self, EnvType, ctx=None, num_episodes=100, max_steps=1000, verbose=False, stochastic=True):
+        """evaluate_gpu[EnvType](ctx, num_episodes, max_steps, verbose, stochastic) -> mean episode reward
+        (ppo.mojo:2846 ff., ppo_continuous.mojo:703-976).  The policy runs on n_envs parallel environments for
+        at most max_steps steps; stochastic=False takes the arg-max action (the mean for a Gaussian policy).
+        Uses the fused rollout phase, so episodes are counted once per chunk of rollout_len steps and the
+        per-step seeds are those of a training rollout rather than evaluate_gpu's UInt64(step)."""
+        L = _lib.lib()
+        saved = self.ROLLOUT
+        self.ROLLOUT = max(1, min(saved, max_steps))
+        try:
+            cfg = self.make_config(EnvType.KIND, deterministic=not stochastic)
+            cfg.minibatch_size = min(cfg.minibatch_size, cfg.n_envs * cfg.rollout_len)
+            cfg.precision = 0 if cfg.minibatch_size % 128 else cfg.precision
+            h = ctypes.c_void_p()
+            _lib.check(L.mrl_create(ctypes.byref(h), ctypes.byref(cfg)))
+        finally:
+            self.ROLLOUT = saved
+        try:
+            for which, net in ((0, self.actor), (1, self.critic)):
+                _lib.check(L.mrl_set_params(h, which, _lib.ptr(net.params), None))
+            _lib.check(L.mrl_ppo_reset(h, 0))
+            cap = 1 << 16
+            rets, lens = np.empty(cap, np.float32), np.empty(cap, np.float32)
+            rewards, steps = [], 0
+            while len(rewards) < num_episodes and steps < max_steps:
+                _lib.check(L.mrl_ppo_rollout(h))
+                steps += cfg.rollout_len
+                n = _lib.check(L.mrl_drain_episodes(h, _lib.ptr(rets), _lib.ptr(lens), cap))
+                rewards.extend(float(r) for r in rets[:n])
+                if verbose:
+                    print(f"  eval: {steps} steps, {len(rewards)} episodes")
+            rewards = rewards[:num_episodes]
+            if not rewards:
+                if verbose:
+                    print("Warning: No episodes completed!")
+                return 0.0
+            return float(np.mean(rewards))
+        finally:
+            L.mrl_destroy(h)
+
     # -- text checkpoints, ppo.mojo:3926-4055 ----------------------------------
     def save_checkpoint(self, filepath):
         lines = ["# mojo-rl checkpoint v1", "# type: ppo_agent",

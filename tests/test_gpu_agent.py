@@ -152,3 +152,18 @@ def test_continuous_agent_trains_on_pendulum():
     assert np.isfinite(agent.actor.params).all() and not np.array_equal(before, agent.actor.params)
     assert -5.0 <= agent.actor.params[-1] <= 2.0
     assert -1800.0 < m.mean_reward() < -600.0              # a near-random policy on Pendulum
+
+
+def test_evaluate_gpu_counts_episodes_and_is_repeatable():
+    from mojo_rl_b200 import CartPoleEnv, DeepPPOAgent, DeepPPOContinuousAgent, PendulumV2
+    agent = DeepPPOAgent(4, 2, hidden_dim=64, rollout_len=64, n_envs=128, gpu_minibatch_size=1024)
+    r1 = agent.evaluate_gpu(CartPoleEnv, None, num_episodes=200, max_steps=640, stochastic=True)
+    assert 8.0 < r1 < 80.0                     # a random-init policy balances for a few dozen steps (reward 1 per step)
+    # greedy evaluation is deterministic (all completed episodes are averaged: the drain order inside a chunk is not)
+    g1 = agent.evaluate_gpu(CartPoleEnv, None, num_episodes=10 ** 6, max_steps=640, stochastic=False)
+    g2 = agent.evaluate_gpu(CartPoleEnv, None, num_episodes=10 ** 6, max_steps=640, stochastic=False)
+    assert abs(g1 - g2) <= 1e-9 * abs(g1) and g1 > 0
+    cont = DeepPPOContinuousAgent(3, 1, hidden_dim=64, rollout_len=200, n_envs=64, gpu_minibatch_size=1280)
+    r = cont.evaluate_gpu(PendulumV2, None, num_episodes=64, max_steps=400, stochastic=False)
+    assert -1900.0 < r < -500.0
+    assert cont.evaluate_gpu(PendulumV2, None, num_episodes=10, max_steps=100) == 0.0   # no episode ends in 100 steps

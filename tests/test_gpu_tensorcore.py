@@ -75,20 +75,24 @@ def test_splitk_gemm_from_row_major_activations(K):
     assert torch.allclose(got, want, rtol=1e-3, atol=1e-4 * scale), float((got - want).abs().max())
 
 
-def test_update_precision1_matches_fp32_gradients():
+@pytest.mark.parametrize("kind,obs,out,act,head", [(2, 8, 4, 0, 0), (3, 24, 4, 1, 1)])
+def test_update_precision1_matches_fp32_gradients(kind, obs, out, act, head):
     """Same rollout, same permutation, one minibatch: the bf16 tensor-core update's
-    gradients agree with the fp32 path to bf16 accuracy, and training state advances."""
+    gradients agree with the fp32 path to bf16 accuracy, and training state advances.
+    LunarLander: ReLU nets, categorical head; BipedalWalker: tanh nets, Gaussian head."""
     from _gpu import GpuAgent
     from _util import NetSpec, default_config, xavier_params
     rng = np.random.default_rng(0)
-    pa = xavier_params(NetSpec(8, 256, 4, 0, 0), rng) * 3
-    pc = xavier_params(NetSpec(8, 256, 1, 0, 0), rng)
+    pa = xavier_params(NetSpec(obs, 256, out, act, head), rng) * (3 if head == 0 else 1)
+    pc = xavier_params(NetSpec(obs, 256, 1, act, 0), rng)
+    if head == 1:
+        pa[-out:] = -0.5
     total = 256 * 32
     perms = rng.permutation(total).astype(np.int32)[None]
     grads = {}
     params = {}
     for prec in (0, 1):
-        cfg = default_config(env_kind=2, n_envs=256, rollout_len=32, hidden_dim=256, minibatch_size=total,
+        cfg = default_config(env_kind=kind, n_envs=256, rollout_len=32, hidden_dim=256, minibatch_size=total,
                              num_epochs=1, target_kl=0.0, precision=prec, max_grad_norm=0.0)
         g = GpuAgent(cfg)
         try:
