@@ -111,6 +111,12 @@ struct mrl_ctx {
     DeviceCounters* counters;
     ncclComm_t comm;
     std::vector<cudaEvent_t> timer_events[3];  // start/stop pairs per phase, resolved by mrl_get_timers
+    // The per-step launch sequence of a rollout is fixed (per-step arguments are compile-time of the
+    // sequence, counters live on the device), so it is captured once into a CUDA graph and replayed.
+    cudaGraphExec_t rollout_graph;
+    long long rollout_graph_launches;
+    int rollout_calls;
+    bool rollout_graph_off;
     unsigned long long ring_tail;  // host: episodes already drained
     unsigned long long update_count;
 };
@@ -418,6 +424,10 @@ extern "C" int mrl_create(mrl_ctx** out, const mrl_config* cfg) {
     c->actor_p = mrl_net_param_size(&c->actor_net);
     c->critic_p = mrl_net_param_size(&c->critic_net);
     c->comm = nullptr;
+    c->rollout_graph = nullptr;
+    c->rollout_graph_launches = 0;
+    c->rollout_calls = 0;
+    c->rollout_graph_off = false;
     c->ring_tail = 0;
     c->update_count = 0;
     if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) {
@@ -488,6 +498,7 @@ extern "C" int mrl_create(mrl_ctx** out, const mrl_config* cfg) {
 extern "C" int mrl_destroy(mrl_ctx* c) {
     if (!c) return MRL_OK;
     cudaStreamSynchronize(c->stream);
+    if (c->rollout_graph) cudaGraphExecDestroy(c->rollout_graph);
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
     for (auto& ev : c->timer_events) for (cudaEvent_t e : ev) cudaEventDestroy(e);
     for (void* p : c->allocs) cudaFree(p);
@@ -574,12 +585,11 @@ extern "C" int mrl_ppo_reset(mrl_ctx* c, uint64_t rng_seed) {
     return MRL_OK;
 }
 
-extern "C" int mrl_ppo_rollout(mrl_ctx* c) {
-    MRL_CHECK_ARG(c);
+// The launches of one rollout: policy (+ sampling + pre-step store) and environment step, T times.
+static int rollout_launches(mrl_ctx* c) {
     const int N = c->cfg.n_envs, T = c->cfg.rollout_len, A = c->num_actions;
     cudaStream_t st = c->stream;
     int rc;
-    PhaseTimer timer(c, 0);
     if (c->use_tc_policy) {
         if ((rc = c->policy.prepare(c->actor_params, c->critic_params, c->obs_dim, st))) return rc;
     }
@@ -622,6 +632,43 @@ extern "C" int mrl_ppo_rollout(mrl_ctx* c) {
         prof_mark("rollout_env_step", st);
     }
     MRL_LAUNCH(add_total_steps_kernel, 1, 1, 0, st, c->counters, (long long)T * N);
+    return MRL_OK;
+}
+
+extern "C" int mrl_ppo_rollout(mrl_ctx* c) {
+    MRL_CHECK_ARG(c);
+    cudaStream_t st = c->stream;
+    PhaseTimer timer(c, 0);
+    c->rollout_calls += 1;
+    // First call: eager (one-time function attributes, tensor maps).  Later calls: one graph launch, unless the
+    // per-kernel profiler wants its events between the launches or the rollout is a single launch anyway.
+    const bool want_graph = c->rollout_calls > 1 && !g_prof_on && !c->rollout_graph_off && !c->use_small_rollout;
+    if (!want_graph) return rollout_launches(c);
+    if (!c->rollout_graph) {
+        const long long before = g_launches.load();
+        cudaGraph_t graph = nullptr;
+        if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+            cudaGetLastError();
+            c->rollout_graph_off = true;
+            return rollout_launches(c);
+        }
+        int rc = rollout_launches(c);
+        cudaError_t e = cudaStreamEndCapture(st, &graph);
+        const long long captured = g_launches.load() - before;
+        g_launches.fetch_sub(captured);   // nothing ran yet; replays are counted below
+        if (rc != MRL_OK || e != cudaSuccess || graph == nullptr ||
+            cudaGraphInstantiate(&c->rollout_graph, graph, 0) != cudaSuccess) {
+            cudaGetLastError();
+            if (graph) cudaGraphDestroy(graph);
+            c->rollout_graph = nullptr;
+            c->rollout_graph_off = true;
+            return rollout_launches(c);
+        }
+        cudaGraphDestroy(graph);
+        c->rollout_graph_launches = captured;
+    }
+    MRL_CUDA_OK(cudaGraphLaunch(c->rollout_graph, st));
+    count_launch((int)c->rollout_graph_launches);
     return MRL_OK;
 }
 

@@ -79,10 +79,9 @@ __device__ __forceinline__ void lidar(const float* __restrict__ s, float hull_x,
     for (int i = 0; i < NUM_LIDAR; ++i) {
         float local_angle = (float)i * 1.5f / (float)(NUM_LIDAR - 1);
         float world_angle = hull_angle - local_angle - 1.5707963267948966f;
-        float sn, cs;
-        mrl_sincosf(world_angle, &sn, &cs);
-        rdx[i] = cs * lidar_range;
-        rdy[i] = sn * lidar_range;
+        const float2 sc = sincos_shared(world_angle);
+        rdx[i] = sc.y * lidar_range;
+        rdy[i] = sc.x * lidar_range;
         xlo = fminf(xlo, hull_x + rdx[i]);
         xhi = fmaxf(xhi, hull_x + rdx[i]);
         out[i] = 1.0f;
@@ -247,11 +246,13 @@ __device__ __forceinline__ void step_row(float* s, const float* __restrict__ act
     prepare_contacts(e.b, c, cp);
     JointPre jpre[MAX_JOINTS];
     prepare_joints<Traits>(e.b, e.jp, jpre);
+#pragma unroll 1
     for (int it = 0; it < VELOCITY_ITERATIONS; ++it) {
         solve_velocity_contacts(e.b, c, cp, (float)FRICTION, (float)RESTITUTION);
         solve_velocity_joints<Traits>(e.b, e.jp, jpre, e.n_joints, dt);
     }
     integrate_positions(e.b, dt);
+#pragma unroll 1
     for (int it = 0; it < POSITION_ITERATIONS; ++it) {
         solve_position_contacts(e.b, c, (float)BAUMGARTE, (float)SLOP);
         solve_position_joints<Traits>(e.b, e.jp, e.n_joints, (float)BAUMGARTE, (float)SLOP);

@@ -156,6 +156,7 @@ __device__ __forceinline__ void step_row(float* s, const float* __restrict__ act
     }
     ctrl_cost = ctrl_cost * (float)CTRL_COST_WEIGHT;
     Contacts<MAX_CONTACTS> c;
+#pragma unroll 1
     for (int sub = 0; sub < FRAME_SKIP; ++sub) {
         float fx[NUM_BODIES], fy[NUM_BODIES], tau[NUM_BODIES];
 #pragma unroll
@@ -171,12 +172,14 @@ __device__ __forceinline__ void step_row(float* s, const float* __restrict__ act
         prepare_contacts(e.b, c, cp);
         JointPre jpre[MAX_JOINTS];
         prepare_joints<Traits>(e.b, e.jp, jpre);
-        for (int it = 0; it < VELOCITY_ITERATIONS; ++it) {
+    #pragma unroll 1
+    for (int it = 0; it < VELOCITY_ITERATIONS; ++it) {
             solve_velocity_contacts(e.b, c, cp, (float)FRICTION, (float)RESTITUTION);
             solve_velocity_joints<Traits>(e.b, e.jp, jpre, e.n_joints, dt);
         }
         integrate_positions(e.b, dt);
-        for (int it = 0; it < POSITION_ITERATIONS; ++it) {
+    #pragma unroll 1
+    for (int it = 0; it < POSITION_ITERATIONS; ++it) {
             solve_position_contacts(e.b, c, (float)BAUMGARTE, (float)SLOP);
             solve_position_joints<Traits>(e.b, e.jp, e.n_joints, (float)BAUMGARTE, (float)SLOP);
         }

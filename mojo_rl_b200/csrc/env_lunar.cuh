@@ -129,8 +129,8 @@ __device__ __forceinline__ void apply_engines(Env& e, int env, int action) {
     rng.step_uniform(r);
     float dispersion_x = (r[0] * 2.0f - 1.0f) / (float)SCALE;
     float dispersion_y = (r[1] * 2.0f - 1.0f) / (float)SCALE;
-    float tip_x, tip_y;
-    mrl_sincosf(e.b.a[0], &tip_x, &tip_y);
+    const float2 tip = sincos_shared(e.b.a[0]);
+    const float tip_x = tip.x, tip_y = tip.y;
     float side_x = -tip_y, side_y = tip_x;
     float dvx = 0.0f, dvy = 0.0f, domega = 0.0f;
     const float main_y_offset = (float)MAIN_ENGINE_Y_OFFSET, side_away = (float)SIDE_ENGINE_AWAY;
@@ -227,11 +227,13 @@ __device__ __forceinline__ void physics_step(Env& e, const Edges& edges, Contact
     prepare_contacts(e.b, c, cp);
     JointPre jpre[MAX_JOINTS];
     prepare_joints<Traits>(e.b, e.jp, jpre);
+#pragma unroll 1
     for (int it = 0; it < VELOCITY_ITERATIONS; ++it) {
         solve_velocity_contacts(e.b, c, cp, (float)FRICTION, (float)RESTITUTION);
         solve_velocity_joints<Traits>(e.b, e.jp, jpre, e.n_joints, dt);
     }
     integrate_positions(e.b, dt);
+#pragma unroll 1
     for (int it = 0; it < POSITION_ITERATIONS; ++it) {
         solve_position_contacts(e.b, c, (float)BAUMGARTE, (float)SLOP);
         solve_position_joints<Traits>(e.b, e.jp, e.n_joints, (float)BAUMGARTE, (float)SLOP);

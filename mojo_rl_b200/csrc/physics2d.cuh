@@ -64,10 +64,23 @@ struct ContactPre {
     float rax[MAXC], ray[MAXC], k[MAXC], kt[MAXC], jn[MAXC], jt[MAXC];
 };
 
+// The step kernels are long straight-line programs run by one or two warps per SM, so their time goes
+// into instruction fetch rather than arithmetic; the sine/cosine pair (~70 instructions, used a dozen
+// times per step) is therefore one shared out-of-line routine instead of a dozen inlined copies.
+static __device__ __noinline__ float2 sincos_shared(float a) {
+    float s, c;
+    mrl_sincosf(a, &s, &c);
+    return make_float2(s, c);
+}
+
 template <int NB>
 __device__ __forceinline__ void refresh_trig(Bodies<NB>& b) {
 #pragma unroll
-    for (int i = 0; i < NB; ++i) mrl_sincosf(b.a[i], &b.sn[i], &b.cs[i]);
+    for (int i = 0; i < NB; ++i) {
+        const float2 sc = sincos_shared(b.a[i]);
+        b.sn[i] = sc.x;
+        b.cs[i] = sc.y;
+    }
 }
 
 // euler.mojo:202-251 with the force slots passed in (fx, fy, tau per body).
@@ -347,8 +360,11 @@ __device__ __forceinline__ void solve_position_joints(Bodies<NB>& b, const Joint
     for (int j = 0; j < NJ; ++j) {
         if (j >= joint_count) break;
         const int A = Traits::ja(j), B = Traits::jb(j);
-        mrl_sincosf(b.a[A], &b.sn[A], &b.cs[A]);
-        mrl_sincosf(b.a[B], &b.sn[B], &b.cs[B]);
+        {
+            const float2 sa = sincos_shared(b.a[A]), sb = sincos_shared(b.a[B]);
+            b.sn[A] = sa.x; b.cs[A] = sa.y;
+            b.sn[B] = sb.x; b.cs[B] = sb.y;
+        }
         float rax, ray, rbx, rby, ik11, ik12, ik22;
         joint_geometry(b, A, B, jp[j], rax, ray, rbx, rby, ik11, ik12, ik22);
         const float xa = b.x[A], ya = b.y[A], xb = b.x[B], yb = b.y[B];
