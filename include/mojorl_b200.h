@@ -398,6 +398,21 @@ void* mrl_stream(mrl_ctx* ctx);
 /* Kernels launched by this library since load (all entry points). */
 int64_t mrl_kernel_launch_count(void);
 
+/* Text checkpoints in the reference's format (DeepPPOAgent.save_checkpoint / load_checkpoint,
+ * ppo.mojo:3926-4055; the continuous agent writes the same sections, ppo_continuous.mojo:493-604): header
+ * comments, the four sections actor_params / actor_optimizer_state / critic_params /
+ * critic_optimizer_state with one number per line, and a metadata section of key=value lines.  The
+ * hyper-parameters the handle owns come from its mrl_config; the ones the host owns travel in meta.
+ * Loading checks the parameter counts, uploads parameters and Adam state, and takes gamma, gae_lambda,
+ * clip_epsilon, value_loss_coef, num_epochs, normalize_advantages, target_kl and max_grad_norm from the file. */
+typedef struct mrl_checkpoint_meta {
+    double actor_lr, critic_lr, entropy_coef;
+    int32_t minibatch_size;    /* the CPU-path minibatch size field of the reference; informational here */
+    int32_t train_step_count;
+} mrl_checkpoint_meta;
+int mrl_save_checkpoint(mrl_ctx* ctx, const char* filepath, const mrl_checkpoint_meta* meta);
+int mrl_load_checkpoint(mrl_ctx* ctx, const char* filepath, mrl_checkpoint_meta* meta_out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -42,6 +42,12 @@ class Stats(ctypes.Structure):
                 ("last_mean_kl", ctypes.c_float), ("actor_adam_t", ctypes.c_int32), ("critic_adam_t", ctypes.c_int32)]
 
 
+class CheckpointMeta(ctypes.Structure):
+    """mrl_checkpoint_meta"""
+    _fields_ = [("actor_lr", ctypes.c_double), ("critic_lr", ctypes.c_double), ("entropy_coef", ctypes.c_double),
+                ("minibatch_size", ctypes.c_int32), ("train_step_count", ctypes.c_int32)]
+
+
 # name -> (restype, argtypes).  Every symbol include/mojorl_b200.h declares.
 SIGNATURES = {
     "mrl_env_info": (ctypes.c_int, [ctypes.c_int] + [ctypes.POINTER(ctypes.c_int)] * 4),
@@ -80,6 +86,8 @@ SIGNATURES = {
     "mrl_fused_train_scratch_doubles": (ctypes.c_int64, [ctypes.POINTER(NetSpec), ctypes.c_int]),
     "mrl_fused_train_step": (ctypes.c_int, [ctypes.POINTER(NetSpec), ctypes.c_int, ctypes.c_int] + [c_void_p] * 7
                              + [ctypes.c_float] * 3 + [ctypes.c_int] + [c_void_p] * 4),
+    "mrl_save_checkpoint": (ctypes.c_int, [c_void_p, ctypes.c_char_p, ctypes.POINTER(CheckpointMeta)]),
+    "mrl_load_checkpoint": (ctypes.c_int, [c_void_p, ctypes.c_char_p, ctypes.POINTER(CheckpointMeta)]),
     "mrl_config_defaults": (None, [ctypes.POINTER(Config)]),
     "mrl_create": (ctypes.c_int, [ctypes.POINTER(c_void_p), ctypes.POINTER(Config)]),
     "mrl_destroy": (ctypes.c_int, [c_void_p]),

@@ -924,3 +924,91 @@ extern "C" int mrl_drain_episodes(mrl_ctx* c, float* returns_host, float* length
     c->ring_tail = tail;
     return n;
 }
+
+// ---- text checkpoints in the reference's format (ppo.mojo:3926-4055, ppo_continuous.mojo:493-604) ----------
+
+extern "C" int mrl_save_checkpoint(mrl_ctx* c, const char* filepath, const mrl_checkpoint_meta* meta) {
+    MRL_CHECK_ARG(c && filepath && meta);
+    std::vector<float> ap(c->actor_p), as(2 * (size_t)c->actor_p), cp(c->critic_p), cs(2 * (size_t)c->critic_p);
+    int rc;
+    if ((rc = mrl_get_params(c, 0, ap.data(), as.data()))) return rc;
+    if ((rc = mrl_get_params(c, 1, cp.data(), cs.data()))) return rc;
+    FILE* f = fopen(filepath, "w");
+    if (!f) { set_error("cannot open %s for writing", filepath); return MRL_ERR_INVALID_ARG; }
+    fprintf(f, "# mojo-rl checkpoint v1\n# type: ppo_agent\n# actor_param_size: %d\n# critic_param_size: %d\n",
+            c->actor_p, c->critic_p);
+    auto dump = [&](const char* name, const std::vector<float>& v) {
+        fprintf(f, "%s\n", name);
+        for (float x : v) fprintf(f, "%.17g\n", (double)x);
+    };
+    dump("actor_params:", ap);
+    dump("actor_optimizer_state:", as);
+    dump("critic_params:", cp);
+    dump("critic_optimizer_state:", cs);
+    const mrl_config& g = c->cfg;
+    fprintf(f, "metadata:\ngamma=%.17g\ngae_lambda=%.17g\nclip_epsilon=%.9g\nactor_lr=%.17g\ncritic_lr=%.17g\n"
+               "entropy_coef=%.17g\nvalue_loss_coef=%.9g\nnum_epochs=%d\nminibatch_size=%d\n"
+               "normalize_advantages=%s\ntarget_kl=%.9g\nmax_grad_norm=%.9g\ntrain_step_count=%d\n",
+            g.gamma, g.gae_lambda, (double)g.clip_epsilon, meta->actor_lr, meta->critic_lr, meta->entropy_coef,
+            (double)g.value_loss_coef, g.num_epochs, meta->minibatch_size, g.normalize_advantages ? "True" : "False",
+            (double)g.target_kl, (double)g.max_grad_norm, meta->train_step_count);
+    const bool ok = ferror(f) == 0;
+    fclose(f);
+    if (!ok) { set_error("write to %s failed", filepath); return MRL_ERR_INVALID_ARG; }
+    return MRL_OK;
+}
+
+extern "C" int mrl_load_checkpoint(mrl_ctx* c, const char* filepath, mrl_checkpoint_meta* meta_out) {
+    MRL_CHECK_ARG(c && filepath);
+    FILE* f = fopen(filepath, "r");
+    if (!f) { set_error("cannot open %s", filepath); return MRL_ERR_INVALID_ARG; }
+    std::vector<float> sec[4];
+    const char* names[4] = {"actor_params:", "actor_optimizer_state:", "critic_params:", "critic_optimizer_state:"};
+    mrl_checkpoint_meta meta{};
+    mrl_config g = c->cfg;
+    int cur = -1;   // 0..3 section, 4 metadata
+    char line[256];
+    while (fgets(line, sizeof line, f)) {
+        size_t n = strlen(line);
+        while (n > 0 && (line[n - 1] == '\n' || line[n - 1] == '\r' || line[n - 1] == ' ')) line[--n] = 0;
+        if (n == 0 || line[0] == '#') continue;
+        bool header = false;
+        for (int k = 0; k < 4; ++k) if (strcmp(line, names[k]) == 0) { cur = k; header = true; }
+        if (strcmp(line, "metadata:") == 0) { cur = 4; header = true; }
+        if (header) continue;
+        if (cur >= 0 && cur < 4) { sec[cur].push_back((float)atof(line)); continue; }
+        if (cur == 4) {
+            char* eq = strchr(line, '=');
+            if (!eq) continue;
+            *eq = 0;
+            const char* k = line; const char* v = eq + 1;
+            if (!strcmp(k, "gamma")) g.gamma = atof(v);
+            else if (!strcmp(k, "gae_lambda")) g.gae_lambda = atof(v);
+            else if (!strcmp(k, "clip_epsilon")) g.clip_epsilon = (float)atof(v);
+            else if (!strcmp(k, "actor_lr")) meta.actor_lr = atof(v);
+            else if (!strcmp(k, "critic_lr")) meta.critic_lr = atof(v);
+            else if (!strcmp(k, "entropy_coef")) meta.entropy_coef = atof(v);
+            else if (!strcmp(k, "value_loss_coef")) g.value_loss_coef = (float)atof(v);
+            else if (!strcmp(k, "num_epochs")) g.num_epochs = atoi(v);
+            else if (!strcmp(k, "minibatch_size")) meta.minibatch_size = atoi(v);
+            else if (!strcmp(k, "normalize_advantages")) g.normalize_advantages = strcmp(v, "True") == 0;
+            else if (!strcmp(k, "target_kl")) g.target_kl = (float)atof(v);
+            else if (!strcmp(k, "max_grad_norm")) g.max_grad_norm = (float)atof(v);
+            else if (!strcmp(k, "train_step_count")) meta.train_step_count = atoi(v);
+        }
+    }
+    fclose(f);
+    if (sec[0].size() != (size_t)c->actor_p || sec[1].size() != 2 * (size_t)c->actor_p ||
+        sec[2].size() != (size_t)c->critic_p || sec[3].size() != 2 * (size_t)c->critic_p) {
+        set_error("checkpoint %s does not fit this agent (actor %zu/%d, critic %zu/%d parameters)", filepath,
+                  sec[0].size(), c->actor_p, sec[2].size(), c->critic_p);
+        return MRL_ERR_INVALID_ARG;
+    }
+    int rc;
+    if ((rc = mrl_set_params(c, 0, sec[0].data(), sec[1].data()))) return rc;
+    if ((rc = mrl_set_params(c, 1, sec[2].data(), sec[3].data()))) return rc;
+    if (g.num_epochs < 0) g.num_epochs = c->cfg.num_epochs;
+    c->cfg = g;
+    if (meta_out) *meta_out = meta;
+    return MRL_OK;
+}

@@ -167,3 +167,52 @@ def test_evaluate_gpu_counts_episodes_and_is_repeatable():
     r = cont.evaluate_gpu(PendulumV2, None, num_episodes=64, max_steps=400, stochastic=False)
     assert -1900.0 < r < -500.0
     assert cont.evaluate_gpu(PendulumV2, None, num_episodes=10, max_steps=100) == 0.0   # no episode ends in 100 steps
+
+
+def test_native_checkpoint_round_trip_and_python_compatibility(tmp_path):
+    """mrl_save_checkpoint / mrl_load_checkpoint write and read the reference's text format: a file written
+    natively loads into the Python mirror and the other way round, bit for bit."""
+    import ctypes
+    from mojo_rl_b200 import CartPoleEnv, DeepPPOAgent, _lib
+    L = _lib.lib()
+    agent = DeepPPOAgent(4, 2, hidden_dim=64, rollout_len=32, n_envs=64, gpu_minibatch_size=512, num_epochs=2,
+                         gamma=0.97, target_kl=0.03)
+    agent.train_gpu(CartPoleEnv, None, num_episodes=10 ** 9, max_rollouts=2)      # non-trivial Adam state
+    h = agent.create_context(CartPoleEnv.KIND)
+    try:
+        meta = _lib.CheckpointMeta(3e-4, 1e-3, 0.01, 64, 7)
+        path = str(tmp_path / "native.ckpt").encode()
+        _lib.check(L.mrl_save_checkpoint(h, path, ctypes.byref(meta)))
+        text = open(path.decode()).read().splitlines()
+        assert text[0] == "# mojo-rl checkpoint v1" and text[1] == "# type: ppo_agent"
+        assert text[2] == f"# actor_param_size: {agent.actor.params.size}" and text[4] == "actor_params:"
+        assert "metadata:" in text and "gamma=0.96999999999999997" in text and "train_step_count=7" in text
+        assert "normalize_advantages=True" in text
+        other = DeepPPOAgent(4, 2, hidden_dim=64, rollout_len=32, n_envs=64, gpu_minibatch_size=512, seed=5)
+        other.load_checkpoint(path.decode())
+        assert np.array_equal(other.actor.params, agent.actor.params)
+        assert np.array_equal(other.critic.optimizer_state, agent.critic.optimizer_state)
+        # Python-written file into a fresh native context
+        py_path = str(tmp_path / "python.ckpt")
+        agent.save_checkpoint(py_path)
+    finally:
+        L.mrl_destroy(h)
+    h2 = other.create_context(CartPoleEnv.KIND)
+    try:
+        for which in (0, 1):   # scramble, then load
+            n = L.mrl_param_size(h2, which)
+            _lib.check(L.mrl_set_params(h2, which, _lib.ptr(np.zeros(n, np.float32)), _lib.ptr(np.ones(2 * n, np.float32))))
+        out = _lib.CheckpointMeta()
+        _lib.check(L.mrl_load_checkpoint(h2, py_path.encode(), ctypes.byref(out)))
+        assert abs(out.actor_lr - agent.actor_lr) < 1e-12 and out.train_step_count == agent.train_step_count
+        p = np.empty(agent.actor.params.size, np.float32); s = np.empty(2 * p.size, np.float32)
+        _lib.check(L.mrl_get_params(h2, 0, _lib.ptr(p), _lib.ptr(s)))
+        assert np.array_equal(p, agent.actor.params) and np.array_equal(s, agent.actor.optimizer_state)
+        # a checkpoint of another shape is refused
+        big = DeepPPOAgent(8, 4, hidden_dim=64)
+        big_path = str(tmp_path / "big.ckpt")
+        big.save_checkpoint(big_path)
+        assert L.mrl_load_checkpoint(h2, big_path.encode(), None) == -1
+        assert b"does not fit" in L.mrl_last_error_string()
+    finally:
+        L.mrl_destroy(h2)
