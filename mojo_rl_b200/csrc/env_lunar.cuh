@@ -162,6 +162,84 @@ __device__ __forceinline__ void apply_engines(Env& e, int env, int action) {
     e.b.w[0] = e.b.w[0] + domega;
 }
 
+// Fuel cost of a discrete action (lunar_lander_v2.mojo:2380-2388).
+__device__ __forceinline__ float discrete_fuel(int action) {
+    if (action == 2) return (float)MAIN_ENGINE_FUEL_COST;
+    if (action == 1 || action == 3) return (float)SIDE_ENGINE_FUEL_COST;
+    return 0.0f;
+}
+
+// Continuous controls (lunar_lander_v2.mojo:2907-2944): action[0] main throttle remapped from [-1, 1] to
+// [0, 1], action[1] side control; a side engine fires beyond +-0.5 with power (|a| - 0.5) * 2.
+__device__ __forceinline__ void continuous_powers(float raw_throttle, float side_control, float& m_power,
+                                                  float& s_power, float& direction) {
+    float main_throttle = (raw_throttle + 1.0f) * 0.5f;
+    if (main_throttle < 0.0f) main_throttle = 0.0f;
+    if (main_throttle > 1.0f) main_throttle = 1.0f;
+    if (side_control < -1.0f) side_control = -1.0f;
+    if (side_control > 1.0f) side_control = 1.0f;
+    m_power = main_throttle;
+    s_power = 0.0f;
+    direction = 0.0f;
+    if (side_control < -0.5f) { direction = -1.0f; s_power = (-side_control - 0.5f) * 2.0f; }
+    else if (side_control > 0.5f) { direction = 1.0f; s_power = (side_control - 0.5f) * 2.0f; }
+}
+// The two fuel terms of _finalize_single_env_continuous (:3375-3409); the side term looks at the unclamped control.
+__device__ __forceinline__ void continuous_fuel(float raw_throttle, float side_control, float& fuel_a, float& fuel_b) {
+    float m_power, s_power, direction;
+    continuous_powers(raw_throttle, side_control, m_power, s_power, direction);
+    fuel_a = m_power * (float)MAIN_ENGINE_FUEL_COST;
+    fuel_b = 0.0f;
+    float abs_side = side_control;
+    if (abs_side < 0.0f) abs_side = -abs_side;
+    if (abs_side > 0.5f) fuel_b = (abs_side - 0.5f) * 2.0f * (float)SIDE_ENGINE_FUEL_COST;
+}
+
+// _setup_single_env_continuous, lunar_lander_v2.mojo:2852-3025 (wind is compile-time off).
+__device__ __forceinline__ void apply_engines_continuous(Env& e, int env, float raw_throttle, float side_control) {
+    if (e.done > 0.5f) return;
+    float m_power, s_power, direction;
+    continuous_powers(raw_throttle, side_control, m_power, s_power, direction);
+    if (m_power <= 0.0f && s_power <= 0.0f) return;
+    int step_count = (int)e.step_count;
+    Philox rng((uint64_t)(int64_t)(env + 12345), (uint64_t)(int64_t)step_count);
+    float r[4];
+    rng.step_uniform(r);
+    float dispersion_x = (r[0] * 2.0f - 1.0f) / (float)SCALE;
+    float dispersion_y = (r[1] * 2.0f - 1.0f) / (float)SCALE;
+    const float2 tip = sincos_shared(e.b.a[0]);
+    const float tip_x = tip.x, tip_y = tip.y;
+    float side_x = -tip_y, side_y = tip_x;
+    float dvx = 0.0f, dvy = 0.0f, domega = 0.0f;
+    const float main_y_offset = (float)MAIN_ENGINE_Y_OFFSET, side_away = (float)SIDE_ENGINE_AWAY;
+    const float side_height = (float)SIDE_ENGINE_HEIGHT, main_power = (float)MAIN_ENGINE_POWER;
+    const float side_power = (float)SIDE_ENGINE_POWER, lander_mass = (float)LANDER_MASS;
+    const float lander_inertia = (float)LANDER_INERTIA, scale = (float)SCALE;
+    if (m_power > 0.0f) {
+        float ox = tip_x * (main_y_offset + 2.0f * dispersion_x) + side_x * dispersion_y;
+        float oy = -tip_y * (main_y_offset + 2.0f * dispersion_x) - side_y * dispersion_y;
+        float impulse_x = -ox * main_power * m_power, impulse_y = -oy * main_power * m_power;
+        dvx += impulse_x / lander_mass;
+        dvy += impulse_y / lander_mass;
+        float torque = ox * impulse_y - oy * impulse_x;
+        domega += torque / lander_inertia;
+    }
+    if (s_power > 0.0f) {
+        float ox = tip_x * dispersion_x + side_x * (3.0f * dispersion_y + direction * side_away);
+        float oy = -tip_y * dispersion_x - side_y * (3.0f * dispersion_y + direction * side_away);
+        float impulse_x = -ox * side_power * s_power, impulse_y = -oy * side_power * s_power;
+        dvx += impulse_x / lander_mass;
+        dvy += impulse_y / lander_mass;
+        float r_x = ox - tip_x * 17.0f / scale;
+        float r_y = oy + tip_y * side_height;
+        float torque = r_x * impulse_y - r_y * impulse_x;
+        domega += torque / lander_inertia;
+    }
+    e.b.vx[0] = e.b.vx[0] + dvx;
+    e.b.vy[0] = e.b.vy[0] + dvy;
+    e.b.w[0] = e.b.w[0] + domega;
+}
+
 // The fused physics step, lunar_lander_v2.mojo:2671-2752.
 template <class Edges>
 __device__ __forceinline__ void physics_step(Env& e, const Edges& edges, Contacts<MAX_CONTACTS>& c) {
@@ -249,12 +327,12 @@ __device__ __forceinline__ float terrain_y_at(const Edges& edges, float leg_x) {
     return edges.y0_of(chunk);
 }
 
-// _finalize_single_env, lunar_lander_v2.mojo:2266-2482.  obs[8] is written
+// _finalize_single_env / _finalize_single_env_continuous, lunar_lander_v2.mojo:2266-2482, :3250-3490.  obs[8] is written
 // only when the env was not already done (the reference leaves the row's
 // observation untouched in that case).
 template <class Edges>
 __device__ __forceinline__ void finalize(Env& e, const Edges& edges, const Contacts<MAX_CONTACTS>& c,
-                                         int action, float (&obs)[OBS_DIM], bool& obs_written,
+                                         float fuel_a, float fuel_b, float (&obs)[OBS_DIM], bool& obs_written,
                                          float& reward_out, float& done_out) {
     obs_written = false;
     if (e.done > 0.5f) { reward_out = 0.0f; done_out = 1.0f; return; }
@@ -280,8 +358,8 @@ __device__ __forceinline__ void finalize(Env& e, const Edges& edges, const Conta
                     10.0f * right_contact;
     float reward = shaping - e.prev_shaping;
     e.prev_shaping = shaping;
-    if (action == 2) reward = reward - (float)MAIN_ENGINE_FUEL_COST;
-    else if (action == 1 || action == 3) reward = reward - (float)SIDE_ENGINE_FUEL_COST;
+    reward = reward - fuel_a;   // discrete: the engine's cost (0 for no-op); continuous: main throttle term,
+    reward = reward - fuel_b;   // then the side-engine term (lunar_lander_v2.mojo:3390-3409)
     float done = 0.0f;
     if (x_norm >= 1.0f || x_norm <= -1.0f) { done = 1.0f; reward = (float)CRASH_PENALTY; }
     if (y > (float)(H_UNITS * 1.5)) { done = 1.0f; reward = (float)CRASH_PENALTY; }

@@ -133,17 +133,29 @@ __device__ __forceinline__ void lunar_rows_from_smem(float* __restrict__ states,
     }
 }
 
-// One step of one environment whose row lives at s (lunar_lander_v2.mojo:1453-1517).
-__device__ __forceinline__ void lunar_step_row(float* s, int env, int action, float& reward, float& done) {
+// One step of one environment whose row lives at s (lunar_lander_v2.mojo:1453-1517 discrete,
+// :1519-1589 continuous: act points at the env's action index or at its two controls).
+template <bool CONT>
+__device__ __forceinline__ void lunar_step_row(float* s, int env, const float* __restrict__ act, float& reward,
+                                               float& done) {
     lunar::Env e;
     lunar::load_row(s, e);
-    lunar::apply_engines(e, env, action);
+    float fuel_a, fuel_b = 0.0f;
+    if (CONT) {
+        const float a0 = act[0], a1 = act[1];
+        lunar::apply_engines_continuous(e, env, a0, a1);
+        lunar::continuous_fuel(a0, a1, fuel_a, fuel_b);
+    } else {
+        const int action = (int)act[0];
+        lunar::apply_engines(e, env, action);
+        fuel_a = lunar::discrete_fuel(action);
+    }
     lunar::RowEdges edges{s};
     phys::Contacts<lunar::MAX_CONTACTS> c;
     lunar::physics_step(e, edges, c);
     float o[lunar::OBS_DIM];
     bool obs_written;
-    lunar::finalize(e, edges, c, action, o, obs_written, reward, done);
+    lunar::finalize(e, edges, c, fuel_a, fuel_b, o, obs_written, reward, done);
     lunar::store_row(s, e);
     if (obs_written) {
 #pragma unroll
@@ -151,6 +163,7 @@ __device__ __forceinline__ void lunar_step_row(float* s, int env, int action, fl
     }
 }
 
+template <bool CONT>
 __global__ void __launch_bounds__(LUNAR_TPB)
 lunar_step_rows_kernel(float* __restrict__ states, const float* __restrict__ actions,
                        float* __restrict__ rewards, float* __restrict__ dones,
@@ -163,7 +176,7 @@ lunar_step_rows_kernel(float* __restrict__ states, const float* __restrict__ act
     if (env < n) {
         float* s = sm + threadIdx.x * LUNAR_PITCH;
         float reward, done;
-        lunar_step_row(s, env, (int)actions[env], reward, done);
+        lunar_step_row<CONT>(s, env, actions + (size_t)env * (CONT ? 2 : 1), reward, done);
         float4* ob = reinterpret_cast<float4*>(obs + (size_t)env * lunar::OBS_DIM);
         ob[0] = make_float4(s[0], s[1], s[2], s[3]);
         ob[1] = make_float4(s[4], s[5], s[6], s[7]);
@@ -174,6 +187,7 @@ lunar_step_rows_kernel(float* __restrict__ states, const float* __restrict__ act
 }
 
 // Rollout step: step, store, episode tracking, selective reset, observation.
+template <bool CONT>
 __global__ void __launch_bounds__(LUNAR_TPB) lunar_rollout_step_kernel(RolloutStepArgs a) {
     extern __shared__ __align__(128) float sm[];
     uint64_t* bar = reinterpret_cast<uint64_t*>(sm + LUNAR_TPB * LUNAR_PITCH);
@@ -183,7 +197,7 @@ __global__ void __launch_bounds__(LUNAR_TPB) lunar_rollout_step_kernel(RolloutSt
     if (env < a.n) {
         float* s = sm + threadIdx.x * LUNAR_PITCH;
         float reward, done;
-        lunar_step_row(s, env, (int)a.actions[env], reward, done);
+        lunar_step_row<CONT>(s, env, a.actions + (size_t)env * (CONT ? 2 : 1), reward, done);
         a.rewards[env] = reward;
         a.dones[env] = done;  // the reference's selective reset leaves the flag set (:1643-1701)
         track_episode(a, env, reward, done);
@@ -384,9 +398,13 @@ __global__ void lunar_reset_rows_kernel(float* __restrict__ states, const float*
 static cudaError_t ensure_lunar_smem() {
     static bool done = false;
     if (done) return cudaSuccess;
-    cudaError_t e = cudaFuncSetAttribute(lunar_step_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LUNAR_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(lunar_step_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, LUNAR_SMEM);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(lunar_rollout_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LUNAR_SMEM);
+    e = cudaFuncSetAttribute(lunar_step_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, LUNAR_SMEM);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(lunar_rollout_step_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, LUNAR_SMEM);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(lunar_rollout_step_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, LUNAR_SMEM);
     if (e == cudaSuccess) done = true;
     return e;
 }
@@ -425,7 +443,11 @@ int rollout_env_step(int env_kind, const RolloutStepArgs& a, cudaStream_t st) {
             return MRL_OK;
         case MRL_ENV_LUNAR_LANDER:
             MRL_CUDA_OK(ensure_lunar_smem());
-            MRL_LAUNCH(lunar_rollout_step_kernel, ceil_div(a.n, LUNAR_TPB), LUNAR_TPB, LUNAR_SMEM, st, a);
+            MRL_LAUNCH(lunar_rollout_step_kernel<false>, ceil_div(a.n, LUNAR_TPB), LUNAR_TPB, LUNAR_SMEM, st, a);
+            return MRL_OK;
+        case MRL_ENV_LUNAR_LANDER_CONTINUOUS:
+            MRL_CUDA_OK(ensure_lunar_smem());
+            MRL_LAUNCH(lunar_rollout_step_kernel<true>, ceil_div(a.n, LUNAR_TPB), LUNAR_TPB, LUNAR_SMEM, st, a);
             return MRL_OK;
         default:
             set_error("rollout: env kind %d is not built", env_kind);
@@ -443,6 +465,7 @@ extern "C" int mrl_env_info(int env_kind, int* state_size, int* obs_dim, int* nu
     switch (env_kind) {
         case MRL_ENV_CARTPOLE: ss = 4; od = 4; na = 2; ad = 0; break;
         case MRL_ENV_LUNAR_LANDER: ss = lunar::STATE_SIZE; od = 8; na = 4; ad = 0; break;
+        case MRL_ENV_LUNAR_LANDER_CONTINUOUS: ss = lunar::STATE_SIZE; od = 8; na = 0; ad = 2; break;
         case MRL_ENV_PENDULUM: ss = 8; od = 3; na = 0; ad = 1; break;
         case MRL_ENV_HALF_CHEETAH: ss = cheetah::STATE_SIZE; od = 17; na = 0; ad = 6; break;
         case MRL_ENV_BIPEDAL_WALKER: ss = bipedal::STATE_SIZE; od = 24; na = 0; ad = 4; break;
@@ -465,6 +488,7 @@ extern "C" int mrl_env_reset(int env_kind, int batch, float* states, uint64_t rn
             MRL_LAUNCH(cartpole_reset_kernel, ceil_div(batch, 256), 256, 0, st, states, batch);
             return MRL_OK;
         case MRL_ENV_LUNAR_LANDER:
+        case MRL_ENV_LUNAR_LANDER_CONTINUOUS:
             MRL_LAUNCH(lunar_reset_rows_kernel, ceil_div(batch, ENV_TPB), ENV_TPB, 0, st, states,
                        (const float*)nullptr, (float)rng_seed, batch);
             return MRL_OK;
@@ -517,8 +541,15 @@ extern "C" int mrl_env_step(int env_kind, int batch, float* states, const float*
             MRL_CUDA_OK(ensure_lunar_smem());
             MRL_CHECK_ARG(((uintptr_t)states & 15) == 0);
             MRL_CUDA_OK(boundary_err_word(&err_word));
-            MRL_LAUNCH(lunar_step_rows_kernel, ceil_div(batch, LUNAR_TPB), LUNAR_TPB, LUNAR_SMEM, st, states, actions,
-                       rewards, dones, obs, batch, err_word);
+            MRL_LAUNCH(lunar_step_rows_kernel<false>, ceil_div(batch, LUNAR_TPB), LUNAR_TPB, LUNAR_SMEM, st, states,
+                       actions, rewards, dones, obs, batch, err_word);
+            return MRL_OK;
+        case MRL_ENV_LUNAR_LANDER_CONTINUOUS:
+            MRL_CUDA_OK(ensure_lunar_smem());
+            MRL_CHECK_ARG(((uintptr_t)states & 15) == 0);
+            MRL_CUDA_OK(boundary_err_word(&err_word));
+            MRL_LAUNCH(lunar_step_rows_kernel<true>, ceil_div(batch, LUNAR_TPB), LUNAR_TPB, LUNAR_SMEM, st, states,
+                       actions, rewards, dones, obs, batch, err_word);
             return MRL_OK;
         default:
             set_error("mrl_env_step: env kind %d is not built", env_kind);
@@ -536,6 +567,7 @@ extern "C" int mrl_env_selective_reset(int env_kind, int batch, float* states, f
                        (uint32_t)rng_seed, batch);
             return MRL_OK;
         case MRL_ENV_LUNAR_LANDER:
+        case MRL_ENV_LUNAR_LANDER_CONTINUOUS:
             MRL_LAUNCH(lunar_reset_rows_kernel, ceil_div(batch, ENV_TPB), ENV_TPB, 0, st, states,
                        (const float*)dones, (float)rng_seed, batch);
             return MRL_OK;

@@ -101,3 +101,11 @@ class BipedalWalkerV2(_GPUContinuousEnv):
     ACTION_DIM 4 (hip / knee motors of both legs in [-1, 1])."""
     KIND = ENV_KINDS["bipedal_walker"]
     STATE_SIZE, OBS_DIM, ACTION_DIM = 950, 24, 4
+
+
+class LunarLanderV2Continuous(_GPUContinuousEnv):
+    """LunarLanderV2 through its GPUContinuousEnv trait (lunar_lander_v2.mojo:1519-1589, :2781-3495):
+    same rows and physics as the discrete variant; actions are (main throttle in [-1, 1] remapped to [0, 1],
+    side control in [-1, 1], engines on beyond +-0.5)."""
+    KIND = ENV_KINDS["lunar_lander_continuous"]
+    STATE_SIZE, OBS_DIM, ACTION_DIM = 192, 8, 2

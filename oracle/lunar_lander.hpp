@@ -237,6 +237,73 @@ inline void setup_env_discrete(float* s, int env, int action) {
     s[BODIES_OFFSET + IDX_OMEGA] = omega + domega;
 }
 
+// lunar_lander_v2.mojo:2852-3025 (continuous): action[0] main throttle remapped from [-1, 1] to [0, 1],
+// action[1] side control, engines on beyond +-0.5 with power (|a| - 0.5) * 2.
+inline void continuous_powers(float raw_throttle, float side_control, float* m_power, float* s_power,
+                              float* direction) {
+    float main_throttle = (raw_throttle + 1.0f) * 0.5f;
+    if (main_throttle < 0.0f) main_throttle = 0.0f;
+    if (main_throttle > 1.0f) main_throttle = 1.0f;
+    if (side_control < -1.0f) side_control = -1.0f;
+    if (side_control > 1.0f) side_control = 1.0f;
+    *m_power = main_throttle;
+    *s_power = 0.0f;
+    *direction = 0.0f;
+    if (side_control < -0.5f) { *direction = -1.0f; *s_power = (-side_control - 0.5f) * 2.0f; }
+    else if (side_control > 0.5f) { *direction = 1.0f; *s_power = (side_control - 0.5f) * 2.0f; }
+}
+
+inline void setup_env_continuous(float* s, int env, float raw_throttle, float side_control) {
+    for (int b = 0; b < NUM_BODIES; ++b) {
+        float* f = s + FORCES_OFFSET + b * 3;
+        f[0] = 0.0f; f[1] = 0.0f; f[2] = 0.0f;
+    }
+    if (s[METADATA_OFFSET + META_DONE] > 0.5f) return;
+    int step_count = (int)s[METADATA_OFFSET + META_STEP_COUNT];
+    float m_power, s_power, direction;
+    continuous_powers(raw_throttle, side_control, &m_power, &s_power, &direction);
+    if (m_power <= 0.0f && s_power <= 0.0f) return;
+    Philox rng((uint64_t)(int64_t)(env + 12345), (uint64_t)(int64_t)step_count);
+    float r[4];
+    rng.step_uniform(r);
+    float dispersion_x = (r[0] * 2.0f - 1.0f) / (float)SCALE;
+    float dispersion_y = (r[1] * 2.0f - 1.0f) / (float)SCALE;
+    float angle = s[BODIES_OFFSET + IDX_ANGLE];
+    float tip_x, tip_y;
+    mrl_sincosf(angle, &tip_x, &tip_y);
+    float side_x = -tip_y, side_y = tip_x;
+    float vx = s[BODIES_OFFSET + IDX_VX], vy = s[BODIES_OFFSET + IDX_VY];
+    float omega = s[BODIES_OFFSET + IDX_OMEGA];
+    float dvx = 0.0f, dvy = 0.0f, domega = 0.0f;
+    const float main_y_offset = (float)MAIN_ENGINE_Y_OFFSET, side_away = (float)SIDE_ENGINE_AWAY;
+    const float side_height = (float)SIDE_ENGINE_HEIGHT, main_power = (float)MAIN_ENGINE_POWER;
+    const float side_power = (float)SIDE_ENGINE_POWER, lander_mass = (float)LANDER_MASS;
+    const float lander_inertia = (float)LANDER_INERTIA, scale = (float)SCALE;
+    if (m_power > 0.0f) {
+        float ox = tip_x * (main_y_offset + 2.0f * dispersion_x) + side_x * dispersion_y;
+        float oy = -tip_y * (main_y_offset + 2.0f * dispersion_x) - side_y * dispersion_y;
+        float impulse_x = -ox * main_power * m_power, impulse_y = -oy * main_power * m_power;
+        dvx += impulse_x / lander_mass;
+        dvy += impulse_y / lander_mass;
+        float torque = ox * impulse_y - oy * impulse_x;
+        domega += torque / lander_inertia;
+    }
+    if (s_power > 0.0f) {
+        float ox = tip_x * dispersion_x + side_x * (3.0f * dispersion_y + direction * side_away);
+        float oy = -tip_y * dispersion_x - side_y * (3.0f * dispersion_y + direction * side_away);
+        float impulse_x = -ox * side_power * s_power, impulse_y = -oy * side_power * s_power;
+        dvx += impulse_x / lander_mass;
+        dvy += impulse_y / lander_mass;
+        float r_x = ox - tip_x * 17.0f / scale;
+        float r_y = oy + tip_y * side_height;
+        float torque = r_x * impulse_y - r_y * impulse_x;
+        domega += torque / lander_inertia;
+    }
+    s[BODIES_OFFSET + IDX_VX] = vx + dvx;
+    s[BODIES_OFFSET + IDX_VY] = vy + dvy;
+    s[BODIES_OFFSET + IDX_OMEGA] = omega + domega;
+}
+
 // helpers.mojo:10-133
 inline float compute_shaping(float x_norm, float y_norm, float vx_norm, float vy_norm, float angle,
                              float left_contact, float right_contact) {
@@ -259,7 +326,7 @@ inline float terrain_y_at(const float* s, float leg_x) {
 // lunar_lander_v2.mojo:2266-2482.  fuel_cost: 0 none, 1 side, 2 main for the
 // discrete variant; the continuous variant passes its own fuel term.
 inline void finalize_env(float* s, const float* contacts, int n_contacts, float fuel_penalty,
-                         float* reward_out, float* done_out) {
+                         float* reward_out, float* done_out, float fuel_penalty2 = 0.0f) {
     if (s[METADATA_OFFSET + META_DONE] > 0.5f) {
         *reward_out = 0.0f;
         *done_out = 1.0f;
@@ -290,6 +357,7 @@ inline void finalize_env(float* s, const float* contacts, int n_contacts, float 
     float reward = shaping - prev_shaping;
     s[METADATA_OFFSET + META_PREV_SHAPING] = shaping;
     reward = reward - fuel_penalty;
+    reward = reward - fuel_penalty2;   // continuous variant: main then side (:3390-3409); 0 otherwise
     float done = 0.0f;
     if (x_norm >= 1.0f || x_norm <= -1.0f) { done = 1.0f; reward = (float)CRASH_PENALTY; }
     const float h_units_max = (float)(H_UNITS * 1.5);
@@ -355,6 +423,32 @@ inline void step_all(float* states, const float* actions, float* rewards, float*
         if (action == 2) fuel = (float)MAIN_ENGINE_FUEL_COST;
         else if (action == 1 || action == 3) fuel = (float)SIDE_ENGINE_FUEL_COST;
         finalize_env(s, contacts, n_contacts, fuel, &rewards[env], &dones[env]);
+        for (int d = 0; d < OBS_DIM; ++d) obs[(size_t)env * OBS_DIM + d] = s[d];
+    }
+}
+
+// step_kernel_gpu of the GPUContinuousEnv trait (lunar_lander_v2.mojo:1519-1589): actions are [n, 2].
+inline void step_all_continuous(float* states, const float* actions, float* rewards, float* dones, float* obs, int n) {
+    float shapes[NUM_BODIES * SHAPE_MAX_SIZE];
+    init_shapes(shapes);
+#ifdef _OPENMP
+#pragma omp parallel for schedule(static)
+#endif
+    for (int env = 0; env < n; ++env) {
+        float* s = states + (size_t)env * STATE_SIZE;
+        float contacts[MAX_CONTACTS * CONTACT_DATA_SIZE];
+        const float a0 = actions[(size_t)env * 2], a1 = actions[(size_t)env * 2 + 1];
+        setup_env_continuous(s, env, a0, a1);
+        int n_contacts = physics_step(s, shapes, contacts);
+        float m_power, s_power_unused, dir_unused;
+        continuous_powers(a0, a1, &m_power, &s_power_unused, &dir_unused);
+        float fuel_main = m_power * (float)MAIN_ENGINE_FUEL_COST;
+        float fuel_side = 0.0f;
+        float abs_side = a1;
+        if (abs_side < 0.0f) abs_side = -abs_side;
+        bool side_on = abs_side > 0.5f;    // on the unclamped control (:3399-3409)
+        if (side_on) fuel_side = (abs_side - 0.5f) * 2.0f * (float)SIDE_ENGINE_FUEL_COST;
+        finalize_env(s, contacts, n_contacts, fuel_main, &rewards[env], &dones[env], fuel_side);
         for (int d = 0; d < OBS_DIM; ++d) obs[(size_t)env * OBS_DIM + d] = s[d];
     }
 }

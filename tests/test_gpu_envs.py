@@ -7,11 +7,11 @@ from _util import fp, oracle
 
 pytestmark = pytest.mark.gpu
 
-CARTPOLE, PENDULUM, LUNAR, BIPEDAL, CHEETAH = 0, 1, 2, 3, 4
-STATE = {CARTPOLE: 4, PENDULUM: 8, LUNAR: 192, BIPEDAL: 950, CHEETAH: 253}
-OBS = {CARTPOLE: 4, PENDULUM: 3, LUNAR: 8, BIPEDAL: 24, CHEETAH: 17}
+CARTPOLE, PENDULUM, LUNAR, BIPEDAL, CHEETAH, LUNAR_C = 0, 1, 2, 3, 4, 5
+STATE = {CARTPOLE: 4, PENDULUM: 8, LUNAR: 192, BIPEDAL: 950, CHEETAH: 253, LUNAR_C: 192}
+OBS = {CARTPOLE: 4, PENDULUM: 3, LUNAR: 8, BIPEDAL: 24, CHEETAH: 17, LUNAR_C: 8}
 NACT = {CARTPOLE: 2, LUNAR: 4}
-ADIM = {PENDULUM: 1, BIPEDAL: 4, CHEETAH: 6}
+ADIM = {PENDULUM: 1, BIPEDAL: 4, CHEETAH: 6, LUNAR_C: 2}
 
 
 def _run_both(kind, n, steps, seed, policy):
@@ -20,7 +20,7 @@ def _run_both(kind, n, steps, seed, policy):
     o = oracle()
     S, O = STATE[kind], OBS[kind]
     rng = np.random.default_rng(seed)
-    garbage = rng.standard_normal((n, S)).astype(np.float32) if kind == LUNAR else np.zeros((n, S), np.float32)
+    garbage = rng.standard_normal((n, S)).astype(np.float32) if kind in (LUNAR, LUNAR_C) else np.zeros((n, S), np.float32)
     # slots the reference never writes (mass, force, motor fields) must be inert: zero them like a fresh buffer
     st_c = np.zeros((n, S), np.float32)
     st_g = dev(st_c)
@@ -47,7 +47,7 @@ def _run_both(kind, n, steps, seed, policy):
         o.orc_env_selective_reset(kind, n, fp(st_c), fp(done_c), rs)
         call("mrl_env_selective_reset", kind, n, st_g, done_g, rs, stream())
         assert np.array_equal(host(st_g), st_c) and np.array_equal(host(done_g), done_c)
-        if kind in (LUNAR, PENDULUM, CHEETAH, BIPEDAL):   # the row starts with the observation
+        if kind in (LUNAR, LUNAR_C, PENDULUM, CHEETAH, BIPEDAL):   # the row starts with the observation
             obs_c[:] = st_c[:, :O]
     return n_done, worst
 
@@ -62,6 +62,9 @@ def _deterministic_policy(kind):
     # a fixed function of the observation (stands in for argmax of a frozen net)
     if kind == CARTPOLE:
         return lambda rng, obs, n: (obs[:, 2] + 0.5 * obs[:, 3] > 0).astype(np.float32)
+    if kind == LUNAR_C:   # throttle against the fall, side engine against the tilt (fires beyond +-0.5)
+        return lambda rng, obs, n: np.ascontiguousarray(
+            np.stack([np.tanh(-4.0 * obs[:, 3] - 0.5), np.clip(-3.0 * obs[:, 4] - obs[:, 5], -1.5, 1.5)], 1), np.float32)
     if kind == BIPEDAL:   # keeps the hull up for a while: hips follow the hull tilt, knees stay bent
         def walker(rng, obs, n):
             a = np.zeros((n, 4), np.float32)
@@ -85,7 +88,7 @@ def _deterministic_policy(kind):
     return pol
 
 
-@pytest.mark.parametrize("kind", [CARTPOLE, PENDULUM, LUNAR, BIPEDAL, CHEETAH])
+@pytest.mark.parametrize("kind", [CARTPOLE, PENDULUM, LUNAR, BIPEDAL, CHEETAH, LUNAR_C])
 @pytest.mark.parametrize("n", [1, 33, 1024])
 def test_100_steps_deterministic_policy(kind, n):
     n_done, worst = _run_both(kind, n, 100, 0, _deterministic_policy(kind))
@@ -93,7 +96,7 @@ def test_100_steps_deterministic_policy(kind, n):
     assert worst <= 1e-4
 
 
-@pytest.mark.parametrize("kind", [CARTPOLE, PENDULUM, LUNAR, BIPEDAL])
+@pytest.mark.parametrize("kind", [CARTPOLE, PENDULUM, LUNAR, BIPEDAL, LUNAR_C])
 def test_400_steps_random_policy_with_resets(kind):
     n_done, worst = _run_both(kind, 512, 400, 7, _random_policy(kind))
     assert n_done > 100           # crashes / landings / time-outs and their resets were exercised

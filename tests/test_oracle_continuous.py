@@ -416,3 +416,62 @@ def test_bipedal_step_rewards_and_terminations():
     s[:, BW_B0:BW_B0 + 65:13] = -0.5      # every body, so that the joints stay satisfied
     r, d, ob = _wstep(s, np.zeros((2, 4), np.float32))
     assert np.all(d == 1.0) and np.all(r == -100.0)
+
+
+# ---------------------------------------------------------------- LunarLander, continuous controls
+LUNAR, LUNAR_C = 2, 5
+
+
+def _lunar_pair(n, seed):
+    o = oracle()
+    a, b = np.zeros((n, 192), np.float32), np.zeros((n, 192), np.float32)
+    o.orc_env_reset(LUNAR, n, fp(a), seed)
+    o.orc_env_reset(LUNAR_C, n, fp(b), seed)
+    assert np.array_equal(a, b)                       # one reset serves both traits
+    return a, b
+
+
+def _lstep(kind, s, act):
+    o = oracle()
+    n = s.shape[0]
+    r, d, ob = np.zeros(n, np.float32), np.zeros(n, np.float32), np.zeros((n, 8), np.float32)
+    o.orc_env_step(kind, n, fp(s), fp(np.ascontiguousarray(act, np.float32)), fp(r), fp(d), fp(ob), 0)
+    return r, d, ob
+
+
+def test_lunar_continuous_matches_discrete_at_full_throttle_and_charges_fuel_proportionally():
+    o = oracle()
+    dims = [ctypes.c_int() for _ in range(4)]
+    assert o.orc_env_info(LUNAR_C, *[ctypes.byref(x) for x in dims]) == 0
+    assert [x.value for x in dims] == [192, 8, 0, 2]
+    n = 64
+    # full main throttle (+1) == discrete action 2; side control -1 / +1 == discrete actions 1 / 3 (power 1)
+    for disc, cont in ((2, (1.0, 0.0)), (1, (-1.0, -1.0)), (3, (-1.0, 1.0)), (0, (-1.0, 0.2))):
+        a, b = _lunar_pair(n, seed=3)
+        for t in range(20):
+            ra, da, oa = _lstep(LUNAR, a, np.full(n, disc, np.float32))
+            rb, db, ob = _lstep(LUNAR_C, b, np.tile(np.array([cont], np.float32), (n, 1)))
+            assert np.array_equal(a, b) and np.array_equal(oa, ob) and np.array_equal(da, db)
+            assert np.allclose(ra, rb, atol=1e-5)    # same fuel charge: 0.30 main / 0.03 side / none
+    # half throttle: half the main impulse and half the fuel charge; side engine off inside +-0.5
+    a, b = _lunar_pair(n, seed=4)
+    vy0 = a[:, 8 + 4].copy()
+    r_full, _, _ = _lstep(LUNAR_C, a, np.tile(np.array([[1.0, 0.4]], np.float32), (n, 1)))
+    r_half, _, _ = _lstep(LUNAR_C, b, np.tile(np.array([[0.0, -0.4]], np.float32), (n, 1)))
+    dv_full, dv_half = a[:, 12] - vy0, b[:, 12] - vy0
+    g = -10.0 * 0.02
+    assert np.allclose(dv_half - g, 0.5 * (dv_full - g), rtol=2e-3, atol=2e-4)
+    # side power ramps from 0 at |a| = 0.5 to 1 at |a| = 1: at 0.75 the lander gets half the angular impulse
+    a, b = _lunar_pair(n, seed=5)
+    c, _ = _lunar_pair(n, seed=5)
+    _lstep(LUNAR_C, a, np.tile(np.array([[-1.0, 0.5]], np.float32), (n, 1)))     # exactly at the threshold: off
+    _lstep(LUNAR_C, b, np.tile(np.array([[-1.0, 0.75]], np.float32), (n, 1)))
+    _lstep(LUNAR_C, c, np.tile(np.array([[-1.0, 1.0]], np.float32), (n, 1)))
+    w_off, w_half, w_full = a[:, 8 + 5], b[:, 8 + 5], c[:, 8 + 5]
+    assert np.all(np.abs(w_full - w_off) > 1e-3)
+    assert np.allclose(w_half - w_off, 0.5 * (w_full - w_off), rtol=5e-2, atol=1e-4)
+    # actions beyond the range are clamped for the impulse; the side fuel term uses the unclamped control
+    a, b = _lunar_pair(n, seed=6)
+    _lstep(LUNAR_C, a, np.tile(np.array([[5.0, 0.0]], np.float32), (n, 1)))
+    _lstep(LUNAR_C, b, np.tile(np.array([[1.0, 0.0]], np.float32), (n, 1)))
+    assert np.array_equal(a[:, 8:47], b[:, 8:47])
