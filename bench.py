@@ -241,7 +241,7 @@ def main():
     L = _lib.lib()
     agent = make_params(w, seed=0)   # same seed on every rank: replicas start identical
     # BASELINE.json: LunarLander "update matmuls in bf16"; the hidden-64 configs stay fp32 (launch-bound)
-    default_precision = 1 if w["hidden"] == 256 else 0
+    default_precision = 1 if w["hidden"] in (256, 512) else 0
     agent.precision = args.precision if args.precision is not None else int(
         os.environ.get("MRL_PRECISION", str(default_precision)))
     h = agent.create_context(w["kind"], world_size=world, rank=rank)

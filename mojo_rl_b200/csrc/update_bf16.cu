@@ -38,6 +38,10 @@ struct K1Params {
     const float* W2; const float* b2; int out_dim; bf16* h1; float* head_out; int head_ld;
     const bf16* h0; bf16* g0;       // mode 2: mask source and masked output
     int act;                        // modes 1, 2: 0 ReLU, 1 tanh (derivative 1 - y^2 from the stored bf16 y)
+    // Hidden widths above 256 are computed in 256-wide blocks: a second launch adds the first one's fp32
+    // result (prev, [M, 256]) to its accumulator before the epilogue, and bf16 rows have their own pitch.
+    const float* prev;
+    int out_ld, mask_ld;            // row pitch of h1 / g0 and of h0 in elements; 0 = 256
     int* err;
 };
 
@@ -162,7 +166,7 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 uint4 hm[4];
                 if (MODE == 2) {  // the ReLU mask source, fetched before the accumulator read so that both latencies overlap
                     if (in_range) {
-                        const uint4* src = reinterpret_cast<const uint4*>(p.h0 + (size_t)row * H + ch * 32);
+                        const uint4* src = reinterpret_cast<const uint4*>(p.h0 + (size_t)row * (p.mask_ld ? p.mask_ld : H) + ch * 32);
 #pragma unroll
                         for (int i = 0; i < 4; ++i) hm[i] = __ldg(src + i);
                     } else {
@@ -170,8 +174,21 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                         for (int i = 0; i < 4; ++i) hm[i] = make_uint4(0, 0, 0, 0);
                     }
                 }
+                float4 pv[8];
+                const bool has_prev = MODE != 0 && p.prev != nullptr && in_range;
+                if (has_prev) {
+                    const float4* src = reinterpret_cast<const float4*>(p.prev + (size_t)row * H + ch * 32);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) pv[i] = __ldg(src + i);
+                }
                 float v[32];
                 tmem_ld_32x32(taddr + ch * 32, v);
+                if (has_prev) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        v[4 * i] += pv[i].x; v[4 * i + 1] += pv[i].y; v[4 * i + 2] += pv[i].z; v[4 * i + 3] += pv[i].w;
+                    }
+                }
                 if (MODE == 0) {
                     if (in_range) {
                         float4* dst = reinterpret_cast<float4*>(p.out_f32 + (size_t)row * H + ch * 32);
@@ -217,7 +234,7 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                         }
                     }
                     if (in_range) {
-                        bf16* dstp = (MODE == 1 ? p.h1 : p.g0) + (size_t)row * H + ch * 32;
+                        bf16* dstp = (MODE == 1 ? p.h1 : p.g0) + (size_t)row * (p.out_ld ? p.out_ld : H) + ch * 32;
                         uint4* dst = reinterpret_cast<uint4*>(dstp);
 #pragma unroll
                         for (int i = 0; i < 4; ++i)
@@ -372,21 +389,21 @@ k2_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
 // W1 fp32 [256 (i), 256 (j)] -> bf16 copies: w1[i][j] (K-major for dX, where k = j)
 // and w1t[j][i] (K-major for the forward pass, where k = i).
-__global__ void convert_w1_kernel(const float* __restrict__ W1, bf16* __restrict__ w1, bf16* __restrict__ w1t) {
+__global__ void convert_w1_kernel(const float* __restrict__ W1, bf16* __restrict__ w1, bf16* __restrict__ w1t, int hh) {
     __shared__ float tile[32][33];
     int bx = blockIdx.x * 32, by = blockIdx.y * 32;
     for (int r = threadIdx.y; r < 32; r += blockDim.y) {
-        float v = W1[(size_t)(by + r) * H + bx + threadIdx.x];
+        float v = W1[(size_t)(by + r) * hh + bx + threadIdx.x];
         tile[r][threadIdx.x] = v;
-        w1[(size_t)(by + r) * H + bx + threadIdx.x] = __float2bfloat16_rn(v);
+        w1[(size_t)(by + r) * hh + bx + threadIdx.x] = __float2bfloat16_rn(v);
     }
     __syncthreads();
     for (int r = threadIdx.y; r < 32; r += blockDim.y)
-        w1t[(size_t)(bx + r) * H + by + threadIdx.x] = __float2bfloat16_rn(tile[threadIdx.x][r]);
+        w1t[(size_t)(bx + r) * hh + by + threadIdx.x] = __float2bfloat16_rn(tile[threadIdx.x][r]);
 }
 
 int convert_w1(const float* W1, bf16* w1, bf16* w1t, cudaStream_t st) {
-    MRL_LAUNCH(convert_w1_kernel, dim3(H / 32, H / 32), dim3(32, 8), 0, st, W1, w1, w1t);
+    MRL_LAUNCH(convert_w1_kernel, dim3(H / 32, H / 32), dim3(32, 8), 0, st, W1, w1, w1t, H);
     return MRL_OK;
 }
 
@@ -428,8 +445,8 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 }
 
 // First layer (LinearReLU / LinearTanh[obs, 256], K = obs_dim): h0 = act(x . W0 + b0) in bf16, row-major.
-template <int IN>
-__global__ void __launch_bounds__(H)
+template <int IN, int HH>
+__global__ void __launch_bounds__(HH)
 l0_forward_kernel(const float* __restrict__ x, const float* __restrict__ W0, const float* __restrict__ b0,
                   bf16* __restrict__ h0, int M, int rows_per_block, int act) {
     const VecMap vm;
@@ -438,12 +455,12 @@ l0_forward_kernel(const float* __restrict__ x, const float* __restrict__ W0, con
     for (int u = 0; u < 8; ++u) {
         b[u] = b0[vm.col0 + u];
 #pragma unroll
-        for (int k = 0; k < IN; ++k) w[k][u] = W0[k * H + vm.col0 + u];
+        for (int k = 0; k < IN; ++k) w[k][u] = W0[k * HH + vm.col0 + u];
     }
     const int rb = blockIdx.x * rows_per_block;
     const int re = min(M, rb + rows_per_block);
     extern __shared__ float s_rows[];  // the slab's x rows: (re - rb) * IN floats
-    for (int i = threadIdx.x; i < (re - rb) * IN; i += H) s_rows[i] = x[(size_t)rb * IN + i];
+    for (int i = threadIdx.x; i < (re - rb) * IN; i += HH) s_rows[i] = x[(size_t)rb * IN + i];
     __syncthreads();
 #pragma unroll 2
     for (int r = rb + vm.row_lane; r < re; r += 8) {
@@ -458,7 +475,7 @@ l0_forward_kernel(const float* __restrict__ x, const float* __restrict__ W0, con
             for (int k = 0; k < IN; ++k) acc = fmaf(xr[k], w[k][u], acc);
             hv[u] = act == 0 ? fmaxf(acc, 0.0f) : tanh_fast(acc);
         }
-        *reinterpret_cast<uint4*>(h0 + (size_t)r * H + vm.col0) = pack8(hv);
+        *reinterpret_cast<uint4*>(h0 + (size_t)r * HH + vm.col0) = pack8(hv);
     }
 }
 
@@ -466,8 +483,8 @@ l0_forward_kernel(const float* __restrict__ x, const float* __restrict__ W0, con
 //   g1[r][j]  = act'(h1[r][j]) * sum_a dout[r][a] * W2[j][a]        (dX of the head; ReLU mask or 1 - h1^2)
 //   dW2[j][a] = sum_r h1[r][j] * dout[r][a],  db2[a] = sum_r dout[r][a],  db1[j] = sum_r g1[r][j]
 // part layout per block: [OUT][256] dW2^T, [256] db1, [OUT] db2.
-template <int OUT>
-__global__ void __launch_bounds__(H)
+template <int OUT, int HH>
+__global__ void __launch_bounds__(HH)
 head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout, int ldd,
                      const float* __restrict__ W2, int out_dim, bf16* __restrict__ g1,
                      float* __restrict__ part, int M, int rows_per_block, int act) {
@@ -487,7 +504,7 @@ head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout
     const int rb = blockIdx.x * rows_per_block;
     const int re = min(M, rb + rows_per_block);
     extern __shared__ float s_rows[];  // the slab's dout rows: (re - rb) * OUT floats
-    for (int i = threadIdx.x; i < (re - rb) * OUT; i += H) {
+    for (int i = threadIdx.x; i < (re - rb) * OUT; i += HH) {
         int rr = i / OUT, a = i % OUT;
         s_rows[i] = a < out_dim ? dout[(size_t)(rb + rr) * ldd + a] : 0.0f;
     }
@@ -498,7 +515,7 @@ head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout
 #pragma unroll
         for (int i = 0; i < UNR; ++i) {
             const int r = r0 + 8 * i;
-            raw[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(h1 + (size_t)r * H + vm.col0)) : make_uint4(0, 0, 0, 0);
+            raw[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(h1 + (size_t)r * HH + vm.col0)) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
         for (int i = 0; i < UNR; ++i) {
@@ -522,32 +539,32 @@ head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout
                 g[u] = act == 0 ? (h[u] > 0.0f ? dh : 0.0f) : dh * (1.0f - h[u] * h[u]);
                 db1[u] += g[u];
             }
-            *reinterpret_cast<uint4*>(g1 + (size_t)r * H + vm.col0) = pack8(g);
+            *reinterpret_cast<uint4*>(g1 + (size_t)r * HH + vm.col0) = pack8(g);
         }
     }
-    float* pb = part + (size_t)blockIdx.x * ((OUT + 1) * H + OUT);
+    float* pb = part + (size_t)blockIdx.x * ((OUT + 1) * HH + OUT);
 #pragma unroll
     for (int a = 0; a < OUT; ++a)
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             float v = sum_row_lanes(dw2[a][u]);
-            if (vm.row_lane == 0) pb[a * H + vm.col0 + u] = v;
+            if (vm.row_lane == 0) pb[a * HH + vm.col0 + u] = v;
         }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
         float v = sum_row_lanes(db1[u]);
-        if (vm.row_lane == 0) pb[OUT * H + vm.col0 + u] = v;
+        if (vm.row_lane == 0) pb[OUT * HH + vm.col0 + u] = v;
     }
 #pragma unroll
     for (int a = 0; a < OUT; ++a) {
         float v = sum_row_lanes(db2[a]);  // every column group sees every row: take column group 0
-        if (threadIdx.x == 0) pb[(OUT + 1) * H + a] = v;
+        if (threadIdx.x == 0) pb[(OUT + 1) * HH + a] = v;
     }
 }
 
 // dW0[k][j] = sum_r x[r][k] * g0[r][j], db0[j] = sum_r g0[r][j]; part per block: [IN + 1][256].
-template <int IN>
-__global__ void __launch_bounds__(H)
+template <int IN, int HH>
+__global__ void __launch_bounds__(HH)
 l0_backward_kernel(const bf16* __restrict__ g0, const float* __restrict__ x, float* __restrict__ part, int M,
                    int rows_per_block) {
     const VecMap vm;
@@ -561,7 +578,7 @@ l0_backward_kernel(const bf16* __restrict__ g0, const float* __restrict__ x, flo
     const int rb = blockIdx.x * rows_per_block;
     const int re = min(M, rb + rows_per_block);
     extern __shared__ float s_rows[];  // the slab's x rows
-    for (int i = threadIdx.x; i < (re - rb) * IN; i += H) s_rows[i] = x[(size_t)rb * IN + i];
+    for (int i = threadIdx.x; i < (re - rb) * IN; i += HH) s_rows[i] = x[(size_t)rb * IN + i];
     __syncthreads();
     constexpr int UNR = 4;
     for (int r0 = rb + vm.row_lane; r0 < re; r0 += 8 * UNR) {
@@ -569,7 +586,7 @@ l0_backward_kernel(const bf16* __restrict__ g0, const float* __restrict__ x, flo
 #pragma unroll
         for (int i = 0; i < UNR; ++i) {
             const int r = r0 + 8 * i;
-            raw[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(g0 + (size_t)r * H + vm.col0)) : make_uint4(0, 0, 0, 0);
+            raw[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(g0 + (size_t)r * HH + vm.col0)) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
         for (int i = 0; i < UNR; ++i) {
@@ -587,18 +604,18 @@ l0_backward_kernel(const bf16* __restrict__ g0, const float* __restrict__ x, flo
             }
         }
     }
-    float* pb = part + (size_t)blockIdx.x * (IN + 1) * H;
+    float* pb = part + (size_t)blockIdx.x * (IN + 1) * HH;
 #pragma unroll
     for (int k = 0; k < IN; ++k)
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             float v = sum_row_lanes(dw[k][u]);
-            if (vm.row_lane == 0) pb[k * H + vm.col0 + u] = v;
+            if (vm.row_lane == 0) pb[k * HH + vm.col0 + u] = v;
         }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
         float v = sum_row_lanes(db[u]);
-        if (vm.row_lane == 0) pb[IN * H + vm.col0 + u] = v;
+        if (vm.row_lane == 0) pb[IN * HH + vm.col0 + u] = v;
     }
 }
 
@@ -651,7 +668,8 @@ __global__ void reduce_parts_kernel(const float* __restrict__ part, int nblocks,
 // Head parts -> dW2 [256][out_dim] (transposed from [OUT][256]), db2, and db1.
 __global__ void reduce_head_parts_kernel(const float* __restrict__ part, int nblocks, int OUT, int out_dim,
                                          float* __restrict__ dW2, float* __restrict__ db2,
-                                         float* __restrict__ db1) {
+                                         float* __restrict__ db1, int hh) {
+    const int H = hh;   // hidden width of this launch (shadows the 256 of the tensor-core tiles)
     const int i = blockIdx.x * 32 + (threadIdx.x & 31);
     const int stride = (OUT + 1) * H + OUT;
     float acc = block_sum_parts(part, nblocks, stride, i, i < stride);
@@ -664,6 +682,44 @@ __global__ void reduce_head_parts_kernel(const float* __restrict__ part, int nbl
     } else {
         int a = i - (OUT + 1) * H;
         if (a < out_dim) db2[a] = acc;
+    }
+}
+
+// out[(i / 256) * out_ld + i % 256] = sum_b part[b * 65536 + i]: one 256 x 256 block of a wider matrix.
+__global__ void reduce_parts_block_kernel(const float* __restrict__ part, int nblocks, float* __restrict__ out,
+                                          int out_ld) {
+    const int i = blockIdx.x * 32 + (threadIdx.x & 31);
+    float acc = block_sum_parts(part, nblocks, H * H, i, i < H * H);
+    if ((threadIdx.x >> 5) == 0 && i < H * H) out[(size_t)(i / H) * out_ld + (i % H)] = acc;
+}
+
+// Head of a network wider than 256 (the 256-wide path computes it in the GEMM epilogue):
+// out[r][a] = b2[a] + sum_j h1[r][j] * W2[j][a], one warp per row, fp32 accumulation, fixed order.
+template <int OUT>
+__global__ void __launch_bounds__(256)
+head_forward_kernel(const bf16* __restrict__ h1, int hh, const float* __restrict__ W2, const float* __restrict__ b2,
+                    int out_dim, float* __restrict__ out, int out_ld, int M) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= M) return;
+    float acc[OUT];
+#pragma unroll
+    for (int a = 0; a < OUT; ++a) acc[a] = 0.0f;
+    for (int c0 = lane * 8; c0 < hh; c0 += 256) {
+        float h[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(h1 + (size_t)row * hh + c0)), h);
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+#pragma unroll
+            for (int a = 0; a < OUT; ++a)
+                if (a < out_dim) acc[a] = fmaf(h[u], W2[(c0 + u) * out_dim + a], acc[a]);
+    }
+#pragma unroll
+    for (int a = 0; a < OUT; ++a) {
+        float v = acc[a];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0 && a < out_dim) out[(size_t)row * out_ld + a] = v + b2[a];
     }
 }
 
@@ -686,16 +742,19 @@ static int get_encode() {
     return MRL_OK;
 }
 
-// bf16 matrix [rows, cols] with cols contiguous; box = [box_rows, 64 cols], 128-byte swizzle.
-int make_tensor_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+// bf16 matrix [rows, cols] with cols contiguous and a row pitch of pitch_elems (0: cols) - a view into a
+// wider matrix when pitch_elems > cols; box = [box_rows, 64 cols], 128-byte swizzle.
+int make_tensor_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                    uint64_t pitch_elems) {
     int rc = get_encode();
     if (rc) return rc;
-    if (((uintptr_t)base & 15) || ((cols * 2) & 15)) {
+    if (pitch_elems == 0) pitch_elems = cols;
+    if (((uintptr_t)base & 15) || ((pitch_elems * 2) & 15)) {
         set_error("tensor map: base %p / row pitch %llu bytes not 16-byte aligned", base, (unsigned long long)cols * 2);
         return MRL_ERR_INVALID_ARG;
     }
     cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {cols * 2};
+    cuuint64_t strides[1] = {pitch_elems * 2};
     cuuint32_t box[2] = {64, box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
@@ -777,35 +836,48 @@ static int launch_k2(const CUtensorMap& tmA, const CUtensorMap& tmB, int Ktot, f
 int max_splits() { return sm_count(); }
 
 bool supported(const mrl_net_spec* net, int batch) {
-    return net->hidden_dim == H && (net->activation == MRL_ACT_RELU || net->activation == MRL_ACT_TANH) &&
-           (net->head == MRL_HEAD_LINEAR || net->head == MRL_HEAD_STOCHASTIC_ACTOR) && net->out_dim <= 8 && (net->in_dim == 4 || net->in_dim == 8 || net->in_dim == 24) && batch % 32 == 0;
+    return (net->hidden_dim == H || net->hidden_dim == 2 * H) &&
+           (net->activation == MRL_ACT_RELU || net->activation == MRL_ACT_TANH) &&
+           (net->head == MRL_HEAD_LINEAR || net->head == MRL_HEAD_STOCHASTIC_ACTOR) && net->out_dim <= 8 &&
+           (net->in_dim == 4 || net->in_dim == 8 || net->in_dim == 17 || net->in_dim == 24) && batch % 32 == 0;
 }
 
-int64_t workspace_bytes(int batch) {
-    int64_t act = (int64_t)batch * H * 2;                 // one bf16 activation array
+int64_t workspace_bytes(int batch, int hidden) {
+    int64_t act = (int64_t)batch * hidden * 2;            // one bf16 activation array
     int64_t parts = (int64_t)max_splits() * H * H * 4;    // K2 partials (also reused by the small reductions)
-    return 4 * act + 2 * (int64_t)H * H * 2 + parts + 4096;
+    int64_t small_parts = (int64_t)4 * sm_count() * (25 * (int64_t)hidden + 8) * 4;   // l0 / head partials per block
+    if (small_parts > parts) parts = small_parts;
+    int64_t tmp = hidden > H ? (int64_t)batch * H * 4 : 0;   // fp32 result of the first 256-wide K block
+    return 4 * act + 2 * (int64_t)hidden * hidden * 2 + parts + tmp + 4096;
 }
 
-int State::init(void* workspace, int batch_, int* err_flag) {
+int State::init(void* workspace, int batch_, int hidden, int* err_flag) {
     batch = batch_;
+    hh = hidden;
+    nb = hidden / H;
     err = err_flag;
     uint8_t* p = (uint8_t*)workspace;
-    int64_t act = (int64_t)batch * H * 2;
+    int64_t act = (int64_t)batch * hh * 2;
     h0 = (bf16*)p; p += act;
     h1 = (bf16*)p; p += act;
     g1 = (bf16*)p; p += act;
     g0 = (bf16*)p; p += act;
-    w1 = (bf16*)p; p += H * H * 2;
-    w1t = (bf16*)p; p += H * H * 2;
+    w1 = (bf16*)p; p += (int64_t)hh * hh * 2;
+    w1t = (bf16*)p; p += (int64_t)hh * hh * 2;
+    tmp = nullptr;
+    if (nb > 1) { tmp = (float*)p; p += (int64_t)batch * H * 4; }
     part = (float*)p;
     int rc;
-    if ((rc = make_tensor_map(&tm_h0, h0, batch, H, TILE_M))) return rc;
-    if ((rc = make_tensor_map(&tm_g1, g1, batch, H, TILE_M))) return rc;
-    if ((rc = make_tensor_map(&tm_w1t, w1t, H, H, H))) return rc;
-    if ((rc = make_tensor_map(&tm_w1, w1, H, H, H))) return rc;
-    if ((rc = make_tensor_map(&tm_h0_mn, h0, batch, H, 64))) return rc;
-    if ((rc = make_tensor_map(&tm_g1_mn, g1, batch, H, 64))) return rc;
+    for (int i = 0; i < nb; ++i) {      // 256-wide column blocks of the activations, K-major and MN-major views
+        if ((rc = make_tensor_map(&tm_h0[i], h0 + i * H, batch, H, TILE_M, hh))) return rc;
+        if ((rc = make_tensor_map(&tm_g1[i], g1 + i * H, batch, H, TILE_M, hh))) return rc;
+        if ((rc = make_tensor_map(&tm_h0_mn[i], h0 + i * H, batch, H, 64, hh))) return rc;
+        if ((rc = make_tensor_map(&tm_g1_mn[i], g1 + i * H, batch, H, 64, hh))) return rc;
+        for (int j = 0; j < nb; ++j) {  // [n block i][k block j] of W1^T (forward) and of W1 (dX)
+            if ((rc = make_tensor_map(&tm_w1t[i][j], w1t + ((size_t)i * H) * hh + j * H, H, H, H, hh))) return rc;
+            if ((rc = make_tensor_map(&tm_w1[i][j], w1 + ((size_t)i * H) * hh + j * H, H, H, H, hh))) return rc;
+        }
+    }
     return MRL_OK;
 }
 
@@ -828,49 +900,106 @@ __global__ void log_std_grad_kernel(const float* __restrict__ dout, int ldd, int
     if (threadIdx.x == 0) out[j] = (float)acc;
 }
 
-template <int IN>
+template <int IN, int HH>
 static int l0_forward(const float* x, const float* W0, const float* b0, bf16* h0, int M, int act, cudaStream_t st) {
     const int rows_per_block = slab_rows(M, IN);
-    MRL_LAUNCH((l0_forward_kernel<IN>), (M + rows_per_block - 1) / rows_per_block, H, rows_per_block * IN * 4, st, x,
-               W0, b0, h0, M, rows_per_block, act);
+    MRL_LAUNCH((l0_forward_kernel<IN, HH>), (M + rows_per_block - 1) / rows_per_block, HH, rows_per_block * IN * 4, st,
+               x, W0, b0, h0, M, rows_per_block, act);
     return MRL_OK;
+}
+template <int HH>
+static int l0_forward_any(int I, const float* x, const float* W0, const float* b0, bf16* h0, int M, int act,
+                          cudaStream_t st) {
+    if (I == 4) return l0_forward<4, HH>(x, W0, b0, h0, M, act, st);
+    if (I == 8) return l0_forward<8, HH>(x, W0, b0, h0, M, act, st);
+    if (I == 17) return l0_forward<17, HH>(x, W0, b0, h0, M, act, st);
+    return l0_forward<24, HH>(x, W0, b0, h0, M, act, st);
+}
+template <int OUT, int HH>
+static int head_backward(const bf16* h1, const float* dout, int ldd, const float* W2, int O, bf16* g1, float* part,
+                         int batch, int rows_per_block, int nblocks, int act, cudaStream_t st) {
+    MRL_LAUNCH((head_backward_kernel<OUT, HH>), nblocks, HH, rows_per_block * OUT * 4, st, h1, dout, ldd, W2, O, g1, part,
+               batch, rows_per_block, act);
+    return MRL_OK;
+}
+template <int HH>
+static int head_backward_any(int OUT, const bf16* h1, const float* dout, int ldd, const float* W2, int O, bf16* g1,
+                             float* part, int batch, int rows_per_block, int nblocks, int act, cudaStream_t st) {
+    if (OUT == 1) return head_backward<1, HH>(h1, dout, ldd, W2, O, g1, part, batch, rows_per_block, nblocks, act, st);
+    if (OUT == 2) return head_backward<2, HH>(h1, dout, ldd, W2, O, g1, part, batch, rows_per_block, nblocks, act, st);
+    if (OUT == 4) return head_backward<4, HH>(h1, dout, ldd, W2, O, g1, part, batch, rows_per_block, nblocks, act, st);
+    return head_backward<8, HH>(h1, dout, ldd, W2, O, g1, part, batch, rows_per_block, nblocks, act, st);
+}
+template <int IN, int HH>
+static int l0_backward(const bf16* g0, const float* x, float* part, int batch, int rows_per_block, int nblocks,
+                       cudaStream_t st) {
+    MRL_LAUNCH((l0_backward_kernel<IN, HH>), nblocks, HH, rows_per_block * IN * 4, st, g0, x, part, batch,
+               rows_per_block);
+    return MRL_OK;
+}
+template <int HH>
+static int l0_backward_any(int I, const bf16* g0, const float* x, float* part, int batch, int rows_per_block,
+                           int nblocks, cudaStream_t st) {
+    if (I == 4) return l0_backward<4, HH>(g0, x, part, batch, rows_per_block, nblocks, st);
+    if (I == 8) return l0_backward<8, HH>(g0, x, part, batch, rows_per_block, nblocks, st);
+    if (I == 17) return l0_backward<17, HH>(g0, x, part, batch, rows_per_block, nblocks, st);
+    return l0_backward<24, HH>(g0, x, part, batch, rows_per_block, nblocks, st);
 }
 
 int State::forward(const mrl_net_spec* net, const float* params, const float* x, float* head_out, cudaStream_t st) {
     const int I = net->in_dim, O = net->out_dim;
-    const float* W0 = params; const float* b0 = W0 + (size_t)I * H;
-    const float* W1 = b0 + H; const float* b1 = W1 + (size_t)H * H;
-    const float* W2 = b1 + H; const float* b2 = W2 + (size_t)H * O;
+    const float* W0 = params; const float* b0 = W0 + (size_t)I * hh;
+    const float* W1 = b0 + hh; const float* b1 = W1 + (size_t)hh * hh;
+    const float* W2 = b1 + hh; const float* b2 = W2 + (size_t)hh * O;
     prof_mark("(other)", st);
-    MRL_LAUNCH(convert_w1_kernel, dim3(H / 32, H / 32), dim3(32, 8), 0, st, W1, w1, w1t);
+    MRL_LAUNCH(convert_w1_kernel, dim3(hh / 32, hh / 32), dim3(32, 8), 0, st, W1, w1, w1t, hh);
     prof_mark("convert_w1", st);
     int rc;
     const int act = net->activation == MRL_ACT_RELU ? 0 : 1;
     const bool gaussian = net->head == MRL_HEAD_STOCHASTIC_ACTOR;
-    if (I == 4) rc = l0_forward<4>(x, W0, b0, h0, batch, act, st);
-    else if (I == 8) rc = l0_forward<8>(x, W0, b0, h0, batch, act, st);
-    else rc = l0_forward<24>(x, W0, b0, h0, batch, act, st);
+    const int head_ld = gaussian ? 2 * O : O;
+    rc = nb == 1 ? l0_forward_any<256>(I, x, W0, b0, h0, batch, act, st)
+                 : l0_forward_any<512>(I, x, W0, b0, h0, batch, act, st);
     if (rc) return rc;
     prof_mark("l0_forward", st);
-    K1Params p{};
-    p.M = batch; p.bias = b1; p.W2 = W2; p.b2 = b2; p.out_dim = O; p.h1 = h1; p.head_out = head_out;
-    p.head_ld = gaussian ? 2 * O : O;
-    p.act = act;
-    p.err = err;
-    rc = launch_k1_forward(tm_h0, tm_w1t, p, st);
-    if (rc) return rc;
+    if (nb == 1) {
+        K1Params p{};
+        p.M = batch; p.bias = b1; p.W2 = W2; p.b2 = b2; p.out_dim = O; p.h1 = h1; p.head_out = head_out;
+        p.head_ld = head_ld;
+        p.act = act;
+        p.err = err;
+        if ((rc = launch_k1_forward(tm_h0[0], tm_w1t[0][0], p, st))) return rc;
+    } else {
+        // h1[:, n block] = act(h0[:, k block 0] W1[k0, n] + h0[:, k block 1] W1[k1, n] + b1[n block]):
+        // the first launch leaves its fp32 product in tmp, the second adds it before the epilogue.
+        for (int n = 0; n < nb; ++n) {
+            K1Params p0{};
+            p0.M = batch; p0.out_f32 = tmp; p0.err = err;
+            if ((rc = launch_k1<0, 1>(tm_h0[0], tm_w1t[n][0], p0, st))) return rc;
+            K1Params p{};
+            p.M = batch; p.bias = b1 + n * H; p.W2 = W2; p.b2 = b2; p.out_dim = 0; p.h1 = h1 + n * H;
+            p.head_out = head_out; p.head_ld = head_ld; p.act = act; p.prev = tmp; p.out_ld = hh; p.err = err;
+            if ((rc = launch_k1<1, 1>(tm_h0[1], tm_w1t[n][1], p, st))) return rc;
+        }
+        const int OUT = O <= 1 ? 1 : (O <= 2 ? 2 : (O <= 4 ? 4 : 8));
+        const int grid = (batch + 7) / 8;
+        if (OUT == 1) { MRL_LAUNCH((head_forward_kernel<1>), grid, 256, 0, st, h1, hh, W2, b2, O, head_out, head_ld, batch); }
+        else if (OUT == 2) { MRL_LAUNCH((head_forward_kernel<2>), grid, 256, 0, st, h1, hh, W2, b2, O, head_out, head_ld, batch); }
+        else if (OUT == 4) { MRL_LAUNCH((head_forward_kernel<4>), grid, 256, 0, st, h1, hh, W2, b2, O, head_out, head_ld, batch); }
+        else { MRL_LAUNCH((head_forward_kernel<8>), grid, 256, 0, st, h1, hh, W2, b2, O, head_out, head_ld, batch); }
+    }
     if (gaussian) {  // columns O..2O-1 carry the clamped state-independent log_std (stochastic_actor.mojo:386-575)
         MRL_LAUNCH(fill_log_std_cols_kernel, ceil_div((int64_t)batch * O, 256), 256, 0, st, b2 + O, head_out, batch, O);
     }
     prof_mark("k1_forward_gemm", st);
-    return rc;
+    return MRL_OK;
 }
 
 int State::backward(const mrl_net_spec* net, const float* params, const float* x, const float* dout, float* grads,
                     cudaStream_t st) {
     const int I = net->in_dim, O = net->out_dim;
-    const size_t oW0 = 0, ob0 = (size_t)I * H, oW1 = ob0 + H, ob1 = oW1 + (size_t)H * H, oW2 = ob1 + H,
-                 ob2 = oW2 + (size_t)H * O;
+    const size_t oW0 = 0, ob0 = (size_t)I * hh, oW1 = ob0 + hh, ob1 = oW1 + (size_t)hh * hh, oW2 = ob1 + hh,
+                 ob2 = oW2 + (size_t)hh * O;
     const float* W2 = params + oW2;
     const int act = net->activation == MRL_ACT_RELU ? 0 : 1;
     const bool gaussian = net->head == MRL_HEAD_STOCHASTIC_ACTOR;
@@ -878,39 +1007,56 @@ int State::backward(const mrl_net_spec* net, const float* params, const float* x
     const int rows_per_block = slab_rows(batch, I > 8 ? I : 8);
     const int nblocks = (batch + rows_per_block - 1) / rows_per_block;
     const int OUT = O <= 1 ? 1 : (O <= 2 ? 2 : (O <= 4 ? 4 : 8));
-    if (OUT == 1) { MRL_LAUNCH((head_backward_kernel<1>), nblocks, H, rows_per_block * 1 * 4, st, h1, dout, ldd, W2, O, g1, part, batch, rows_per_block, act); }
-    else if (OUT == 2) { MRL_LAUNCH((head_backward_kernel<2>), nblocks, H, rows_per_block * 2 * 4, st, h1, dout, ldd, W2, O, g1, part, batch, rows_per_block, act); }
-    else if (OUT == 4) { MRL_LAUNCH((head_backward_kernel<4>), nblocks, H, rows_per_block * 4 * 4, st, h1, dout, ldd, W2, O, g1, part, batch, rows_per_block, act); }
-    else { MRL_LAUNCH((head_backward_kernel<8>), nblocks, H, rows_per_block * 8 * 4, st, h1, dout, ldd, W2, O, g1, part, batch, rows_per_block, act); }
+    int rc = nb == 1 ? head_backward_any<256>(OUT, h1, dout, ldd, W2, O, g1, part, batch, rows_per_block, nblocks, act, st)
+                     : head_backward_any<512>(OUT, h1, dout, ldd, W2, O, g1, part, batch, rows_per_block, nblocks, act, st);
+    if (rc) return rc;
     prof_mark("head_backward", st);
-    const int hstride = (OUT + 1) * H + OUT;
+    const int hstride = (OUT + 1) * hh + OUT;
     MRL_LAUNCH(reduce_head_parts_kernel, ceil_div(hstride, 32), 256, 0, st, part, nblocks, OUT, O, grads + oW2,
-               grads + ob2, grads + ob1);
+               grads + ob2, grads + ob1, hh);
     if (gaussian) {  // dlog_std[j] = sum over rows of dout[:, O + j] (stochastic_actor.mojo:727-966)
         MRL_LAUNCH(log_std_grad_kernel, O, 256, 0, st, dout, ldd, O, batch, grads + ob2 + O);
     }
     prof_mark("reduce_head", st);
     // dh0 = g1 . W1^T times the activation derivative at h0 -> g0
-    K1Params p{};
-    p.M = batch; p.h0 = h0; p.g0 = g0; p.act = act; p.err = err;
-    int rc = launch_k1<2, 1>(tm_g1, tm_w1, p, st);
-    if (rc) return rc;
+    if (nb == 1) {
+        K1Params p{};
+        p.M = batch; p.h0 = h0; p.g0 = g0; p.act = act; p.err = err;
+        if ((rc = launch_k1<2, 1>(tm_g1[0], tm_w1[0][0], p, st))) return rc;
+    } else {
+        for (int i = 0; i < nb; ++i) {   // output block i of g0: sum over the two column blocks of g1
+            K1Params p0{};
+            p0.M = batch; p0.out_f32 = tmp; p0.err = err;
+            if ((rc = launch_k1<0, 1>(tm_g1[0], tm_w1[i][0], p0, st))) return rc;
+            K1Params p{};
+            p.M = batch; p.h0 = h0 + i * H; p.g0 = g0 + i * H; p.act = act; p.prev = tmp; p.out_ld = hh; p.mask_ld = hh;
+            p.err = err;
+            if ((rc = launch_k1<2, 1>(tm_g1[1], tm_w1[i][1], p, st))) return rc;
+        }
+    }
     prof_mark("k1_dx_gemm", st);
     // dW0, db0
-    if (I == 4) { MRL_LAUNCH((l0_backward_kernel<4>), nblocks, H, rows_per_block * 4 * 4, st, g0, x, part, batch, rows_per_block); }
-    else if (I == 8) { MRL_LAUNCH((l0_backward_kernel<8>), nblocks, H, rows_per_block * 8 * 4, st, g0, x, part, batch, rows_per_block); }
-    else { MRL_LAUNCH((l0_backward_kernel<24>), nblocks, H, rows_per_block * 24 * 4, st, g0, x, part, batch, rows_per_block); }
-    prof_mark("l0_backward", st);
-    MRL_LAUNCH(reduce_parts_kernel, ceil_div((I + 1) * H, 32), 256, 0, st, part, nblocks, (I + 1) * H, (I + 1) * H,
-               grads + oW0);  // dW0 [I][256] then db0 [256] are adjacent in the gradient vector
-    prof_mark("reduce_l0", st);
-    // dW1 = h0^T . g1 (split-K over the SMs), then the fixed-order reduction
-    int splits = 0;
-    rc = launch_k2<true>(tm_h0_mn, tm_g1_mn, batch, part, &splits, err, st);
+    rc = nb == 1 ? l0_backward_any<256>(I, g0, x, part, batch, rows_per_block, nblocks, st)
+                 : l0_backward_any<512>(I, g0, x, part, batch, rows_per_block, nblocks, st);
     if (rc) return rc;
-    prof_mark("k2_dw_gemm", st);
-    MRL_LAUNCH(reduce_parts_kernel, ceil_div(H * H, 32), 256, 0, st, part, splits, H * H, H * H, grads + oW1);
-    prof_mark("reduce_dw1", st);
+    prof_mark("l0_backward", st);
+    MRL_LAUNCH(reduce_parts_kernel, ceil_div((I + 1) * hh, 32), 256, 0, st, part, nblocks, (I + 1) * hh, (I + 1) * hh,
+               grads + oW0);  // dW0 [I][hidden] then db0 [hidden] are adjacent in the gradient vector
+    prof_mark("reduce_l0", st);
+    // dW1 = h0^T . g1 (split-K over the SMs) in 256 x 256 blocks, each followed by its fixed-order reduction
+    for (int i = 0; i < nb; ++i)
+        for (int j = 0; j < nb; ++j) {
+            int splits = 0;
+            if ((rc = launch_k2<true>(tm_h0_mn[i], tm_g1_mn[j], batch, part, &splits, err, st))) return rc;
+            prof_mark("k2_dw_gemm", st);
+            if (nb == 1) {
+                MRL_LAUNCH(reduce_parts_kernel, ceil_div(H * H, 32), 256, 0, st, part, splits, H * H, H * H, grads + oW1);
+            } else {
+                MRL_LAUNCH(reduce_parts_block_kernel, ceil_div(H * H, 32), 256, 0, st, part, splits,
+                           grads + oW1 + ((size_t)i * H) * hh + j * H, hh);
+            }
+            prof_mark("reduce_dw1", st);
+        }
     return MRL_OK;
 }
 

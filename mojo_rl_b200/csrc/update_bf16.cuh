@@ -11,20 +11,24 @@ constexpr int H = 256;  // hidden width this path is specialised for
 // True when the network / minibatch shape is covered by the tensor-core kernels.
 bool supported(const mrl_net_spec* net, int batch);
 // Bytes of device workspace State::init needs for minibatches of `batch` rows.
-int64_t workspace_bytes(int batch);
+int64_t workspace_bytes(int batch, int hidden);
 int max_splits();
-int make_tensor_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
+int make_tensor_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                    uint64_t pitch_elems = 0);
 
 // Activation buffers, bf16 weight copies and TMA descriptors of one minibatch
 // shape; shared by the actor and the critic, which run one after the other.
 struct State {
     int batch;
     int* err;  // device word: 0, or the code of the first wait that gave up
-    __nv_bfloat16 *h0, *h1, *g1, *g0, *w1, *w1t;
+    int hh, nb;  // hidden width (256 or 512) and its number of 256-wide blocks
+    __nv_bfloat16 *h0, *h1, *g1, *g0, *w1, *w1t;   // activations [batch, hh]; W1 and W1^T as bf16 [hh, hh]
     float* part;
-    CUtensorMap tm_h0, tm_g1, tm_w1t, tm_w1, tm_h0_mn, tm_g1_mn;
+    float* tmp;  // hh = 512: fp32 [batch, 256] product of the first K block
+    CUtensorMap tm_h0[2], tm_g1[2], tm_h0_mn[2], tm_g1_mn[2];   // 256-wide column blocks of the activations
+    CUtensorMap tm_w1t[2][2], tm_w1[2][2];                       // [row block][column block] of W1^T and W1
 
-    int init(void* workspace, int batch, int* err_flag);
+    int init(void* workspace, int batch, int hidden, int* err_flag);
     // head_out [batch, out_dim] = logits / values (fp32)
     int forward(const mrl_net_spec* net, const float* params, const float* x, float* head_out, cudaStream_t st);
     // grads [PARAM_SIZE] is overwritten (fp32, reference parameter order)

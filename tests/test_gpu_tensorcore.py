@@ -75,16 +75,18 @@ def test_splitk_gemm_from_row_major_activations(K):
     assert torch.allclose(got, want, rtol=1e-3, atol=1e-4 * scale), float((got - want).abs().max())
 
 
-@pytest.mark.parametrize("kind,obs,out,act,head", [(2, 8, 4, 0, 0), (3, 24, 4, 1, 1)])
-def test_update_precision1_matches_fp32_gradients(kind, obs, out, act, head):
+@pytest.mark.parametrize("kind,obs,out,act,head,hidden", [(2, 8, 4, 0, 0, 256), (3, 24, 4, 1, 1, 256),
+                                                            (4, 17, 6, 1, 1, 512), (2, 8, 4, 0, 0, 512)])
+def test_update_precision1_matches_fp32_gradients(kind, obs, out, act, head, hidden):
     """Same rollout, same permutation, one minibatch: the bf16 tensor-core update's
     gradients agree with the fp32 path to bf16 accuracy, and training state advances.
-    LunarLander: ReLU nets, categorical head; BipedalWalker: tanh nets, Gaussian head."""
+    LunarLander: ReLU nets, categorical head; BipedalWalker: tanh nets, Gaussian head; HalfCheetah: hidden
+    width 512, computed in 256-wide tensor-core blocks."""
     from _gpu import GpuAgent
     from _util import NetSpec, default_config, xavier_params
     rng = np.random.default_rng(0)
-    pa = xavier_params(NetSpec(obs, 256, out, act, head), rng) * (3 if head == 0 else 1)
-    pc = xavier_params(NetSpec(obs, 256, 1, act, 0), rng)
+    pa = xavier_params(NetSpec(obs, hidden, out, act, head), rng) * (3 if head == 0 else 1)
+    pc = xavier_params(NetSpec(obs, hidden, 1, act, 0), rng)
     if head == 1:
         pa[-out:] = -0.5
     total = 256 * 32
@@ -92,7 +94,7 @@ def test_update_precision1_matches_fp32_gradients(kind, obs, out, act, head):
     grads = {}
     params = {}
     for prec in (0, 1):
-        cfg = default_config(env_kind=kind, n_envs=256, rollout_len=32, hidden_dim=256, minibatch_size=total,
+        cfg = default_config(env_kind=kind, n_envs=256, rollout_len=32, hidden_dim=hidden, minibatch_size=total,
                              num_epochs=1, target_kl=0.0, precision=prec, max_grad_norm=0.0)
         g = GpuAgent(cfg)
         try:
@@ -110,7 +112,8 @@ def test_update_precision1_matches_fp32_gradients(kind, obs, out, act, head):
         a, b = grads[1][which], grads[0][which]
         assert np.isfinite(a).all()
         denom = np.abs(b).max()
-        assert np.abs(a - b).max() <= 3e-2 * denom, (which, np.abs(a - b).max(), denom)
+        # bf16 rounding of 256 (512) products per sum: 3 % (5 %) of the largest entry
+        assert np.abs(a - b).max() <= (3e-2 if hidden == 256 else 5e-2) * denom, (which, np.abs(a - b).max(), denom)
         # cosine similarity of the whole gradient
         cos = float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b)))
         assert cos > 0.999, (which, cos)
