@@ -354,6 +354,10 @@ typedef enum mrl_buffer {
 int mrl_get_buffer(mrl_ctx* ctx, int which, float** device_ptr, int64_t* n_floats);
 /* Synchronous copy of one resident buffer to HOST memory (n_floats must match). */
 int mrl_read_buffer(mrl_ctx* ctx, int which, float* out_host, int64_t n_floats);
+/* The reverse copy: replaces one resident buffer by HOST data (n_floats must match), e.g. to replay a
+ * recorded rollout through mrl_ppo_gae / mrl_ppo_update.  No counterpart in the reference, whose
+ * train_gpu owns its buffers (ppo.mojo:1902-2060). */
+int mrl_write_buffer(mrl_ctx* ctx, int which, const float* in_host, int64_t n_floats);
 
 /* Device-side replacement of the host Fisher-Yates shuffle (ppo.mojo:2425-2434,
  * core/utils/shuffle.mojo:51-82): indices[i] = P_key(i), a keyed bijection of

@@ -103,6 +103,7 @@ SIGNATURES = {
     "mrl_ppo_update": (ctypes.c_int, [c_void_p, ctypes.c_float, ctypes.c_float, ctypes.c_float, c_void_p]),
     "mrl_get_buffer": (ctypes.c_int, [c_void_p, ctypes.c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(ctypes.c_int64)]),
     "mrl_read_buffer": (ctypes.c_int, [c_void_p, ctypes.c_int, c_void_p, ctypes.c_int64]),
+    "mrl_write_buffer": (ctypes.c_int, [c_void_p, ctypes.c_int, c_void_p, ctypes.c_int64]),
     "mrl_make_permutation": (ctypes.c_int, [ctypes.c_int64, ctypes.c_uint64, c_void_p, c_void_p]),
     "mrl_get_stats": (ctypes.c_int, [c_void_p, ctypes.POINTER(Stats)]),
     "mrl_drain_episodes": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_int]),

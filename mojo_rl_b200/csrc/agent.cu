@@ -479,7 +479,7 @@ extern "C" int mrl_create(mrl_ctx** out, const mrl_config* cfg) {
         rc = c->tc.init(c->tc_workspace, (int)B, cfg->hidden_dim, c->tc_err);
         if (rc) { mrl_destroy(c); return rc; }
         c->use_tc = true;
-        if (!c->continuous && tc::policy_supported(od, na, cfg->hidden_dim)) {
+        if (tc::policy_supported(od, c->continuous ? c->action_dim : na, cfg->hidden_dim)) {
             A_(policy_workspace, (size_t)tc::policy_workspace_bytes());
             rc = c->policy.init(c->policy_workspace, c->tc_err);
             if (rc) { mrl_destroy(c); return rc; }
@@ -607,7 +607,9 @@ static int rollout_launches(mrl_ctx* c) {
     }
     for (int t = 0; t < T; ++t) {
         if (c->use_tc_policy) {
-            tc::PolicyStepArgs pa{c->obs, c->actor_params, c->critic_params, N, c->obs_dim, A, t, c->cfg.deterministic,
+            tc::PolicyStepArgs pa{c->obs, c->actor_params, c->critic_params, N, c->obs_dim,
+                                  c->continuous ? c->action_dim : A, t, c->cfg.deterministic,
+                                  c->actor_net.activation == MRL_ACT_RELU ? 0 : 1, c->continuous ? 1 : 0,
                                   c->actions, c->values, c->r_obs, c->r_actions, c->r_log_probs, c->r_values,
                                   c->counters};
             if ((rc = c->policy.step(pa, st))) return rc;
@@ -869,6 +871,17 @@ extern "C" int mrl_read_buffer(mrl_ctx* c, int which, float* out_host, int64_t n
     MRL_CHECK_ARG(out_host && n_floats == n);
     MRL_CUDA_OK(cudaStreamSynchronize(c->stream));
     MRL_CUDA_OK(cudaMemcpy(out_host, p, sizeof(float) * n, cudaMemcpyDeviceToHost));
+    return MRL_OK;
+}
+
+extern "C" int mrl_write_buffer(mrl_ctx* c, int which, const float* in_host, int64_t n_floats) {
+    float* p = nullptr;
+    int64_t n = 0;
+    int rc = mrl_get_buffer(c, which, &p, &n);
+    if (rc) return rc;
+    MRL_CHECK_ARG(in_host && n_floats == n);
+    MRL_CUDA_OK(cudaStreamSynchronize(c->stream));
+    MRL_CUDA_OK(cudaMemcpy(p, in_host, sizeof(float) * n, cudaMemcpyHostToDevice));
     return MRL_OK;
 }
 

@@ -9,8 +9,11 @@
 //      cores (K = obs_dim) and write it as bf16 in the 128-byte-swizzled K-major
 //      layout the tensor core reads;
 //   3. one thread issues 16 tcgen05.mma (128 x 256 x 16) into TMEM;
-//   4. four warps read the accumulators, add b1, apply ReLU, contract with W2 in
-//      fp32 (logits / value), then the actor's threads sample the action.
+//   4. four warps read the accumulators, add b1, apply the activation, contract
+//      with W2 in fp32 (logits or Gaussian means / value), then the actor's
+//      threads sample the action (categorical, or Gaussian with the
+//      state-independent log_std that follows b2 in the parameter vector:
+//      ppo_continuous.mojo:2640-2690).
 // The fp32 path (precision 0) keeps the reference's summation order instead.
 #include "rollout.cuh"
 #include "update_bf16.cuh"
@@ -25,25 +28,26 @@ constexpr int P_THREADS = 256;
 constexpr int P_TILE = 128;
 constexpr int P_B_BYTES = H * H * 2;            // 131072: W1^T as four [256 x 64] chunks
 constexpr int P_A_BYTES = P_TILE * H * 2;       // 65536: h0 tile as four [128 x 64] chunks
-constexpr int P_MAX_IN = 8;
 constexpr int P_MAX_OUT = 4;
-// fp32 parameters in shared memory: W0 [IN][256], b0, b1, W2 [256][OUT], b2
-constexpr int P_PARAM_FLOATS = P_MAX_IN * H + H + H + H * P_MAX_OUT + P_MAX_OUT;
-constexpr int P_BAR_OFF = P_B_BYTES + P_A_BYTES + P_PARAM_FLOATS * 4;
-constexpr int P_SMEM = P_BAR_OFF + 64 + 1024;
+// fp32 parameters in shared memory: W0 [IN][256], b0, b1, W2 [256][OUT], b2 (+ log_std)
+__host__ __device__ constexpr int p_param_floats(int in) { return in * H + H + H + H * P_MAX_OUT + 2 * P_MAX_OUT; }
+__host__ __device__ constexpr int p_bar_off(int in) { return P_B_BYTES + P_A_BYTES + p_param_floats(in) * 4; }
+__host__ __device__ constexpr int p_smem(int in) { return p_bar_off(in) + 64 + 1024; }
+static_assert(p_smem(24) <= 232448, "policy kernel shared memory");
 
 struct PolicyArgs {
     const float* obs;            // [n, IN]
     const float* params[2];      // fp32 parameter vectors of actor, critic
     int n, in_dim, num_actions, t, greedy;
-    float* actions;              // [n]
+    int act;                     // 0 ReLU, 1 tanh
+    float* actions;              // [n] action index, or [n, num_actions] continuous actions
     float* values;               // [n]
     float* r_obs; float* r_actions; float* r_log_probs; float* r_values;  // [T, n, ...]
     const DeviceCounters* ctr;
     int* err;
 };
 
-template <int IN>
+template <int IN, bool CONT>
 __global__ void __launch_bounds__(P_THREADS, 1)
 rollout_policy_kernel(const __grid_constant__ CUtensorMap tm_actor_w1t,
                       const __grid_constant__ CUtensorMap tm_critic_w1t, PolicyArgs a) {
@@ -52,11 +56,11 @@ rollout_policy_kernel(const __grid_constant__ CUtensorMap tm_actor_w1t,
     uint8_t* sB = smem;
     uint8_t* sA = smem + P_B_BYTES;
     float* sW0 = (float*)(smem + P_B_BYTES + P_A_BYTES);
-    float* sb0 = sW0 + P_MAX_IN * H;
+    float* sb0 = sW0 + IN * H;
     float* sb1 = sb0 + H;
     float* sW2 = sb1 + H;
-    float* sb2 = sW2 + H * P_MAX_OUT;
-    uint64_t* b_full = (uint64_t*)(smem + P_BAR_OFF);
+    float* sb2 = sW2 + H * P_MAX_OUT;   // b2 [P_MAX_OUT] then log_std [P_MAX_OUT]
+    uint64_t* b_full = (uint64_t*)(smem + p_bar_off(IN));
     uint64_t* t_full = b_full + 1;
     uint32_t* tmem_slot = (uint32_t*)(t_full + 1);
 
@@ -87,7 +91,10 @@ rollout_policy_kernel(const __grid_constant__ CUtensorMap tm_actor_w1t,
         int j = i / P_MAX_OUT, o = i % P_MAX_OUT;
         sW2[i] = o < out_dim ? W2[j * out_dim + o] : 0.0f;
     }
-    if (threadIdx.x < P_MAX_OUT) sb2[threadIdx.x] = threadIdx.x < out_dim ? b2[threadIdx.x] : 0.0f;
+    if (threadIdx.x < P_MAX_OUT) {
+        sb2[threadIdx.x] = threadIdx.x < out_dim ? b2[threadIdx.x] : 0.0f;
+        sb2[P_MAX_OUT + threadIdx.x] = (CONT && net == 0 && threadIdx.x < out_dim) ? b2[out_dim + threadIdx.x] : 0.0f;
+    }
     __syncthreads();
 
     // ---- h0 tile: thread -> (row, half of the 256 columns)
@@ -107,7 +114,7 @@ rollout_policy_kernel(const __grid_constant__ CUtensorMap tm_actor_w1t,
                 float acc = sb0[j0 + u];
 #pragma unroll
                 for (int k = 0; k < IN; ++k) acc = fmaf(x[k], sW0[k * H + j0 + u], acc);
-                h[u] = fmaxf(acc, 0.0f);
+                h[u] = a.act == 0 ? fmaxf(acc, 0.0f) : tanh_fast(acc);
             }
             uint32_t w[4];
 #pragma unroll
@@ -156,7 +163,8 @@ rollout_policy_kernel(const __grid_constant__ CUtensorMap tm_actor_w1t,
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     const int j = ch * 32 + i;
-                    float hv = fmaxf(v[i] + sb1[j], 0.0f);
+                    const float z = v[i] + sb1[j];
+                    const float hv = a.act == 0 ? fmaxf(z, 0.0f) : tanh_fast(z);
 #pragma unroll
                     for (int u = 0; u < P_MAX_OUT; ++u) o[u] = fmaf(hv, sW2[j * P_MAX_OUT + u], o[u]);
                 }
@@ -166,10 +174,25 @@ rollout_policy_kernel(const __grid_constant__ CUtensorMap tm_actor_w1t,
                 if (net == 0) {
                     unsigned long long ts = (unsigned long long)a.ctr->total_steps + (unsigned long long)a.t * (unsigned long long)a.n;
                     uint32_t seed = (uint32_t)(ts * 2654435761ull + (unsigned long long)a.t * 7919ull);  // ppo.mojo:2071
-                    float act, lp;
-                    sample_one(o, a.num_actions, seed, row, a.greedy, act, lp);
-                    a.actions[row] = act;
-                    a.r_actions[off] = act;
+                    float lp;
+                    if (CONT) {
+                        const int A = a.num_actions;
+                        float head[2 * P_MAX_OUT], act[P_MAX_OUT];
+#pragma unroll
+                        for (int u = 0; u < P_MAX_OUT; ++u) {
+                            if (u < A) { head[u] = o[u]; head[A + u] = sb2[P_MAX_OUT + u]; }
+                        }
+                        sample_continuous_one(head, A, seed, row, a.greedy, act, lp);
+                        for (int u = 0; u < A; ++u) {
+                            a.actions[(size_t)row * A + u] = act[u];
+                            a.r_actions[off * A + u] = act[u];
+                        }
+                    } else {
+                        float act;
+                        sample_one(o, a.num_actions, seed, row, a.greedy, act, lp);
+                        a.actions[row] = act;
+                        a.r_actions[off] = act;
+                    }
                     a.r_log_probs[off] = lp;
 #pragma unroll
                     for (int k = 0; k < IN; ++k) a.r_obs[off * IN + k] = a.obs[(size_t)row * IN + k];
@@ -194,7 +217,7 @@ rollout_policy_kernel(const __grid_constant__ CUtensorMap tm_actor_w1t,
 // of the GAE phase uses the fp32 forward (one call per rollout).
 
 bool policy_supported(int in_dim, int num_actions, int hidden) {
-    return hidden == H && (in_dim == 4 || in_dim == 8) && num_actions <= P_MAX_OUT;
+    return hidden == H && (in_dim == 4 || in_dim == 8 || in_dim == 24) && num_actions <= P_MAX_OUT;
 }
 
 int PolicyState::init(void* workspace, int* err_flag) {
@@ -217,15 +240,16 @@ int PolicyState::prepare(const float* actor_params, const float* critic_params, 
     return convert_w1(critic_params + oW1, scratch_w1, w1t[1], st);
 }
 
-template <int IN>
+template <int IN, bool CONT>
 static int launch_policy(const CUtensorMap& ta, const CUtensorMap& tb, const PolicyArgs& a, cudaStream_t st) {
     static bool attr_set = false;
     if (!attr_set) {
-        MRL_CUDA_OK(cudaFuncSetAttribute(rollout_policy_kernel<IN>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM));
+        MRL_CUDA_OK(cudaFuncSetAttribute(rollout_policy_kernel<IN, CONT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         p_smem(IN)));
         attr_set = true;
     }
     dim3 grid((a.n + P_TILE - 1) / P_TILE, 2);
-    rollout_policy_kernel<IN><<<grid, P_THREADS, P_SMEM, st>>>(ta, tb, a);
+    rollout_policy_kernel<IN, CONT><<<grid, P_THREADS, p_smem(IN), st>>>(ta, tb, a);
     count_launch();
     MRL_CUDA_OK(cudaGetLastError());
     return MRL_OK;
@@ -235,11 +259,19 @@ int PolicyState::step(const PolicyStepArgs& s, cudaStream_t st) {
     PolicyArgs a;
     a.obs = s.obs; a.params[0] = s.actor_params; a.params[1] = s.critic_params;
     a.n = s.n; a.in_dim = s.in_dim; a.num_actions = s.num_actions; a.t = s.t; a.greedy = s.greedy;
+    a.act = s.act;
     a.actions = s.actions; a.values = s.values;
     a.r_obs = s.r_obs; a.r_actions = s.r_actions; a.r_log_probs = s.r_log_probs; a.r_values = s.r_values;
     a.ctr = (const DeviceCounters*)s.counters; a.err = err;
-    if (s.in_dim == 4) return launch_policy<4>(tm_w1t[0], tm_w1t[1], a, st);
-    if (s.in_dim == 8) return launch_policy<8>(tm_w1t[0], tm_w1t[1], a, st);
+    if (s.continuous) {
+        if (s.in_dim == 4) return launch_policy<4, true>(tm_w1t[0], tm_w1t[1], a, st);
+        if (s.in_dim == 8) return launch_policy<8, true>(tm_w1t[0], tm_w1t[1], a, st);
+        if (s.in_dim == 24) return launch_policy<24, true>(tm_w1t[0], tm_w1t[1], a, st);
+    } else {
+        if (s.in_dim == 4) return launch_policy<4, false>(tm_w1t[0], tm_w1t[1], a, st);
+        if (s.in_dim == 8) return launch_policy<8, false>(tm_w1t[0], tm_w1t[1], a, st);
+        if (s.in_dim == 24) return launch_policy<24, false>(tm_w1t[0], tm_w1t[1], a, st);
+    }
     set_error("rollout policy kernel: obs_dim %d is not built", s.in_dim);
     return MRL_ERR_UNSUPPORTED;
 }

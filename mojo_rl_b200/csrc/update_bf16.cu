@@ -8,6 +8,7 @@
 // reductions stay on CUDA cores in fp32.  Activations are stored once, in bf16
 // and row-major (h0, h1, g1, g0): the dW GEMM reads them as MN-major operands.
 // The reference has no counterpart: its matmuls are fp32 16x16 tiles.
+#include <cstdlib>
 #include "update_bf16.cuh"
 
 namespace mrl {
@@ -20,72 +21,128 @@ constexpr int TILE_M = 128, KCH = 64;
 constexpr int NTHREADS = 192;     // split-K kernel: warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 epilogue
 constexpr int K1_THREADS = 320;   // row-tile kernel: two epilogue groups (warps 2-5, 6-9), one per TMEM buffer
 
+// bf16 x 8 <-> fp32 x 8 (one 16-byte vector)
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __nv_bfloat162 pk = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&pk);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // ---------------------------------------------------------------- K1
 // D[128-row tile, 256] = A[tile rows, 256] . B^T with B [256 (n), 256 (k)]
 // resident in shared memory for the CTA's lifetime; A tiles stream through a
-// 5-deep ring; two TMEM accumulators overlap the epilogue with the next tile.
-constexpr int K1_STAGES = 5;
+// ring of 64-column chunks; two TMEM accumulators overlap the epilogue with the
+// next tile.  An epilogue warp owns 32 rows (one TMEM lane quarter) and walks
+// the 256 columns in chunks of 32: its bf16 results go through a per-warp
+// [32 rows x 64 bytes] staging buffer (64-byte swizzle) and leave with one TMA
+// store per chunk, and in mode 2 the matching chunk of the mask source arrives
+// the same way, two chunks ahead.  (Per-thread row stores and loads would touch
+// 32 different 128-byte lines per warp instruction and saturate the L1 path.)
 constexpr int K1_B_BYTES = 4 * H * KCH * 2;           // 131072
 constexpr int K1_A_STAGE = TILE_M * KCH * 2;          // 16384
 constexpr int K1_PARAM_FLOATS = H + H * 8 + 8;        // bias, W2 (up to 8 outputs), b2
-constexpr int K1_BAR_OFF = K1_B_BYTES + K1_STAGES * K1_A_STAGE + K1_PARAM_FLOATS * 4;
-constexpr int K1_SMEM = K1_BAR_OFF + 16 * 8 + 1024;   // + barriers + alignment slack
+constexpr int K1_EPI_WARPS = 8;
+constexpr int K1_CHUNK_BYTES = 32 * 64;               // 32 rows x 32 bf16
+// IN > 0 (mode 1 only) fuses the first layer: the A chunks are computed on CUDA cores by four producer warps
+// instead of arriving by TMA, and W0 / b0 stay in shared memory as floats.
+__host__ __device__ constexpr int k1_stages(int mode, int in = 0) { return (mode == 2 || in > 0) ? 3 : 4; }
+__host__ __device__ constexpr int k1_out_bufs(int mode) { return mode == 0 ? 0 : 1; }
+// mode 1: bias / W2 / b2 as floats; mode 2: two mask chunks per epilogue warp
+__host__ __device__ constexpr int k1_aux_bytes(int mode) {
+    return mode == 2 ? K1_EPI_WARPS * 2 * K1_CHUNK_BYTES : ((K1_PARAM_FLOATS * 4 + 1023) / 1024) * 1024;
+}
+__host__ __device__ constexpr int k1_out_off(int mode, int in = 0) { return K1_B_BYTES + k1_stages(mode, in) * K1_A_STAGE; }
+__host__ __device__ constexpr int k1_aux_off(int mode, int in = 0) {
+    return k1_out_off(mode, in) + k1_out_bufs(mode) * K1_EPI_WARPS * K1_CHUNK_BYTES;
+}
+__host__ __device__ constexpr int k1_w0_off(int mode, int in = 0) { return k1_aux_off(mode, in) + k1_aux_bytes(mode); }
+__host__ __device__ constexpr int k1_x_off(int mode, int in = 0) { return k1_w0_off(mode, in) + (in > 0 ? (in + 1) * H * 4 : 0); }
+__host__ __device__ constexpr int k1_bar_off(int mode, int in = 0) { return k1_x_off(mode, in) + in * TILE_M * 4; }
+__host__ __device__ constexpr int k1_smem(int mode, int in = 0) { return k1_bar_off(mode, in) + 32 * 8 + 1024; }  // + barriers + alignment slack
+__host__ __device__ constexpr int k1_threads(int in) { return in > 0 ? K1_THREADS + 128 : K1_THREADS; }
+static_assert(k1_smem(1) <= 232448 && k1_smem(2) <= 232448 && k1_smem(0) <= 232448 && k1_smem(1, 8) <= 232448,
+              "K1 shared memory");
 
 struct K1Params {
     int M;
     float* out_f32;                 // mode 0: D as fp32 [M, 256]
     const float* bias;              // mode 1: b1
-    const float* W2; const float* b2; int out_dim; bf16* h1; float* head_out; int head_ld;
-    const bf16* h0; bf16* g0;       // mode 2: mask source and masked output
+    const float* W2; const float* b2; int out_dim; float* head_out; int head_ld;
     int act;                        // modes 1, 2: 0 ReLU, 1 tanh (derivative 1 - y^2 from the stored bf16 y)
     // Hidden widths above 256 are computed in 256-wide blocks: a second launch adds the first one's fp32
-    // result (prev, [M, 256]) to its accumulator before the epilogue, and bf16 rows have their own pitch.
+    // result (prev, [M, 256]) to its accumulator before the epilogue.
     const float* prev;
-    int out_ld, mask_ld;            // row pitch of h1 / g0 and of h0 in elements; 0 = 256
+    const float* x; const float* W0; const float* b0;   // fused first layer: x [M, IN], W0 [IN, 256], b0 [256]
     int* err;
 };
-
-// Hardware tanh (MUFU, ~2^-11 relative error): the result is rounded to bf16 (2^-9) right away.
-__device__ __forceinline__ float tanh_fast(float x) {
-    float y;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
 
 __device__ __forceinline__ void drain_on_error(const int* err) {
     if (*(volatile const int*)err != 0)
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // let copies in flight land before the CTA exits
 }
 
-template <int MODE, int OUT>
-__global__ void __launch_bounds__(K1_THREADS, 1)
-k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, K1Params p) {
+// tmOut: [32 rows x 32 columns] boxes (64-byte swizzle) of the bf16 output (h1 in mode 1, g0 in mode 2);
+// tmMask: the same boxes of the mask source h0 (mode 2).  Unused maps are passed as copies of tmA.
+// With IN > 0, tmA is the map of h0 itself: the producer warps (10-13) store every chunk they compute through it.
+template <int MODE, int OUT, int IN = 0>
+__global__ void __launch_bounds__(k1_threads(IN), 1)
+k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmMask, K1Params p) {
+    static_assert(IN == 0 || MODE == 1, "the fused first layer belongs to the forward pass");
+    constexpr int STAGES = k1_stages(MODE, IN);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* sB = smem;
     uint8_t* sA = smem + K1_B_BYTES;
-    float* sP = (float*)(smem + K1_B_BYTES + K1_STAGES * K1_A_STAGE);
-    uint64_t* bars = (uint64_t*)(smem + K1_BAR_OFF);
+    uint8_t* sOut = smem + k1_out_off(MODE, IN);
+    uint8_t* sAux = smem + k1_aux_off(MODE, IN);
+    float* sP = (float*)sAux;
+    float* sW0 = (float*)(smem + k1_w0_off(MODE, IN));   // [IN][256] then b0 [256]
+    float* sX = (float*)(smem + k1_x_off(MODE, IN));     // the tile's rows of x: [128][IN]
+    uint64_t* bars = (uint64_t*)(smem + k1_bar_off(MODE, IN));
     uint64_t* b_full = bars;
     uint64_t* a_full = bars + 1;
-    uint64_t* a_empty = bars + 1 + K1_STAGES;
-    uint64_t* t_full = bars + 1 + 2 * K1_STAGES;
+    uint64_t* a_empty = a_full + STAGES;
+    uint64_t* t_full = a_empty + STAGES;
     uint64_t* t_empty = t_full + 2;
-    uint32_t* tmem_slot = (uint32_t*)(t_empty + 2);
+    uint64_t* m_full_all = t_empty + 2;                 // 2 per epilogue warp (mode 2)
+    uint32_t* tmem_slot = (uint32_t*)(m_full_all + 2 * K1_EPI_WARPS);
+    uint32_t* prod_fail = tmem_slot + 1;                // set when the producer group's wait gave up
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_tiles = (p.M + TILE_M - 1) / TILE_M;
 
     if (threadIdx.x == 0) {
+        *prod_fail = 0u;
         mbar_init(b_full, 1);
-        for (int s = 0; s < K1_STAGES; ++s) { mbar_init(&a_full[s], 1); mbar_init(&a_empty[s], 1); }
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&a_full[s], 1); mbar_init(&a_empty[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&t_full[b], 1); mbar_init(&t_empty[b], 4); }
+        for (int b = 0; b < 2 * K1_EPI_WARPS; ++b) mbar_init(&m_full_all[b], 1);
         fence_barrier_init();
         prefetch_tensormap(&tmA);
         prefetch_tensormap(&tmB);
+        if (MODE != 0) prefetch_tensormap(&tmOut);
+        if (MODE == 2) prefetch_tensormap(&tmMask);
     }
     if (warp == 1) tmem_alloc(tmem_slot, 512);
-    if (warp >= 2 && MODE == 1) {
+    if (IN > 0 && warp >= 10) {
+        int t = threadIdx.x - 320;
+        for (int i = t; i < IN * H; i += 128) sW0[i] = p.W0[i];
+        for (int i = t; i < H; i += 128) sW0[IN * H + i] = p.b0[i];
+    }
+    if (warp >= 2 && warp < 10 && MODE == 1) {
         int t = threadIdx.x - 64;
         for (int i = t; i < H; i += 256) sP[i] = p.bias[i];
         for (int i = t; i < H * OUT; i += 256) {
@@ -105,10 +162,10 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             for (int c = 0; c < 4; ++c) tma_load_2d(sB + c * (H * KCH * 2), &tmB, b_full, c * KCH, 0);
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int tile = blockIdx.x; IN == 0 && tile < num_tiles && ok; tile += gridDim.x) {
                 for (int c = 0; c < 4 && ok; ++c, ++it) {
-                    int s = it % K1_STAGES;
-                    uint32_t ph = (it / K1_STAGES) & 1u;
+                    int s = it % STAGES;
+                    uint32_t ph = (it / STAGES) & 1u;
                     ok = mbar_wait(&a_empty[s], ph ^ 1u, p.err, 101);
                     if (!ok) break;
                     mbar_arrive_expect_tx(&a_full[s], K1_A_STAGE);
@@ -127,8 +184,8 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 if (!ok) break;
                 tc_fence_after_sync();
                 for (int c = 0; c < 4 && ok; ++c, ++it) {
-                    int s = it % K1_STAGES;
-                    uint32_t ph = (it / K1_STAGES) & 1u;
+                    int s = it % STAGES;
+                    uint32_t ph = (it / STAGES) & 1u;
                     ok = mbar_wait(&a_full[s], ph, p.err, 104);
                     if (!ok) break;
                     tc_fence_after_sync();
@@ -142,18 +199,122 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 if (ok) mma_commit(&t_full[buf]);
             }
         }
+    } else if (IN > 0 && warp >= 10) {
+        // First layer on CUDA cores (same fmaf order as l0_forward_kernel).  Thread = (8-column group g of the
+        // 64-column chunk, row set rs): the chunk's weights stay in registers while the thread walks its 8 rows
+        // (rs, rs + 16, ...); the eight lanes of a quarter-warp write one 128-byte row of the K-major
+        // 128-byte-swizzled A stage.  Each finished chunk is handed to the MMA warp and stored to global memory
+        // (the backward pass reads h0) by one TMA store.
+        const int t = threadIdx.x - 320;
+        const int g = t & 7, rs = t >> 3;
+        constexpr int XV = (IN * TILE_M) / (128 * 4);   // float4 per thread of the [128, IN] x tile
+        float4 xnext[XV > 0 ? XV : 1];
+        auto fetch_x = [&](int tile) {
+#pragma unroll
+            for (int i = 0; i < XV; ++i) {
+                const int e = (i * 128 + t) * 4;          // element of the tile's x block (rows are contiguous)
+                const size_t ge = (size_t)tile * TILE_M * IN + e;
+                xnext[i] = ge + 3 < (size_t)p.M * IN ? __ldg(reinterpret_cast<const float4*>(p.x + ge))
+                                                    : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+        };
+        if ((int)blockIdx.x < num_tiles) fetch_x(blockIdx.x);
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            asm volatile("bar.sync 1, 128;" ::: "memory");   // every thread is done reading the previous x tile
+#pragma unroll
+            for (int i = 0; i < XV; ++i) *reinterpret_cast<float4*>(sX + (i * 128 + t) * 4) = xnext[i];
+            if (tile + (int)gridDim.x < num_tiles) fetch_x(tile + gridDim.x);
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            for (int c = 0; c < 4; ++c, ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1u;
+                float w[IN > 0 ? IN : 1][8], bias[8];
+                {
+                    const int j0 = c * KCH + g * 8;
+#pragma unroll
+                    for (int k = 0; k < IN; ++k) {
+                        const float4 lo = *reinterpret_cast<const float4*>(sW0 + k * H + j0);
+                        const float4 hi = *reinterpret_cast<const float4*>(sW0 + k * H + j0 + 4);
+                        w[k][0] = lo.x; w[k][1] = lo.y; w[k][2] = lo.z; w[k][3] = lo.w;
+                        w[k][4] = hi.x; w[k][5] = hi.y; w[k][6] = hi.z; w[k][7] = hi.w;
+                    }
+                    const float4 lo = *reinterpret_cast<const float4*>(sW0 + IN * H + j0);
+                    const float4 hi = *reinterpret_cast<const float4*>(sW0 + IN * H + j0 + 4);
+                    bias[0] = lo.x; bias[1] = lo.y; bias[2] = lo.z; bias[3] = lo.w;
+                    bias[4] = hi.x; bias[5] = hi.y; bias[6] = hi.z; bias[7] = hi.w;
+                }
+                // the stage is free once the MMAs that read it have retired and its previous store has read it
+                if (t == 0) {
+                    bulk_store_wait_read_n<STAGES - 1>();
+                    if (!mbar_wait(&a_empty[s], ph ^ 1u, p.err, 107)) *(volatile uint32_t*)prod_fail = 1u;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                ok = *(volatile uint32_t*)prod_fail == 0u;   // the same answer for all 128 producer threads
+                if (!ok) break;
+                uint8_t* stage = sA + s * K1_A_STAGE;
+#pragma unroll 2
+                for (int i = 0; i < 8; ++i) {
+                    const int r = rs + 16 * i;
+                    float xr[IN > 0 ? IN : 1];
+                    if (IN % 4 == 0) {
+#pragma unroll
+                        for (int k = 0; k < IN; k += 4) {
+                            const float4 t4 = *reinterpret_cast<const float4*>(sX + r * IN + k);
+                            xr[k] = t4.x; xr[k + 1] = t4.y; xr[k + 2] = t4.z; xr[k + 3] = t4.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < IN; ++k) xr[k] = sX[r * IN + k];
+                    }
+                    float h[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        float acc = bias[u];
+#pragma unroll
+                        for (int k = 0; k < IN; ++k) acc = fmaf(xr[k], w[k][u], acc);
+                        h[u] = p.act == 0 ? fmaxf(acc, 0.0f) : tanh_fast(acc);
+                    }
+                    *reinterpret_cast<uint4*>(stage + r * 128 + ((g ^ (r & 7)) << 4)) = pack8(h);
+                }
+                fence_proxy_async_smem();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (t == 0) {
+                    mbar_arrive(&a_full[s]);
+                    tma_store_2d(&tmA, sA + s * K1_A_STAGE, c * KCH, tile * TILE_M);
+                }
+            }
+        }
+        if (t == 0) bulk_store_wait_read_n<0>();
     } else {
-        const int q = warp & 3;  // TMEM lane quarter this warp may read
-        const int group = (warp - 2) >> 2;  // epilogue group = TMEM buffer it drains (tiles lt with lt % 2 == group)
-        uint32_t lt = 0;
+        const int q = warp & 3;             // TMEM lane quarter this warp may read
+        const int ew = warp - 2;            // epilogue warp 0..7
+        const int group = ew >> 2;          // epilogue group = TMEM buffer it drains (tiles lt with lt % 2 == group)
+        const int swz = (lane >> 1) & 3;    // 64-byte swizzle: 16-byte chunk index ^ address bits 7..8
+        uint8_t* obuf = sOut + ew * K1_CHUNK_BYTES;
+        uint8_t* mbuf = sAux + ew * 2 * K1_CHUNK_BYTES;
+        uint64_t* m_full = m_full_all + 2 * ew;
+        // Mask chunk g of this warp's stream: chunk g % 8 of the (g / 8)-th tile of its group.
+        auto issue_mask = [&](uint32_t g) {
+            const int tile_g = blockIdx.x + (group + 2 * (int)(g >> 3)) * gridDim.x;
+            if (tile_g < num_tiles) {
+                mbar_arrive_expect_tx(&m_full[g & 1u], K1_CHUNK_BYTES);
+                tma_load_2d(mbuf + (g & 1u) * K1_CHUNK_BYTES, &tmMask, &m_full[g & 1u], (int)(g & 7u) * 32,
+                            tile_g * TILE_M + q * 32);
+            }
+        };
+        if (MODE == 2 && lane == 0) { issue_mask(0); issue_mask(1); }
+        uint32_t lt = 0, mk = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
             int buf = lt & 1;
             if (buf != group) continue;
-            ok = mbar_wait(&t_full[buf], (lt >> 1) & 1u, p.err, 105);
+            ok = __all_sync(0xffffffffu, mbar_wait(&t_full[buf], (lt >> 1) & 1u, p.err, 105));   // warp-uniform
             if (!ok) break;
             tc_fence_after_sync();
-            const int row = tile * TILE_M + q * 32 + lane;
+            const int row0 = tile * TILE_M + q * 32;
+            const int row = row0 + lane;
             const bool in_range = row < p.M;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * H;
             float o[OUT];
@@ -164,15 +325,12 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll 1
             for (int ch = 0; ch < 8; ++ch) {
                 uint4 hm[4];
-                if (MODE == 2) {  // the ReLU mask source, fetched before the accumulator read so that both latencies overlap
-                    if (in_range) {
-                        const uint4* src = reinterpret_cast<const uint4*>(p.h0 + (size_t)row * (p.mask_ld ? p.mask_ld : H) + ch * 32);
+                if (MODE == 2) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(&m_full[mk & 1u], (mk >> 1) & 1u, p.err, 106));
+                    if (!ok) break;
+                    const uint4* src = reinterpret_cast<const uint4*>(mbuf + (mk & 1u) * K1_CHUNK_BYTES + lane * 64);
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) hm[i] = __ldg(src + i);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) hm[i] = make_uint4(0, 0, 0, 0);
-                    }
+                    for (int i = 0; i < 4; ++i) hm[i] = src[i ^ swz];
                 }
                 float4 pv[8];
                 const bool has_prev = MODE != 0 && p.prev != nullptr && in_range;
@@ -233,15 +391,23 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                             packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
                         }
                     }
-                    if (in_range) {
-                        bf16* dstp = (MODE == 1 ? p.h1 : p.g0) + (size_t)row * (p.out_ld ? p.out_ld : H) + ch * 32;
-                        uint4* dst = reinterpret_cast<uint4*>(dstp);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                    // the previous chunk's store must have finished reading the staging buffer
+                    if (lane == 0) bulk_store_wait_read_n<0>();
+                    __syncwarp();
+                    if (MODE == 2) {  // every lane has consumed mask chunk mk: refill its buffer two chunks ahead
+                        if (lane == 0) issue_mask(mk + 2);
+                        ++mk;
                     }
+                    uint4* dst = reinterpret_cast<uint4*>(obuf + lane * 64);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        dst[i ^ swz] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) tma_store_2d(&tmOut, obuf, ch * 32, row0);
                 }
             }
+            if (!ok) break;
             if (MODE == 1 && in_range) {
                 for (int a = 0; a < OUT; ++a)
                     if (a < p.out_dim) p.head_out[(size_t)row * p.head_ld + a] = o[a];
@@ -250,6 +416,7 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(&t_empty[buf]);
         }
+        if (MODE != 0 && lane == 0) bulk_store_wait_read_n<0>();
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -407,49 +574,36 @@ int convert_w1(const float* W1, bf16* w1, bf16* w1t, cudaStream_t st) {
     return MRL_OK;
 }
 
-// Thread mapping of the CUDA-core kernels below: a block has 256 threads =
-// 8 warps; a warp covers 4 column groups of 8 columns (16 bytes of bf16) for 8
-// rows at a time, so a block covers all 256 columns of 8 rows per iteration and
-// every access is a 16-byte vector.  Sums over rows are finished inside a warp
-// with shuffles over the 8 row lanes.
+// Thread mapping of the CUDA-core kernels below: a block has HH threads; a warp covers 64 columns (eight
+// lanes x 8 columns = 16 bytes of bf16 each, so a quarter-warp touches one contiguous 128-byte line) for 4 rows
+// at a time, and two warps share a 64-column block, so a block covers all HH columns of 8 rows per iteration.
+// (With the lanes of a quarter-warp on different rows every 16-byte access costs eight L1 wavefronts instead
+// of one, and the L1 data pipe, not HBM, bounds these kernels.)  Sums over rows are finished inside a warp with
+// shuffles over its 4 row lanes; the two warps of a column block write separate partials (part 2 b and 2 b + 1).
+template <int HH>
 struct VecMap {
-    int row_lane, col0;
+    int row_lane, col0, part, writer;
     __device__ __forceinline__ VecMap() {
         const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-        row_lane = lane & 7;
-        col0 = (warp * 4 + (lane >> 3)) * 8;
+        constexpr int CB = HH / 64;            // column blocks
+        const int rh = warp / CB;              // 0 or 1: which 4 of the 8 rows
+        row_lane = rh * 4 + (lane >> 3);
+        col0 = ((warp % CB) * 8 + (lane & 7)) * 8;
+        part = blockIdx.x * 2 + rh;
+        writer = (lane >> 3) == 0;
     }
 };
 __device__ __forceinline__ float sum_row_lanes(float v) {
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    v += __shfl_xor_sync(0xffffffffu, v, 2);
-    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    v += __shfl_xor_sync(0xffffffffu, v, 8);
+    v += __shfl_xor_sync(0xffffffffu, v, 16);
     return v;
 }
-__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        f[2 * i] = __uint_as_float(w[i] << 16);
-        f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-    }
-}
-__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
-    uint32_t w[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        __nv_bfloat162 pk = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-        w[i] = *reinterpret_cast<uint32_t*>(&pk);
-    }
-    return make_uint4(w[0], w[1], w[2], w[3]);
-}
-
 // First layer (LinearReLU / LinearTanh[obs, 256], K = obs_dim): h0 = act(x . W0 + b0) in bf16, row-major.
 template <int IN, int HH>
 __global__ void __launch_bounds__(HH)
 l0_forward_kernel(const float* __restrict__ x, const float* __restrict__ W0, const float* __restrict__ b0,
                   bf16* __restrict__ h0, int M, int rows_per_block, int act) {
-    const VecMap vm;
+    const VecMap<HH> vm;
     float w[IN][8], b[8];
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
@@ -488,7 +642,7 @@ __global__ void __launch_bounds__(HH)
 head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout, int ldd,
                      const float* __restrict__ W2, int out_dim, bf16* __restrict__ g1,
                      float* __restrict__ part, int M, int rows_per_block, int act) {
-    const VecMap vm;
+    const VecMap<HH> vm;
     float w2[OUT][8], dw2[OUT][8], db1[8], db2[OUT];
 #pragma unroll
     for (int a = 0; a < OUT; ++a) {
@@ -509,13 +663,19 @@ head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout
         s_rows[i] = a < out_dim ? dout[(size_t)(rb + rr) * ldd + a] : 0.0f;
     }
     __syncthreads();
-    constexpr int UNR = 4;  // independent 16-byte loads in flight per thread
+    constexpr int UNR = 4;  // independent 16-byte loads in flight per thread, fetched one iteration ahead
+    uint4 raw[UNR], nxt[UNR];
+#pragma unroll
+    for (int i = 0; i < UNR; ++i) {
+        const int r = rb + vm.row_lane + 8 * i;
+        nxt[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(h1 + (size_t)r * HH + vm.col0)) : make_uint4(0, 0, 0, 0);
+    }
     for (int r0 = rb + vm.row_lane; r0 < re; r0 += 8 * UNR) {
-        uint4 raw[UNR];
 #pragma unroll
         for (int i = 0; i < UNR; ++i) {
-            const int r = r0 + 8 * i;
-            raw[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(h1 + (size_t)r * HH + vm.col0)) : make_uint4(0, 0, 0, 0);
+            raw[i] = nxt[i];
+            const int r = r0 + 8 * (UNR + i);
+            nxt[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(h1 + (size_t)r * HH + vm.col0)) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
         for (int i = 0; i < UNR; ++i) {
@@ -542,23 +702,23 @@ head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout
             *reinterpret_cast<uint4*>(g1 + (size_t)r * HH + vm.col0) = pack8(g);
         }
     }
-    float* pb = part + (size_t)blockIdx.x * ((OUT + 1) * HH + OUT);
+    float* pb = part + (size_t)vm.part * ((OUT + 1) * HH + OUT);
 #pragma unroll
     for (int a = 0; a < OUT; ++a)
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             float v = sum_row_lanes(dw2[a][u]);
-            if (vm.row_lane == 0) pb[a * HH + vm.col0 + u] = v;
+            if (vm.writer) pb[a * HH + vm.col0 + u] = v;
         }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
         float v = sum_row_lanes(db1[u]);
-        if (vm.row_lane == 0) pb[OUT * HH + vm.col0 + u] = v;
+        if (vm.writer) pb[OUT * HH + vm.col0 + u] = v;
     }
 #pragma unroll
     for (int a = 0; a < OUT; ++a) {
-        float v = sum_row_lanes(db2[a]);  // every column group sees every row: take column group 0
-        if (threadIdx.x == 0) pb[(OUT + 1) * HH + a] = v;
+        float v = sum_row_lanes(db2[a]);  // every column group sees the rows of its half: take column 0's thread
+        if (vm.writer && vm.col0 == 0) pb[(OUT + 1) * HH + a] = v;
     }
 }
 
@@ -567,7 +727,7 @@ template <int IN, int HH>
 __global__ void __launch_bounds__(HH)
 l0_backward_kernel(const bf16* __restrict__ g0, const float* __restrict__ x, float* __restrict__ part, int M,
                    int rows_per_block) {
-    const VecMap vm;
+    const VecMap<HH> vm;
     float dw[IN][8], db[8];
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
@@ -580,13 +740,19 @@ l0_backward_kernel(const bf16* __restrict__ g0, const float* __restrict__ x, flo
     extern __shared__ float s_rows[];  // the slab's x rows
     for (int i = threadIdx.x; i < (re - rb) * IN; i += HH) s_rows[i] = x[(size_t)rb * IN + i];
     __syncthreads();
-    constexpr int UNR = 4;
+    constexpr int UNR = 4;  // loads are issued one iteration ahead of their use
+    uint4 raw[UNR], nxt[UNR];
+#pragma unroll
+    for (int i = 0; i < UNR; ++i) {
+        const int r = rb + vm.row_lane + 8 * i;
+        nxt[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(g0 + (size_t)r * HH + vm.col0)) : make_uint4(0, 0, 0, 0);
+    }
     for (int r0 = rb + vm.row_lane; r0 < re; r0 += 8 * UNR) {
-        uint4 raw[UNR];
 #pragma unroll
         for (int i = 0; i < UNR; ++i) {
-            const int r = r0 + 8 * i;
-            raw[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(g0 + (size_t)r * HH + vm.col0)) : make_uint4(0, 0, 0, 0);
+            raw[i] = nxt[i];
+            const int r = r0 + 8 * (UNR + i);
+            nxt[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(g0 + (size_t)r * HH + vm.col0)) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
         for (int i = 0; i < UNR; ++i) {
@@ -604,18 +770,18 @@ l0_backward_kernel(const bf16* __restrict__ g0, const float* __restrict__ x, flo
             }
         }
     }
-    float* pb = part + (size_t)blockIdx.x * (IN + 1) * HH;
+    float* pb = part + (size_t)vm.part * (IN + 1) * HH;
 #pragma unroll
     for (int k = 0; k < IN; ++k)
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             float v = sum_row_lanes(dw[k][u]);
-            if (vm.row_lane == 0) pb[k * HH + vm.col0 + u] = v;
+            if (vm.writer) pb[k * HH + vm.col0 + u] = v;
         }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
         float v = sum_row_lanes(db[u]);
-        if (vm.row_lane == 0) pb[IN * HH + vm.col0 + u] = v;
+        if (vm.writer) pb[IN * HH + vm.col0 + u] = v;
     }
 }
 
@@ -639,15 +805,22 @@ __device__ __forceinline__ float block_sum_parts(const float* __restrict__ part,
                                                  bool valid) {
     __shared__ float sm[8][33];
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    float a0 = 0.0f, a1 = 0.0f;
+    // eight independent loads in flight per thread (the sums are latency-bound, not bandwidth-bound);
+    // the order of the additions is fixed, so the result is deterministic
+    float a[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) a[k] = 0.0f;
     if (valid) {
         int b = w;
-        for (; b + 8 < nblocks; b += 16) {
-            a0 += part[(size_t)b * stride + i];
-            a1 += part[(size_t)(b + 8) * stride + i];
+        for (; b + 56 < nblocks; b += 64) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) a[k] += part[(size_t)(b + 8 * k) * stride + i];
         }
-        if (b < nblocks) a0 += part[(size_t)b * stride + i];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (b + 8 * k < nblocks) a[k] += part[(size_t)(b + 8 * k) * stride + i];
     }
+    const float a0 = (a[0] + a[1]) + (a[2] + a[3]), a1 = (a[4] + a[5]) + (a[6] + a[7]);
     sm[w][lane] = a0 + a1;
     __syncthreads();
     float acc = 0.0f;
@@ -744,8 +917,10 @@ static int get_encode() {
 
 // bf16 matrix [rows, cols] with cols contiguous and a row pitch of pitch_elems (0: cols) - a view into a
 // wider matrix when pitch_elems > cols; box = [box_rows, 64 cols], 128-byte swizzle.
-int make_tensor_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                    uint64_t pitch_elems) {
+// [box_rows x box_cols] boxes of a row-major bf16 matrix; 64 columns use the 128-byte swizzle (MMA operands),
+// 32 columns the 64-byte swizzle (epilogue staging).
+static int make_map_impl(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                         uint32_t box_cols, uint64_t pitch_elems) {
     int rc = get_encode();
     if (rc) return rc;
     if (pitch_elems == 0) pitch_elems = cols;
@@ -755,17 +930,25 @@ int make_tensor_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t co
     }
     cuuint64_t dims[2] = {cols, rows};
     cuuint64_t strides[1] = {pitch_elems * 2};
-    cuuint32_t box[2] = {64, box_rows};
+    cuuint32_t box[2] = {box_cols, box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                          CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled failed (%d) for [%llu x %llu]", (int)r, (unsigned long long)rows,
                   (unsigned long long)cols);
         return MRL_ERR_CUDA;
     }
     return MRL_OK;
+}
+int make_tensor_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                    uint64_t pitch_elems) {
+    return make_map_impl(m, base, rows, cols, box_rows, 64, pitch_elems);
+}
+int make_box_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems) {
+    return make_map_impl(m, base, rows, cols, 32, 32, pitch_elems);
 }
 
 static int g_sm_count = 0;
@@ -779,37 +962,54 @@ static int sm_count() {
     return g_sm_count;
 }
 
-// Rows per block of the CUDA-core kernels: four blocks per SM, each walking a
-// contiguous slab of rows (a multiple of 8, at least 64).
+// Rows per block of the CUDA-core kernels: two blocks per SM (what their register use allows, so one wave),
+// each walking a contiguous slab of rows (a multiple of 8, at least 64).
 // The per-row fp32 operand of a slab (floats_per_row each) is staged in at most 40 KB of shared memory.
 static int slab_rows(int M, int floats_per_row) {
-    int blocks = 4 * sm_count();
+    int blocks = 2 * sm_count();
     int r = ((M + blocks - 1) / blocks + 7) & ~7;
     int cap = (40960 / (4 * floats_per_row)) & ~7;
     if (r > cap) r = cap;
     return r < 64 ? 64 : r;
 }
 
-template <int MODE, int OUT>
-static int launch_k1(const CUtensorMap& tmA, const CUtensorMap& tmB, const K1Params& p, cudaStream_t st) {
+// tmOut / tmMask: staging-box maps (make_box_map) of the bf16 output and, in mode 2, of the mask source;
+// mode 0 ignores both.
+template <int MODE, int OUT, int IN = 0>
+static int launch_k1(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmOut,
+                     const CUtensorMap& tmMask, const K1Params& p, cudaStream_t st) {
     static bool attr_set = false;
     if (!attr_set) {
-        MRL_CUDA_OK(cudaFuncSetAttribute(k1_rowtile_kernel<MODE, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, K1_SMEM));
+        MRL_CUDA_OK(cudaFuncSetAttribute(k1_rowtile_kernel<MODE, OUT, IN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         k1_smem(MODE, IN)));
         attr_set = true;
     }
     int tiles = (p.M + TILE_M - 1) / TILE_M;
     int grid = tiles < sm_count() ? tiles : sm_count();
-    k1_rowtile_kernel<MODE, OUT><<<grid, K1_THREADS, K1_SMEM, st>>>(tmA, tmB, p);
+    k1_rowtile_kernel<MODE, OUT, IN><<<grid, k1_threads(IN), k1_smem(MODE, IN), st>>>(tmA, tmB, tmOut, tmMask, p);
     count_launch();
     MRL_CUDA_OK(cudaGetLastError());
     return MRL_OK;
 }
 
-static int launch_k1_forward(const CUtensorMap& tmA, const CUtensorMap& tmB, const K1Params& p, cudaStream_t st) {
-    if (p.out_dim <= 1) return launch_k1<1, 1>(tmA, tmB, p, st);
-    if (p.out_dim <= 2) return launch_k1<1, 2>(tmA, tmB, p, st);
-    if (p.out_dim <= 4) return launch_k1<1, 4>(tmA, tmB, p, st);
-    if (p.out_dim <= 8) return launch_k1<1, 8>(tmA, tmB, p, st);
+// Forward with the first layer fused (p.x / p.W0 / p.b0 set; tmH0 is both the store map of h0 and the A slot).
+template <int IN>
+static int launch_k1_forward_fused(const CUtensorMap& tmH0, const CUtensorMap& tmB, const CUtensorMap& tmOut,
+                                   const K1Params& p, cudaStream_t st) {
+    if (p.out_dim <= 1) return launch_k1<1, 1, IN>(tmH0, tmB, tmOut, tmOut, p, st);
+    if (p.out_dim <= 2) return launch_k1<1, 2, IN>(tmH0, tmB, tmOut, tmOut, p, st);
+    if (p.out_dim <= 4) return launch_k1<1, 4, IN>(tmH0, tmB, tmOut, tmOut, p, st);
+    if (p.out_dim <= 8) return launch_k1<1, 8, IN>(tmH0, tmB, tmOut, tmOut, p, st);
+    set_error("bf16 path: head width %d > 8 is not built", p.out_dim);
+    return MRL_ERR_UNSUPPORTED;
+}
+
+static int launch_k1_forward(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmOut,
+                             const K1Params& p, cudaStream_t st) {
+    if (p.out_dim <= 1) return launch_k1<1, 1>(tmA, tmB, tmOut, tmOut, p, st);
+    if (p.out_dim <= 2) return launch_k1<1, 2>(tmA, tmB, tmOut, tmOut, p, st);
+    if (p.out_dim <= 4) return launch_k1<1, 4>(tmA, tmB, tmOut, tmOut, p, st);
+    if (p.out_dim <= 8) return launch_k1<1, 8>(tmA, tmB, tmOut, tmOut, p, st);
     set_error("bf16 path: head width %d > 8 is not built", p.out_dim);
     return MRL_ERR_UNSUPPORTED;
 }
@@ -842,11 +1042,20 @@ bool supported(const mrl_net_spec* net, int batch) {
            (net->in_dim == 4 || net->in_dim == 8 || net->in_dim == 17 || net->in_dim == 24) && batch % 32 == 0;
 }
 
+// Bytes of the partial-sum area: the K2 partials, or the l0 / head partials (two per block of the
+// CUDA-core kernels, whose slabs are capped by their shared-memory staging), whichever is larger.
+static int64_t part_area_bytes(int batch, int hidden) {
+    int64_t parts = (int64_t)max_splits() * H * H * 4;
+    const int64_t min_rows = (40960 / (4 * 24)) & ~7;     // smallest slab cap (24 inputs)
+    int64_t blocks = 2 * (int64_t)sm_count();
+    if ((batch + min_rows - 1) / min_rows > blocks) blocks = (batch + min_rows - 1) / min_rows;
+    const int64_t small_parts = 2 * blocks * (25 * (int64_t)hidden + 8) * 4;
+    return small_parts > parts ? small_parts : parts;
+}
+
 int64_t workspace_bytes(int batch, int hidden) {
     int64_t act = (int64_t)batch * hidden * 2;            // one bf16 activation array
-    int64_t parts = (int64_t)max_splits() * H * H * 4;    // K2 partials (also reused by the small reductions)
-    int64_t small_parts = (int64_t)4 * sm_count() * (25 * (int64_t)hidden + 8) * 4;   // l0 / head partials per block
-    if (small_parts > parts) parts = small_parts;
+    int64_t parts = part_area_bytes(batch, hidden);
     int64_t tmp = hidden > H ? (int64_t)batch * H * 4 : 0;   // fp32 result of the first 256-wide K block
     return 4 * act + 2 * (int64_t)hidden * hidden * 2 + parts + tmp + 4096;
 }
@@ -873,6 +1082,9 @@ int State::init(void* workspace, int batch_, int hidden, int* err_flag) {
         if ((rc = make_tensor_map(&tm_g1[i], g1 + i * H, batch, H, TILE_M, hh))) return rc;
         if ((rc = make_tensor_map(&tm_h0_mn[i], h0 + i * H, batch, H, 64, hh))) return rc;
         if ((rc = make_tensor_map(&tm_g1_mn[i], g1 + i * H, batch, H, 64, hh))) return rc;
+        if ((rc = make_box_map(&tm_h1_box[i], h1 + i * H, batch, H, hh))) return rc;
+        if ((rc = make_box_map(&tm_g0_box[i], g0 + i * H, batch, H, hh))) return rc;
+        if ((rc = make_box_map(&tm_h0_box[i], h0 + i * H, batch, H, hh))) return rc;
         for (int j = 0; j < nb; ++j) {  // [n block i][k block j] of W1^T (forward) and of W1 (dX)
             if ((rc = make_tensor_map(&tm_w1t[i][j], w1t + ((size_t)i * H) * hh + j * H, H, H, H, hh))) return rc;
             if ((rc = make_tensor_map(&tm_w1[i][j], w1 + ((size_t)i * H) * hh + j * H, H, H, H, hh))) return rc;
@@ -958,28 +1170,49 @@ int State::forward(const mrl_net_spec* net, const float* params, const float* x,
     const int act = net->activation == MRL_ACT_RELU ? 0 : 1;
     const bool gaussian = net->head == MRL_HEAD_STOCHASTIC_ACTOR;
     const int head_ld = gaussian ? 2 * O : O;
+    // Width 256 with 4 or 8 inputs: the first layer runs inside the GEMM kernel (h0 never comes back from HBM).
+    // Tuning knob.  Measured at B = 262 144: the fused kernel takes 132 us, l0_forward + the GEMM kernel 95 us
+    // (the four producer warps cannot keep up with the tensor core), so the separate launch is the default.
+    static const bool fuse_allowed = getenv("MRL_FUSED_L0") != nullptr;
+    const bool fused_l0 = fuse_allowed && nb == 1 && (I == 4 || I == 8) && ((uintptr_t)x & 15) == 0;
+    if (fused_l0) {
+        K1Params p{};
+        p.M = batch; p.bias = b1; p.W2 = W2; p.b2 = b2; p.out_dim = O; p.head_out = head_out;
+        p.head_ld = head_ld;
+        p.act = act;
+        p.x = x; p.W0 = W0; p.b0 = b0;
+        p.err = err;
+        rc = I == 4 ? launch_k1_forward_fused<4>(tm_h0[0], tm_w1t[0][0], tm_h1_box[0], p, st)
+                    : launch_k1_forward_fused<8>(tm_h0[0], tm_w1t[0][0], tm_h1_box[0], p, st);
+        if (rc) return rc;
+        if (gaussian) {
+            MRL_LAUNCH(fill_log_std_cols_kernel, ceil_div((int64_t)batch * O, 256), 256, 0, st, b2 + O, head_out, batch, O);
+        }
+        prof_mark("k1_forward_fused", st);
+        return MRL_OK;
+    }
     rc = nb == 1 ? l0_forward_any<256>(I, x, W0, b0, h0, batch, act, st)
                  : l0_forward_any<512>(I, x, W0, b0, h0, batch, act, st);
     if (rc) return rc;
     prof_mark("l0_forward", st);
     if (nb == 1) {
         K1Params p{};
-        p.M = batch; p.bias = b1; p.W2 = W2; p.b2 = b2; p.out_dim = O; p.h1 = h1; p.head_out = head_out;
+        p.M = batch; p.bias = b1; p.W2 = W2; p.b2 = b2; p.out_dim = O; p.head_out = head_out;
         p.head_ld = head_ld;
         p.act = act;
         p.err = err;
-        if ((rc = launch_k1_forward(tm_h0[0], tm_w1t[0][0], p, st))) return rc;
+        if ((rc = launch_k1_forward(tm_h0[0], tm_w1t[0][0], tm_h1_box[0], p, st))) return rc;
     } else {
         // h1[:, n block] = act(h0[:, k block 0] W1[k0, n] + h0[:, k block 1] W1[k1, n] + b1[n block]):
         // the first launch leaves its fp32 product in tmp, the second adds it before the epilogue.
         for (int n = 0; n < nb; ++n) {
             K1Params p0{};
             p0.M = batch; p0.out_f32 = tmp; p0.err = err;
-            if ((rc = launch_k1<0, 1>(tm_h0[0], tm_w1t[n][0], p0, st))) return rc;
+            if ((rc = launch_k1<0, 1>(tm_h0[0], tm_w1t[n][0], tm_h0[0], tm_h0[0], p0, st))) return rc;
             K1Params p{};
-            p.M = batch; p.bias = b1 + n * H; p.W2 = W2; p.b2 = b2; p.out_dim = 0; p.h1 = h1 + n * H;
-            p.head_out = head_out; p.head_ld = head_ld; p.act = act; p.prev = tmp; p.out_ld = hh; p.err = err;
-            if ((rc = launch_k1<1, 1>(tm_h0[1], tm_w1t[n][1], p, st))) return rc;
+            p.M = batch; p.bias = b1 + n * H; p.W2 = W2; p.b2 = b2; p.out_dim = 0;
+            p.head_out = head_out; p.head_ld = head_ld; p.act = act; p.prev = tmp; p.err = err;
+            if ((rc = launch_k1<1, 1>(tm_h0[1], tm_w1t[n][1], tm_h1_box[n], tm_h1_box[n], p, st))) return rc;
         }
         const int OUT = O <= 1 ? 1 : (O <= 2 ? 2 : (O <= 4 ? 4 : 8));
         const int grid = (batch + 7) / 8;
@@ -1012,7 +1245,7 @@ int State::backward(const mrl_net_spec* net, const float* params, const float* x
     if (rc) return rc;
     prof_mark("head_backward", st);
     const int hstride = (OUT + 1) * hh + OUT;
-    MRL_LAUNCH(reduce_head_parts_kernel, ceil_div(hstride, 32), 256, 0, st, part, nblocks, OUT, O, grads + oW2,
+    MRL_LAUNCH(reduce_head_parts_kernel, ceil_div(hstride, 32), 256, 0, st, part, 2 * nblocks, OUT, O, grads + oW2,
                grads + ob2, grads + ob1, hh);
     if (gaussian) {  // dlog_std[j] = sum over rows of dout[:, O + j] (stochastic_actor.mojo:727-966)
         MRL_LAUNCH(log_std_grad_kernel, O, 256, 0, st, dout, ldd, O, batch, grads + ob2 + O);
@@ -1021,17 +1254,16 @@ int State::backward(const mrl_net_spec* net, const float* params, const float* x
     // dh0 = g1 . W1^T times the activation derivative at h0 -> g0
     if (nb == 1) {
         K1Params p{};
-        p.M = batch; p.h0 = h0; p.g0 = g0; p.act = act; p.err = err;
-        if ((rc = launch_k1<2, 1>(tm_g1[0], tm_w1[0][0], p, st))) return rc;
+        p.M = batch; p.act = act; p.err = err;
+        if ((rc = launch_k1<2, 1>(tm_g1[0], tm_w1[0][0], tm_g0_box[0], tm_h0_box[0], p, st))) return rc;
     } else {
         for (int i = 0; i < nb; ++i) {   // output block i of g0: sum over the two column blocks of g1
             K1Params p0{};
             p0.M = batch; p0.out_f32 = tmp; p0.err = err;
-            if ((rc = launch_k1<0, 1>(tm_g1[0], tm_w1[i][0], p0, st))) return rc;
+            if ((rc = launch_k1<0, 1>(tm_g1[0], tm_w1[i][0], tm_g1[0], tm_g1[0], p0, st))) return rc;
             K1Params p{};
-            p.M = batch; p.h0 = h0 + i * H; p.g0 = g0 + i * H; p.act = act; p.prev = tmp; p.out_ld = hh; p.mask_ld = hh;
-            p.err = err;
-            if ((rc = launch_k1<2, 1>(tm_g1[1], tm_w1[i][1], p, st))) return rc;
+            p.M = batch; p.act = act; p.prev = tmp; p.err = err;
+            if ((rc = launch_k1<2, 1>(tm_g1[1], tm_w1[i][1], tm_g0_box[i], tm_h0_box[i], p, st))) return rc;
         }
     }
     prof_mark("k1_dx_gemm", st);
@@ -1040,7 +1272,7 @@ int State::backward(const mrl_net_spec* net, const float* params, const float* x
                  : l0_backward_any<512>(I, g0, x, part, batch, rows_per_block, nblocks, st);
     if (rc) return rc;
     prof_mark("l0_backward", st);
-    MRL_LAUNCH(reduce_parts_kernel, ceil_div((I + 1) * hh, 32), 256, 0, st, part, nblocks, (I + 1) * hh, (I + 1) * hh,
+    MRL_LAUNCH(reduce_parts_kernel, ceil_div((I + 1) * hh, 32), 256, 0, st, part, 2 * nblocks, (I + 1) * hh, (I + 1) * hh,
                grads + oW0);  // dW0 [I][hidden] then db0 [hidden] are adjacent in the gradient vector
     prof_mark("reduce_l0", st);
     // dW1 = h0^T . g1 (split-K over the SMs) in 256 x 256 blocks, each followed by its fixed-order reduction
@@ -1076,7 +1308,7 @@ extern "C" int mrl_bf16_rowtile_gemm(int M, const void* A_bf16, const void* B_bf
     if ((rc = tc::make_tensor_map(&tb, B_bf16, tc::H, tc::H, tc::H))) return rc;
     tc::K1Params p{};
     p.M = M; p.out_f32 = D; p.err = err_flag;
-    return tc::launch_k1<0, 1>(ta, tb, p, as_stream(stream));
+    return tc::launch_k1<0, 1>(ta, tb, ta, ta, p, as_stream(stream));
 }
 
 extern "C" int mrl_bf16_splitk_gemm(int K, const void* A_bf16, const void* B_bf16, float* partial, int* splits,

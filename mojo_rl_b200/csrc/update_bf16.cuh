@@ -15,6 +15,8 @@ int64_t workspace_bytes(int batch, int hidden);
 int max_splits();
 int make_tensor_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
                     uint64_t pitch_elems = 0);
+// [32 rows x 32 columns] boxes with the 64-byte swizzle: the epilogue staging tiles of the row-tile kernel.
+int make_box_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems = 0);
 
 // Activation buffers, bf16 weight copies and TMA descriptors of one minibatch
 // shape; shared by the actor and the critic, which run one after the other.
@@ -27,6 +29,7 @@ struct State {
     float* tmp;  // hh = 512: fp32 [batch, 256] product of the first K block
     CUtensorMap tm_h0[2], tm_g1[2], tm_h0_mn[2], tm_g1_mn[2];   // 256-wide column blocks of the activations
     CUtensorMap tm_w1t[2][2], tm_w1[2][2];                       // [row block][column block] of W1^T and W1
+    CUtensorMap tm_h1_box[2], tm_g0_box[2], tm_h0_box[2];        // [32 x 32] epilogue staging boxes per column block
 
     int init(void* workspace, int batch, int hidden, int* err_flag);
     // head_out [batch, out_dim] = logits / values (fp32)
@@ -46,6 +49,8 @@ struct PolicyStepArgs {
     const float* actor_params;
     const float* critic_params;
     int n, in_dim, num_actions, t, greedy;
+    int act;          // trunk activation: 0 ReLU, 1 tanh
+    int continuous;   // 1: Gaussian head (num_actions means; log_std follows b2), actions [n, num_actions]
     float* actions;
     float* values;
     float* r_obs; float* r_actions; float* r_log_probs; float* r_values;

@@ -62,6 +62,10 @@ class GpuAgent:
         _lib.check(self.L.mrl_read_buffer(self.h, which, _lib.ptr(out), n.value))
         return out
 
+    def write_buffer(self, which, arr):
+        arr = np.ascontiguousarray(arr, np.float32)
+        _lib.check(self.L.mrl_write_buffer(self.h, which, _lib.ptr(arr), arr.size))
+
     def stats(self):
         st = _lib.Stats()
         _lib.check(self.L.mrl_get_stats(self.h, ctypes.byref(st)))

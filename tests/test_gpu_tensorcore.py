@@ -78,7 +78,8 @@ def test_splitk_gemm_from_row_major_activations(K):
 @pytest.mark.parametrize("kind,obs,out,act,head,hidden", [(2, 8, 4, 0, 0, 256), (3, 24, 4, 1, 1, 256),
                                                             (4, 17, 6, 1, 1, 512), (2, 8, 4, 0, 0, 512)])
 def test_update_precision1_matches_fp32_gradients(kind, obs, out, act, head, hidden):
-    """Same rollout, same permutation, one minibatch: the bf16 tensor-core update's
+    """Same rollout (the fp32 context's slab and GAE results are written into the bf16 context, whose
+    own rollout policy runs on tensor cores), same permutation, one minibatch: the bf16 tensor-core update's
     gradients agree with the fp32 path to bf16 accuracy, and training state advances.
     LunarLander: ReLU nets, categorical head; BipedalWalker: tanh nets, Gaussian head; HalfCheetah: hidden
     width 512, computed in 256-wide tensor-core blocks."""
@@ -101,6 +102,11 @@ def test_update_precision1_matches_fp32_gradients(kind, obs, out, act, head, hid
             g.set_params(0, pa, np.zeros(2 * pa.size, np.float32))
             g.set_params(1, pc, np.zeros(2 * pc.size, np.float32))
             g.reset(0); g.rollout(); g.gae()
+            if prec == 0:
+                slab = {i: g.buffer(i) for i in (2, 3, 4, 5, 6, 7, 8, 9)}
+            else:
+                for i, arr in slab.items():
+                    g.write_buffer(i, arr)
             g.update(3e-4, 1e-3, 0.01, perms)
             st = g.stats()
             assert st.minibatches_done == 1 and st.actor_adam_t == 1
@@ -162,3 +168,39 @@ def test_rollout_policy_kernel_matches_fp32_policy():
         agree = (a["act"] == b["act"])
         assert agree.mean() > 0.97, agree.mean()
         assert np.allclose(a["lp"][agree], b["lp"][agree], rtol=0, atol=3e-2)
+
+
+@pytest.mark.gpu
+def test_rollout_policy_kernel_gaussian_matches_fp32_policy():
+    """Same comparison for a tanh / Gaussian policy (BipedalWalker: 24 observations, 4 action means,
+    state-independent log_std): actions differ from the fp32 path only through the bf16 means, the
+    noise draws are identical."""
+    from _gpu import GpuAgent
+    from _util import NetSpec, default_config, xavier_params
+    rng = np.random.default_rng(2)
+    pa = xavier_params(NetSpec(24, 256, 4, 1, 1), rng) * 0.25
+    pa[-4:] = np.array([-0.5, 0.0, 0.3, -1.0], np.float32)   # log_std
+    pc = xavier_params(NetSpec(24, 256, 1, 1, 0), rng) * 0.25
+    n = 512
+    out = {}
+    for prec in (0, 1):
+        for det in (0, 1):
+            cfg = default_config(env_kind=3, n_envs=n, rollout_len=2, hidden_dim=256, minibatch_size=2 * n,
+                                 num_epochs=1, precision=prec, deterministic=det)
+            g = GpuAgent(cfg)
+            try:
+                g.set_params(0, pa, np.zeros(2 * pa.size, np.float32))
+                g.set_params(1, pc, np.zeros(2 * pc.size, np.float32))
+                g.reset(5); g.rollout()
+                out[(prec, det)] = {k: g.buffer(i)[:n * w] for k, i, w in
+                                    (("obs", 2, 24), ("act", 3, 4), ("lp", 4, 1), ("val", 5, 1))}
+                assert g.stats().total_steps == 2 * n
+            finally:
+                g.close()
+    for det in (0, 1):
+        a, b = out[(1, det)], out[(0, det)]
+        assert np.array_equal(a["obs"], b["obs"])
+        assert np.allclose(a["val"], b["val"], rtol=2e-2, atol=2e-2), np.abs(a["val"] - b["val"]).max()
+        assert np.allclose(a["act"], b["act"], rtol=0, atol=3e-2), np.abs(a["act"] - b["act"]).max()
+        # log-prob depends on the noise only (action - mean = std * noise in both paths)
+        assert np.allclose(a["lp"], b["lp"], rtol=0, atol=1e-3), np.abs(a["lp"] - b["lp"]).max()
