@@ -30,7 +30,10 @@ constexpr int P_B_BYTES = H * H * 2;            // 131072: W1^T as four [256 x 6
 constexpr int P_A_BYTES = P_TILE * H * 2;       // 65536: h0 tile as four [128 x 64] chunks
 constexpr int P_MAX_OUT = 4;
 // fp32 parameters in shared memory: W0 [IN][256], b0, b1, W2 [256][OUT], b2 (+ log_std)
-__host__ __device__ constexpr int p_param_floats(int in) { return in * H + H + H + H * P_MAX_OUT + 2 * P_MAX_OUT; }
+// (+ the tile's observations [128][IN] when IN <= 8, and the upper column half's partial head sums [128][P_MAX_OUT])
+__host__ __device__ constexpr int p_param_floats(int in) {
+    return in * H + H + H + H * P_MAX_OUT + 2 * P_MAX_OUT + (in <= 8 ? P_TILE * in : 0) + P_TILE * P_MAX_OUT;
+}
 __host__ __device__ constexpr int p_bar_off(int in) { return P_B_BYTES + P_A_BYTES + p_param_floats(in) * 4; }
 __host__ __device__ constexpr int p_smem(int in) { return p_bar_off(in) + 64 + 1024; }
 static_assert(p_smem(24) <= 232448, "policy kernel shared memory");
@@ -60,6 +63,8 @@ rollout_policy_kernel(const __grid_constant__ CUtensorMap tm_actor_w1t,
     float* sb1 = sb0 + H;
     float* sW2 = sb1 + H;
     float* sb2 = sW2 + H * P_MAX_OUT;   // b2 [P_MAX_OUT] then log_std [P_MAX_OUT]
+    float* sX = sb2 + 2 * P_MAX_OUT;    // observations of the tile [128][IN] (IN <= 8 only)
+    float* sO = sX + (IN <= 8 ? P_TILE * IN : 0);   // partial head sums of columns 128..255 [128][P_MAX_OUT]
     uint64_t* b_full = (uint64_t*)(smem + p_bar_off(IN));
     uint64_t* t_full = b_full + 1;
     uint32_t* tmem_slot = (uint32_t*)(t_full + 1);
@@ -85,8 +90,13 @@ rollout_policy_kernel(const __grid_constant__ CUtensorMap tm_actor_w1t,
         for (int c = 0; c < 4; ++c) tma_load_2d(sB + c * (H * 64 * 2), tmB, b_full, c * 64, 0);
     }
     if (warp == 1) tmem_alloc(tmem_slot, 256);
-    for (int i = threadIdx.x; i < IN * H; i += P_THREADS) sW0[i] = W0[i];
+    constexpr bool REG_W = IN <= 8;     // first-layer weights of 8 columns fit in registers
+    if (!REG_W)
+        for (int i = threadIdx.x; i < IN * H; i += P_THREADS) sW0[i] = W0[i];
     for (int i = threadIdx.x; i < H; i += P_THREADS) { sb0[i] = b0[i]; sb1[i] = b1[i]; }
+    if (REG_W)
+        for (int i = threadIdx.x; i < P_TILE * IN; i += P_THREADS)
+            sX[i] = (size_t)row0 * IN + i < (size_t)a.n * IN ? a.obs[(size_t)row0 * IN + i] : 0.0f;
     for (int i = threadIdx.x; i < H * P_MAX_OUT; i += P_THREADS) {
         int j = i / P_MAX_OUT, o = i % P_MAX_OUT;
         sW2[i] = o < out_dim ? W2[j * out_dim + o] : 0.0f;
@@ -97,14 +107,53 @@ rollout_policy_kernel(const __grid_constant__ CUtensorMap tm_actor_w1t,
     }
     __syncthreads();
 
-    // ---- h0 tile: thread -> (row, half of the 256 columns)
-    {
+    // ---- h0 tile = act(obs . W0 + b0) as bf16 in the K-major 128-byte-swizzled layout (64-column chunk kc,
+    // 16-byte unit (j % 64) / 8 XOR (row % 8)).
+    if (REG_W) {
+        // thread -> (8-column group g, row set rs): the group's weights stay in registers over 16 rows, and the
+        // eight lanes of a quarter-warp write one 128-byte row of a chunk
+        const int g = threadIdx.x & 31, rs = threadIdx.x >> 5;
+        float w[IN][8], bias[8];
+#pragma unroll
+        for (int k = 0; k < IN; ++k) {
+            const float4 lo = __ldg(reinterpret_cast<const float4*>(W0 + k * H + g * 8));
+            const float4 hi = __ldg(reinterpret_cast<const float4*>(W0 + k * H + g * 8 + 4));
+            w[k][0] = lo.x; w[k][1] = lo.y; w[k][2] = lo.z; w[k][3] = lo.w;
+            w[k][4] = hi.x; w[k][5] = hi.y; w[k][6] = hi.z; w[k][7] = hi.w;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) bias[u] = sb0[g * 8 + u];
+        const int kc = g >> 3, unit = g & 7;
+#pragma unroll 2
+        for (int i = 0; i < P_TILE / 8; ++i) {
+            const int r = rs + 8 * i;
+            float x[IN];
+#pragma unroll
+            for (int k = 0; k < IN; ++k) x[k] = sX[r * IN + k];
+            float h[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                float acc = bias[u];
+#pragma unroll
+                for (int k = 0; k < IN; ++k) acc = fmaf(x[k], w[k][u], acc);
+                h[u] = a.act == 0 ? fmaxf(acc, 0.0f) : tanh_fast(acc);
+            }
+            uint32_t pw[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                __nv_bfloat162 pk = __floats2bfloat162_rn(h[2 * u], h[2 * u + 1]);
+                pw[u] = *reinterpret_cast<uint32_t*>(&pk);
+            }
+            uint8_t* dst = sA + kc * (P_TILE * 128) + r * 128 + ((unit ^ (r & 7)) << 4);
+            *reinterpret_cast<uint4*>(dst) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+        }
+    } else {
+        // wide inputs: thread -> (row, half of the 256 columns), weights read from shared memory
         const int r = threadIdx.x & (P_TILE - 1);
         const int half = threadIdx.x >> 7;
-        const int row = row0 + r;
         float x[IN];
 #pragma unroll
-        for (int k = 0; k < IN; ++k) x[k] = row < a.n ? a.obs[(size_t)row * IN + k] : 0.0f;
+        for (int k = 0; k < IN; ++k) x[k] = row0 + r < a.n ? a.obs[(size_t)(row0 + r) * IN + k] : 0.0f;
 #pragma unroll 2
         for (int c8 = 0; c8 < 16; ++c8) {
             const int j0 = half * 128 + c8 * 8;
@@ -122,7 +171,6 @@ rollout_policy_kernel(const __grid_constant__ CUtensorMap tm_actor_w1t,
                 __nv_bfloat162 pk = __floats2bfloat162_rn(h[2 * u], h[2 * u + 1]);
                 w[u] = *reinterpret_cast<uint32_t*>(&pk);
             }
-            // K-major, 128-byte swizzle: 64-column chunk kc, 16-byte unit (j % 64) / 8 XOR (row % 8)
             const int kc = j0 >> 6, unit = (j0 & 63) >> 3;
             uint8_t* dst = sA + kc * (P_TILE * 128) + r * 128 + ((unit ^ (r & 7)) << 4);
             *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -147,59 +195,72 @@ rollout_policy_kernel(const __grid_constant__ CUtensorMap tm_actor_w1t,
             mma_commit(t_full);
         }
     }
-    if (warp >= 4) {
-        const int q = warp & 3;
-        if (mbar_wait(t_full, 0, a.err, 302)) {
-            tc_fence_after_sync();
-            const int row = row0 + q * 32 + lane;
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
-            float o[P_MAX_OUT];
+    __syncwarp();
+    // Epilogue on all eight warps: warp w reads TMEM lane quarter w % 4 (its 32 rows) and the column half w / 4;
+    // the upper half hands its partial head sums to the lower half through shared memory.
+    const int q = warp & 3, hf = warp >> 2;
+    const int row = row0 + q * 32 + lane;
+    float o[P_MAX_OUT];
+    const bool ok = __all_sync(0xffffffffu, mbar_wait(t_full, 0, a.err, 302));
+    if (ok) {
+        tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
 #pragma unroll
-            for (int u = 0; u < P_MAX_OUT; ++u) o[u] = sb2[u];
+        for (int u = 0; u < P_MAX_OUT; ++u) o[u] = hf == 0 ? sb2[u] : 0.0f;
 #pragma unroll 1
-            for (int ch = 0; ch < 8; ++ch) {
-                float v[32];
-                tmem_ld_32x32(taddr + ch * 32, v);
+        for (int ch = hf * 4; ch < hf * 4 + 4; ++ch) {
+            float v[32];
+            tmem_ld_32x32(taddr + ch * 32, v);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int j = ch * 32 + i;
-                    const float z = v[i] + sb1[j];
-                    const float hv = a.act == 0 ? fmaxf(z, 0.0f) : tanh_fast(z);
+            for (int i = 0; i < 32; ++i) {
+                const int j = ch * 32 + i;
+                const float z = v[i] + sb1[j];
+                const float hv = a.act == 0 ? fmaxf(z, 0.0f) : tanh_fast(z);
 #pragma unroll
-                    for (int u = 0; u < P_MAX_OUT; ++u) o[u] = fmaf(hv, sW2[j * P_MAX_OUT + u], o[u]);
-                }
+                for (int u = 0; u < P_MAX_OUT; ++u) o[u] = fmaf(hv, sW2[j * P_MAX_OUT + u], o[u]);
             }
-            if (row < a.n) {
-                const size_t off = (size_t)a.t * a.n + row;
-                if (net == 0) {
-                    unsigned long long ts = (unsigned long long)a.ctr->total_steps + (unsigned long long)a.t * (unsigned long long)a.n;
-                    uint32_t seed = (uint32_t)(ts * 2654435761ull + (unsigned long long)a.t * 7919ull);  // ppo.mojo:2071
-                    float lp;
-                    if (CONT) {
-                        const int A = a.num_actions;
-                        float head[2 * P_MAX_OUT], act[P_MAX_OUT];
+        }
+        if (hf == 1) {
 #pragma unroll
-                        for (int u = 0; u < P_MAX_OUT; ++u) {
-                            if (u < A) { head[u] = o[u]; head[A + u] = sb2[P_MAX_OUT + u]; }
-                        }
-                        sample_continuous_one(head, A, seed, row, a.greedy, act, lp);
-                        for (int u = 0; u < A; ++u) {
-                            a.actions[(size_t)row * A + u] = act[u];
-                            a.r_actions[off * A + u] = act[u];
-                        }
-                    } else {
-                        float act;
-                        sample_one(o, a.num_actions, seed, row, a.greedy, act, lp);
-                        a.actions[row] = act;
-                        a.r_actions[off] = act;
+            for (int u = 0; u < P_MAX_OUT; ++u) sO[(q * 32 + lane) * P_MAX_OUT + u] = o[u];
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (ok && hf == 0) {
+#pragma unroll
+        for (int u = 0; u < P_MAX_OUT; ++u) o[u] += sO[(q * 32 + lane) * P_MAX_OUT + u];
+        if (row < a.n) {
+            const size_t off = (size_t)a.t * a.n + row;
+            if (net == 0) {
+                unsigned long long ts = (unsigned long long)a.ctr->total_steps + (unsigned long long)a.t * (unsigned long long)a.n;
+                uint32_t seed = (uint32_t)(ts * 2654435761ull + (unsigned long long)a.t * 7919ull);  // ppo.mojo:2071
+                float lp;
+                if (CONT) {
+                    const int A = a.num_actions;
+                    float head[2 * P_MAX_OUT], act[P_MAX_OUT];
+#pragma unroll
+                    for (int u = 0; u < P_MAX_OUT; ++u) {
+                        if (u < A) { head[u] = o[u]; head[A + u] = sb2[P_MAX_OUT + u]; }
                     }
-                    a.r_log_probs[off] = lp;
-#pragma unroll
-                    for (int k = 0; k < IN; ++k) a.r_obs[off * IN + k] = a.obs[(size_t)row * IN + k];
+                    sample_continuous_one(head, A, seed, row, a.greedy, act, lp);
+                    for (int u = 0; u < A; ++u) {
+                        a.actions[(size_t)row * A + u] = act[u];
+                        a.r_actions[off * A + u] = act[u];
+                    }
                 } else {
-                    a.values[row] = o[0];
-                    a.r_values[off] = o[0];
+                    float act;
+                    sample_one(o, a.num_actions, seed, row, a.greedy, act, lp);
+                    a.actions[row] = act;
+                    a.r_actions[off] = act;
                 }
+                a.r_log_probs[off] = lp;
+#pragma unroll
+                for (int k = 0; k < IN; ++k)
+                    a.r_obs[off * IN + k] = REG_W ? sX[(q * 32 + lane) * IN + k] : a.obs[(size_t)row * IN + k];
+            } else {
+                a.values[row] = o[0];
+                a.r_values[off] = o[0];
             }
         }
     }

@@ -322,29 +322,25 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
                 for (int a = 0; a < OUT; ++a) o[a] = sP[H + H * 8 + a];
             }
-#pragma unroll 1
-            for (int ch = 0; ch < 8; ++ch) {
+            // One 32-column chunk: activation / mask, bf16 pack, staging, TMA store.  The accumulator registers of
+            // the next chunk are already in flight (see the loop below), so the TMEM latency is off this path.
+            auto process = [&](int ch, const uint32_t (&acc)[32]) -> bool {
                 uint4 hm[4];
                 if (MODE == 2) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(&m_full[mk & 1u], (mk >> 1) & 1u, p.err, 106));
-                    if (!ok) break;
+                    if (!__all_sync(0xffffffffu, mbar_wait(&m_full[mk & 1u], (mk >> 1) & 1u, p.err, 106))) return false;
                     const uint4* src = reinterpret_cast<const uint4*>(mbuf + (mk & 1u) * K1_CHUNK_BYTES + lane * 64);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) hm[i] = src[i ^ swz];
                 }
-                float4 pv[8];
-                const bool has_prev = MODE != 0 && p.prev != nullptr && in_range;
-                if (has_prev) {
+                float v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]);
+                if (MODE != 0 && p.prev != nullptr && in_range) {
                     const float4* src = reinterpret_cast<const float4*>(p.prev + (size_t)row * H + ch * 32);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) pv[i] = __ldg(src + i);
-                }
-                float v[32];
-                tmem_ld_32x32(taddr + ch * 32, v);
-                if (has_prev) {
-#pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        v[4 * i] += pv[i].x; v[4 * i + 1] += pv[i].y; v[4 * i + 2] += pv[i].z; v[4 * i + 3] += pv[i].w;
+                        const float4 pv = __ldg(src + i);
+                        v[4 * i] += pv.x; v[4 * i + 1] += pv.y; v[4 * i + 2] += pv.z; v[4 * i + 3] += pv.w;
                     }
                 }
                 if (MODE == 0) {
@@ -353,60 +349,73 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
                         for (int i = 0; i < 8; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
                     }
-                } else {
-                    uint32_t packed[16];
-                    if (MODE == 1) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            int j = ch * 32 + i;
-                            float h_lo = v[i] + sP[j], h_hi = v[i + 1] + sP[j + 1];
-                            if (p.act == 0) { h_lo = fmaxf(h_lo, 0.0f); h_hi = fmaxf(h_hi, 0.0f); }
-                            else { h_lo = tanh_fast(h_lo); h_hi = tanh_fast(h_hi); }
-#pragma unroll
-                            for (int a = 0; a < OUT; ++a) {
-                                o[a] = fmaf(h_lo, sP[H + j * OUT + a], o[a]);
-                                o[a] = fmaf(h_hi, sP[H + (j + 1) * OUT + a], o[a]);
-                            }
-                            __nv_bfloat162 pk = __floats2bfloat162_rn(h_lo, h_hi);
-                            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
-                        }
-                    } else {
-                        const uint32_t* hw = reinterpret_cast<const uint32_t*>(hm);
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            uint32_t w = hw[i >> 1];
-                            // bf16 > 0  <=>  sign bit clear and magnitude non-zero
-                            float g_lo, g_hi;
-                            if (p.act == 0) {
-                                bool lo_pos = (w & 0x8000u) == 0 && (w & 0x7FFFu) != 0;
-                                bool hi_pos = (w & 0x80000000u) == 0 && (w & 0x7FFF0000u) != 0;
-                                g_lo = lo_pos ? v[i] : 0.0f;
-                                g_hi = hi_pos ? v[i + 1] : 0.0f;
-                            } else {
-                                const float y_lo = __uint_as_float(w << 16), y_hi = __uint_as_float(w & 0xFFFF0000u);
-                                g_lo = v[i] * (1.0f - y_lo * y_lo);
-                                g_hi = v[i + 1] * (1.0f - y_hi * y_hi);
-                            }
-                            __nv_bfloat162 pk = __floats2bfloat162_rn(g_lo, g_hi);
-                            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
-                        }
-                    }
-                    // the previous chunk's store must have finished reading the staging buffer
-                    if (lane == 0) bulk_store_wait_read_n<0>();
-                    __syncwarp();
-                    if (MODE == 2) {  // every lane has consumed mask chunk mk: refill its buffer two chunks ahead
-                        if (lane == 0) issue_mask(mk + 2);
-                        ++mk;
-                    }
-                    uint4* dst = reinterpret_cast<uint4*>(obuf + lane * 64);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        dst[i ^ swz] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) tma_store_2d(&tmOut, obuf, ch * 32, row0);
+                    return true;
                 }
+                uint32_t packed[16];
+                if (MODE == 1) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        int j = ch * 32 + i;
+                        float h_lo = v[i] + sP[j], h_hi = v[i + 1] + sP[j + 1];
+                        if (p.act == 0) { h_lo = fmaxf(h_lo, 0.0f); h_hi = fmaxf(h_hi, 0.0f); }
+                        else { h_lo = tanh_fast(h_lo); h_hi = tanh_fast(h_hi); }
+#pragma unroll
+                        for (int a = 0; a < OUT; ++a) {
+                            o[a] = fmaf(h_lo, sP[H + j * OUT + a], o[a]);
+                            o[a] = fmaf(h_hi, sP[H + (j + 1) * OUT + a], o[a]);
+                        }
+                        __nv_bfloat162 pk = __floats2bfloat162_rn(h_lo, h_hi);
+                        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
+                    }
+                } else {
+                    const uint32_t* hw = reinterpret_cast<const uint32_t*>(hm);
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        uint32_t w = hw[i >> 1];
+                        // bf16 > 0  <=>  sign bit clear and magnitude non-zero
+                        float g_lo, g_hi;
+                        if (p.act == 0) {
+                            bool lo_pos = (w & 0x8000u) == 0 && (w & 0x7FFFu) != 0;
+                            bool hi_pos = (w & 0x80000000u) == 0 && (w & 0x7FFF0000u) != 0;
+                            g_lo = lo_pos ? v[i] : 0.0f;
+                            g_hi = hi_pos ? v[i + 1] : 0.0f;
+                        } else {
+                            const float y_lo = __uint_as_float(w << 16), y_hi = __uint_as_float(w & 0xFFFF0000u);
+                            g_lo = v[i] * (1.0f - y_lo * y_lo);
+                            g_hi = v[i + 1] * (1.0f - y_hi * y_hi);
+                        }
+                        __nv_bfloat162 pk = __floats2bfloat162_rn(g_lo, g_hi);
+                        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
+                    }
+                }
+                // the previous chunk's store must have finished reading the staging buffer
+                if (lane == 0) bulk_store_wait_read_n<0>();
+                __syncwarp();
+                if (MODE == 2) {  // every lane has consumed mask chunk mk: refill its buffer two chunks ahead
+                    if (lane == 0) issue_mask(mk + 2);
+                    ++mk;
+                }
+                uint4* dst = reinterpret_cast<uint4*>(obuf + lane * 64);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    dst[i ^ swz] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) tma_store_2d(&tmOut, obuf, ch * 32, row0);
+                return true;
+            };
+            uint32_t ra[32], rb[32];
+            tmem_ld_32x32_issue(taddr, ra);
+#pragma unroll 1
+            for (int ch = 0; ch < 8 && ok; ch += 2) {
+                tmem_ld_wait(ra);
+                tmem_ld_32x32_issue(taddr + (ch + 1) * 32, rb);
+                ok = process(ch, ra);
+                tmem_ld_wait(rb);   // also when the chunk failed: no TMEM load may be in flight at the exit
+                if (ch + 2 < 8) tmem_ld_32x32_issue(taddr + (ch + 2) * 32, ra);
+                if (ok) ok = process(ch + 1, rb);
             }
+            tmem_ld_wait(ra);
             if (!ok) break;
             if (MODE == 1 && in_range) {
                 for (int a = 0; a < OUT; ++a)
@@ -574,9 +583,11 @@ int convert_w1(const float* W1, bf16* w1, bf16* w1t, cudaStream_t st) {
     return MRL_OK;
 }
 
-// Thread mapping of the CUDA-core kernels below: a block has HH threads; a warp covers 64 columns (eight
+// Thread mapping of the CUDA-core kernels below: a block has 256 threads and handles 256 columns
+// (column block blockIdx.y of a hidden width HH = 256 or 512: 512 threads per block would cap the kernels at
+// 128 registers and spill their weight tiles); a warp covers 64 columns (eight
 // lanes x 8 columns = 16 bytes of bf16 each, so a quarter-warp touches one contiguous 128-byte line) for 4 rows
-// at a time, and two warps share a 64-column block, so a block covers all HH columns of 8 rows per iteration.
+// at a time, and two warps share a 64-column block, so a block covers its 256 columns of 8 rows per iteration.
 // (With the lanes of a quarter-warp on different rows every 16-byte access costs eight L1 wavefronts instead
 // of one, and the L1 data pipe, not HBM, bounds these kernels.)  Sums over rows are finished inside a warp with
 // shuffles over its 4 row lanes; the two warps of a column block write separate partials (part 2 b and 2 b + 1).
@@ -600,21 +611,22 @@ __device__ __forceinline__ float sum_row_lanes(float v) {
 }
 // First layer (LinearReLU / LinearTanh[obs, 256], K = obs_dim): h0 = act(x . W0 + b0) in bf16, row-major.
 template <int IN, int HH>
-__global__ void __launch_bounds__(HH)
+__global__ void __launch_bounds__(256)
 l0_forward_kernel(const float* __restrict__ x, const float* __restrict__ W0, const float* __restrict__ b0,
                   bf16* __restrict__ h0, int M, int rows_per_block, int act) {
-    const VecMap<HH> vm;
+    const VecMap<256> vm;
+    const int col = blockIdx.y * 256 + vm.col0;   // first of this thread's 8 columns
     float w[IN][8], b[8];
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
-        b[u] = b0[vm.col0 + u];
+        b[u] = b0[col + u];
 #pragma unroll
-        for (int k = 0; k < IN; ++k) w[k][u] = W0[k * HH + vm.col0 + u];
+        for (int k = 0; k < IN; ++k) w[k][u] = W0[k * HH + col + u];
     }
     const int rb = blockIdx.x * rows_per_block;
     const int re = min(M, rb + rows_per_block);
     extern __shared__ float s_rows[];  // the slab's x rows: (re - rb) * IN floats
-    for (int i = threadIdx.x; i < (re - rb) * IN; i += HH) s_rows[i] = x[(size_t)rb * IN + i];
+    for (int i = threadIdx.x; i < (re - rb) * IN; i += 256) s_rows[i] = x[(size_t)rb * IN + i];
     __syncthreads();
 #pragma unroll 2
     for (int r = rb + vm.row_lane; r < re; r += 8) {
@@ -629,7 +641,7 @@ l0_forward_kernel(const float* __restrict__ x, const float* __restrict__ W0, con
             for (int k = 0; k < IN; ++k) acc = fmaf(xr[k], w[k][u], acc);
             hv[u] = act == 0 ? fmaxf(acc, 0.0f) : tanh_fast(acc);
         }
-        *reinterpret_cast<uint4*>(h0 + (size_t)r * HH + vm.col0) = pack8(hv);
+        *reinterpret_cast<uint4*>(h0 + (size_t)r * HH + col) = pack8(hv);
     }
 }
 
@@ -638,18 +650,19 @@ l0_forward_kernel(const float* __restrict__ x, const float* __restrict__ W0, con
 //   dW2[j][a] = sum_r h1[r][j] * dout[r][a],  db2[a] = sum_r dout[r][a],  db1[j] = sum_r g1[r][j]
 // part layout per block: [OUT][256] dW2^T, [256] db1, [OUT] db2.
 template <int OUT, int HH>
-__global__ void __launch_bounds__(HH)
+__global__ void __launch_bounds__(256)
 head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout, int ldd,
                      const float* __restrict__ W2, int out_dim, bf16* __restrict__ g1,
                      float* __restrict__ part, int M, int rows_per_block, int act) {
-    const VecMap<HH> vm;
+    const VecMap<256> vm;
+    const int col = blockIdx.y * 256 + vm.col0;   // first of this thread's 8 columns
     float w2[OUT][8], dw2[OUT][8], db1[8], db2[OUT];
 #pragma unroll
     for (int a = 0; a < OUT; ++a) {
         db2[a] = 0.0f;
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            w2[a][u] = a < out_dim ? W2[(vm.col0 + u) * out_dim + a] : 0.0f;
+            w2[a][u] = a < out_dim ? W2[(col + u) * out_dim + a] : 0.0f;
             dw2[a][u] = 0.0f;
         }
     }
@@ -658,7 +671,7 @@ head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout
     const int rb = blockIdx.x * rows_per_block;
     const int re = min(M, rb + rows_per_block);
     extern __shared__ float s_rows[];  // the slab's dout rows: (re - rb) * OUT floats
-    for (int i = threadIdx.x; i < (re - rb) * OUT; i += HH) {
+    for (int i = threadIdx.x; i < (re - rb) * OUT; i += 256) {
         int rr = i / OUT, a = i % OUT;
         s_rows[i] = a < out_dim ? dout[(size_t)(rb + rr) * ldd + a] : 0.0f;
     }
@@ -668,14 +681,14 @@ head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout
 #pragma unroll
     for (int i = 0; i < UNR; ++i) {
         const int r = rb + vm.row_lane + 8 * i;
-        nxt[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(h1 + (size_t)r * HH + vm.col0)) : make_uint4(0, 0, 0, 0);
+        nxt[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(h1 + (size_t)r * HH + col)) : make_uint4(0, 0, 0, 0);
     }
     for (int r0 = rb + vm.row_lane; r0 < re; r0 += 8 * UNR) {
 #pragma unroll
         for (int i = 0; i < UNR; ++i) {
             raw[i] = nxt[i];
             const int r = r0 + 8 * (UNR + i);
-            nxt[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(h1 + (size_t)r * HH + vm.col0)) : make_uint4(0, 0, 0, 0);
+            nxt[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(h1 + (size_t)r * HH + col)) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
         for (int i = 0; i < UNR; ++i) {
@@ -699,7 +712,7 @@ head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout
                 g[u] = act == 0 ? (h[u] > 0.0f ? dh : 0.0f) : dh * (1.0f - h[u] * h[u]);
                 db1[u] += g[u];
             }
-            *reinterpret_cast<uint4*>(g1 + (size_t)r * HH + vm.col0) = pack8(g);
+            *reinterpret_cast<uint4*>(g1 + (size_t)r * HH + col) = pack8(g);
         }
     }
     float* pb = part + (size_t)vm.part * ((OUT + 1) * HH + OUT);
@@ -708,26 +721,27 @@ head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             float v = sum_row_lanes(dw2[a][u]);
-            if (vm.writer) pb[a * HH + vm.col0 + u] = v;
+            if (vm.writer) pb[a * HH + col + u] = v;
         }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
         float v = sum_row_lanes(db1[u]);
-        if (vm.writer) pb[OUT * HH + vm.col0 + u] = v;
+        if (vm.writer) pb[OUT * HH + col + u] = v;
     }
 #pragma unroll
     for (int a = 0; a < OUT; ++a) {
         float v = sum_row_lanes(db2[a]);  // every column group sees the rows of its half: take column 0's thread
-        if (vm.writer && vm.col0 == 0) pb[(OUT + 1) * HH + a] = v;
+        if (vm.writer && col == 0) pb[(OUT + 1) * HH + a] = v;
     }
 }
 
 // dW0[k][j] = sum_r x[r][k] * g0[r][j], db0[j] = sum_r g0[r][j]; part per block: [IN + 1][256].
 template <int IN, int HH>
-__global__ void __launch_bounds__(HH)
+__global__ void __launch_bounds__(256)
 l0_backward_kernel(const bf16* __restrict__ g0, const float* __restrict__ x, float* __restrict__ part, int M,
                    int rows_per_block) {
-    const VecMap<HH> vm;
+    const VecMap<256> vm;
+    const int col = blockIdx.y * 256 + vm.col0;   // first of this thread's 8 columns
     float dw[IN][8], db[8];
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
@@ -738,21 +752,21 @@ l0_backward_kernel(const bf16* __restrict__ g0, const float* __restrict__ x, flo
     const int rb = blockIdx.x * rows_per_block;
     const int re = min(M, rb + rows_per_block);
     extern __shared__ float s_rows[];  // the slab's x rows
-    for (int i = threadIdx.x; i < (re - rb) * IN; i += HH) s_rows[i] = x[(size_t)rb * IN + i];
+    for (int i = threadIdx.x; i < (re - rb) * IN; i += 256) s_rows[i] = x[(size_t)rb * IN + i];
     __syncthreads();
     constexpr int UNR = 4;  // loads are issued one iteration ahead of their use
     uint4 raw[UNR], nxt[UNR];
 #pragma unroll
     for (int i = 0; i < UNR; ++i) {
         const int r = rb + vm.row_lane + 8 * i;
-        nxt[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(g0 + (size_t)r * HH + vm.col0)) : make_uint4(0, 0, 0, 0);
+        nxt[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(g0 + (size_t)r * HH + col)) : make_uint4(0, 0, 0, 0);
     }
     for (int r0 = rb + vm.row_lane; r0 < re; r0 += 8 * UNR) {
 #pragma unroll
         for (int i = 0; i < UNR; ++i) {
             raw[i] = nxt[i];
             const int r = r0 + 8 * (UNR + i);
-            nxt[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(g0 + (size_t)r * HH + vm.col0)) : make_uint4(0, 0, 0, 0);
+            nxt[i] = r < re ? __ldg(reinterpret_cast<const uint4*>(g0 + (size_t)r * HH + col)) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
         for (int i = 0; i < UNR; ++i) {
@@ -776,12 +790,12 @@ l0_backward_kernel(const bf16* __restrict__ g0, const float* __restrict__ x, flo
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             float v = sum_row_lanes(dw[k][u]);
-            if (vm.writer) pb[k * HH + vm.col0 + u] = v;
+            if (vm.writer) pb[k * HH + col + u] = v;
         }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
         float v = sum_row_lanes(db[u]);
-        if (vm.writer) pb[IN * HH + vm.col0 + u] = v;
+        if (vm.writer) pb[IN * HH + col + u] = v;
     }
 }
 
@@ -1102,20 +1116,34 @@ __global__ void fill_log_std_cols_kernel(const float* __restrict__ log_std, floa
     else if (ls > 2.0f) ls = 2.0f;
     out[(size_t)r * 2 * A + A + j] = ls;
 }
-// One block per action dimension: column sum of dout[:, A + j] in double.
-__global__ void log_std_grad_kernel(const float* __restrict__ dout, int ldd, int A, int batch, float* __restrict__ out) {
+// Column sums of dout[:, A .. 2A) in double, two stages with a fixed summation order: every block sums a
+// contiguous slab of rows into part[block][A]; one block then adds the partials in block order.
+__global__ void __launch_bounds__(256)
+log_std_grad_partial_kernel(const float* __restrict__ dout, int ldd, int A, int batch, int rows_per_block,
+                            double* __restrict__ part) {
     __shared__ double sm[32];
-    const int j = blockIdx.x;
+    const int rb = blockIdx.x * rows_per_block, re = min(batch, rb + rows_per_block);
+    for (int j = 0; j < A; ++j) {
+        double acc = 0.0;
+        for (int r = rb + threadIdx.x; r < re; r += 256) acc += (double)dout[(size_t)r * ldd + A + j];
+        acc = block_sum(acc, sm);
+        if (threadIdx.x == 0) part[(size_t)blockIdx.x * A + j] = acc;
+        __syncthreads();
+    }
+}
+__global__ void log_std_grad_final_kernel(const double* __restrict__ part, int nblocks, int A, float* __restrict__ out) {
+    const int j = threadIdx.x;
+    if (j >= A) return;
     double acc = 0.0;
-    for (int r = threadIdx.x; r < batch; r += blockDim.x) acc += (double)dout[(size_t)r * ldd + A + j];
-    acc = block_sum(acc, sm);
-    if (threadIdx.x == 0) out[j] = (float)acc;
+    for (int b = 0; b < nblocks; ++b) acc += part[(size_t)b * A + j];
+    out[j] = (float)acc;
 }
 
 template <int IN, int HH>
 static int l0_forward(const float* x, const float* W0, const float* b0, bf16* h0, int M, int act, cudaStream_t st) {
     const int rows_per_block = slab_rows(M, IN);
-    MRL_LAUNCH((l0_forward_kernel<IN, HH>), (M + rows_per_block - 1) / rows_per_block, HH, rows_per_block * IN * 4, st,
+    MRL_LAUNCH((l0_forward_kernel<IN, HH>), dim3((M + rows_per_block - 1) / rows_per_block, HH / 256), 256,
+               rows_per_block * IN * 4, st,
                x, W0, b0, h0, M, rows_per_block, act);
     return MRL_OK;
 }
@@ -1130,7 +1158,7 @@ static int l0_forward_any(int I, const float* x, const float* W0, const float* b
 template <int OUT, int HH>
 static int head_backward(const bf16* h1, const float* dout, int ldd, const float* W2, int O, bf16* g1, float* part,
                          int batch, int rows_per_block, int nblocks, int act, cudaStream_t st) {
-    MRL_LAUNCH((head_backward_kernel<OUT, HH>), nblocks, HH, rows_per_block * OUT * 4, st, h1, dout, ldd, W2, O, g1, part,
+    MRL_LAUNCH((head_backward_kernel<OUT, HH>), dim3(nblocks, HH / 256), 256, rows_per_block * OUT * 4, st, h1, dout, ldd, W2, O, g1, part,
                batch, rows_per_block, act);
     return MRL_OK;
 }
@@ -1145,7 +1173,7 @@ static int head_backward_any(int OUT, const bf16* h1, const float* dout, int ldd
 template <int IN, int HH>
 static int l0_backward(const bf16* g0, const float* x, float* part, int batch, int rows_per_block, int nblocks,
                        cudaStream_t st) {
-    MRL_LAUNCH((l0_backward_kernel<IN, HH>), nblocks, HH, rows_per_block * IN * 4, st, g0, x, part, batch,
+    MRL_LAUNCH((l0_backward_kernel<IN, HH>), dim3(nblocks, HH / 256), 256, rows_per_block * IN * 4, st, g0, x, part, batch,
                rows_per_block);
     return MRL_OK;
 }
@@ -1248,7 +1276,11 @@ int State::backward(const mrl_net_spec* net, const float* params, const float* x
     MRL_LAUNCH(reduce_head_parts_kernel, ceil_div(hstride, 32), 256, 0, st, part, 2 * nblocks, OUT, O, grads + oW2,
                grads + ob2, grads + ob1, hh);
     if (gaussian) {  // dlog_std[j] = sum over rows of dout[:, O + j] (stochastic_actor.mojo:727-966)
-        MRL_LAUNCH(log_std_grad_kernel, O, 256, 0, st, dout, ldd, O, batch, grads + ob2 + O);
+        const int lrows = (batch + 2 * sm_count() - 1) / (2 * sm_count());
+        const int lblocks = (batch + lrows - 1) / lrows;
+        double* lpart = reinterpret_cast<double*>(part);   // free between the head and first-layer reductions
+        MRL_LAUNCH(log_std_grad_partial_kernel, lblocks, 256, 0, st, dout, ldd, O, batch, lrows, lpart);
+        MRL_LAUNCH(log_std_grad_final_kernel, 1, 32, 0, st, lpart, lblocks, O, grads + ob2 + O);
     }
     prof_mark("reduce_head", st);
     // dh0 = g1 . W1^T times the activation derivative at h0 -> g0
