@@ -61,7 +61,6 @@ def kernel_algorithmic_bytes(w, total):
         "rollout_persistent": w["T"] * n * (w["step_bytes"] + 8 * i + 20),
         "l0_forward": B * (4 * i + 2 * h),
         "k1_forward_gemm": B * (4 * h + 4 * act_out),
-        "k1_forward_fused": B * (4 * i + 4 * h + 4 * act_out),   # x in, h0 and h1 out, head out
         "head_backward": B * (4 * h + 4 * act_out),
         "k1_dx_gemm": B * 6 * h,
         "l0_backward": B * (2 * h + 4 * i),

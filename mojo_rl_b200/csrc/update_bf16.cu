@@ -8,7 +8,6 @@
 // reductions stay on CUDA cores in fp32.  Activations are stored once, in bf16
 // and row-major (h0, h1, g1, g0): the dW GEMM reads them as MN-major operands.
 // The reference has no counterpart: its matmuls are fp32 16x16 tiles.
-#include <cstdlib>
 #include "update_bf16.cuh"
 
 namespace mrl {
@@ -55,25 +54,19 @@ constexpr int K1_A_STAGE = TILE_M * KCH * 2;          // 16384
 constexpr int K1_PARAM_FLOATS = H + H * 8 + 8;        // bias, W2 (up to 8 outputs), b2
 constexpr int K1_EPI_WARPS = 8;
 constexpr int K1_CHUNK_BYTES = 32 * 64;               // 32 rows x 32 bf16
-// IN > 0 (mode 1 only) fuses the first layer: the A chunks are computed on CUDA cores by four producer warps
-// instead of arriving by TMA, and W0 / b0 stay in shared memory as floats.
-__host__ __device__ constexpr int k1_stages(int mode, int in = 0) { return (mode == 2 || in > 0) ? 3 : 4; }
+__host__ __device__ constexpr int k1_stages(int mode) { return mode == 2 ? 3 : 4; }
 __host__ __device__ constexpr int k1_out_bufs(int mode) { return mode == 0 ? 0 : 1; }
 // mode 1: bias / W2 / b2 as floats; mode 2: two mask chunks per epilogue warp
 __host__ __device__ constexpr int k1_aux_bytes(int mode) {
     return mode == 2 ? K1_EPI_WARPS * 2 * K1_CHUNK_BYTES : ((K1_PARAM_FLOATS * 4 + 1023) / 1024) * 1024;
 }
-__host__ __device__ constexpr int k1_out_off(int mode, int in = 0) { return K1_B_BYTES + k1_stages(mode, in) * K1_A_STAGE; }
-__host__ __device__ constexpr int k1_aux_off(int mode, int in = 0) {
-    return k1_out_off(mode, in) + k1_out_bufs(mode) * K1_EPI_WARPS * K1_CHUNK_BYTES;
+__host__ __device__ constexpr int k1_out_off(int mode) { return K1_B_BYTES + k1_stages(mode) * K1_A_STAGE; }
+__host__ __device__ constexpr int k1_aux_off(int mode) {
+    return k1_out_off(mode) + k1_out_bufs(mode) * K1_EPI_WARPS * K1_CHUNK_BYTES;
 }
-__host__ __device__ constexpr int k1_w0_off(int mode, int in = 0) { return k1_aux_off(mode, in) + k1_aux_bytes(mode); }
-__host__ __device__ constexpr int k1_x_off(int mode, int in = 0) { return k1_w0_off(mode, in) + (in > 0 ? (in + 1) * H * 4 : 0); }
-__host__ __device__ constexpr int k1_bar_off(int mode, int in = 0) { return k1_x_off(mode, in) + in * TILE_M * 4; }
-__host__ __device__ constexpr int k1_smem(int mode, int in = 0) { return k1_bar_off(mode, in) + 32 * 8 + 1024; }  // + barriers + alignment slack
-__host__ __device__ constexpr int k1_threads(int in) { return in > 0 ? K1_THREADS + 128 : K1_THREADS; }
-static_assert(k1_smem(1) <= 232448 && k1_smem(2) <= 232448 && k1_smem(0) <= 232448 && k1_smem(1, 8) <= 232448,
-              "K1 shared memory");
+__host__ __device__ constexpr int k1_bar_off(int mode) { return k1_aux_off(mode) + k1_aux_bytes(mode); }
+__host__ __device__ constexpr int k1_smem(int mode) { return k1_bar_off(mode) + 32 * 8 + 1024; }  // + barriers + alignment slack
+static_assert(k1_smem(1) <= 232448 && k1_smem(2) <= 232448 && k1_smem(0) <= 232448, "K1 shared memory");
 
 struct K1Params {
     int M;
@@ -84,7 +77,6 @@ struct K1Params {
     // Hidden widths above 256 are computed in 256-wide blocks: a second launch adds the first one's fp32
     // result (prev, [M, 256]) to its accumulator before the epilogue.
     const float* prev;
-    const float* x; const float* W0; const float* b0;   // fused first layer: x [M, IN], W0 [IN, 256], b0 [256]
     int* err;
 };
 
@@ -95,23 +87,19 @@ __device__ __forceinline__ void drain_on_error(const int* err) {
 
 // tmOut: [32 rows x 32 columns] boxes (64-byte swizzle) of the bf16 output (h1 in mode 1, g0 in mode 2);
 // tmMask: the same boxes of the mask source h0 (mode 2).  Unused maps are passed as copies of tmA.
-// With IN > 0, tmA is the map of h0 itself: the producer warps (10-13) store every chunk they compute through it.
-template <int MODE, int OUT, int IN = 0>
-__global__ void __launch_bounds__(k1_threads(IN), 1)
+template <int MODE, int OUT>
+__global__ void __launch_bounds__(K1_THREADS, 1)
 k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmMask, K1Params p) {
-    static_assert(IN == 0 || MODE == 1, "the fused first layer belongs to the forward pass");
-    constexpr int STAGES = k1_stages(MODE, IN);
+    constexpr int STAGES = k1_stages(MODE);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* sB = smem;
     uint8_t* sA = smem + K1_B_BYTES;
-    uint8_t* sOut = smem + k1_out_off(MODE, IN);
-    uint8_t* sAux = smem + k1_aux_off(MODE, IN);
+    uint8_t* sOut = smem + k1_out_off(MODE);
+    uint8_t* sAux = smem + k1_aux_off(MODE);
     float* sP = (float*)sAux;
-    float* sW0 = (float*)(smem + k1_w0_off(MODE, IN));   // [IN][256] then b0 [256]
-    float* sX = (float*)(smem + k1_x_off(MODE, IN));     // the tile's rows of x: [128][IN]
-    uint64_t* bars = (uint64_t*)(smem + k1_bar_off(MODE, IN));
+    uint64_t* bars = (uint64_t*)(smem + k1_bar_off(MODE));
     uint64_t* b_full = bars;
     uint64_t* a_full = bars + 1;
     uint64_t* a_empty = a_full + STAGES;
@@ -119,13 +107,11 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     uint64_t* t_empty = t_full + 2;
     uint64_t* m_full_all = t_empty + 2;                 // 2 per epilogue warp (mode 2)
     uint32_t* tmem_slot = (uint32_t*)(m_full_all + 2 * K1_EPI_WARPS);
-    uint32_t* prod_fail = tmem_slot + 1;                // set when the producer group's wait gave up
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_tiles = (p.M + TILE_M - 1) / TILE_M;
 
     if (threadIdx.x == 0) {
-        *prod_fail = 0u;
         mbar_init(b_full, 1);
         for (int s = 0; s < STAGES; ++s) { mbar_init(&a_full[s], 1); mbar_init(&a_empty[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&t_full[b], 1); mbar_init(&t_empty[b], 4); }
@@ -137,12 +123,7 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (MODE == 2) prefetch_tensormap(&tmMask);
     }
     if (warp == 1) tmem_alloc(tmem_slot, 512);
-    if (IN > 0 && warp >= 10) {
-        int t = threadIdx.x - 320;
-        for (int i = t; i < IN * H; i += 128) sW0[i] = p.W0[i];
-        for (int i = t; i < H; i += 128) sW0[IN * H + i] = p.b0[i];
-    }
-    if (warp >= 2 && warp < 10 && MODE == 1) {
+    if (warp >= 2 && MODE == 1) {
         int t = threadIdx.x - 64;
         for (int i = t; i < H; i += 256) sP[i] = p.bias[i];
         for (int i = t; i < H * OUT; i += 256) {
@@ -162,7 +143,7 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             for (int c = 0; c < 4; ++c) tma_load_2d(sB + c * (H * KCH * 2), &tmB, b_full, c * KCH, 0);
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; IN == 0 && tile < num_tiles && ok; tile += gridDim.x) {
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 for (int c = 0; c < 4 && ok; ++c, ++it) {
                     int s = it % STAGES;
                     uint32_t ph = (it / STAGES) & 1u;
@@ -199,94 +180,6 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 if (ok) mma_commit(&t_full[buf]);
             }
         }
-    } else if (IN > 0 && warp >= 10) {
-        // First layer on CUDA cores (same fmaf order as l0_forward_kernel).  Thread = (8-column group g of the
-        // 64-column chunk, row set rs): the chunk's weights stay in registers while the thread walks its 8 rows
-        // (rs, rs + 16, ...); the eight lanes of a quarter-warp write one 128-byte row of the K-major
-        // 128-byte-swizzled A stage.  Each finished chunk is handed to the MMA warp and stored to global memory
-        // (the backward pass reads h0) by one TMA store.
-        const int t = threadIdx.x - 320;
-        const int g = t & 7, rs = t >> 3;
-        constexpr int XV = (IN * TILE_M) / (128 * 4);   // float4 per thread of the [128, IN] x tile
-        float4 xnext[XV > 0 ? XV : 1];
-        auto fetch_x = [&](int tile) {
-#pragma unroll
-            for (int i = 0; i < XV; ++i) {
-                const int e = (i * 128 + t) * 4;          // element of the tile's x block (rows are contiguous)
-                const size_t ge = (size_t)tile * TILE_M * IN + e;
-                xnext[i] = ge + 3 < (size_t)p.M * IN ? __ldg(reinterpret_cast<const float4*>(p.x + ge))
-                                                    : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            }
-        };
-        if ((int)blockIdx.x < num_tiles) fetch_x(blockIdx.x);
-        uint32_t it = 0;
-        bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            asm volatile("bar.sync 1, 128;" ::: "memory");   // every thread is done reading the previous x tile
-#pragma unroll
-            for (int i = 0; i < XV; ++i) *reinterpret_cast<float4*>(sX + (i * 128 + t) * 4) = xnext[i];
-            if (tile + (int)gridDim.x < num_tiles) fetch_x(tile + gridDim.x);
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            for (int c = 0; c < 4; ++c, ++it) {
-                const int s = it % STAGES;
-                const uint32_t ph = (it / STAGES) & 1u;
-                float w[IN > 0 ? IN : 1][8], bias[8];
-                {
-                    const int j0 = c * KCH + g * 8;
-#pragma unroll
-                    for (int k = 0; k < IN; ++k) {
-                        const float4 lo = *reinterpret_cast<const float4*>(sW0 + k * H + j0);
-                        const float4 hi = *reinterpret_cast<const float4*>(sW0 + k * H + j0 + 4);
-                        w[k][0] = lo.x; w[k][1] = lo.y; w[k][2] = lo.z; w[k][3] = lo.w;
-                        w[k][4] = hi.x; w[k][5] = hi.y; w[k][6] = hi.z; w[k][7] = hi.w;
-                    }
-                    const float4 lo = *reinterpret_cast<const float4*>(sW0 + IN * H + j0);
-                    const float4 hi = *reinterpret_cast<const float4*>(sW0 + IN * H + j0 + 4);
-                    bias[0] = lo.x; bias[1] = lo.y; bias[2] = lo.z; bias[3] = lo.w;
-                    bias[4] = hi.x; bias[5] = hi.y; bias[6] = hi.z; bias[7] = hi.w;
-                }
-                // the stage is free once the MMAs that read it have retired and its previous store has read it
-                if (t == 0) {
-                    bulk_store_wait_read_n<STAGES - 1>();
-                    if (!mbar_wait(&a_empty[s], ph ^ 1u, p.err, 107)) *(volatile uint32_t*)prod_fail = 1u;
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                ok = *(volatile uint32_t*)prod_fail == 0u;   // the same answer for all 128 producer threads
-                if (!ok) break;
-                uint8_t* stage = sA + s * K1_A_STAGE;
-#pragma unroll 2
-                for (int i = 0; i < 8; ++i) {
-                    const int r = rs + 16 * i;
-                    float xr[IN > 0 ? IN : 1];
-                    if (IN % 4 == 0) {
-#pragma unroll
-                        for (int k = 0; k < IN; k += 4) {
-                            const float4 t4 = *reinterpret_cast<const float4*>(sX + r * IN + k);
-                            xr[k] = t4.x; xr[k + 1] = t4.y; xr[k + 2] = t4.z; xr[k + 3] = t4.w;
-                        }
-                    } else {
-#pragma unroll
-                        for (int k = 0; k < IN; ++k) xr[k] = sX[r * IN + k];
-                    }
-                    float h[8];
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        float acc = bias[u];
-#pragma unroll
-                        for (int k = 0; k < IN; ++k) acc = fmaf(xr[k], w[k][u], acc);
-                        h[u] = p.act == 0 ? fmaxf(acc, 0.0f) : tanh_fast(acc);
-                    }
-                    *reinterpret_cast<uint4*>(stage + r * 128 + ((g ^ (r & 7)) << 4)) = pack8(h);
-                }
-                fence_proxy_async_smem();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (t == 0) {
-                    mbar_arrive(&a_full[s]);
-                    tma_store_2d(&tmA, sA + s * K1_A_STAGE, c * KCH, tile * TILE_M);
-                }
-            }
-        }
-        if (t == 0) bulk_store_wait_read_n<0>();
     } else {
         const int q = warp & 3;             // TMEM lane quarter this warp may read
         const int ew = warp - 2;            // epilogue warp 0..7
@@ -989,33 +882,21 @@ static int slab_rows(int M, int floats_per_row) {
 
 // tmOut / tmMask: staging-box maps (make_box_map) of the bf16 output and, in mode 2, of the mask source;
 // mode 0 ignores both.
-template <int MODE, int OUT, int IN = 0>
+template <int MODE, int OUT>
 static int launch_k1(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmOut,
                      const CUtensorMap& tmMask, const K1Params& p, cudaStream_t st) {
     static bool attr_set = false;
     if (!attr_set) {
-        MRL_CUDA_OK(cudaFuncSetAttribute(k1_rowtile_kernel<MODE, OUT, IN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         k1_smem(MODE, IN)));
+        MRL_CUDA_OK(cudaFuncSetAttribute(k1_rowtile_kernel<MODE, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         k1_smem(MODE)));
         attr_set = true;
     }
     int tiles = (p.M + TILE_M - 1) / TILE_M;
     int grid = tiles < sm_count() ? tiles : sm_count();
-    k1_rowtile_kernel<MODE, OUT, IN><<<grid, k1_threads(IN), k1_smem(MODE, IN), st>>>(tmA, tmB, tmOut, tmMask, p);
+    k1_rowtile_kernel<MODE, OUT><<<grid, K1_THREADS, k1_smem(MODE), st>>>(tmA, tmB, tmOut, tmMask, p);
     count_launch();
     MRL_CUDA_OK(cudaGetLastError());
     return MRL_OK;
-}
-
-// Forward with the first layer fused (p.x / p.W0 / p.b0 set; tmH0 is both the store map of h0 and the A slot).
-template <int IN>
-static int launch_k1_forward_fused(const CUtensorMap& tmH0, const CUtensorMap& tmB, const CUtensorMap& tmOut,
-                                   const K1Params& p, cudaStream_t st) {
-    if (p.out_dim <= 1) return launch_k1<1, 1, IN>(tmH0, tmB, tmOut, tmOut, p, st);
-    if (p.out_dim <= 2) return launch_k1<1, 2, IN>(tmH0, tmB, tmOut, tmOut, p, st);
-    if (p.out_dim <= 4) return launch_k1<1, 4, IN>(tmH0, tmB, tmOut, tmOut, p, st);
-    if (p.out_dim <= 8) return launch_k1<1, 8, IN>(tmH0, tmB, tmOut, tmOut, p, st);
-    set_error("bf16 path: head width %d > 8 is not built", p.out_dim);
-    return MRL_ERR_UNSUPPORTED;
 }
 
 static int launch_k1_forward(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmOut,
@@ -1198,27 +1079,6 @@ int State::forward(const mrl_net_spec* net, const float* params, const float* x,
     const int act = net->activation == MRL_ACT_RELU ? 0 : 1;
     const bool gaussian = net->head == MRL_HEAD_STOCHASTIC_ACTOR;
     const int head_ld = gaussian ? 2 * O : O;
-    // Width 256 with 4 or 8 inputs: the first layer runs inside the GEMM kernel (h0 never comes back from HBM).
-    // Tuning knob.  Measured at B = 262 144: the fused kernel takes 132 us, l0_forward + the GEMM kernel 95 us
-    // (the four producer warps cannot keep up with the tensor core), so the separate launch is the default.
-    static const bool fuse_allowed = getenv("MRL_FUSED_L0") != nullptr;
-    const bool fused_l0 = fuse_allowed && nb == 1 && (I == 4 || I == 8) && ((uintptr_t)x & 15) == 0;
-    if (fused_l0) {
-        K1Params p{};
-        p.M = batch; p.bias = b1; p.W2 = W2; p.b2 = b2; p.out_dim = O; p.head_out = head_out;
-        p.head_ld = head_ld;
-        p.act = act;
-        p.x = x; p.W0 = W0; p.b0 = b0;
-        p.err = err;
-        rc = I == 4 ? launch_k1_forward_fused<4>(tm_h0[0], tm_w1t[0][0], tm_h1_box[0], p, st)
-                    : launch_k1_forward_fused<8>(tm_h0[0], tm_w1t[0][0], tm_h1_box[0], p, st);
-        if (rc) return rc;
-        if (gaussian) {
-            MRL_LAUNCH(fill_log_std_cols_kernel, ceil_div((int64_t)batch * O, 256), 256, 0, st, b2 + O, head_out, batch, O);
-        }
-        prof_mark("k1_forward_fused", st);
-        return MRL_OK;
-    }
     rc = nb == 1 ? l0_forward_any<256>(I, x, W0, b0, h0, batch, act, st)
                  : l0_forward_any<512>(I, x, W0, b0, h0, batch, act, st);
     if (rc) return rc;
