@@ -240,6 +240,9 @@ int mrl_ppo_continuous_critic_grad(int batch, const float* values, const float* 
 /* clamp_log_std_params_kernel (kernels.mojo:842-873): clamps the state-independent
  * log_std parameters (the last action_dim floats of the actor) to [-5, 2]. */
 int mrl_clamp_log_std(int action_dim, float* log_std_params, void* stream);
+/* add_obs_noise_kernel (deep_agents/ppo/kernels.mojo:882-925): obs[i][d] += noise_std * N(0, 1), Box-Muller on a
+ * Philox stream seeded rng_seed + i * obs_dim + d; noise_std <= 0 leaves obs untouched. */
+int mrl_add_obs_noise(int n_envs, int obs_dim, float* obs, float noise_std, uint32_t rng_seed, void* stream);
 
 /* RunningMeanStd.update followed by RunningMeanStd.normalize
  * (core/utils/normalization.mojo:188-292) over one rollout of rewards.
@@ -302,6 +305,8 @@ typedef struct mrl_config {
     float adam_beta1;
     float adam_beta2;
     float adam_eps;
+    float obs_noise_std;     /* continuous agent only: observation noise (ppo_continuous.mojo:265,2557-2565);
+                                0 = off (the reference default)                                             */
 } mrl_config;
 
 /* Reference defaults (ppo.mojo:869-892; adam.mojo:38-50). */

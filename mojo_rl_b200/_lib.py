@@ -31,7 +31,7 @@ class Config(ctypes.Structure):
                 ("gamma", ctypes.c_double), ("gae_lambda", ctypes.c_double), ("clip_epsilon", ctypes.c_float),
                 ("value_loss_coef", ctypes.c_float), ("target_kl", ctypes.c_float),
                 ("max_grad_norm", ctypes.c_float), ("adam_beta1", ctypes.c_float), ("adam_beta2", ctypes.c_float),
-                ("adam_eps", ctypes.c_float)]
+                ("adam_eps", ctypes.c_float), ("obs_noise_std", ctypes.c_float)]
 
 
 class Stats(ctypes.Structure):
@@ -81,6 +81,7 @@ SIGNATURES = {
     "mrl_ppo_continuous_actor_grad": (ctypes.c_int, [ctypes.c_int, ctypes.c_int] + [c_void_p] * 4 + [ctypes.c_float, ctypes.c_float] + [c_void_p] * 3),
     "mrl_ppo_continuous_critic_grad": (ctypes.c_int, [ctypes.c_int] + [c_void_p] * 3 + [ctypes.c_float, ctypes.c_int, c_void_p, c_void_p]),
     "mrl_clamp_log_std": (ctypes.c_int, [ctypes.c_int, c_void_p, c_void_p]),
+    "mrl_add_obs_noise": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, c_void_p, ctypes.c_float, ctypes.c_uint32, c_void_p]),
     "mrl_reward_rms_update_normalize": (ctypes.c_int, [ctypes.c_int64] + [c_void_p] * 5),
     "mrl_normalize_advantages_f64sqrt": (ctypes.c_int, [ctypes.c_int64, c_void_p, c_void_p, c_void_p]),
     "mrl_fused_train_scratch_doubles": (ctypes.c_int64, [ctypes.POINTER(NetSpec), ctypes.c_int]),

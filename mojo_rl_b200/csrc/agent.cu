@@ -348,6 +348,7 @@ extern "C" void mrl_config_defaults(mrl_config* cfg) {
     cfg->world_size = 1;
     cfg->rank = 0;
     cfg->normalize_rewards = 1;  // ppo_continuous.mojo:258
+    cfg->obs_noise_std = 0.0f;   // ppo_continuous.mojo:265
     cfg->gamma = 0.99;
     cfg->gae_lambda = 0.95;
     cfg->clip_epsilon = 0.2f;
@@ -580,6 +581,13 @@ extern "C" int mrl_ppo_reset(mrl_ctx* c, uint64_t rng_seed) {
     if (rc) return rc;
     MRL_LAUNCH(extract_obs_kernel, ceil_div((int64_t)N * c->obs_dim, 256), 256, 0, c->stream, c->states, c->obs, N,
                c->state_size, c->obs_dim);
+    // Observation noise of the continuous agent (ppo_continuous.mojo:2557-2565, seed 42).  The reference also
+    // launches the kernel after every env step (:2705-2713), but the observation extraction that follows the
+    // selective reset (:2832-2838) rewrites every row from the state buffer before anything reads the noisy
+    // values, so only this launch reaches the policy.
+    if (c->continuous && c->cfg.obs_noise_std > 0.0f) {
+        if ((rc = add_obs_noise_impl(N, c->obs_dim, c->obs, c->cfg.obs_noise_std, 42u, c->stream))) return rc;
+    }
     MRL_CUDA_OK(cudaMemsetAsync(c->episode_rewards, 0, sizeof(float) * N, c->stream));
     MRL_CUDA_OK(cudaMemsetAsync(c->episode_steps, 0, sizeof(float) * N, c->stream));
     return MRL_OK;

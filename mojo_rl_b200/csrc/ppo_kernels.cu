@@ -390,6 +390,31 @@ extern "C" int mrl_ppo_continuous_critic_grad(int batch, const float* values, co
     return MRL_OK;
 }
 
+// add_obs_noise_kernel (kernels.mojo:882-925): one thread per environment, one Philox stream per (env, dim).
+__global__ void add_obs_noise_kernel(float* __restrict__ obs, int n, int obs_dim, float noise_std, uint32_t rng_seed) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n || noise_std <= 0.0f) return;
+    for (int d = 0; d < obs_dim; ++d) {
+        Philox ph((uint64_t)((int64_t)rng_seed + (int64_t)i * obs_dim + d), 0);
+        float r[4];
+        ph.step_uniform(r);
+        const float u1 = r[0] + 1e-8f, u2 = r[1];
+        const float mag = sqrtf(-2.0f * mrl_logf(u1));
+        const float noise = mag * mrl_cosf(u2 * 6.283185307179586f);
+        obs[(size_t)i * obs_dim + d] = obs[(size_t)i * obs_dim + d] + noise * noise_std;
+    }
+}
+namespace mrl {
+int add_obs_noise_impl(int n, int obs_dim, float* obs, float noise_std, uint32_t rng_seed, cudaStream_t st) {
+    MRL_LAUNCH(add_obs_noise_kernel, ceil_div(n, 128), 128, 0, st, obs, n, obs_dim, noise_std, rng_seed);
+    return MRL_OK;
+}
+}  // namespace mrl
+extern "C" int mrl_add_obs_noise(int n_envs, int obs_dim, float* obs, float noise_std, uint32_t rng_seed, void* stream) {
+    MRL_CHECK_ARG(n_envs > 0 && obs_dim > 0 && obs);
+    return mrl::add_obs_noise_impl(n_envs, obs_dim, obs, noise_std, rng_seed, as_stream(stream));
+}
+
 extern "C" int mrl_clamp_log_std(int action_dim, float* log_std_params, void* stream) {
     MRL_CHECK_ARG(action_dim > 0 && action_dim <= 32 && log_std_params);
     launch_clamp_log_std(log_std_params, action_dim, nullptr, as_stream(stream));

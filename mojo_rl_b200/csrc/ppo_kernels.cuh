@@ -194,6 +194,7 @@ int normalize_advantages_impl(int64_t n, float* adv, double* stats2, cudaStream_
 // RunningMeanStd.update + normalize (core/utils/normalization.mojo:188-292):
 // state3 = {count, mean, var_sum} on the device, scratch2 two doubles.
 int reward_rms_impl(int64_t n, const float* in, float* out, double* state3, double* scratch2, cudaStream_t st);
+int add_obs_noise_impl(int n, int obs_dim, float* obs, float noise_std, uint32_t rng_seed, cudaStream_t st);
 int grad_clip_impl(int n, float* grads, float max_norm, double* sumsq, float* report, cudaStream_t st);
 int mlp_forward_impl(const mrl_net_spec* net, int batch, const float* in, const float* params, float* out,
                      float* cache, float* workspace, cudaStream_t st);

@@ -270,21 +270,22 @@ class DeepPPOContinuousAgent(DeepPPOAgent):
     """DeepPPOContinuousAgent[obs_dim, action_dim, hidden_dim, rollout_len, n_envs, gpu_minibatch_size]
     with the constructor defaults of ppo_continuous.mojo:232-266: tanh trunk, StochasticActor head
     (state-independent log_std), Kaiming init with a small mean head and log_std = -0.5, reward
-    normalisation by a running mean / std, no value-loss coefficient in the critic gradient.
-    Observation noise (obs_noise_std, default 0 in the reference) is not built."""
+    normalisation by a running mean / std, no value-loss coefficient in the critic gradient,
+    obs_noise_std (:265; Gaussian noise on the observations after the initial reset, :2557-2565)."""
 
     def __init__(self, obs_dim, action_dim, hidden_dim=64, rollout_len=128, n_envs=1024, gpu_minibatch_size=256,
                  gamma=0.99, gae_lambda=0.95, clip_epsilon=0.2, actor_lr=0.0003, critic_lr=0.001,
                  entropy_coef=0.01, value_loss_coef=0.5, num_epochs=10, normalize_advantages=True, target_kl=0.02,
                  max_grad_norm=0.5, anneal_lr=True, anneal_entropy=False, target_total_steps=0,
                  norm_adv_per_minibatch=True, action_scale=1.0, action_bias=0.0, checkpoint_every=0,
-                 checkpoint_path="", normalize_rewards=True, clip_value=True, precision=0, seed=0):
+                 checkpoint_path="", normalize_rewards=True, obs_noise_std=0.0, clip_value=True, precision=0, seed=0):
         super().__init__(obs_dim, action_dim, hidden_dim, rollout_len, n_envs, gpu_minibatch_size, gamma, gae_lambda,
                          clip_epsilon, actor_lr, critic_lr, entropy_coef, value_loss_coef, num_epochs, 64,
                          normalize_advantages, target_kl, max_grad_norm, anneal_lr, anneal_entropy,
                          target_total_steps, clip_value, norm_adv_per_minibatch, checkpoint_every, checkpoint_path,
                          precision, seed)
         self.action_scale, self.action_bias, self.normalize_rewards = action_scale, action_bias, normalize_rewards
+        self.obs_noise_std = obs_noise_std
         rng = np.random.default_rng(seed)
         # ppo_continuous.mojo:171-194, :296-343
         self.actor = Network(seq(LinearTanh(obs_dim, hidden_dim), LinearTanh(hidden_dim, hidden_dim),
@@ -303,6 +304,7 @@ class DeepPPOContinuousAgent(DeepPPOAgent):
     def make_config(self, env_kind, deterministic=False, world_size=1, rank=0):
         cfg = super().make_config(env_kind, deterministic, world_size, rank)
         cfg.normalize_rewards = int(self.normalize_rewards)
+        cfg.obs_noise_std = float(self.obs_noise_std)
         return cfg
 
     def train_gpu(self, EnvType, ctx=None, num_episodes=100, verbose=False, print_every=10, max_rollouts=None):

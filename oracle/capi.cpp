@@ -123,6 +123,9 @@ void orc_ppo_critic_grad(int batch, const float* values, const float* old_values
     ppo::critic_grad(values, old_values, returns, batch, value_loss_coef, clip_epsilon, clip_value != 0,
                      (float)batch, grad_values);
 }
+void orc_add_obs_noise(int n, int obs_dim, float* obs, float noise_std, uint32_t rng_seed) {
+    ppo::add_obs_noise(obs, n, obs_dim, noise_std, rng_seed);
+}
 void orc_sample_continuous_actions(int n, int A, const float* actor_out, float* actions, float* log_probs,
                                    uint32_t seed, int greedy) {
     ppo::sample_continuous_actions(actor_out, n, A, seed, greedy, actions, log_probs);

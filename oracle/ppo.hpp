@@ -410,6 +410,21 @@ inline void sample_continuous_actions(const float* actor_out, int n, int A, uint
     }
 }
 
+// add_obs_noise_kernel, kernels.mojo:882-925.
+inline void add_obs_noise(float* obs, int n, int obs_dim, float noise_std, uint32_t rng_seed) {
+    if (noise_std <= 0.0f) return;
+    for (int i = 0; i < n; ++i)
+        for (int d = 0; d < obs_dim; ++d) {
+            Philox ph((uint64_t)((int64_t)rng_seed + (int64_t)i * obs_dim + d), 0);
+            float r[4];
+            ph.step_uniform(r);
+            float u1 = r[0] + 1e-8f, u2 = r[1];
+            float mag = sqrtf(-2.0f * mrl_logf(u1));
+            float noise = mag * mrl_cosf(u2 * 6.283185307179586f);
+            obs[(size_t)i * obs_dim + d] = obs[(size_t)i * obs_dim + d] + noise * noise_std;
+        }
+}
+
 // ppo_continuous_actor_grad_kernel, kernels.mojo:230-412.  grad_out is [batch, 2A].
 inline void continuous_actor_grad(const float* actor_out, const float* old_log_probs, const float* advantages,
                                   const float* actions, int batch, int A, float clip_epsilon,

@@ -113,6 +113,9 @@ struct Agent {
     void reset(uint64_t seed) {
         env_reset(cfg.env_kind, states.data(), cfg.n_envs, seed);
         extract_obs();
+        // ppo_continuous.mojo:2557-2565; the per-step launches (:2705-2713) are overwritten by :2832-2838
+        if (continuous && cfg.obs_noise_std > 0.0f)
+            ppo::add_obs_noise(obs.data(), cfg.n_envs, obs_dim, cfg.obs_noise_std, 42u);
     }
     // ppo.mojo:712-736
     void extract_obs() {

@@ -39,6 +39,7 @@ _SIGS = {
     "orc_normalize_advantages": (None, [ctypes.c_int64, F, ctypes.c_int]),
     "orc_ppo_actor_grad": (None, [ctypes.c_int, ctypes.c_int, F, F, F, F, ctypes.c_float, ctypes.c_float, F, F]),
     "orc_ppo_critic_grad": (None, [ctypes.c_int, F, F, F, ctypes.c_float, ctypes.c_float, ctypes.c_int, F]),
+    "orc_add_obs_noise": (None, [ctypes.c_int, ctypes.c_int, F, ctypes.c_float, ctypes.c_uint32]),
     "orc_sample_continuous_actions": (None, [ctypes.c_int, ctypes.c_int, F, F, F, ctypes.c_uint32, ctypes.c_int]),
     "orc_ppo_continuous_actor_grad": (None, [ctypes.c_int, ctypes.c_int, F, F, F, F, ctypes.c_float, ctypes.c_float,
                                              F, F]),
@@ -101,6 +102,7 @@ def default_config(lib_defaults=None, **kw):
     cfg.gamma, cfg.gae_lambda, cfg.clip_epsilon, cfg.value_loss_coef = 0.99, 0.95, 0.2, 0.5
     cfg.target_kl, cfg.max_grad_norm = 0.015, 0.5
     cfg.adam_beta1, cfg.adam_beta2, cfg.adam_eps = 0.9, 0.999, 1e-8
+    cfg.obs_noise_std = 0.0
     for k, v in kw.items():
         assert hasattr(cfg, k), k
         setattr(cfg, k, v)

@@ -216,3 +216,29 @@ def test_native_checkpoint_round_trip_and_python_compatibility(tmp_path):
         assert b"does not fit" in L.mrl_last_error_string()
     finally:
         L.mrl_destroy(h2)
+
+
+def test_observation_noise_reaches_the_first_rollout_step_only():
+    """obs_noise_std of the continuous agent (ppo_continuous.mojo:265, 2557-2565): the observations after the
+    initial reset carry Gaussian noise (seed 42); the launches after every env step are overwritten by the
+    observation extraction that follows the selective reset, so later steps see clean observations."""
+    runs = {}
+    for std in (0.0, 0.05):
+        cfg = default_config(env_kind=1, n_envs=256, rollout_len=8, hidden_dim=64, minibatch_size=512,
+                             obs_noise_std=std)
+        o, g = _pair(cfg, seed=11)
+        try:
+            o.o.orc_agent_reset(o.h, 3); g.reset(3)
+            assert np.array_equal(g.buffer(BUF["obs"]), o.buffer(BUF["obs"]))
+            o.o.orc_agent_rollout(o.h); g.rollout()
+            for k in ("r_obs", "r_actions", "r_log_probs", "r_dones"):
+                assert np.array_equal(g.buffer(BUF[k]), o.buffer(BUF[k])), k
+            runs[std] = (g.buffer(BUF["r_obs"]).reshape(8, 256, 3), g.buffer(BUF["states"]))
+        finally:
+            o.close(); g.close()
+    clean, noisy = runs[0.0][0], runs[0.05][0]
+    d0 = noisy[0] - clean[0]
+    assert 0.03 < d0.std() < 0.07 and abs(d0.mean()) < 0.01          # step 0: obs + 0.05 * N(0, 1)
+    # from step 1 on the stored observations are extracted from the states: cos^2 + sin^2 = 1 again
+    assert np.allclose(noisy[1:, :, 0] ** 2 + noisy[1:, :, 1] ** 2, 1.0, atol=1e-5)
+    assert not np.allclose(noisy[0, :, 0] ** 2 + noisy[0, :, 1] ** 2, 1.0, atol=1e-3)

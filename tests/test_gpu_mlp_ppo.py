@@ -270,3 +270,18 @@ def test_fused_train_step_matches_layerwise_oracle(case, batch):
     if mode < 2:
         assert abs(float(kl_g.item()) - float(kl.astype(np.float64).sum())) <= 1e-5 * max(1.0, abs(float(kl.sum())))
     assert L.mrl_fused_train_scratch_doubles(NetSpec(24, 64, 4, 0, 0), batch) == -1
+
+
+def test_add_obs_noise_matches_oracle():
+    import torch
+    from mojo_rl_b200 import _lib
+    L, o = _lib.lib(), oracle()
+    n, d = 1000, 24
+    rng = np.random.default_rng(5)
+    obs = rng.standard_normal((n, d)).astype(np.float32)
+    want = obs.copy()
+    o.orc_add_obs_noise(n, d, fp(want), 0.05, 99)
+    t = torch.from_numpy(obs).cuda()
+    _lib.check(L.mrl_add_obs_noise(n, d, t.data_ptr(), 0.05, 99, None))
+    torch.cuda.synchronize()
+    assert np.array_equal(t.cpu().numpy(), want)

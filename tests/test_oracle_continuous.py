@@ -475,3 +475,26 @@ def test_lunar_continuous_matches_discrete_at_full_throttle_and_charges_fuel_pro
     _lstep(LUNAR_C, a, np.tile(np.array([[5.0, 0.0]], np.float32), (n, 1)))
     _lstep(LUNAR_C, b, np.tile(np.array([[1.0, 0.0]], np.float32), (n, 1)))
     assert np.array_equal(a[:, 8:47], b[:, 8:47])
+
+
+def test_observation_noise_kernel_math():
+    """add_obs_noise_kernel (kernels.mojo:882-925): obs += std * Box-Muller noise on the Philox stream
+    seed + env * obs_dim + dim -- the same stream and transform as the Gaussian sampler's noise, which
+    gives an independent check: with mean 0 and log_std 0 the sampler's action IS the noise."""
+    from _util import fp, oracle
+    o = oracle()
+    n, d = 4096, 5
+    obs = np.zeros((n, d), np.float32)
+    o.orc_add_obs_noise(n, d, fp(obs), 0.25, 1234)
+    assert abs(obs.mean()) < 0.01 and abs(obs.std() - 0.25) < 0.01
+    actor_out = np.zeros((n, 2 * d), np.float32)          # means 0, log_std 0 -> std 1
+    actions, lp = np.zeros((n, d), np.float32), np.zeros(n, np.float32)
+    o.orc_sample_continuous_actions(n, d, fp(actor_out), fp(actions), fp(lp), 1234, 0)
+    assert np.allclose(obs, actions * np.float32(0.25), rtol=0, atol=1e-7)
+    # std <= 0 leaves the observations untouched; the call is deterministic
+    ref = np.arange(n * d, dtype=np.float32).reshape(n, d)
+    a = ref.copy(); o.orc_add_obs_noise(n, d, fp(a), 0.0, 7)
+    assert np.array_equal(a, ref)
+    b, c = ref.copy(), ref.copy()
+    o.orc_add_obs_noise(n, d, fp(b), 0.1, 7); o.orc_add_obs_noise(n, d, fp(c), 0.1, 7)
+    assert np.array_equal(b, c) and not np.array_equal(b, ref)
