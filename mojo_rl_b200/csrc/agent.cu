@@ -107,6 +107,12 @@ struct mrl_ctx {
     bool use_tc_policy;  // precision == 1 and the rollout policy kernel covers this shape
     mrl::tc::PolicyState policy;
     uint8_t* policy_workspace;
+    // precision == 1, shape not covered by the policy kernel (hidden 512): the per-step actor / critic forward
+    // runs on the update path's tensor-core kernels at batch n_envs, one State per network so that the bf16
+    // copies of W1 are converted once per rollout
+    bool use_tc_rollout_fwd;
+    mrl::tc::State tc_roll[2];
+    uint8_t* tc_roll_workspace[2];
     int* tc_err;    // device word written by a kernel whose bounded wait gave up
     DeviceCounters* counters;
     ncclComm_t comm;
@@ -460,6 +466,7 @@ extern "C" int mrl_create(mrl_ctx** out, const mrl_config* cfg) {
     A_(tc_err, 4);
     c->use_tc = false;
     c->use_tc_policy = false;
+    c->use_tc_rollout_fwd = false;
     c->use_small = false;
     c->use_small_rollout = false;
     if (cfg->precision == 0 && small::supported(&c->actor_net) && small::supported(&c->critic_net)) {
@@ -485,6 +492,13 @@ extern "C" int mrl_create(mrl_ctx** out, const mrl_config* cfg) {
             rc = c->policy.init(c->policy_workspace, c->tc_err);
             if (rc) { mrl_destroy(c); return rc; }
             c->use_tc_policy = true;
+        } else if (tc::supported(&c->actor_net, N) && tc::supported(&c->critic_net, N)) {
+            for (int w = 0; w < 2; ++w) {
+                A_(tc_roll_workspace[w], (size_t)tc::workspace_bytes(N, cfg->hidden_dim));
+                rc = c->tc_roll[w].init(c->tc_roll_workspace[w], N, cfg->hidden_dim, c->tc_err);
+                if (rc) { mrl_destroy(c); return rc; }
+            }
+            c->use_tc_rollout_fwd = true;
         }
     } else if (cfg->precision != 0) {
         set_error("precision must be 0 (fp32) or 1 (bf16 tensor-core update)");
@@ -622,8 +636,13 @@ static int rollout_launches(mrl_ctx* c) {
                                   c->counters};
             if ((rc = c->policy.step(pa, st))) return rc;
         } else {
-            if ((rc = mlp_forward_impl(&c->actor_net, N, c->obs, c->actor_params, c->logits, nullptr, c->workspace, st))) return rc;
-            if ((rc = mlp_forward_impl(&c->critic_net, N, c->obs, c->critic_params, c->values, nullptr, c->workspace, st))) return rc;
+            if (c->use_tc_rollout_fwd) {   // W1 -> bf16 at the first step only: the parameters do not change in a rollout
+                if ((rc = c->tc_roll[0].forward(&c->actor_net, c->actor_params, c->obs, c->logits, st, t == 0))) return rc;
+                if ((rc = c->tc_roll[1].forward(&c->critic_net, c->critic_params, c->obs, c->values, st, t == 0))) return rc;
+            } else {
+                if ((rc = mlp_forward_impl(&c->actor_net, N, c->obs, c->actor_params, c->logits, nullptr, c->workspace, st))) return rc;
+                if ((rc = mlp_forward_impl(&c->critic_net, N, c->obs, c->critic_params, c->values, nullptr, c->workspace, st))) return rc;
+            }
             if (c->continuous) {
                 MRL_LAUNCH(rollout_pre_step_continuous_kernel, ceil_div(N, 128), 128, 0, st, c->logits, c->values,
                            c->obs, c->actions, c->r_obs, c->r_actions, c->r_log_probs, c->r_values, c->counters, t, N,

@@ -1,5 +1,5 @@
-// bf16 tensor-core path of the PPO update for hidden width 256 (LunarLander,
-// BipedalWalker): the three 256-wide GEMMs of a minibatch
+// bf16 tensor-core path of the PPO update for hidden widths 256 (LunarLander,
+// BipedalWalker) and 512 (HalfCheetah): the three hidden x hidden GEMMs of a minibatch
 //     z1  = h0 . W1            (forward,  Linear[256,256] of linear_relu.mojo:134-219)
 //     dh0 = g1 . W1^T          (backward dX, linear_relu.mojo:355-396)
 //     dW1 = h0^T . g1          (backward dW, linear_relu.mojo:398-447)
@@ -74,9 +74,6 @@ struct K1Params {
     const float* bias;              // mode 1: b1
     const float* W2; const float* b2; int out_dim; float* head_out; int head_ld;
     int act;                        // modes 1, 2: 0 ReLU, 1 tanh (derivative 1 - y^2 from the stored bf16 y)
-    // Hidden widths above 256 are computed in 256-wide blocks: a second launch adds the first one's fp32
-    // result (prev, [M, 256]) to its accumulator before the epilogue.
-    const float* prev;
     int* err;
 };
 
@@ -87,11 +84,19 @@ __device__ __forceinline__ void drain_on_error(const int* err) {
 
 // tmOut: [32 rows x 32 columns] boxes (64-byte swizzle) of the bf16 output (h1 in mode 1, g0 in mode 2);
 // tmMask: the same boxes of the mask source h0 (mode 2).  Unused maps are passed as copies of tmA.
-template <int MODE, int OUT>
+// NW x KC: width of the CTA's output block and number of 64-wide K chunks; NW * KC = 1024, so W1's block always
+// fills the same 128 KB.  256 x 4 is the hidden-256 kernel (and one 256-wide K block of the carry scheme);
+// 128 x 8 is hidden 512: CTA b works on output block b % 4 of the row tiles b / 4, b / 4 + grid / 4, ..., so the
+// four CTAs of a group read the same A tile at about the same time (one trip to DRAM, three L2 hits) and no
+// partial sums leave the SM.  tmB then covers all of W1^T / W1 and tmOut / tmMask the full-width matrices.
+template <int MODE, int OUT, int NW = 256, int KC = 4>
 __global__ void __launch_bounds__(K1_THREADS, 1)
 k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmMask, K1Params p) {
+    static_assert(NW * KC == 4 * H && (NW == H || MODE != 0), "row-tile kernel shape");
     constexpr int STAGES = k1_stages(MODE);
+    constexpr int CH = NW / 32;                 // 32-column chunks per tile in the epilogue
+    constexpr int NB = (KC * KCH) / NW;         // output blocks across the hidden width (1 or 4)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* sB = smem;
@@ -110,6 +115,9 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_tiles = (p.M + TILE_M - 1) / TILE_M;
+    const int nblk = NB == 1 ? 0 : (int)blockIdx.x % NB;
+    const int first_tile = NB == 1 ? (int)blockIdx.x : (int)blockIdx.x / NB;
+    const int tile_step = NB == 1 ? (int)gridDim.x : (int)gridDim.x / NB;
 
     if (threadIdx.x == 0) {
         mbar_init(b_full, 1);
@@ -125,7 +133,7 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (warp == 1) tmem_alloc(tmem_slot, 512);
     if (warp >= 2 && MODE == 1) {
         int t = threadIdx.x - 64;
-        for (int i = t; i < H; i += 256) sP[i] = p.bias[i];
+        for (int i = t; i < NW; i += 256) sP[i] = p.bias[nblk * NW + i];
         for (int i = t; i < H * OUT; i += 256) {
             int j = i / OUT, a = i % OUT;
             sP[H + i] = a < p.out_dim ? p.W2[j * p.out_dim + a] : 0.0f;
@@ -140,11 +148,11 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (warp == 0) {
         if (lane == 0) {
             mbar_arrive_expect_tx(b_full, K1_B_BYTES);
-            for (int c = 0; c < 4; ++c) tma_load_2d(sB + c * (H * KCH * 2), &tmB, b_full, c * KCH, 0);
+            for (int c = 0; c < KC; ++c) tma_load_2d(sB + c * (NW * KCH * 2), &tmB, b_full, c * KCH, nblk * NW);
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                for (int c = 0; c < 4 && ok; ++c, ++it) {
+            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+                for (int c = 0; c < KC && ok; ++c, ++it) {
                     int s = it % STAGES;
                     uint32_t ph = (it / STAGES) & 1u;
                     ok = mbar_wait(&a_empty[s], ph ^ 1u, p.err, 101);
@@ -156,25 +164,25 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = make_idesc_bf16_f32(TILE_M, H);
+            const uint32_t idesc = make_idesc_bf16_f32(TILE_M, NW);
             bool ok = mbar_wait(b_full, 0, p.err, 102);
             uint32_t it = 0, lt = 0;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
+            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++lt) {
                 int buf = lt & 1;
                 ok = mbar_wait(&t_empty[buf], ((lt >> 1) & 1u) ^ 1u, p.err, 103);
                 if (!ok) break;
                 tc_fence_after_sync();
-                for (int c = 0; c < 4 && ok; ++c, ++it) {
+                for (int c = 0; c < KC && ok; ++c, ++it) {
                     int s = it % STAGES;
                     uint32_t ph = (it / STAGES) & 1u;
                     ok = mbar_wait(&a_full[s], ph, p.err, 104);
                     if (!ok) break;
                     tc_fence_after_sync();
                     uint64_t da = make_kmajor_sw128_desc(sA + s * K1_A_STAGE);
-                    uint64_t db = make_kmajor_sw128_desc(sB + c * (H * KCH * 2));
+                    uint64_t db = make_kmajor_sw128_desc(sB + c * (NW * KCH * 2));
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        mma_bf16_ss(tmem_base + buf * H, da + 2 * k, db + 2 * k, idesc, (c | k) != 0 ? 1u : 0u);
+                        mma_bf16_ss(tmem_base + buf * NW, da + 2 * k, db + 2 * k, idesc, (c | k) != 0 ? 1u : 0u);
                     mma_commit(&a_empty[s]);
                 }
                 if (ok) mma_commit(&t_full[buf]);
@@ -188,19 +196,19 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         uint8_t* obuf = sOut + ew * K1_CHUNK_BYTES;
         uint8_t* mbuf = sAux + ew * 2 * K1_CHUNK_BYTES;
         uint64_t* m_full = m_full_all + 2 * ew;
-        // Mask chunk g of this warp's stream: chunk g % 8 of the (g / 8)-th tile of its group.
+        // Mask chunk g of this warp's stream: chunk g % CH of the (g / CH)-th tile of its group.
         auto issue_mask = [&](uint32_t g) {
-            const int tile_g = blockIdx.x + (group + 2 * (int)(g >> 3)) * gridDim.x;
+            const int tile_g = first_tile + (group + 2 * (int)(g / CH)) * tile_step;
             if (tile_g < num_tiles) {
                 mbar_arrive_expect_tx(&m_full[g & 1u], K1_CHUNK_BYTES);
-                tma_load_2d(mbuf + (g & 1u) * K1_CHUNK_BYTES, &tmMask, &m_full[g & 1u], (int)(g & 7u) * 32,
+                tma_load_2d(mbuf + (g & 1u) * K1_CHUNK_BYTES, &tmMask, &m_full[g & 1u], nblk * NW + (int)(g % CH) * 32,
                             tile_g * TILE_M + q * 32);
             }
         };
         if (MODE == 2 && lane == 0) { issue_mask(0); issue_mask(1); }
         uint32_t lt = 0, mk = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
+        for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++lt) {
             int buf = lt & 1;
             if (buf != group) continue;
             ok = __all_sync(0xffffffffu, mbar_wait(&t_full[buf], (lt >> 1) & 1u, p.err, 105));   // warp-uniform
@@ -209,7 +217,7 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             const int row0 = tile * TILE_M + q * 32;
             const int row = row0 + lane;
             const bool in_range = row < p.M;
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * H;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * NW;
             float o[OUT];
             if (MODE == 1) {
 #pragma unroll
@@ -228,14 +236,6 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 float v[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]);
-                if (MODE != 0 && p.prev != nullptr && in_range) {
-                    const float4* src = reinterpret_cast<const float4*>(p.prev + (size_t)row * H + ch * 32);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float4 pv = __ldg(src + i);
-                        v[4 * i] += pv.x; v[4 * i + 1] += pv.y; v[4 * i + 2] += pv.z; v[4 * i + 3] += pv.w;
-                    }
-                }
                 if (MODE == 0) {
                     if (in_range) {
                         float4* dst = reinterpret_cast<float4*>(p.out_f32 + (size_t)row * H + ch * 32);
@@ -294,18 +294,18 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     dst[i ^ swz] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) tma_store_2d(&tmOut, obuf, ch * 32, row0);
+                if (lane == 0) tma_store_2d(&tmOut, obuf, nblk * NW + ch * 32, row0);
                 return true;
             };
             uint32_t ra[32], rb[32];
             tmem_ld_32x32_issue(taddr, ra);
 #pragma unroll 1
-            for (int ch = 0; ch < 8 && ok; ch += 2) {
+            for (int ch = 0; ch < CH && ok; ch += 2) {
                 tmem_ld_wait(ra);
                 tmem_ld_32x32_issue(taddr + (ch + 1) * 32, rb);
                 ok = process(ch, ra);
                 tmem_ld_wait(rb);   // also when the chunk failed: no TMEM load may be in flight at the exit
-                if (ch + 2 < 8) tmem_ld_32x32_issue(taddr + (ch + 2) * 32, ra);
+                if (ch + 2 < CH) tmem_ld_32x32_issue(taddr + (ch + 2) * 32, ra);
                 if (ok) ok = process(ch + 1, rb);
             }
             tmem_ld_wait(ra);
@@ -427,20 +427,33 @@ k2_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
     } else {
         const int q = warp & 3;
-        if (mbar_wait(t_full, 0, err, 203)) {
+        if (__all_sync(0xffffffffu, mbar_wait(t_full, 0, err, 203))) {
             tc_fence_after_sync();
+            // Every load has landed and every MMA has retired, so the operand ring is free: each warp stages its
+            // [32 rows x 32 columns] chunk there (thread = row, 128-byte swizzle against bank conflicts) and writes
+            // it out with a quarter-warp per 128-byte line instead of one line per lane.
             float* out = partial + (size_t)blockIdx.x * H * H;
+            uint8_t* stg = smem + (warp - 2) * 4096;
 #pragma unroll 1
             for (int half = 0; half < 2; ++half) {
-                const int m = half * TILE_M + q * 32 + lane;
+                const int m0 = half * TILE_M + q * 32;
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + half * H;
 #pragma unroll 1
                 for (int ch = 0; ch < 8; ++ch) {
                     float v[32];
                     tmem_ld_32x32(taddr + ch * 32, v);
-                    float4* dst = reinterpret_cast<float4*>(out + (size_t)m * H + ch * 32);
+                    __syncwarp();   // the previous chunk has been read back
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    for (int i = 0; i < 8; ++i)
+                        *reinterpret_cast<float4*>(stg + lane * 128 + ((i ^ (lane & 7)) << 4)) =
+                            make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int r = j * 4 + (lane >> 3), c = lane & 7;
+                        const float4 t4 = *reinterpret_cast<const float4*>(stg + r * 128 + ((c ^ (r & 7)) << 4));
+                        *reinterpret_cast<float4*>(out + (size_t)(m0 + r) * H + ch * 32 + c * 4) = t4;
+                    }
                 }
             }
         }
@@ -706,39 +719,37 @@ __device__ __forceinline__ float sum_parts(const float* __restrict__ p, int nblo
     return (a0 + a1) + (a2 + a3);
 }
 
-// Sum over partials for 32 consecutive outputs per block: lane = output, warp w
-// takes partials w, w + 8, ...; the eight warp sums are added in warp order.
+// Sum over partials for 32 consecutive outputs per block: lane = output, warp w of the block's NW warps takes
+// partials w, w + NW, ... with eight independent loads in flight (the sums are latency-bound: a few MB spread over
+// hundreds of partials); the warp sums are added in warp order, so the result is deterministic.
+constexpr int REDUCE_THREADS = 1024;
 __device__ __forceinline__ float block_sum_parts(const float* __restrict__ part, int nblocks, int stride, int i,
                                                  bool valid) {
-    __shared__ float sm[8][33];
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    // eight independent loads in flight per thread (the sums are latency-bound, not bandwidth-bound);
-    // the order of the additions is fixed, so the result is deterministic
+    __shared__ float sm[32][33];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
     float a[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) a[k] = 0.0f;
     if (valid) {
         int b = w;
-        for (; b + 56 < nblocks; b += 64) {
+        for (; b + 7 * nw < nblocks; b += 8 * nw) {
 #pragma unroll
-            for (int k = 0; k < 8; ++k) a[k] += part[(size_t)(b + 8 * k) * stride + i];
+            for (int k = 0; k < 8; ++k) a[k] += part[(size_t)(b + k * nw) * stride + i];
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-            if (b + 8 * k < nblocks) a[k] += part[(size_t)(b + 8 * k) * stride + i];
+            if (b + k * nw < nblocks) a[k] += part[(size_t)(b + k * nw) * stride + i];
     }
     const float a0 = (a[0] + a[1]) + (a[2] + a[3]), a1 = (a[4] + a[5]) + (a[6] + a[7]);
     sm[w][lane] = a0 + a1;
     __syncthreads();
     float acc = 0.0f;
-    if (w == 0) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) acc += sm[k][lane];
-    }
+    if (w == 0)
+        for (int k = 0; k < nw; ++k) acc += sm[k][lane];
     return acc;  // valid in warp 0
 }
 
-// out[i] = sum_b part[b * stride + i]; grid = ceil(n / 32) blocks of 256 threads
+// out[i] = sum_b part[b * stride + i]; grid = ceil(n / 32) blocks of REDUCE_THREADS threads
 __global__ void reduce_parts_kernel(const float* __restrict__ part, int nblocks, int stride, int n,
                                     float* __restrict__ out) {
     const int i = blockIdx.x * 32 + (threadIdx.x & 31);
@@ -773,33 +784,48 @@ __global__ void reduce_parts_block_kernel(const float* __restrict__ part, int nb
     if ((threadIdx.x >> 5) == 0 && i < H * H) out[(size_t)(i / H) * out_ld + (i % H)] = acc;
 }
 
-// Head of a network wider than 256 (the 256-wide path computes it in the GEMM epilogue):
-// out[r][a] = b2[a] + sum_j h1[r][j] * W2[j][a], one warp per row, fp32 accumulation, fixed order.
+// Head of a network 512 wide (the 256-wide path computes it in the GEMM epilogue):
+// out[r][a] = b2[a] + sum_j h1[r][j] * W2[j][a].  One warp per row, rows strided over the grid; lane l owns
+// columns 8 l .. 8 l + 7 and 256 + 8 l .. (two 16-byte loads per row) and keeps their W2 rows in registers;
+// fp32 accumulation in a fixed order, warp shuffle reduction.
 template <int OUT>
 __global__ void __launch_bounds__(256)
 head_forward_kernel(const bf16* __restrict__ h1, int hh, const float* __restrict__ W2, const float* __restrict__ b2,
                     int out_dim, float* __restrict__ out, int out_ld, int M) {
     const int lane = threadIdx.x & 31;
-    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (row >= M) return;
-    float acc[OUT];
+    float w2[2][8][OUT];
 #pragma unroll
-    for (int a = 0; a < OUT; ++a) acc[a] = 0.0f;
-    for (int c0 = lane * 8; c0 < hh; c0 += 256) {
-        float h[8];
-        unpack8(__ldg(reinterpret_cast<const uint4*>(h1 + (size_t)row * hh + c0)), h);
+    for (int s = 0; s < 2; ++s)
 #pragma unroll
         for (int u = 0; u < 8; ++u)
 #pragma unroll
-            for (int a = 0; a < OUT; ++a)
-                if (a < out_dim) acc[a] = fmaf(h[u], W2[(c0 + u) * out_dim + a], acc[a]);
-    }
+            for (int a = 0; a < OUT; ++a) {
+                const int c = s * 256 + lane * 8 + u;
+                w2[s][u][a] = (a < out_dim && c < hh) ? W2[c * out_dim + a] : 0.0f;
+            }
+    for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < M; row += gridDim.x * 8) {
+        float acc[OUT];
 #pragma unroll
-    for (int a = 0; a < OUT; ++a) {
-        float v = acc[a];
+        for (int a = 0; a < OUT; ++a) acc[a] = 0.0f;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0 && a < out_dim) out[(size_t)row * out_ld + a] = v + b2[a];
+        for (int s = 0; s < 2; ++s) {
+            const int c0 = s * 256 + lane * 8;
+            if (c0 < hh) {
+                float h[8];
+                unpack8(__ldg(reinterpret_cast<const uint4*>(h1 + (size_t)row * hh + c0)), h);
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+#pragma unroll
+                    for (int a = 0; a < OUT; ++a) acc[a] = fmaf(h[u], w2[s][u][a], acc[a]);
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < OUT; ++a) {
+            float v = acc[a];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0 && a < out_dim) out[(size_t)row * out_ld + a] = v + b2[a];
+        }
     }
 }
 
@@ -870,30 +896,32 @@ static int sm_count() {
 }
 
 // Rows per block of the CUDA-core kernels: two blocks per SM (what their register use allows, so one wave),
-// each walking a contiguous slab of rows (a multiple of 8, at least 64).
+// each walking a contiguous slab of rows (a multiple of 8, at least 256: below that the per-block prologue - the
+// weight tile from L2, the staged rows - and the partials it writes cost more than the lost parallelism).
 // The per-row fp32 operand of a slab (floats_per_row each) is staged in at most 40 KB of shared memory.
 static int slab_rows(int M, int floats_per_row) {
     int blocks = 2 * sm_count();
     int r = ((M + blocks - 1) / blocks + 7) & ~7;
     int cap = (40960 / (4 * floats_per_row)) & ~7;
     if (r > cap) r = cap;
-    return r < 64 ? 64 : r;
+    return r < 256 ? 256 : r;
 }
 
 // tmOut / tmMask: staging-box maps (make_box_map) of the bf16 output and, in mode 2, of the mask source;
 // mode 0 ignores both.
-template <int MODE, int OUT>
+template <int MODE, int OUT, int NW = 256, int KC = 4>
 static int launch_k1(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmOut,
                      const CUtensorMap& tmMask, const K1Params& p, cudaStream_t st) {
     static bool attr_set = false;
     if (!attr_set) {
-        MRL_CUDA_OK(cudaFuncSetAttribute(k1_rowtile_kernel<MODE, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         k1_smem(MODE)));
+        MRL_CUDA_OK(cudaFuncSetAttribute(k1_rowtile_kernel<MODE, OUT, NW, KC>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, k1_smem(MODE)));
         attr_set = true;
     }
+    constexpr int NB = (KC * KCH) / NW;   // CTAs per row tile (output blocks across the hidden width)
     int tiles = (p.M + TILE_M - 1) / TILE_M;
-    int grid = tiles < sm_count() ? tiles : sm_count();
-    k1_rowtile_kernel<MODE, OUT><<<grid, K1_THREADS, k1_smem(MODE), st>>>(tmA, tmB, tmOut, tmMask, p);
+    int grid = tiles * NB < sm_count() ? tiles * NB : (sm_count() / NB) * NB;
+    k1_rowtile_kernel<MODE, OUT, NW, KC><<<grid, K1_THREADS, k1_smem(MODE), st>>>(tmA, tmB, tmOut, tmMask, p);
     count_launch();
     MRL_CUDA_OK(cudaGetLastError());
     return MRL_OK;
@@ -951,8 +979,7 @@ static int64_t part_area_bytes(int batch, int hidden) {
 int64_t workspace_bytes(int batch, int hidden) {
     int64_t act = (int64_t)batch * hidden * 2;            // one bf16 activation array
     int64_t parts = part_area_bytes(batch, hidden);
-    int64_t tmp = hidden > H ? (int64_t)batch * H * 4 : 0;   // fp32 result of the first 256-wide K block
-    return 4 * act + 2 * (int64_t)hidden * hidden * 2 + parts + tmp + 4096;
+    return 4 * act + 2 * (int64_t)hidden * hidden * 2 + parts + 4096;
 }
 
 int State::init(void* workspace, int batch_, int hidden, int* err_flag) {
@@ -968,8 +995,6 @@ int State::init(void* workspace, int batch_, int hidden, int* err_flag) {
     g0 = (bf16*)p; p += act;
     w1 = (bf16*)p; p += (int64_t)hh * hh * 2;
     w1t = (bf16*)p; p += (int64_t)hh * hh * 2;
-    tmp = nullptr;
-    if (nb > 1) { tmp = (float*)p; p += (int64_t)batch * H * 4; }
     part = (float*)p;
     int rc;
     for (int i = 0; i < nb; ++i) {      // 256-wide column blocks of the activations, K-major and MN-major views
@@ -980,6 +1005,17 @@ int State::init(void* workspace, int batch_, int hidden, int* err_flag) {
         if ((rc = make_box_map(&tm_h1_box[i], h1 + i * H, batch, H, hh))) return rc;
         if ((rc = make_box_map(&tm_g0_box[i], g0 + i * H, batch, H, hh))) return rc;
         if ((rc = make_box_map(&tm_h0_box[i], h0 + i * H, batch, H, hh))) return rc;
+    }
+    if (nb > 1) {   // full-width views for the 128-wide / K = 512 row-tile kernel
+        if ((rc = make_tensor_map(&tm_h0_full, h0, batch, hh, TILE_M))) return rc;
+        if ((rc = make_tensor_map(&tm_g1_full, g1, batch, hh, TILE_M))) return rc;
+        if ((rc = make_tensor_map(&tm_w1t_full, w1t, hh, hh, 128))) return rc;
+        if ((rc = make_tensor_map(&tm_w1_full, w1, hh, hh, 128))) return rc;
+        if ((rc = make_box_map(&tm_h1_boxf, h1, batch, hh))) return rc;
+        if ((rc = make_box_map(&tm_g0_boxf, g0, batch, hh))) return rc;
+        if ((rc = make_box_map(&tm_h0_boxf, h0, batch, hh))) return rc;
+    }
+    for (int i = 0; i < nb; ++i) {
         for (int j = 0; j < nb; ++j) {  // [n block i][k block j] of W1^T (forward) and of W1 (dX)
             if ((rc = make_tensor_map(&tm_w1t[i][j], w1t + ((size_t)i * H) * hh + j * H, H, H, H, hh))) return rc;
             if ((rc = make_tensor_map(&tm_w1[i][j], w1 + ((size_t)i * H) * hh + j * H, H, H, H, hh))) return rc;
@@ -1067,14 +1103,17 @@ static int l0_backward_any(int I, const bf16* g0, const float* x, float* part, i
     return l0_backward<24, HH>(g0, x, part, batch, rows_per_block, nblocks, st);
 }
 
-int State::forward(const mrl_net_spec* net, const float* params, const float* x, float* head_out, cudaStream_t st) {
+int State::forward(const mrl_net_spec* net, const float* params, const float* x, float* head_out, cudaStream_t st,
+                   bool convert) {
     const int I = net->in_dim, O = net->out_dim;
     const float* W0 = params; const float* b0 = W0 + (size_t)I * hh;
     const float* W1 = b0 + hh; const float* b1 = W1 + (size_t)hh * hh;
     const float* W2 = b1 + hh; const float* b2 = W2 + (size_t)hh * O;
     prof_mark("(other)", st);
-    MRL_LAUNCH(convert_w1_kernel, dim3(hh / 32, hh / 32), dim3(32, 8), 0, st, W1, w1, w1t, hh);
-    prof_mark("convert_w1", st);
+    if (convert) {
+        MRL_LAUNCH(convert_w1_kernel, dim3(hh / 32, hh / 32), dim3(32, 8), 0, st, W1, w1, w1t, hh);
+        prof_mark("convert_w1", st);
+    }
     int rc;
     const int act = net->activation == MRL_ACT_RELU ? 0 : 1;
     const bool gaussian = net->head == MRL_HEAD_STOCHASTIC_ACTOR;
@@ -1091,19 +1130,14 @@ int State::forward(const mrl_net_spec* net, const float* params, const float* x,
         p.err = err;
         if ((rc = launch_k1_forward(tm_h0[0], tm_w1t[0][0], tm_h1_box[0], p, st))) return rc;
     } else {
-        // h1[:, n block] = act(h0[:, k block 0] W1[k0, n] + h0[:, k block 1] W1[k1, n] + b1[n block]):
-        // the first launch leaves its fp32 product in tmp, the second adds it before the epilogue.
-        for (int n = 0; n < nb; ++n) {
-            K1Params p0{};
-            p0.M = batch; p0.out_f32 = tmp; p0.err = err;
-            if ((rc = launch_k1<0, 1>(tm_h0[0], tm_w1t[n][0], tm_h0[0], tm_h0[0], p0, st))) return rc;
-            K1Params p{};
-            p.M = batch; p.bias = b1 + n * H; p.W2 = W2; p.b2 = b2; p.out_dim = 0;
-            p.head_out = head_out; p.head_ld = head_ld; p.act = act; p.prev = tmp; p.err = err;
-            if ((rc = launch_k1<1, 1>(tm_h0[1], tm_w1t[n][1], tm_h1_box[n], tm_h1_box[n], p, st))) return rc;
-        }
+        // hidden 512: one launch, CTA = (row tile, 128-wide output block), K = 512 accumulated in TMEM; the head
+        // follows as its own kernel because a row's 512 hidden values are spread over four CTAs
+        K1Params p{};
+        p.M = batch; p.bias = b1; p.W2 = W2; p.b2 = b2; p.out_dim = 0;
+        p.head_out = head_out; p.head_ld = head_ld; p.act = act; p.err = err;
+        if ((rc = launch_k1<1, 1, 128, 8>(tm_h0_full, tm_w1t_full, tm_h1_boxf, tm_h1_boxf, p, st))) return rc;
         const int OUT = O <= 1 ? 1 : (O <= 2 ? 2 : (O <= 4 ? 4 : 8));
-        const int grid = (batch + 7) / 8;
+        const int grid = (batch + 7) / 8 < 8 * sm_count() ? (batch + 7) / 8 : 8 * sm_count();
         if (OUT == 1) { MRL_LAUNCH((head_forward_kernel<1>), grid, 256, 0, st, h1, hh, W2, b2, O, head_out, head_ld, batch); }
         else if (OUT == 2) { MRL_LAUNCH((head_forward_kernel<2>), grid, 256, 0, st, h1, hh, W2, b2, O, head_out, head_ld, batch); }
         else if (OUT == 4) { MRL_LAUNCH((head_forward_kernel<4>), grid, 256, 0, st, h1, hh, W2, b2, O, head_out, head_ld, batch); }
@@ -1133,7 +1167,7 @@ int State::backward(const mrl_net_spec* net, const float* params, const float* x
     if (rc) return rc;
     prof_mark("head_backward", st);
     const int hstride = (OUT + 1) * hh + OUT;
-    MRL_LAUNCH(reduce_head_parts_kernel, ceil_div(hstride, 32), 256, 0, st, part, 2 * nblocks, OUT, O, grads + oW2,
+    MRL_LAUNCH(reduce_head_parts_kernel, ceil_div(hstride, 32), REDUCE_THREADS, 0, st, part, 2 * nblocks, OUT, O, grads + oW2,
                grads + ob2, grads + ob1, hh);
     if (gaussian) {  // dlog_std[j] = sum over rows of dout[:, O + j] (stochastic_actor.mojo:727-966)
         const int lrows = (batch + 2 * sm_count() - 1) / (2 * sm_count());
@@ -1149,14 +1183,9 @@ int State::backward(const mrl_net_spec* net, const float* params, const float* x
         p.M = batch; p.act = act; p.err = err;
         if ((rc = launch_k1<2, 1>(tm_g1[0], tm_w1[0][0], tm_g0_box[0], tm_h0_box[0], p, st))) return rc;
     } else {
-        for (int i = 0; i < nb; ++i) {   // output block i of g0: sum over the two column blocks of g1
-            K1Params p0{};
-            p0.M = batch; p0.out_f32 = tmp; p0.err = err;
-            if ((rc = launch_k1<0, 1>(tm_g1[0], tm_w1[i][0], tm_g1[0], tm_g1[0], p0, st))) return rc;
-            K1Params p{};
-            p.M = batch; p.act = act; p.prev = tmp; p.err = err;
-            if ((rc = launch_k1<2, 1>(tm_g1[1], tm_w1[i][1], tm_g0_box[i], tm_h0_box[i], p, st))) return rc;
-        }
+        K1Params p{};
+        p.M = batch; p.act = act; p.err = err;
+        if ((rc = launch_k1<2, 1, 128, 8>(tm_g1_full, tm_w1_full, tm_g0_boxf, tm_h0_boxf, p, st))) return rc;
     }
     prof_mark("k1_dx_gemm", st);
     // dW0, db0
@@ -1164,7 +1193,7 @@ int State::backward(const mrl_net_spec* net, const float* params, const float* x
                  : l0_backward_any<512>(I, g0, x, part, batch, rows_per_block, nblocks, st);
     if (rc) return rc;
     prof_mark("l0_backward", st);
-    MRL_LAUNCH(reduce_parts_kernel, ceil_div((I + 1) * hh, 32), 256, 0, st, part, 2 * nblocks, (I + 1) * hh, (I + 1) * hh,
+    MRL_LAUNCH(reduce_parts_kernel, ceil_div((I + 1) * hh, 32), REDUCE_THREADS, 0, st, part, 2 * nblocks, (I + 1) * hh, (I + 1) * hh,
                grads + oW0);  // dW0 [I][hidden] then db0 [hidden] are adjacent in the gradient vector
     prof_mark("reduce_l0", st);
     // dW1 = h0^T . g1 (split-K over the SMs) in 256 x 256 blocks, each followed by its fixed-order reduction
@@ -1174,6 +1203,7 @@ int State::backward(const mrl_net_spec* net, const float* params, const float* x
             if ((rc = launch_k2<true>(tm_h0_mn[i], tm_g1_mn[j], batch, part, &splits, err, st))) return rc;
             prof_mark("k2_dw_gemm", st);
             if (nb == 1) {
+                // 148 partials of 256 KB: bandwidth-bound, eight warps per block are enough (32 were slower)
                 MRL_LAUNCH(reduce_parts_kernel, ceil_div(H * H, 32), 256, 0, st, part, splits, H * H, H * H, grads + oW1);
             } else {
                 MRL_LAUNCH(reduce_parts_block_kernel, ceil_div(H * H, 32), 256, 0, st, part, splits,

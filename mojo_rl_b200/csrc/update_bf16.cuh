@@ -26,14 +26,17 @@ struct State {
     int hh, nb;  // hidden width (256 or 512) and its number of 256-wide blocks
     __nv_bfloat16 *h0, *h1, *g1, *g0, *w1, *w1t;   // activations [batch, hh]; W1 and W1^T as bf16 [hh, hh]
     float* part;
-    float* tmp;  // hh = 512: fp32 [batch, 256] product of the first K block
     CUtensorMap tm_h0[2], tm_g1[2], tm_h0_mn[2], tm_g1_mn[2];   // 256-wide column blocks of the activations
     CUtensorMap tm_w1t[2][2], tm_w1[2][2];                       // [row block][column block] of W1^T and W1
     CUtensorMap tm_h1_box[2], tm_g0_box[2], tm_h0_box[2];        // [32 x 32] epilogue staging boxes per column block
+    // hh = 512: full-width views for the row-tile kernel with 128-wide output blocks and K = 512
+    CUtensorMap tm_h0_full, tm_g1_full, tm_w1t_full, tm_w1_full, tm_h1_boxf, tm_g0_boxf, tm_h0_boxf;
 
     int init(void* workspace, int batch, int hidden, int* err_flag);
-    // head_out [batch, out_dim] = logits / values (fp32)
-    int forward(const mrl_net_spec* net, const float* params, const float* x, float* head_out, cudaStream_t st);
+    // head_out [batch, out_dim] = logits / values (fp32).  convert = false reuses the bf16 copies of W1 made
+    // by the previous call (same network, unchanged parameters).
+    int forward(const mrl_net_spec* net, const float* params, const float* x, float* head_out, cudaStream_t st,
+                bool convert = true);
     // grads [PARAM_SIZE] is overwritten (fp32, reference parameter order)
     int backward(const mrl_net_spec* net, const float* params, const float* x, const float* dout, float* grads,
                  cudaStream_t st);

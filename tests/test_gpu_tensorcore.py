@@ -171,21 +171,23 @@ def test_rollout_policy_kernel_matches_fp32_policy():
 
 
 @pytest.mark.gpu
-def test_rollout_policy_kernel_gaussian_matches_fp32_policy():
-    """Same comparison for a tanh / Gaussian policy (BipedalWalker: 24 observations, 4 action means,
-    state-independent log_std): actions differ from the fp32 path only through the bf16 means, the
-    noise draws are identical."""
+@pytest.mark.parametrize("kind,obs_dim,A,hidden", [(3, 24, 4, 256), (4, 17, 6, 512)])
+def test_rollout_policy_kernel_gaussian_matches_fp32_policy(kind, obs_dim, A, hidden):
+    """Same comparison for a tanh / Gaussian policy (state-independent log_std): actions differ from the fp32
+    path only through the bf16 means, the noise draws are identical.  BipedalWalker (24 observations, 4 means,
+    hidden 256) runs the single policy kernel; HalfCheetah (17, 6, hidden 512) runs the update path's
+    tensor-core forward kernels at batch n_envs followed by the fp32 sampler."""
     from _gpu import GpuAgent
     from _util import NetSpec, default_config, xavier_params
     rng = np.random.default_rng(2)
-    pa = xavier_params(NetSpec(24, 256, 4, 1, 1), rng) * 0.25
-    pa[-4:] = np.array([-0.5, 0.0, 0.3, -1.0], np.float32)   # log_std
-    pc = xavier_params(NetSpec(24, 256, 1, 1, 0), rng) * 0.25
+    pa = xavier_params(NetSpec(obs_dim, hidden, A, 1, 1), rng) * 0.25
+    pa[-A:] = np.linspace(-1.0, 0.3, A).astype(np.float32)   # log_std
+    pc = xavier_params(NetSpec(obs_dim, hidden, 1, 1, 0), rng) * 0.25
     n = 512
     out = {}
     for prec in (0, 1):
         for det in (0, 1):
-            cfg = default_config(env_kind=3, n_envs=n, rollout_len=2, hidden_dim=256, minibatch_size=2 * n,
+            cfg = default_config(env_kind=kind, n_envs=n, rollout_len=2, hidden_dim=hidden, minibatch_size=2 * n,
                                  num_epochs=1, precision=prec, deterministic=det)
             g = GpuAgent(cfg)
             try:
@@ -193,7 +195,7 @@ def test_rollout_policy_kernel_gaussian_matches_fp32_policy():
                 g.set_params(1, pc, np.zeros(2 * pc.size, np.float32))
                 g.reset(5); g.rollout()
                 out[(prec, det)] = {k: g.buffer(i)[:n * w] for k, i, w in
-                                    (("obs", 2, 24), ("act", 3, 4), ("lp", 4, 1), ("val", 5, 1))}
+                                    (("obs", 2, obs_dim), ("act", 3, A), ("lp", 4, 1), ("val", 5, 1))}
                 assert g.stats().total_steps == 2 * n
             finally:
                 g.close()
