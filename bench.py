@@ -71,8 +71,9 @@ def kernel_algorithmic_bytes(w, total):
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures of the same
 # kernels at this workload's sizes (profiles/); not measured live - a profiler never runs inside the bench.
 NCU_TRAFFIC = {
-    "lunar_lander": {"rollout_env_step": 6.49e6, "k1_dx_gemm": 268.6e6 + 101.2e6, "k1_forward_gemm": 134.4e6 + 88.0e6,
-                     "head_backward": 136.9e6 + 95.2e6, "l0_forward": 8.4e6 + 80.2e6, "l0_backward": 142.6e6 + 4.2e6},
+    "lunar_lander": {"rollout_env_step": 6.51e6, "rollout_policy": 0.62e6, "l0_forward": 8.4e6 + 74.9e6,
+                     "k1_forward_gemm": 134.4e6 + 87.9e6, "head_backward": 138.4e6 + 91.1e6,
+                     "k1_dx_gemm": 268.6e6 + 101.2e6, "l0_backward": 142.6e6 + 3.5e6, "k2_dw_gemm": 268.5e6 + 4.5e6},
 }
 
 

@@ -49,24 +49,40 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 // store per chunk, and in mode 2 the matching chunk of the mask source arrives
 // the same way, two chunks ahead.  (Per-thread row stores and loads would touch
 // 32 different 128-byte lines per warp instruction and saturate the L1 path.)
-constexpr int K1_B_BYTES = 4 * H * KCH * 2;           // 131072
+constexpr int K1_B_FULL = 4 * H * KCH * 2;            // 131072: a [256 x 256] (or [128 x 512]) block of W1
 constexpr int K1_A_STAGE = TILE_M * KCH * 2;          // 16384
 constexpr int K1_PARAM_FLOATS = H + H * 8 + 8;        // bias, W2 (up to 8 outputs), b2
 constexpr int K1_EPI_WARPS = 8;
 constexpr int K1_CHUNK_BYTES = 32 * 64;               // 32 rows x 32 bf16
-__host__ __device__ constexpr int k1_stages(int mode) { return mode == 2 ? 3 : 4; }
+constexpr int K1_SMEM_MAX = 232448;                   // opt-in shared memory per CTA
+constexpr int K1_BAR_BYTES = 48 * 8;                  // up to 21 + 2 x 8 mbarriers and the TMEM slot
 __host__ __device__ constexpr int k1_out_bufs(int mode) { return mode == 0 ? 0 : 1; }
 // mode 1: bias / W2 / b2 as floats; mode 2: two mask chunks per epilogue warp
 __host__ __device__ constexpr int k1_aux_bytes(int mode) {
     return mode == 2 ? K1_EPI_WARPS * 2 * K1_CHUNK_BYTES : ((K1_PARAM_FLOATS * 4 + 1023) / 1024) * 1024;
 }
-__host__ __device__ constexpr int k1_out_off(int mode) { return K1_B_BYTES + k1_stages(mode) * K1_A_STAGE; }
-__host__ __device__ constexpr int k1_aux_off(int mode) {
-    return k1_out_off(mode) + k1_out_bufs(mode) * K1_EPI_WARPS * K1_CHUNK_BYTES;
+// The A ring takes whatever the resident block of W1 (bbytes), the staging buffers and the barriers leave:
+// 4 stages next to 128 KB of W1 in mode 1, 3 in mode 2, 7 next to a 64 KB block.
+__host__ __device__ constexpr int k1_stages(int mode, int bbytes = K1_B_FULL) {
+    const int room = K1_SMEM_MAX - (K1_BAR_BYTES + 1024) - bbytes - k1_out_bufs(mode) * K1_EPI_WARPS * K1_CHUNK_BYTES -
+                     k1_aux_bytes(mode);
+    return room / K1_A_STAGE > 8 ? 8 : room / K1_A_STAGE;
 }
-__host__ __device__ constexpr int k1_bar_off(int mode) { return k1_aux_off(mode) + k1_aux_bytes(mode); }
-__host__ __device__ constexpr int k1_smem(int mode) { return k1_bar_off(mode) + 32 * 8 + 1024; }  // + barriers + alignment slack
-static_assert(k1_smem(1) <= 232448 && k1_smem(2) <= 232448 && k1_smem(0) <= 232448, "K1 shared memory");
+__host__ __device__ constexpr int k1_out_off(int mode, int bbytes = K1_B_FULL) {
+    return bbytes + k1_stages(mode, bbytes) * K1_A_STAGE;
+}
+__host__ __device__ constexpr int k1_aux_off(int mode, int bbytes = K1_B_FULL) {
+    return k1_out_off(mode, bbytes) + k1_out_bufs(mode) * K1_EPI_WARPS * K1_CHUNK_BYTES;
+}
+__host__ __device__ constexpr int k1_bar_off(int mode, int bbytes = K1_B_FULL) {
+    return k1_aux_off(mode, bbytes) + k1_aux_bytes(mode);
+}
+__host__ __device__ constexpr int k1_smem(int mode, int bbytes = K1_B_FULL) {
+    return k1_bar_off(mode, bbytes) + K1_BAR_BYTES + 1024;   // + barriers + alignment slack
+}
+static_assert(k1_smem(1) <= K1_SMEM_MAX && k1_smem(2) <= K1_SMEM_MAX && k1_smem(0) <= K1_SMEM_MAX &&
+              k1_smem(2, K1_B_FULL / 2) <= K1_SMEM_MAX && k1_stages(1) == 4 && k1_stages(2) == 3,
+              "K1 shared memory");
 
 struct K1Params {
     int M;
@@ -94,17 +110,18 @@ __global__ void __launch_bounds__(K1_THREADS, 1)
 k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmMask, K1Params p) {
     static_assert(NW * KC == 4 * H && (NW == H || MODE != 0), "row-tile kernel shape");
-    constexpr int STAGES = k1_stages(MODE);
+    constexpr int B_BYTES = KC * NW * KCH * 2;  // the CTA's resident block of W1^T / W1
+    constexpr int STAGES = k1_stages(MODE, B_BYTES);
     constexpr int CH = NW / 32;                 // 32-column chunks per tile in the epilogue
     constexpr int NB = (KC * KCH) / NW;         // output blocks across the hidden width (1 or 4)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* sB = smem;
-    uint8_t* sA = smem + K1_B_BYTES;
-    uint8_t* sOut = smem + k1_out_off(MODE);
-    uint8_t* sAux = smem + k1_aux_off(MODE);
+    uint8_t* sA = smem + B_BYTES;
+    uint8_t* sOut = smem + k1_out_off(MODE, B_BYTES);
+    uint8_t* sAux = smem + k1_aux_off(MODE, B_BYTES);
     float* sP = (float*)sAux;
-    uint64_t* bars = (uint64_t*)(smem + k1_bar_off(MODE));
+    uint64_t* bars = (uint64_t*)(smem + k1_bar_off(MODE, B_BYTES));
     uint64_t* b_full = bars;
     uint64_t* a_full = bars + 1;
     uint64_t* a_empty = a_full + STAGES;
@@ -147,7 +164,7 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
     if (warp == 0) {
         if (lane == 0) {
-            mbar_arrive_expect_tx(b_full, K1_B_BYTES);
+            mbar_arrive_expect_tx(b_full, B_BYTES);
             for (int c = 0; c < KC; ++c) tma_load_2d(sB + c * (NW * KCH * 2), &tmB, b_full, c * KCH, nblk * NW);
             uint32_t it = 0;
             bool ok = true;
@@ -915,13 +932,13 @@ static int launch_k1(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
     static bool attr_set = false;
     if (!attr_set) {
         MRL_CUDA_OK(cudaFuncSetAttribute(k1_rowtile_kernel<MODE, OUT, NW, KC>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, k1_smem(MODE)));
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, k1_smem(MODE, KC * NW * KCH * 2)));
         attr_set = true;
     }
     constexpr int NB = (KC * KCH) / NW;   // CTAs per row tile (output blocks across the hidden width)
     int tiles = (p.M + TILE_M - 1) / TILE_M;
     int grid = tiles * NB < sm_count() ? tiles * NB : (sm_count() / NB) * NB;
-    k1_rowtile_kernel<MODE, OUT, NW, KC><<<grid, K1_THREADS, k1_smem(MODE), st>>>(tmA, tmB, tmOut, tmMask, p);
+    k1_rowtile_kernel<MODE, OUT, NW, KC><<<grid, K1_THREADS, k1_smem(MODE, KC * NW * KCH * 2), st>>>(tmA, tmB, tmOut, tmMask, p);
     count_launch();
     MRL_CUDA_OK(cudaGetLastError());
     return MRL_OK;
