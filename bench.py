@@ -102,14 +102,46 @@ def mlp_flops_per_env_step(w):
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+    """Samples SM clocks / throttle reasons while the timed region runs (NVML polling; nvidia-smi as fallback)."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
         self.gpu, self.samples, self.stop_flag, self.thread = gpu_index, [], False, None
 
+    def _run_nvml(self):
+        """NVML polling (read-only) every 10 ms: the timed region is ~100 ms, too short for nvidia-smi calls."""
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            # NVML indexes physical GPUs: map through CUDA_VISIBLE_DEVICES when it lists indices
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            idx = self.gpu
+            if vis and all(x.strip().isdigit() for x in vis.split(",")):
+                ids = [int(x) for x in vis.split(",")]
+                if self.gpu < len(ids):
+                    idx = ids[self.gpu]
+            h = pynvml.nvmlDeviceGetHandleByIndex(idx)
+            mx = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            bits = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
+                    ("sw_power_cap", 0x4))
+            while not self.stop_flag:
+                mhz = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+                try:
+                    r = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+                except Exception:
+                    r = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                self.samples.append([str(mhz), str(mx)] + ["Active" if r & b else "Not Active" for _, b in bits])
+                time.sleep(0.01)
+        finally:
+            pynvml.nvmlShutdown()
+
     def _run(self):
+        try:
+            self._run_nvml()
+            return
+        except Exception:
+            pass
         while not self.stop_flag:
             try:
                 out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i",
