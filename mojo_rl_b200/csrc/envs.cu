@@ -107,7 +107,7 @@ __global__ void pendulum_rollout_step_kernel(RolloutStepArgs a) {
 // block instead brings its 64 rows (48 KB, contiguous) into shared memory with
 // one bulk copy (TMA), steps every environment there, and writes the rows back
 // with one bulk store.  err: device word set when the bounded wait gives up.
-constexpr int LUNAR_TPB = 64;
+constexpr int LUNAR_TPB = 32;
 constexpr int LUNAR_PITCH = lunar::STATE_SIZE;
 constexpr int LUNAR_SMEM = LUNAR_TPB * LUNAR_PITCH * 4 + 16;
 

@@ -91,19 +91,42 @@ rollout_policy_kernel(const __grid_constant__ CUtensorMap tm_actor_w1t,
     }
     if (warp == 1) tmem_alloc(tmem_slot, 256);
     constexpr bool REG_W = IN <= 8;     // first-layer weights of 8 columns fit in registers
-    if (!REG_W)
-        for (int i = threadIdx.x; i < IN * H; i += P_THREADS) sW0[i] = W0[i];
-    for (int i = threadIdx.x; i < H; i += P_THREADS) { sb0[i] = b0[i]; sb1[i] = b1[i]; }
-    if (REG_W)
+    // Parameter staging.  With register-resident first-layer weights only the observations have to be in shared
+    // memory before the first layer runs; b1 / W2 / b2 are fetched into registers now and parked in shared memory
+    // after it, so their latency hides behind the first layer instead of in front of it.
+    float r_b1 = 0.0f, r_w2[P_MAX_OUT];
+    if (REG_W) {
         for (int i = threadIdx.x; i < P_TILE * IN; i += P_THREADS)
             sX[i] = (size_t)row0 * IN + i < (size_t)a.n * IN ? a.obs[(size_t)row0 * IN + i] : 0.0f;
-    for (int i = threadIdx.x; i < H * P_MAX_OUT; i += P_THREADS) {
-        int j = i / P_MAX_OUT, o = i % P_MAX_OUT;
-        sW2[i] = o < out_dim ? W2[j * out_dim + o] : 0.0f;
+        r_b1 = b1[threadIdx.x];                       // H == P_THREADS
+#pragma unroll
+        for (int o = 0; o < P_MAX_OUT; ++o) r_w2[o] = o < out_dim ? W2[threadIdx.x * out_dim + o] : 0.0f;
+    } else {
+        for (int i = threadIdx.x; i < IN * H; i += P_THREADS) sW0[i] = W0[i];
+        for (int i = threadIdx.x; i < H; i += P_THREADS) { sb0[i] = b0[i]; sb1[i] = b1[i]; }
+        for (int i = threadIdx.x; i < H * P_MAX_OUT; i += P_THREADS) {
+            int j = i / P_MAX_OUT, o = i % P_MAX_OUT;
+            sW2[i] = o < out_dim ? W2[j * out_dim + o] : 0.0f;
+        }
     }
     if (threadIdx.x < P_MAX_OUT) {
         sb2[threadIdx.x] = threadIdx.x < out_dim ? b2[threadIdx.x] : 0.0f;
         sb2[P_MAX_OUT + threadIdx.x] = (CONT && net == 0 && threadIdx.x < out_dim) ? b2[out_dim + threadIdx.x] : 0.0f;
+    }
+    float w0r[REG_W ? IN : 1][8], bias0[8];
+    if (REG_W) {   // issued before the barrier: in flight while the observations land
+        const int g = threadIdx.x & 31;
+#pragma unroll
+        for (int k = 0; k < IN; ++k) {
+            const float4 lo = __ldg(reinterpret_cast<const float4*>(W0 + k * H + g * 8));
+            const float4 hi = __ldg(reinterpret_cast<const float4*>(W0 + k * H + g * 8 + 4));
+            w0r[k][0] = lo.x; w0r[k][1] = lo.y; w0r[k][2] = lo.z; w0r[k][3] = lo.w;
+            w0r[k][4] = hi.x; w0r[k][5] = hi.y; w0r[k][6] = hi.z; w0r[k][7] = hi.w;
+        }
+        const float4 lo = __ldg(reinterpret_cast<const float4*>(b0 + g * 8));
+        const float4 hi = __ldg(reinterpret_cast<const float4*>(b0 + g * 8 + 4));
+        bias0[0] = lo.x; bias0[1] = lo.y; bias0[2] = lo.z; bias0[3] = lo.w;
+        bias0[4] = hi.x; bias0[5] = hi.y; bias0[6] = hi.z; bias0[7] = hi.w;
     }
     __syncthreads();
 
@@ -113,16 +136,8 @@ rollout_policy_kernel(const __grid_constant__ CUtensorMap tm_actor_w1t,
         // thread -> (8-column group g, row set rs): the group's weights stay in registers over 16 rows, and the
         // eight lanes of a quarter-warp write one 128-byte row of a chunk
         const int g = threadIdx.x & 31, rs = threadIdx.x >> 5;
-        float w[IN][8], bias[8];
-#pragma unroll
-        for (int k = 0; k < IN; ++k) {
-            const float4 lo = __ldg(reinterpret_cast<const float4*>(W0 + k * H + g * 8));
-            const float4 hi = __ldg(reinterpret_cast<const float4*>(W0 + k * H + g * 8 + 4));
-            w[k][0] = lo.x; w[k][1] = lo.y; w[k][2] = lo.z; w[k][3] = lo.w;
-            w[k][4] = hi.x; w[k][5] = hi.y; w[k][6] = hi.z; w[k][7] = hi.w;
-        }
-#pragma unroll
-        for (int u = 0; u < 8; ++u) bias[u] = sb0[g * 8 + u];
+        auto& w = w0r;
+        auto& bias = bias0;
         const int kc = g >> 3, unit = g & 7;
 #pragma unroll 2
         for (int i = 0; i < P_TILE / 8; ++i) {
@@ -176,6 +191,11 @@ rollout_policy_kernel(const __grid_constant__ CUtensorMap tm_actor_w1t,
             *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
         }
     }
+    if (REG_W) {
+        sb1[threadIdx.x] = r_b1;
+#pragma unroll
+        for (int o = 0; o < P_MAX_OUT; ++o) sW2[threadIdx.x * P_MAX_OUT + o] = r_w2[o];
+    }
     fence_proxy_async_smem();  // the tensor core reads sA through the async proxy
     tc_fence_before_sync();
     __syncthreads();
@@ -207,18 +227,28 @@ rollout_policy_kernel(const __grid_constant__ CUtensorMap tm_actor_w1t,
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
 #pragma unroll
         for (int u = 0; u < P_MAX_OUT; ++u) o[u] = hf == 0 ? sb2[u] : 0.0f;
-#pragma unroll 1
-        for (int ch = hf * 4; ch < hf * 4 + 4; ++ch) {
-            float v[32];
-            tmem_ld_32x32(taddr + ch * 32, v);
+        // four 32-column chunks per warp; the next chunk's TMEM load is in flight while one is processed
+        auto contract = [&](int ch, const uint32_t (&acc)[32]) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
                 const int j = ch * 32 + i;
-                const float z = v[i] + sb1[j];
+                const float z = __uint_as_float(acc[i]) + sb1[j];
                 const float hv = a.act == 0 ? fmaxf(z, 0.0f) : tanh_fast(z);
 #pragma unroll
                 for (int u = 0; u < P_MAX_OUT; ++u) o[u] = fmaf(hv, sW2[j * P_MAX_OUT + u], o[u]);
             }
+        };
+        uint32_t ra[32], rb[32];
+        const int ch0 = hf * 4;
+        tmem_ld_32x32_issue(taddr + ch0 * 32, ra);
+#pragma unroll
+        for (int c = 0; c < 4; c += 2) {
+            tmem_ld_wait(ra);
+            tmem_ld_32x32_issue(taddr + (ch0 + c + 1) * 32, rb);
+            contract(ch0 + c, ra);
+            tmem_ld_wait(rb);
+            if (c + 2 < 4) tmem_ld_32x32_issue(taddr + (ch0 + c + 2) * 32, ra);
+            contract(ch0 + c + 1, rb);
         }
         if (hf == 1) {
 #pragma unroll
