@@ -55,11 +55,13 @@ constexpr int K1_PARAM_FLOATS = H + H * 8 + 8;        // bias, W2 (up to 8 outpu
 constexpr int K1_EPI_WARPS = 8;
 constexpr int K1_CHUNK_BYTES = 32 * 64;               // 32 rows x 32 bf16
 constexpr int K1_SMEM_MAX = 232448;                   // opt-in shared memory per CTA
-constexpr int K1_BAR_BYTES = 48 * 8;                  // up to 21 + 2 x 8 mbarriers and the TMEM slot
+constexpr int K1_BAR_BYTES = 56 * 8;                  // up to 29 + 2 x 8 mbarriers and the TMEM slot
 __host__ __device__ constexpr int k1_out_bufs(int mode) { return mode == 0 ? 0 : 1; }
-// mode 1: bias / W2 / b2 as floats; mode 2: two mask chunks per epilogue warp
+// mode 1: bias / W2 / b2 as floats, then the upper column half's partial head sums [2][128][8];
+// mode 2: two mask chunks per epilogue warp
 __host__ __device__ constexpr int k1_aux_bytes(int mode) {
-    return mode == 2 ? K1_EPI_WARPS * 2 * K1_CHUNK_BYTES : ((K1_PARAM_FLOATS * 4 + 1023) / 1024) * 1024;
+    return mode == 2 ? K1_EPI_WARPS * 2 * K1_CHUNK_BYTES
+                     : K1_PARAM_FLOATS * 4 + 2 * TILE_M * 8 * 4;
 }
 // The A ring takes whatever the resident block of W1 (bbytes), the staging buffers and the barriers leave:
 // 4 stages next to 128 KB of W1 in mode 1, 3 in mode 2, 7 next to a 64 KB block.
@@ -128,7 +130,8 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     uint64_t* t_full = a_empty + STAGES;
     uint64_t* t_empty = t_full + 2;
     uint64_t* m_full_all = t_empty + 2;                 // 2 per epilogue warp (mode 2)
-    uint32_t* tmem_slot = (uint32_t*)(m_full_all + 2 * K1_EPI_WARPS);
+    uint64_t* o_full_all = m_full_all + 2 * K1_EPI_WARPS;   // [lane quarter][tile parity]: head sums of the upper half
+    uint32_t* tmem_slot = (uint32_t*)(o_full_all + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_tiles = (p.M + TILE_M - 1) / TILE_M;
@@ -139,7 +142,8 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (threadIdx.x == 0) {
         mbar_init(b_full, 1);
         for (int s = 0; s < STAGES; ++s) { mbar_init(&a_full[s], 1); mbar_init(&a_empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&t_full[b], 1); mbar_init(&t_empty[b], 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&t_full[b], 1); mbar_init(&t_empty[b], K1_EPI_WARPS); }
+        for (int b = 0; b < 8; ++b) mbar_init(&o_full_all[b], 1);
         for (int b = 0; b < 2 * K1_EPI_WARPS; ++b) mbar_init(&m_full_all[b], 1);
         fence_barrier_init();
         prefetch_tensormap(&tmA);
@@ -208,18 +212,22 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     } else {
         const int q = warp & 3;             // TMEM lane quarter this warp may read
         const int ew = warp - 2;            // epilogue warp 0..7
-        const int group = ew >> 2;          // epilogue group = TMEM buffer it drains (tiles lt with lt % 2 == group)
+        const int group = ew >> 2;          // epilogue group = column half of every tile it drains
+        constexpr int CHG = CH / 2;         // 32-column chunks per tile and group
         const int swz = (lane >> 1) & 3;    // 64-byte swizzle: 16-byte chunk index ^ address bits 7..8
         uint8_t* obuf = sOut + ew * K1_CHUNK_BYTES;
         uint8_t* mbuf = sAux + ew * 2 * K1_CHUNK_BYTES;
         uint64_t* m_full = m_full_all + 2 * ew;
-        // Mask chunk g of this warp's stream: chunk g % CH of the (g / CH)-th tile of its group.
+        float* sO = sP + K1_PARAM_FLOATS;   // mode 1: [2][128][8] partial head sums
+        // Both groups work on every tile (group g on columns g NW/2 ...), so a tile's accumulator is free again
+        // after half an epilogue and the MMAs of the next tile run into the other buffer meanwhile.
+        // Mask chunk g of this warp's stream: chunk g % CHG of its column half, tile g / CHG of the CTA.
         auto issue_mask = [&](uint32_t g) {
-            const int tile_g = first_tile + (group + 2 * (int)(g / CH)) * tile_step;
+            const int tile_g = first_tile + (int)(g / CHG) * tile_step;
             if (tile_g < num_tiles) {
                 mbar_arrive_expect_tx(&m_full[g & 1u], K1_CHUNK_BYTES);
-                tma_load_2d(mbuf + (g & 1u) * K1_CHUNK_BYTES, &tmMask, &m_full[g & 1u], nblk * NW + (int)(g % CH) * 32,
-                            tile_g * TILE_M + q * 32);
+                tma_load_2d(mbuf + (g & 1u) * K1_CHUNK_BYTES, &tmMask, &m_full[g & 1u],
+                            nblk * NW + (group * CHG + (int)(g % CHG)) * 32, tile_g * TILE_M + q * 32);
             }
         };
         if (MODE == 2 && lane == 0) { issue_mask(0); issue_mask(1); }
@@ -227,18 +235,17 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         bool ok = true;
         for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++lt) {
             int buf = lt & 1;
-            if (buf != group) continue;
             ok = __all_sync(0xffffffffu, mbar_wait(&t_full[buf], (lt >> 1) & 1u, p.err, 105));   // warp-uniform
             if (!ok) break;
             tc_fence_after_sync();
             const int row0 = tile * TILE_M + q * 32;
             const int row = row0 + lane;
             const bool in_range = row < p.M;
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * NW;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * NW + group * (NW / 2);
             float o[OUT];
             if (MODE == 1) {
 #pragma unroll
-                for (int a = 0; a < OUT; ++a) o[a] = sP[H + H * 8 + a];
+                for (int a = 0; a < OUT; ++a) o[a] = group == 0 ? sP[H + H * 8 + a] : 0.0f;
             }
             // One 32-column chunk: activation / mask, bf16 pack, staging, TMA store.  The accumulator registers of
             // the next chunk are already in flight (see the loop below), so the TMEM latency is off this path.
@@ -316,20 +323,37 @@ k1_rowtile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             };
             uint32_t ra[32], rb[32];
             tmem_ld_32x32_issue(taddr, ra);
+            const int chb = group * CHG;   // first chunk of this group's column half
 #pragma unroll 1
-            for (int ch = 0; ch < CH && ok; ch += 2) {
+            for (int c = 0; c < CHG && ok; c += 2) {
                 tmem_ld_wait(ra);
-                tmem_ld_32x32_issue(taddr + (ch + 1) * 32, rb);
-                ok = process(ch, ra);
+                tmem_ld_32x32_issue(taddr + (c + 1) * 32, rb);
+                ok = process(chb + c, ra);
                 tmem_ld_wait(rb);   // also when the chunk failed: no TMEM load may be in flight at the exit
-                if (ch + 2 < CH) tmem_ld_32x32_issue(taddr + (ch + 2) * 32, ra);
-                if (ok) ok = process(ch + 1, rb);
+                if (c + 2 < CHG) tmem_ld_32x32_issue(taddr + (c + 2) * 32, ra);
+                if (ok) ok = process(chb + c + 1, rb);
             }
             tmem_ld_wait(ra);
             if (!ok) break;
-            if (MODE == 1 && in_range) {
-                for (int a = 0; a < OUT; ++a)
-                    if (a < p.out_dim) p.head_out[(size_t)row * p.head_ld + a] = o[a];
+            if (MODE == 1 && NW == H) {
+                // head: the upper half parks its partial sums, the lower half adds them and writes the row.  The
+                // slot (tile parity) cannot be overwritten early: the upper half reaches tile lt + 2 only after
+                // this tile's accumulator was released by all eight warps.
+                float* so = sO + ((size_t)buf * TILE_M + q * 32 + lane) * 8;
+                uint64_t* o_full = &o_full_all[q * 2 + buf];
+                if (group == 1) {
+#pragma unroll
+                    for (int a = 0; a < OUT; ++a) so[a] = o[a];
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(o_full);
+                } else {
+                    ok = __all_sync(0xffffffffu, mbar_wait(o_full, (lt >> 1) & 1u, p.err, 108));
+                    if (!ok) break;
+                    if (in_range) {
+                        for (int a = 0; a < OUT; ++a)
+                            if (a < p.out_dim) p.head_out[(size_t)row * p.head_ld + a] = o[a] + so[a];
+                    }
+                }
             }
             tc_fence_before_sync();
             __syncwarp();
