@@ -556,6 +556,21 @@ __device__ __forceinline__ float sum_row_lanes(float v) {
     v += __shfl_xor_sync(0xffffffffu, v, 16);
     return v;
 }
+// row[0 .. N) from shared memory: 16-byte vectors when N is a multiple of 4 (rows of N floats start 16-byte
+// aligned then), scalars otherwise
+template <int N>
+__device__ __forceinline__ void load_row(const float* __restrict__ src, float (&dst)[N]) {
+    if (N % 4 == 0) {
+#pragma unroll
+        for (int k = 0; k < N; k += 4) {
+            const float4 t = *reinterpret_cast<const float4*>(src + k);
+            dst[k] = t.x; dst[k + 1] = t.y; dst[k + 2] = t.z; dst[k + 3] = t.w;
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < N; ++k) dst[k] = src[k];
+    }
+}
 // First layer (LinearReLU / LinearTanh[obs, 256], K = obs_dim): h0 = act(x . W0 + b0) in bf16, row-major.
 template <int IN, int HH>
 __global__ void __launch_bounds__(256)
@@ -572,14 +587,13 @@ l0_forward_kernel(const float* __restrict__ x, const float* __restrict__ W0, con
     }
     const int rb = blockIdx.x * rows_per_block;
     const int re = min(M, rb + rows_per_block);
-    extern __shared__ float s_rows[];  // the slab's x rows: (re - rb) * IN floats
+    extern __shared__ __align__(16) float s_rows[];  // the slab's x rows: (re - rb) * IN floats
     for (int i = threadIdx.x; i < (re - rb) * IN; i += 256) s_rows[i] = x[(size_t)rb * IN + i];
     __syncthreads();
 #pragma unroll 2
     for (int r = rb + vm.row_lane; r < re; r += 8) {
         float xr[IN];
-#pragma unroll
-        for (int k = 0; k < IN; ++k) xr[k] = s_rows[(r - rb) * IN + k];
+        load_row<IN>(s_rows + (r - rb) * IN, xr);
         float hv[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
@@ -617,7 +631,7 @@ head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout
     for (int u = 0; u < 8; ++u) db1[u] = 0.0f;
     const int rb = blockIdx.x * rows_per_block;
     const int re = min(M, rb + rows_per_block);
-    extern __shared__ float s_rows[];  // the slab's dout rows: (re - rb) * OUT floats
+    extern __shared__ __align__(16) float s_rows[];  // the slab's dout rows: (re - rb) * OUT floats
     for (int i = threadIdx.x; i < (re - rb) * OUT; i += 256) {
         int rr = i / OUT, a = i % OUT;
         s_rows[i] = a < out_dim ? dout[(size_t)(rb + rr) * ldd + a] : 0.0f;
@@ -643,11 +657,9 @@ head_backward_kernel(const bf16* __restrict__ h1, const float* __restrict__ dout
             if (r >= re) break;
             float h[8], d[OUT], g[8];
             unpack8(raw[i], h);
+            load_row<OUT>(s_rows + (r - rb) * OUT, d);
 #pragma unroll
-            for (int a = 0; a < OUT; ++a) {
-                d[a] = s_rows[(r - rb) * OUT + a];
-                db2[a] += d[a];
-            }
+            for (int a = 0; a < OUT; ++a) db2[a] += d[a];
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 float dh = 0.0f;
@@ -698,7 +710,7 @@ l0_backward_kernel(const bf16* __restrict__ g0, const float* __restrict__ x, flo
     }
     const int rb = blockIdx.x * rows_per_block;
     const int re = min(M, rb + rows_per_block);
-    extern __shared__ float s_rows[];  // the slab's x rows
+    extern __shared__ __align__(16) float s_rows[];  // the slab's x rows
     for (int i = threadIdx.x; i < (re - rb) * IN; i += 256) s_rows[i] = x[(size_t)rb * IN + i];
     __syncthreads();
     constexpr int UNR = 4;  // loads are issued one iteration ahead of their use
@@ -723,11 +735,12 @@ l0_backward_kernel(const bf16* __restrict__ g0, const float* __restrict__ x, flo
             unpack8(raw[i], g);
 #pragma unroll
             for (int u = 0; u < 8; ++u) db[u] += g[u];
+            float xr[IN];
+            load_row<IN>(s_rows + (r - rb) * IN, xr);
 #pragma unroll
             for (int k = 0; k < IN; ++k) {
-                const float xk = s_rows[(r - rb) * IN + k];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) dw[k][u] = fmaf(xk, g[u], dw[k][u]);
+                for (int u = 0; u < 8; ++u) dw[k][u] = fmaf(xr[k], g[u], dw[k][u]);
             }
         }
     }
