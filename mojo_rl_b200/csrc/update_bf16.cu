@@ -847,6 +847,11 @@ __global__ void __launch_bounds__(256)
 head_forward_kernel(const bf16* __restrict__ h1, int hh, const float* __restrict__ W2, const float* __restrict__ b2,
                     int out_dim, float* __restrict__ out, int out_ld, int M) {
     const int lane = threadIdx.x & 31;
+    // W2 goes through shared memory once per block (coalesced), then into the registers of the lanes that own
+    // the columns: per-thread strided reads of W2 from global memory cost more than the rows at small M
+    extern __shared__ float s_w2[];   // [hh][out_dim]
+    for (int i = threadIdx.x; i < hh * out_dim; i += 256) s_w2[i] = W2[i];
+    __syncthreads();
     float w2[2][8][OUT];
 #pragma unroll
     for (int s = 0; s < 2; ++s)
@@ -855,7 +860,7 @@ head_forward_kernel(const bf16* __restrict__ h1, int hh, const float* __restrict
 #pragma unroll
             for (int a = 0; a < OUT; ++a) {
                 const int c = s * 256 + lane * 8 + u;
-                w2[s][u][a] = (a < out_dim && c < hh) ? W2[c * out_dim + a] : 0.0f;
+                w2[s][u][a] = (a < out_dim && c < hh) ? s_w2[c * out_dim + a] : 0.0f;
             }
     for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < M; row += gridDim.x * 8) {
         float acc[OUT];
@@ -1191,11 +1196,13 @@ int State::forward(const mrl_net_spec* net, const float* params, const float* x,
         p.head_out = head_out; p.head_ld = head_ld; p.act = act; p.err = err;
         if ((rc = launch_k1<1, 1, 128, 8>(tm_h0_full, tm_w1t_full, tm_h1_boxf, tm_h1_boxf, p, st))) return rc;
         const int OUT = O <= 1 ? 1 : (O <= 2 ? 2 : (O <= 4 ? 4 : 8));
-        const int grid = (batch + 7) / 8 < 8 * sm_count() ? (batch + 7) / 8 : 8 * sm_count();
-        if (OUT == 1) { MRL_LAUNCH((head_forward_kernel<1>), grid, 256, 0, st, h1, hh, W2, b2, O, head_out, head_ld, batch); }
-        else if (OUT == 2) { MRL_LAUNCH((head_forward_kernel<2>), grid, 256, 0, st, h1, hh, W2, b2, O, head_out, head_ld, batch); }
-        else if (OUT == 4) { MRL_LAUNCH((head_forward_kernel<4>), grid, 256, 0, st, h1, hh, W2, b2, O, head_out, head_ld, batch); }
-        else { MRL_LAUNCH((head_forward_kernel<8>), grid, 256, 0, st, h1, hh, W2, b2, O, head_out, head_ld, batch); }
+        // at least 8 rows per warp, at most two blocks per SM
+        const int grid = (batch + 63) / 64 < 2 * sm_count() ? (batch + 63) / 64 : 2 * sm_count();
+        const int hsm = hh * O * 4;
+        if (OUT == 1) { MRL_LAUNCH((head_forward_kernel<1>), grid, 256, hsm, st, h1, hh, W2, b2, O, head_out, head_ld, batch); }
+        else if (OUT == 2) { MRL_LAUNCH((head_forward_kernel<2>), grid, 256, hsm, st, h1, hh, W2, b2, O, head_out, head_ld, batch); }
+        else if (OUT == 4) { MRL_LAUNCH((head_forward_kernel<4>), grid, 256, hsm, st, h1, hh, W2, b2, O, head_out, head_ld, batch); }
+        else { MRL_LAUNCH((head_forward_kernel<8>), grid, 256, hsm, st, h1, hh, W2, b2, O, head_out, head_ld, batch); }
     }
     if (gaussian) {  // columns O..2O-1 carry the clamped state-independent log_std (stochastic_actor.mojo:386-575)
         MRL_LAUNCH(fill_log_std_cols_kernel, ceil_div((int64_t)batch * O, 256), 256, 0, st, b2 + O, head_out, batch, O);
