@@ -150,6 +150,11 @@ int mrl_bf16_splitk_gemm(int K, const void* A_bf16, const void* B_bf16, float* p
 int mrl_bf16_splitk_gemm_tn(int K, const void* X_bf16, const void* G_bf16, float* partial,
                             int* splits_host, int* err_flag, void* stream);
 int mrl_bf16_max_splits(void);
+/* Exercises the bounded-wait path of the tensor-core kernels without a fault: one thread waits on an mbarrier
+ * that nothing ever completes, gives up after `poll_limit` polls, records its code in a device error word and the
+ * kernel returns normally.  Returns MRL_ERR_TIMEOUT (the expected outcome) and leaves the context usable; MRL_OK
+ * would mean the wait did not run out.  No counterpart in the reference, whose kernels never wait. */
+int mrl_debug_bounded_wait(uint32_t poll_limit, void* stream);
 
 /* ------------------------------------------------------------------------
  * L4 kernels of DeepPPOAgent.train_gpu, one entry point per reference kernel.

@@ -68,6 +68,7 @@ SIGNATURES = {
     "mrl_bf16_splitk_gemm_tn": (ctypes.c_int, [ctypes.c_int, c_void_p, c_void_p, c_void_p,
                                                ctypes.POINTER(ctypes.c_int), c_void_p, c_void_p]),
     "mrl_bf16_max_splits": (ctypes.c_int, []),
+    "mrl_debug_bounded_wait": (ctypes.c_int, [ctypes.c_uint32, c_void_p]),
     "mrl_sample_actions": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, c_void_p, c_void_p, c_void_p, ctypes.c_uint32, c_void_p]),
     "mrl_argmax_actions": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, c_void_p, c_void_p, c_void_p]),
     "mrl_gae": (ctypes.c_int, [ctypes.c_int, ctypes.c_int] + [c_void_p] * 4 + [ctypes.c_double, ctypes.c_double] + [c_void_p] * 3),

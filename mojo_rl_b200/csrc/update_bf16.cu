@@ -1317,3 +1317,37 @@ extern "C" int mrl_bf16_splitk_gemm_tn(int K, const void* X_bf16, const void* G_
 }
 
 extern "C" int mrl_bf16_max_splits(void) { return tc::max_splits(); }
+
+// A wait that is meant to run out: the same mbar_wait as the GEMM kernels, on a barrier nothing arrives at.
+__global__ void bounded_wait_probe_kernel(int* err, uint32_t limit) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        umma::mbar_init(&bar, 1);
+        umma::fence_barrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) umma::mbar_wait(&bar, 0, err, 900, limit);
+    __syncthreads();
+}
+extern "C" int mrl_debug_bounded_wait(uint32_t poll_limit, void* stream) {
+    MRL_CHECK_ARG(poll_limit > 0 && poll_limit <= (1u << 20));
+    cudaStream_t st = as_stream(stream);
+    int* flag = nullptr;
+    MRL_CUDA_OK(cudaMalloc(&flag, sizeof(int)));
+    int host = 0;
+    cudaError_t e = cudaMemsetAsync(flag, 0, sizeof(int), st);
+    if (e == cudaSuccess) {
+        bounded_wait_probe_kernel<<<1, 32, 0, st>>>(flag, poll_limit);
+        count_launch();
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&host, flag, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(flag);
+    if (e != cudaSuccess) { set_error("bounded-wait probe: %s", cudaGetErrorString(e)); return MRL_ERR_CUDA; }
+    if (host == 900) {
+        set_error("a kernel gave up waiting (code %d) after %u polls, as the probe intends", host, poll_limit);
+        return MRL_ERR_TIMEOUT;
+    }
+    return MRL_OK;
+}

@@ -206,3 +206,15 @@ def test_rollout_policy_kernel_gaussian_matches_fp32_policy(kind, obs_dim, A, hi
         assert np.allclose(a["act"], b["act"], rtol=0, atol=3e-2), np.abs(a["act"] - b["act"]).max()
         # log-prob depends on the noise only (action - mean = std * noise in both paths)
         assert np.allclose(a["lp"], b["lp"], rtol=0, atol=1e-3), np.abs(a["lp"] - b["lp"]).max()
+
+
+@pytest.mark.gpu
+def test_bounded_wait_runs_out_and_reports_timeout():
+    """The waits of the tensor-core kernels are bounded: a wait on a barrier nothing completes gives up after its
+    poll limit, the kernel returns, the host sees MRL_ERR_TIMEOUT (-6), and the context keeps working."""
+    from mojo_rl_b200 import _lib
+    L = _lib.lib()
+    assert L.mrl_debug_bounded_wait(4096, None) == -6
+    assert b"gave up waiting" in L.mrl_last_error_string()
+    # the device is still usable: a real tensor-core GEMM right after
+    test_rowtile_gemm(256)
