@@ -479,7 +479,7 @@ extern "C" int mrl_create(mrl_ctx** out, const mrl_config* cfg) {
     if (cfg->precision == 1) {
         if (!tc::supported(&c->actor_net, (int)B) || !tc::supported(&c->critic_net, (int)B)) {
             set_error("precision 1 (bf16 tensor-core update) needs hidden_dim 256 or 512, obs_dim in {4, 8, 17, 24}, "
-                      "head width <= 8 and a minibatch that is a multiple of 128; use precision 0");
+                      "head width <= 8 and a minibatch that is a multiple of 32; use precision 0");
             mrl_destroy(c);
             return MRL_ERR_UNSUPPORTED;
         }
